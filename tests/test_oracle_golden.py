@@ -1,0 +1,129 @@
+"""The CPU oracle against golden vectors produced by the reference itself (tests/golden/make_golden.py) and against the
+reference's own golden files (GPTQ decode fixtures, trellis tile fixtures)."""
+
+import numpy as np
+import pytest
+
+from oracle import oracle_np as O
+
+
+def test_e4m3_table_and_rounding(golden):
+    g = golden("nvfp4")
+    assert np.array_equal(O.e4m3_value(np.arange(127)), g["e4m3_table"])
+    assert np.array_equal(O.e4m3_encode(g["e4m3_probe"]), g["e4m3_codes"])
+    assert np.array_equal(O.e2m1_encode_magnitude(g["e2m1_probe"]), g["e2m1_codes"])
+
+
+def test_nvfp4_offsets(golden):
+    g = golden("nvfp4")
+    for (n, k), expect in zip(g["offset_shapes"], g["offsets"]):
+        assert O.nvfp4_offsets(int(n), int(k)) == tuple(int(v) for v in expect)
+    # core/src/test/.../artifact/Nvfp4LayoutTest.java:18-30
+    assert O.nvfp4_offsets(3, 1024) == (1536, 1792, 1796)
+
+
+@pytest.mark.parametrize("case", ["gauss", "spread", "padded", "edge"])
+def test_nvfp4_quantize_bytes_and_dequant(golden, case):
+    g = golden("nvfp4")
+    weights, blob, dense = g[f"{case}_weights"], g[f"{case}_blob"].tobytes(), g[f"{case}_dense"]
+    assert O.nvfp4_pack(weights) == blob
+    n, k = weights.shape
+    codes, scales, gs = O.nvfp4_unpack(blob, n, k)
+    mine = O.nvfp4_dequantize(codes, scales, gs)
+    assert np.array_equal(mine.view(np.uint32), dense.view(np.uint32))
+
+
+def test_nvfp4_gptq_fixture_decode(golden):
+    g = golden("gptq_decode")
+    stem = "NVFP4-row-split-k128-v1-seq"
+    codes, scales, decoded = g[f"{stem}-codes"], g[f"{stem}-scales"], g[f"{stem}-decoded"]
+    mine = O.nvfp4_dequantize(codes, scales, np.float32(g["nvfp4_global_scale"]))
+    assert np.array_equal(mine.view(np.uint32), decoded.view(np.uint32))
+
+
+def test_q3_sizes_and_pack_order(golden):
+    g = golden("q3")
+    for (n, k), size in zip(g["size_shapes"], g["sizes"]):
+        assert O.q3_offsets(int(n), int(k))[1] == int(size)
+    assert np.array_equal(O.q3_pack_codes(np.repeat(g["pack_codes"], 1, axis=0)), g["pack_bytes"])
+
+
+@pytest.mark.parametrize("case", ["gauss", "spread", "padded", "edge"])
+def test_q3_quantize_bytes(golden, case):
+    g = golden("q3")
+    weights, blob = g[f"{case}_weights"], g[f"{case}_blob"].tobytes()
+    assert O.q3_pack(weights) == blob
+    n, k = weights.shape
+    codes, scales = O.q3_unpack(blob, n, k)
+    requantized_codes, requantized_scales = O.q3_quantize(weights)
+    assert np.array_equal(codes, requantized_codes)
+    assert np.array_equal(scales.view(np.uint16), requantized_scales.view(np.uint16))
+
+
+@pytest.mark.parametrize("stem", ["Q3G64_F16S-row-split-k128-v1-seq", "Q3G64_F16S-row-split-k128-v1-act"])
+def test_q3_gptq_fixture_decode(golden, stem):
+    g = golden("gptq_decode")
+    codes, scales, decoded = g[f"{stem}-codes"], g[f"{stem}-scales"], g[f"{stem}-decoded"]
+    n, k = codes.shape
+    blob = O.q3_assemble(codes, scales, n, k)
+    mine = O.q3_dense(blob, n, k)
+    # The fixture keeps the sign of the value a zero code came from (-0.0); code * scale gives the scale's sign.
+    nonzero = decoded != 0
+    assert np.array_equal(mine[nonzero].view(np.uint32), decoded[nonzero].view(np.uint32))
+    assert not mine[~nonzero].any()
+
+
+@pytest.mark.parametrize("w", [32, 40, 48, 56, 64, 80, 96])
+def test_trellis_golden_tiles(golden, w):
+    g = golden("trellis")
+    mine = O.trellis_decode_tiles(g[f"tiles_{w}_packed"], w)
+    assert np.array_equal(mine.view(np.uint16), g[f"tiles_{w}_out"].view(np.uint16))
+
+
+@pytest.mark.parametrize("w", list(range(16, 129, 8)))
+def test_trellis_random_words_every_width(golden, w):
+    g = golden("trellis")
+    mine = O.trellis_decode_tiles(g[f"random_{w}_words"], w)
+    assert np.array_equal(mine.view(np.uint16), g[f"random_{w}_values"].view(np.uint16))
+
+
+def test_trellis_linear_and_helpers(golden):
+    g = golden("trellis")
+    q = O.trellis_rotated_weight(g["linear_payload"])
+    assert np.array_equal(q[:48, :48].view(np.uint16), g["linear_q_corner"].view(np.uint16))
+    y = O.trellis_linear_f64(g["linear_x"], g["linear_payload"], g["linear_suh"], g["linear_svh"], [256])
+    assert np.allclose(y, g["linear_y_f64"], rtol=1e-12, atol=1e-12)
+    y2 = O.trellis_linear_f64(g["seg_x"], g["seg_payload"], g["seg_suh"], g["seg_svh"], list(g["seg_ends"]))
+    assert np.allclose(y2, g["seg_y_f64"], rtol=1e-12, atol=1e-12)
+    assert np.array_equal(O.hadamard128(g["hadamard_in"]).view(np.uint32), g["hadamard_out"].view(np.uint32))
+    assert np.array_equal(O.trellis_fragment_order(g["fragment_in"]), g["fragment_out"])
+    for (k, n, t), s in zip(g["splits_cases"], g["splits"]):
+        assert O.trellis_splits(int(k), int(n), int(t)) == int(s)
+    # The float32 production-route model agrees with float64 within the reference's kernel tolerance
+    # (native/tests/test_trellis.py:157-165: 0.004 |y| + 0.004 rms).
+    model = O.trellis_linear_kernel_model(g["linear_x"], g["linear_payload"], g["linear_suh"], g["linear_svh"], [256])
+    rms = float(np.sqrt(np.mean(y ** 2)))
+    assert np.all(np.abs(model - y) <= 0.004 * np.abs(y) + 0.004 * rms)
+
+
+def test_bf16_rounding():
+    values = np.array([1.0, 1.00390625, 1.005859375, -3.1415926, 1e-30, 65504.0], dtype=np.float32)
+    bits = O.bf16_bits(values)
+    assert bits[0] == 0x3F80 and bits[1] == 0x3F80 and bits[2] == 0x3F81  # tie to even, then above the tie
+    assert np.array_equal(O.bf16_to_f32(bits), O.round_bf16(values))
+
+
+def test_activation_quantizer_properties():
+    """Two NVFP4 terms reconstruct BF16 activations to about 1% (native/tests/test_nvfp4_native.py:108-117 asserts
+    < 1.2% for the device quantizer); one term to about 10%."""
+    rng = np.random.default_rng(7)
+    x = O.bf16_bits(rng.standard_normal((4, 512)).astype(np.float32))
+    xf = O.bf16_to_f32(x).astype(np.float64)
+    for terms, bound in ((1, 0.13), (2, 0.012)):
+        codes, scales, g = O.quantize_activations(x, terms)
+        err = np.linalg.norm(O.activations_dense(codes, scales, g) - xf) / np.linalg.norm(xf)
+        assert err < bound, (terms, err)
+    zero = np.zeros((1, 128), dtype=np.uint16)
+    codes, scales, g = O.quantize_activations(zero)
+    assert g[0] == 1.0 and not codes.any() and not scales.any()
+    assert O.activation_layout(4096, 5120)[2] == O.activation_layout(4096, 5120)[1] + 4 * 4096
