@@ -1,0 +1,572 @@
+// Host side of libeuhedral_cuda.so: the C entry points declared in include/euhedral_cuda.h, their argument
+// validation and routing (as native/src/host/{nvfp4_linear,q3_linear_bf16,linear_kernels,kernel_table,reference}.c of
+// the reference do it), and the launches of the sm_100a kernels. No entry point allocates device memory or
+// synchronizes when a stream is selected, so every call can be recorded into a CUDA graph.
+#include "../../include/euhedral_cuda.h"
+
+#include <atomic>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+#include "exact_kernels.cuh"
+#include "nvfp4_gemv.cuh"
+#include "nvfp4_native.cuh"
+#include "q3_gemv.cuh"
+#include "trellis.cuh"
+
+namespace {
+
+// ---- per-thread and per-process selections (native/src/host/euhedral_cuda.c:30-38, cuda_kernel_loader.c:259-300) ---
+thread_local cudaStream_t t_stream = nullptr;
+thread_local int t_pdl = 0;
+thread_local int t_row_exact = 0;
+std::atomic<int> g_exact{0};
+
+__device__ uint32_t g_error_word;
+
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+    std::once_flag once;
+    int status = cudaSuccess;
+    int sms = 0;
+    int major = 0;
+    uint32_t* error_word = nullptr;
+};
+DeviceState g_devices[kMaxDevices];
+
+int finish(cudaError_t status) {
+    if (status != cudaSuccess) return (int)status;
+    if (t_stream != nullptr) return EUHEDRAL_CUDA_SUCCESS;
+    const cudaError_t sync = cudaDeviceSynchronize();
+    return sync == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)sync;
+}
+
+constexpr int kBigSmem = 200 * 1024;
+
+template <typename K>
+cudaError_t allow_big_smem(K kernel) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBigSmem);
+}
+
+template <int W>
+cudaError_t allow_trellis_width() {
+    cudaError_t e = allow_big_smem(trellis::mma_kernel<W, 1>);
+    if (e == cudaSuccess) e = allow_big_smem(trellis::mma_kernel<W, 4>);
+    return e;
+}
+
+void initialize_device(int device, DeviceState* state) {
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e == cudaSuccess) {
+        state->sms = prop.multiProcessorCount;
+        state->major = prop.major;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&state->error_word), g_error_word);
+    }
+    if (e == cudaSuccess) e = allow_big_smem(nvfp4::gemv_kernel<1>);
+    if (e == cudaSuccess) e = allow_big_smem(nvfp4::gemv_kernel<2>);
+    if (e == cudaSuccess) e = allow_big_smem(nvfp4::gemv_kernel<4>);
+    if (e == cudaSuccess) e = allow_big_smem(q3::gemv_kernel<1>);
+    if (e == cudaSuccess) e = allow_big_smem(q3::gemv_kernel<2>);
+    if (e == cudaSuccess) e = allow_big_smem(q3::gemv_kernel<4>);
+    if (e == cudaSuccess) e = allow_big_smem(exact::trellis_linear);
+#define EB_ALLOW(W) if (e == cudaSuccess) e = allow_trellis_width<W>();
+    EB_TRELLIS_WIDTHS(EB_ALLOW)
+#undef EB_ALLOW
+    if (e == cudaSuccess) e = nvfp4n::initialize();
+    state->status = (int)e;
+}
+
+// Binds the call to the thread's current device and makes sure that device's kernels are configured.
+int bind(DeviceState** out) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= kMaxDevices) return EUHEDRAL_CUDA_KERNEL_UNAVAILABLE;
+    DeviceState* state = &g_devices[device];
+    std::call_once(state->once, initialize_device, device, state);
+    if (state->status != cudaSuccess) return state->status;
+    if (state->major != 10) return EUHEDRAL_CUDA_KERNEL_UNAVAILABLE;   // sm_100a code only
+    *out = state;
+    return EUHEDRAL_CUDA_SUCCESS;
+}
+
+// One launch on the selected stream, with the cluster dimension and the programmatic-dependent-launch attribute when asked.
+template <typename... Params, typename... Args>
+cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared, unsigned cluster, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared;
+    config.stream = t_stream;
+    cudaLaunchAttribute attributes[2];
+    unsigned count = 0;
+    if (cluster > 1) {
+        attributes[count].id = cudaLaunchAttributeClusterDimension;
+        attributes[count].val.clusterDim.x = cluster;
+        attributes[count].val.clusterDim.y = 1;
+        attributes[count].val.clusterDim.z = 1;
+        ++count;
+    }
+    if (t_pdl) {
+        attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[count].val.programmaticStreamSerializationAllowed = 1;
+        ++count;
+    }
+    config.attrs = attributes;
+    config.numAttrs = count;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+// ---- decode GEMV planning ---------------------------------------------------------------------------------------------
+// K slices per row depend on K only (nvfp4::split_of); the 16-row tiles per CTA on the shape and the SM count: the
+// largest of 4, 2, 1 that divides the rows, fits two CTAs per SM at 8 activation rows, and still gives two CTAs per SM
+// over the whole grid; else the count that gives the most CTAs.
+struct DecodePlan {
+    uint32_t rt, split, ctas, shared;
+};
+
+template <typename TileT>
+bool plan_decode(uint32_t rows, uint32_t k, uint32_t n, int sms, DecodePlan* plan) {
+    if (k == 0 || k % 128u != 0 || n == 0 || n % 16u != 0 || rows == 0 || rows > 8u) return false;
+    const uint32_t chunks = k / 128u, split = nvfp4::split_of(k);
+    const uint32_t chunks_max = (chunks + split - 1u) / split;
+    uint32_t chosen = 0;
+    for (uint32_t rt = 4; rt >= 1; rt >>= 1) {
+        if (n % (16u * rt) != 0 || TileT(rt, chunks_max, 8, split).bytes > 110u * 1024u) continue;
+        chosen = rt;   // the smallest valid tile count survives when none fills the GPU
+        if ((uint64_t)(n / (16u * rt)) * split >= 2ull * (uint64_t)sms) break;
+    }
+    if (chosen == 0) return false;
+    plan->rt = chosen;
+    plan->split = split;
+    plan->ctas = n / (16u * chosen) * split;
+    plan->shared = TileT(chosen, chunks_max, rows, split).bytes;
+    return plan->shared <= (uint32_t)kBigSmem;
+}
+
+cudaError_t launch_nvfp4(const DecodePlan& p, const void* x, const void* w, void* y, uint32_t rows, uint32_t k, uint32_t n,
+        uint32_t* error) {
+    const dim3 grid(p.ctas), block(64u * p.rt);
+    auto xs = static_cast<const uint16_t*>(x);
+    auto ws = static_cast<const uint8_t*>(w);
+    auto ys = static_cast<uint16_t*>(y);
+    switch (p.rt) {
+        case 4: return launch(nvfp4::gemv_kernel<4>, grid, block, p.shared, p.split, xs, ws, ys, rows, k, n, p.split, error);
+        case 2: return launch(nvfp4::gemv_kernel<2>, grid, block, p.shared, p.split, xs, ws, ys, rows, k, n, p.split, error);
+        default: return launch(nvfp4::gemv_kernel<1>, grid, block, p.shared, p.split, xs, ws, ys, rows, k, n, p.split, error);
+    }
+}
+
+cudaError_t launch_q3(const DecodePlan& p, const void* x, const void* w, void* y, uint32_t rows, uint32_t k, uint32_t n,
+        uint32_t* error) {
+    const dim3 grid(p.ctas), block(64u * p.rt);
+    auto xs = static_cast<const uint16_t*>(x);
+    auto ws = static_cast<const uint8_t*>(w);
+    auto ys = static_cast<uint16_t*>(y);
+    switch (p.rt) {
+        case 4: return launch(q3::gemv_kernel<4>, grid, block, p.shared, p.split, xs, ws, ys, rows, k, n, p.split, error);
+        case 2: return launch(q3::gemv_kernel<2>, grid, block, p.shared, p.split, xs, ws, ys, rows, k, n, p.split, error);
+        default: return launch(q3::gemv_kernel<1>, grid, block, p.shared, p.split, xs, ws, ys, rows, k, n, p.split, error);
+    }
+}
+
+uint32_t capped_grid(uint64_t count) { return count > 2147483647ull ? 2147483647u : (uint32_t)count; }
+
+// NVFP4 tensor byte size: 0 plain, 1 SD4 (table-indexed scales), -1 neither (native/src/host/nvfp4_linear.c:79-91).
+int nvfp4_layout(uint32_t rows, uint32_t k, uint64_t bytes) {
+    if (bytes == nvfp4::Geometry(rows, k).size) return 0;
+    const uint64_t kp = ((uint64_t)k + 127u) / 128u * 128u;
+    const uint64_t index_offset = nvfp4::align256((uint64_t)rows * kp / 2u);
+    if (bytes == nvfp4::align256(index_offset + (uint64_t)rows * kp / 32u) + 20u) return 1;
+    return -1;
+}
+
+// ---- trellis table ------------------------------------------------------------------------------------------------------
+struct TableEntry {
+    const char* name;
+    int available;
+    int count;
+    uint8_t sizes[12];
+};
+// Order is the ABI (native/src/host/linear_kernels.c:7-24). Entries whose kernels this build does not carry stay in
+// the table, unavailable: the whole-K prefill kernels and their epilogue, the FP8 kernels, the embedding lookup.
+const TableEntry kTable[] = {
+        {"euhedral_trellis_prepass", 1, 7, {8, 8, 8, 4, 4, 4, 4}},
+        {"euhedral_trellis_mma", 1, 12, {8, 8, 8, 8, 8, 8, 4, 4, 4, 4, 4, 4}},
+        {"euhedral_trellis_mma_rows", 0, 11, {8, 8, 8, 8, 8, 4, 4, 4, 4, 4, 4}},
+        {"euhedral_trellis_mma_rows64", 0, 11, {8, 8, 8, 8, 8, 4, 4, 4, 4, 4, 4}},
+        {"euhedral_trellis_epilogue", 1, 6, {8, 4, 8, 8, 4, 4}},
+        {"euhedral_trellis_decode_bf16", 1, 5, {8, 8, 4, 4, 4}},
+        {"euhedral_trellis_epilogue_bf16", 0, 7, {8, 8, 4, 8, 8, 4, 4}},
+        {"euhedral_trellis_reference", 1, 11, {8, 8, 8, 8, 8, 4, 8, 4, 4, 4, 4}},
+        {"euhedral_trellis_mma_rows_fp8", 0, 11, {8, 8, 8, 8, 8, 4, 4, 4, 4, 4, 4}},
+        {"euhedral_trellis_mma_rows64_fp8", 0, 11, {8, 8, 8, 8, 8, 4, 4, 4, 4, 4, 4}},
+        {"euhedral_nvfp4_embedding", 0, 0, {0}},
+};
+constexpr int kTableCount = (int)(sizeof(kTable) / sizeof(kTable[0]));
+
+bool trellis_width_valid(int w) { return w >= 16 && w <= 128 && w % 8 == 0; }
+
+template <int W>
+cudaError_t launch_trellis_mma(const uint64_t* a, uint32_t* error) {
+    const int rows = (int)a[6], k = (int)a[7], n = (int)a[8], splits = (int)a[10], s = (int)a[11];
+    const dim3 grid((unsigned)(n / 128), (unsigned)splits), block(256);
+    const size_t shared = (size_t)trellis::kStages * trellis::kStageTiles * 8u * W * 2u;
+    auto act = reinterpret_cast<const uint16_t*>(a[0]);
+    auto words = reinterpret_cast<const uint16_t*>(a[1]);
+    auto ends = reinterpret_cast<const int*>(a[2]);
+    auto svh = reinterpret_cast<const uint16_t*>(a[3]);
+    auto partials = reinterpret_cast<float*>(a[4]);
+    auto out = reinterpret_cast<uint16_t*>(a[5]);
+    if (rows <= 8) return launch(trellis::mma_kernel<W, 1>, grid, block, shared, 1u, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
+    return launch(trellis::mma_kernel<W, 4>, grid, block, shared, 1u, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
+}
+
+}  // namespace
+
+extern "C" {
+
+void* euhedral_cuda_submission_stream(void) { return t_stream; }
+
+int euhedral_cuda_set_include_directory(const char* path) {
+    if (path == nullptr || path[0] == '\0' || std::strlen(path) >= 4096) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    return EUHEDRAL_CUDA_SUCCESS;
+}
+
+void* euhedral_cuda_malloc(uint64_t byte_size) {
+    if (byte_size == 0) return nullptr;
+    void* address = nullptr;
+    return cudaMalloc(&address, (size_t)byte_size) == cudaSuccess ? address : nullptr;
+}
+
+int euhedral_cuda_free(void* address) {
+    if (address == nullptr) return EUHEDRAL_CUDA_SUCCESS;
+    const cudaError_t e = cudaFree(address);
+    return e == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)e;
+}
+
+void* euhedral_cuda_host_malloc(uint64_t byte_size) {
+    if (byte_size == 0) return nullptr;
+    void* address = nullptr;
+    return cudaMallocHost(&address, (size_t)byte_size) == cudaSuccess ? address : nullptr;
+}
+
+int euhedral_cuda_host_free(void* address) {
+    if (address == nullptr) return EUHEDRAL_CUDA_SUCCESS;
+    const cudaError_t e = cudaFreeHost(address);
+    return e == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)e;
+}
+
+int euhedral_cuda_multiprocessor_count(int32_t* count) {
+    if (count == nullptr) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    int device = 0, value = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device);
+    if (e != cudaSuccess) return (int)e;
+    *count = value;
+    return EUHEDRAL_CUDA_SUCCESS;
+}
+
+int euhedral_cuda_compute_capability(int32_t* major, int32_t* minor) {
+    if (major == nullptr || minor == nullptr) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    int device = 0, high = 0, low = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&high, cudaDevAttrComputeCapabilityMajor, device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&low, cudaDevAttrComputeCapabilityMinor, device);
+    if (e != cudaSuccess) return (int)e;
+    *major = high;
+    *minor = low;
+    return EUHEDRAL_CUDA_SUCCESS;
+}
+
+int euhedral_cuda_copy_host_to_device(void* device_address, const void* host_address, uint64_t byte_size) {
+    if (byte_size == 0) return EUHEDRAL_CUDA_SUCCESS;
+    if (device_address == nullptr || host_address == nullptr) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    cudaError_t e = t_stream == nullptr ? cudaMemcpy(device_address, host_address, (size_t)byte_size, cudaMemcpyHostToDevice)
+                                        : cudaMemcpyAsync(device_address, host_address, (size_t)byte_size, cudaMemcpyHostToDevice, t_stream);
+    if (e == cudaSuccess && t_stream != nullptr) e = cudaStreamSynchronize(t_stream);
+    return e == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)e;
+}
+
+int euhedral_cuda_copy_upload_to_device(void* device_address, const void* host_address, uint64_t byte_size) {
+    if (device_address == nullptr || host_address == nullptr || byte_size == 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    const cudaError_t e = t_stream == nullptr ? cudaMemcpy(device_address, host_address, (size_t)byte_size, cudaMemcpyHostToDevice)
+                                              : cudaMemcpyAsync(device_address, host_address, (size_t)byte_size, cudaMemcpyHostToDevice, t_stream);
+    return e == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)e;
+}
+
+int euhedral_cuda_copy_device_to_host(void* host_address, const void* device_address, uint64_t byte_size) {
+    if (byte_size == 0) return EUHEDRAL_CUDA_SUCCESS;
+    if (host_address == nullptr || device_address == nullptr) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    cudaError_t e = t_stream == nullptr ? cudaMemcpy(host_address, device_address, (size_t)byte_size, cudaMemcpyDeviceToHost)
+                                        : cudaMemcpyAsync(host_address, device_address, (size_t)byte_size, cudaMemcpyDeviceToHost, t_stream);
+    if (e == cudaSuccess && t_stream != nullptr) e = cudaStreamSynchronize(t_stream);
+    return e == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)e;
+}
+
+int euhedral_cuda_copy_device_to_readback(void* host_address, const void* device_address, uint64_t byte_size) {
+    if (host_address == nullptr || device_address == nullptr || byte_size == 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    const cudaError_t e = t_stream == nullptr ? cudaMemcpy(host_address, device_address, (size_t)byte_size, cudaMemcpyDeviceToHost)
+                                              : cudaMemcpyAsync(host_address, device_address, (size_t)byte_size, cudaMemcpyDeviceToHost, t_stream);
+    return e == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)e;
+}
+
+int euhedral_cuda_synchronize(void) {
+    const cudaError_t e = cudaDeviceSynchronize();
+    return e == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)e;
+}
+
+uint64_t euhedral_cuda_stream_create(void) {
+    cudaStream_t stream = nullptr;
+    if (cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) != cudaSuccess) return 0;
+    return (uint64_t)(uintptr_t)stream;
+}
+
+int euhedral_cuda_stream_destroy(uint64_t stream) {
+    if (stream == 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    const cudaError_t e = cudaStreamDestroy((cudaStream_t)(uintptr_t)stream);
+    return e == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)e;
+}
+
+int euhedral_cuda_stream_synchronize(uint64_t stream) {
+    if (stream == 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    const cudaError_t e = cudaStreamSynchronize((cudaStream_t)(uintptr_t)stream);
+    return e == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)e;
+}
+
+int euhedral_cuda_stream_select(uint64_t stream) {
+    if (stream == 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    t_stream = (cudaStream_t)(uintptr_t)stream;
+    return EUHEDRAL_CUDA_SUCCESS;
+}
+
+void euhedral_cuda_stream_clear(void) { t_stream = nullptr; }
+void euhedral_cuda_pdl_select(int enabled) { t_pdl = enabled != 0; }
+void euhedral_cuda_row_exact_select(int enabled) { t_row_exact = enabled != 0; }
+int euhedral_cuda_select_exact_numerics(int exact) { return g_exact.exchange(exact != 0 ? 1 : 0); }
+
+// ---- Q3 -------------------------------------------------------------------------------------------------------------
+
+static int q3_reference(DeviceState* state, const void* input, const void* weights, void* output, uint32_t rows,
+        uint32_t in_features, uint32_t out_features) {
+    (void)state;
+    const uint64_t count = (uint64_t)rows * out_features;
+    if (count > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
+    const q3::Geometry geo(out_features, in_features);
+    return finish(launch(exact::q3_linear, dim3((unsigned)count), dim3(128), 0, 1u, static_cast<const uint16_t*>(input),
+            static_cast<const uint8_t*>(weights), static_cast<uint16_t*>(output), rows, in_features, out_features,
+            (uint64_t)geo.scale_offset));
+}
+
+static int q3_validate(const void* input, const void* weights, void* output, uint32_t rows, uint32_t in_features,
+        uint32_t out_features, uint64_t bytes) {
+    if (input == nullptr || weights == nullptr || output == nullptr || rows == 0 || in_features == 0 || out_features == 0 || bytes == 0)
+        return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    if (q3::Geometry(out_features, in_features).size != bytes) return EUHEDRAL_CUDA_FORMAT_MISMATCH;
+    return EUHEDRAL_CUDA_SUCCESS;
+}
+
+int euhedral_cuda_linear_q3_bf16(const void* input, const void* weights, void* output, uint32_t rows, uint32_t in_features,
+        uint32_t out_features, uint64_t weights_byte_size) {
+    int status = q3_validate(input, weights, output, rows, in_features, out_features, weights_byte_size);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    DeviceState* state = nullptr;
+    status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    DecodePlan plan;
+    const bool qualified = rows <= 32u && ((uintptr_t)input & 15u) == 0 && ((uintptr_t)weights & 15u) == 0
+            && plan_decode<q3::Tile>(rows < 8u ? rows : 8u, in_features, out_features, state->sms, &plan);
+    if (g_exact.load() || !qualified) return q3_reference(state, input, weights, output, rows, in_features, out_features);
+    for (uint32_t first = 0; first < rows; first += 8u) {
+        const uint32_t group = rows - first < 8u ? rows - first : 8u;
+        plan_decode<q3::Tile>(group, in_features, out_features, state->sms, &plan);
+        const cudaError_t e = launch_q3(plan, static_cast<const uint16_t*>(input) + (uint64_t)first * in_features, weights,
+                static_cast<uint16_t*>(output) + (uint64_t)first * out_features, group, in_features, out_features, state->error_word);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return finish(cudaSuccess);
+}
+
+int euhedral_cuda_linear_q3_reference_bf16(const void* input, const void* weights, void* output, uint32_t rows,
+        uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size) {
+    int status = q3_validate(input, weights, output, rows, in_features, out_features, weights_byte_size);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    DeviceState* state = nullptr;
+    status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    return q3_reference(state, input, weights, output, rows, in_features, out_features);
+}
+
+// ---- NVFP4 ------------------------------------------------------------------------------------------------------------
+
+int euhedral_cuda_linear_nvfp4_bf16(const void* input, const void* weights, void* output, uint32_t rows, uint32_t in_features,
+        uint32_t out_features, uint64_t weights_byte_size) {
+    if (input == nullptr || weights == nullptr || output == nullptr || rows == 0 || in_features == 0 || out_features == 0)
+        return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    const int layout = nvfp4_layout(out_features, in_features, weights_byte_size);
+    if (layout < 0) return EUHEDRAL_CUDA_FORMAT_MISMATCH;
+    if (in_features % 32u != 0 || ((uintptr_t)input & 15u) != 0 || ((uintptr_t)weights & 15u) != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    if (layout == 1) return EUHEDRAL_CUDA_KERNEL_UNAVAILABLE;   // table-indexed scales (SD4): no kernel in this build
+    DeviceState* state = nullptr;
+    const int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    DecodePlan plan;
+    const bool qualified = rows <= 32u && plan_decode<nvfp4::Tile>(rows < 8u ? rows : 8u, in_features, out_features, state->sms, &plan);
+    if (g_exact.load() || !qualified) {
+        return finish(launch(exact::nvfp4_linear, dim3(capped_grid((uint64_t)rows * out_features)), dim3(128), 0, 1u,
+                static_cast<const uint16_t*>(input), static_cast<const uint8_t*>(weights), static_cast<uint16_t*>(output), rows,
+                in_features, out_features));
+    }
+    for (uint32_t first = 0; first < rows; first += 8u) {
+        const uint32_t group = rows - first < 8u ? rows - first : 8u;
+        plan_decode<nvfp4::Tile>(group, in_features, out_features, state->sms, &plan);
+        const cudaError_t e = launch_nvfp4(plan, static_cast<const uint16_t*>(input) + (uint64_t)first * in_features, weights,
+                static_cast<uint16_t*>(output) + (uint64_t)first * out_features, group, in_features, out_features, state->error_word);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return finish(cudaSuccess);
+}
+
+int euhedral_cuda_nvfp4_native_available(void) {
+    DeviceState* state = nullptr;
+    return bind(&state) == EUHEDRAL_CUDA_SUCCESS ? 1 : 0;
+}
+
+uint64_t euhedral_cuda_nvfp4_native_scratch_bytes(uint32_t rows, uint32_t in_features, uint32_t out_features) {
+    (void)out_features;
+    return nvfp4n::ActivationLayout(rows, in_features).bytes;
+}
+
+int euhedral_cuda_linear_nvfp4_native_bf16(const void* input, const void* weights, void* output, void* scratch, uint32_t rows,
+        uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size, uint64_t scratch_byte_size) {
+    DeviceState* state = nullptr;
+    int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    if (in_features % 128u != 0 || g_exact.load()) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    if (input == nullptr || weights == nullptr || output == nullptr || rows == 0 || in_features == 0 || out_features == 0)
+        return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    const int layout = nvfp4_layout(out_features, in_features, weights_byte_size);
+    if (layout < 0) return EUHEDRAL_CUDA_FORMAT_MISMATCH;
+    if (((uintptr_t)input & 15u) != 0 || ((uintptr_t)weights & 15u) != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    if (layout == 1 || in_features % 256u != 0 || out_features % 128u != 0 || ((uintptr_t)scratch & 127u) != 0)
+        return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    if (scratch == nullptr || scratch_byte_size < nvfp4n::ActivationLayout(rows, in_features).bytes) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    if (((uint64_t)rows + 127u) / 128u * (out_features / 128u) > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
+    return finish(nvfp4n::run(input, weights, output, scratch, rows, in_features, out_features, state->sms, t_stream, t_pdl != 0,
+            state->error_word));
+}
+
+// ---- kernel table -------------------------------------------------------------------------------------------------------
+
+int euhedral_cuda_linear_kernel_count(void) { return kTableCount; }
+
+const char* euhedral_cuda_linear_kernel_name(int index) { return index >= 0 && index < kTableCount ? kTable[index].name : nullptr; }
+
+int euhedral_cuda_linear_kernel_available(int32_t kernel) {
+    if (kernel < 0 || kernel >= kTableCount) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    DeviceState* state = nullptr;
+    const int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    return kTable[kernel].available;
+}
+
+int euhedral_cuda_linear_launch(int32_t kernel, uint32_t grid_x, uint32_t grid_y, uint32_t grid_z, uint32_t block_x,
+        uint32_t block_y, uint32_t block_z, uint32_t shared_bytes, const uint64_t* words, const uint8_t* sizes, int32_t count) {
+    (void)shared_bytes;
+    if (kernel < 0 || kernel >= kTableCount || words == nullptr || sizes == nullptr || count < 0 || count > 32 || grid_x == 0
+            || grid_y == 0 || grid_z == 0 || block_x == 0 || block_y == 0 || block_z == 0)
+        return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    DeviceState* state = nullptr;
+    const int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    const TableEntry& entry = kTable[kernel];
+    if (!entry.available) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    if (count != entry.count) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    uint64_t a[12];
+    for (int i = 0; i < count; ++i) {
+        if (sizes[i] != entry.sizes[i]) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+        a[i] = sizes[i] == 8 ? words[i] : (uint64_t)(uint32_t)words[i];
+    }
+    switch (kernel) {
+        case 0: {   // prepass(x, suh, out, rows, k, s, layout)
+            const int rows = (int)a[3], k = (int)a[4], s = (int)a[5], layout = (int)a[6];
+            if (rows <= 0 || k <= 0 || k % 128 != 0 || s <= 0 || rows > 65535 || s > 65535) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+            if (layout != 0 && layout != 1) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;   // 2 = block FP8: no kernel here
+            return finish(launch(trellis::prepass_kernel, dim3((unsigned)((k + 511) / 512), (unsigned)rows, (unsigned)s), dim3(128), 0, 1u,
+                    reinterpret_cast<const uint16_t*>(a[0]), reinterpret_cast<const uint16_t*>(a[1]), reinterpret_cast<uint16_t*>(a[2]),
+                    rows, k, s, layout));
+        }
+        case 1: {   // mma(act, words, ends, svh, partials, out, rows, k, n, w, splits, s)
+            const int rows = (int)a[6], k = (int)a[7], n = (int)a[8], w = (int)a[9], splits = (int)a[10], s = (int)a[11];
+            if (rows <= 0 || k <= 0 || k % 128 != 0 || n <= 0 || n % 128 != 0 || !trellis_width_valid(w) || splits <= 0
+                    || splits > k / 16 || splits > 65535 || s <= 0 || (a[1] & 15u) != 0)
+                return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+            cudaError_t e = cudaErrorInvalidValue;
+            switch (w) {
+#define EB_CASE(W) case W: e = launch_trellis_mma<W>(a, state->error_word); break;
+                EB_TRELLIS_WIDTHS(EB_CASE)
+#undef EB_CASE
+            }
+            return finish(e);
+        }
+        case 4: {   // epilogue(partials, splits, svh, out, rows, n)
+            const int splits = (int)a[1], rows = (int)a[4], n = (int)a[5];
+            if (splits <= 0 || rows <= 0 || rows > 65535 || n <= 0 || n % 128 != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+            return finish(launch(trellis::epilogue_kernel, dim3((unsigned)((n + 511) / 512), (unsigned)rows), dim3(128), 0, 1u,
+                    reinterpret_cast<const float*>(a[0]), splits, reinterpret_cast<const uint16_t*>(a[2]), reinterpret_cast<uint16_t*>(a[3]), rows, n));
+        }
+        case 5: {   // decode_bf16(words, out, k, n, w)
+            const int k = (int)a[2], n = (int)a[3], w = (int)a[4];
+            if (k <= 0 || k % 16 != 0 || n <= 0 || n % 16 != 0 || !trellis_width_valid(w)) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+            const uint64_t tiles = (uint64_t)(k / 16) * (uint64_t)(n / 16);
+            if (tiles > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
+            return finish(launch(trellis::decode_bf16_kernel, dim3((unsigned)tiles), dim3(256), 0, 1u,
+                    reinterpret_cast<const uint16_t*>(a[0]), reinterpret_cast<uint16_t*>(a[1]), k, n, w));
+        }
+        case 7: {   // reference(x, words, suh, svh, ends, s, out, rows, k, n, w)
+            const int s = (int)a[5], rows = (int)a[7], k = (int)a[8], n = (int)a[9], w = (int)a[10];
+            if (s <= 0 || rows <= 0 || k <= 0 || k % 128 != 0 || n <= 0 || n % 128 != 0 || !trellis_width_valid(w)) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+            const uint64_t grid = (uint64_t)rows * (uint64_t)n;
+            if (grid > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
+            if ((size_t)k * 4u > (size_t)kBigSmem) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+            return finish(launch(exact::trellis_linear, dim3((unsigned)grid), dim3(128), (size_t)k * 4u, 1u,
+                    reinterpret_cast<const uint16_t*>(a[0]), reinterpret_cast<const uint16_t*>(a[1]), reinterpret_cast<const uint16_t*>(a[2]),
+                    reinterpret_cast<const uint16_t*>(a[3]), reinterpret_cast<const int*>(a[4]), s, reinterpret_cast<uint16_t*>(a[6]), rows, k, n, w));
+        }
+        default: return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    }
+}
+
+// ---- additions -----------------------------------------------------------------------------------------------------------
+
+int euhedral_b200_take_device_error(uint32_t* word) {
+    if (word == nullptr) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    DeviceState* state = nullptr;
+    const int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(word, state->error_word, 4, cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess) e = cudaMemset(state->error_word, 0, 4);
+    return e == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)e;
+}
+
+int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t* row_tiles,
+        uint32_t* k_slices, uint32_t* ctas, uint32_t* shared_bytes) {
+    if (row_tiles == nullptr || k_slices == nullptr || ctas == nullptr || shared_bytes == nullptr) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    int sms = 148;
+    DeviceState* state = nullptr;
+    if (bind(&state) == EUHEDRAL_CUDA_SUCCESS) sms = state->sms;
+    DecodePlan plan;
+    const bool ok = format == 0 ? plan_decode<nvfp4::Tile>(rows, in_features, out_features, sms, &plan)
+                                : plan_decode<q3::Tile>(rows, in_features, out_features, sms, &plan);
+    if (!ok) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    *row_tiles = plan.rt;
+    *k_slices = plan.split;
+    *ctas = plan.ctas;
+    *shared_bytes = plan.shared;
+    return EUHEDRAL_CUDA_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,114 @@
+/* C ABI of libeuhedral_cuda.so (sm_100a build): the quantized-linear subset of the reference's native library, with
+ * the same names, argument meaning, status codes and threading rules, so that a host that binds these symbols (the
+ * reference's Java FFM downcalls, its Rust loader, or ctypes) can load this library in place of the reference's for
+ * the linear path. Each declaration cites the reference declaration it replaces (native/include/euhedral_cuda.h of
+ * the reference project unless another file is named).
+ *
+ * Status codes: 0 success; negative = the library's own codes below; positive = a raw cudaError_t.
+ * All pointers named device_* / input / weights / output / scratch are device addresses owned by the caller.
+ * Thread-local state: selected stream, programmatic-dependent-launch flag, row-exact flag. Process-wide: exact numerics.
+ * With a stream selected a call only enqueues work; with none it runs on the default stream and synchronizes the
+ * device before returning. */
+#ifndef EUHEDRAL_B200_CUDA_H
+#define EUHEDRAL_B200_CUDA_H
+
+#include <stdint.h>
+
+#define EUHEDRAL_CUDA_EXPORT __attribute__((visibility("default")))
+
+/* reference :15-21 */
+#define EUHEDRAL_CUDA_SUCCESS 0
+#define EUHEDRAL_CUDA_INVALID_ARGUMENT (-1)
+#define EUHEDRAL_CUDA_SIZE_OVERFLOW (-2)
+#define EUHEDRAL_CUDA_FORMAT_MISMATCH (-3)
+#define EUHEDRAL_CUDA_KERNEL_UNAVAILABLE (-4)
+#define EUHEDRAL_CUDA_ROUTE_UNAVAILABLE (-5)
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- supporting symbols needed to drive the linear path ---------------------------------------------------------- */
+
+/* reference :7 - the calling thread's selected stream, NULL when none. */
+EUHEDRAL_CUDA_EXPORT void* euhedral_cuda_submission_stream(void);
+/* reference :30 - kernels here are prebuilt for sm_100a; accepted and ignored (same argument validation). */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_set_include_directory(const char* path);
+/* reference :31-32 */
+EUHEDRAL_CUDA_EXPORT void* euhedral_cuda_malloc(uint64_t byte_size);
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_free(void* address);
+/* reference :35-36 - pinned host memory. */
+EUHEDRAL_CUDA_EXPORT void* euhedral_cuda_host_malloc(uint64_t byte_size);
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_host_free(void* address);
+/* reference :46-49 */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_multiprocessor_count(int32_t* count);
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_compute_capability(int32_t* major, int32_t* minor);
+/* reference :51-60 - a copy that completes before returning; and a copy queued on the selected stream from pinned memory. */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_copy_host_to_device(void* device_address, const void* host_address, uint64_t byte_size);
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_copy_upload_to_device(void* device_address, const void* host_address, uint64_t byte_size);
+/* reference :62-65 - completes before returning (the selected stream is synchronized). */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_copy_device_to_host(void* host_address, const void* device_address, uint64_t byte_size);
+/* reference :67-72 - pinned destination, queued on the selected stream without synchronizing. */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_copy_device_to_readback(void* host_address, const void* device_address, uint64_t byte_size);
+/* reference :392-397 */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_synchronize(void);
+EUHEDRAL_CUDA_EXPORT uint64_t euhedral_cuda_stream_create(void);
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_stream_destroy(uint64_t stream);
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_stream_synchronize(uint64_t stream);
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_stream_select(uint64_t stream);
+EUHEDRAL_CUDA_EXPORT void euhedral_cuda_stream_clear(void);
+/* reference :399-402 */
+EUHEDRAL_CUDA_EXPORT void euhedral_cuda_pdl_select(int enabled);
+EUHEDRAL_CUDA_EXPORT void euhedral_cuda_row_exact_select(int enabled);
+/* reference :147 - nonzero routes every quantized linear to its scalar FP32 kernel; returns the previous selection. */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_select_exact_numerics(int exact);
+
+/* ---- quantized linears ------------------------------------------------------------------------------------------- */
+
+/* reference :127-134 - Q3G64_F16S weights, BF16 rows in and out. 1..8 rows on the decode kernel, 9..32 as groups of 8
+ * (every row bit for bit the one-row result); exact numerics, other row counts, shapes (in_features % 128,
+ * out_features % 16) or alignments (input, weights 16 bytes) on the scalar kernel. */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_q3_bf16(const void* device_input, const void* device_weights,
+        void* device_output, uint32_t rows, uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size);
+/* reference :136-143 - the scalar Q3 kernel, always. */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_q3_reference_bf16(const void* device_input, const void* device_weights,
+        void* device_output, uint32_t rows, uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size);
+/* reference :152-154 - NVFP4 weights (row-split-k128-v1), BF16 rows in and out, same routing as Q3. */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_nvfp4_bf16(const void* input, const void* weights, void* output,
+        uint32_t rows, uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size);
+/* reference :159-167 - the native FP4 route: activations quantized to two NVFP4 terms in `scratch`, block-scaled FP4
+ * tensor-core GEMM (tcgen05 kind::mxf4nvf4 here). ROUTE_UNAVAILABLE under exact numerics or unsupported shapes. */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_nvfp4_native_available(void);
+EUHEDRAL_CUDA_EXPORT uint64_t euhedral_cuda_nvfp4_native_scratch_bytes(uint32_t rows, uint32_t in_features, uint32_t out_features);
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_nvfp4_native_bf16(const void* input, const void* weights, void* output,
+        void* scratch, uint32_t rows, uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size,
+        uint64_t scratch_byte_size);
+
+/* ---- the shared linear kernel table (trellis launches) ------------------------------------------------------------ */
+
+/* reference :446-453; table order native/src/host/linear_kernels.c:7-24. `words` holds the arguments, each 8 bytes wide
+ * in the array and sizes[i] (4 or 8) bytes wide in the kernel's signature; count and widths are checked. The launch
+ * geometry is re-derived from the arguments; the grid and block passed must be nonzero. */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_kernel_count(void);
+EUHEDRAL_CUDA_EXPORT const char* euhedral_cuda_linear_kernel_name(int index);
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_kernel_available(int32_t kernel);
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_launch(int32_t kernel, uint32_t grid_x, uint32_t grid_y, uint32_t grid_z,
+        uint32_t block_x, uint32_t block_y, uint32_t block_z, uint32_t shared_bytes, const uint64_t* words,
+        const uint8_t* sizes, int32_t count);
+
+/* ---- additions without a counterpart in the reference -------------------------------------------------------------- */
+
+/* Reads and clears the current device's kernel error word: nonzero when a bounded wait inside a kernel gave up
+ * (bit 0 NVFP4 GEMV, bit 1 Q3 GEMV, bit 2 trellis GEMM, bit 3 NVFP4 prefill GEMM). Synchronizes the device. */
+EUHEDRAL_CUDA_EXPORT int euhedral_b200_take_device_error(uint32_t* word);
+/* The launch geometry chosen for a decode GEMV of this shape: 16-row tiles per CTA, K slices per row (cluster size),
+ * CTAs and dynamic shared bytes for `rows` activation rows. format: 0 NVFP4, 1 Q3. Returns 0, or -1 for a shape the
+ * decode kernels do not take. */
+EUHEDRAL_CUDA_EXPORT int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, uint32_t out_features,
+        uint32_t* row_tiles, uint32_t* k_slices, uint32_t* ctas, uint32_t* shared_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif
