@@ -15,12 +15,13 @@ def torch_cuda():
 
 
 class Device:
-    """A CudaGpuMemory with torch-owned buffers; every call is queued on torch's current stream."""
+    """A CudaGpuMemory with torch-owned buffers; every call is queued on a side stream of its own."""
 
     def __init__(self):
         from euhedral_b200.gpu import CudaGpuMemory
         self.torch = torch_cuda()
         self.gpu = CudaGpuMemory()
+        self.side = self.torch.cuda.Stream()   # the library takes a real stream handle, not the default stream's 0
         self.keep = []
 
     def put(self, array: np.ndarray):
@@ -40,9 +41,10 @@ class Device:
         return tensor[:count].cpu().numpy().view(dtype).reshape(shape).copy()
 
     def stream(self) -> int:
-        return self.torch.cuda.current_stream().cuda_stream
+        return self.side.cuda_stream
 
     def submit(self, pdl: bool = False, row_exact: bool = False):
+        self.torch.cuda.current_stream().synchronize()   # uploads ran on torch's stream
         return self.gpu.submit(self.stream(), pdl=pdl, row_exact=row_exact)
 
     def release(self):
