@@ -133,7 +133,11 @@ bool plan_decode(uint32_t rows, uint32_t k, uint32_t n, int sms, DecodePlan* pla
     const uint32_t chunks = k / 128u, split = nvfp4::split_of(k);
     const uint32_t chunks_max = (chunks + split - 1u) / split;
     uint32_t chosen = 0;
+#ifdef EB_FORCE_RT
+    for (uint32_t rt = EB_FORCE_RT; rt >= 1; rt >>= 1) {
+#else
     for (uint32_t rt = 4; rt >= 1; rt >>= 1) {
+#endif
         if (n % (16u * rt) != 0 || TileT(rt, chunks_max, 8, split).bytes > 110u * 1024u) continue;
         chosen = rt;   // the smallest valid tile count survives when none fills the GPU
         if ((uint64_t)(n / (16u * rt)) * split >= 2ull * (uint64_t)sms) break;
@@ -435,8 +439,7 @@ int euhedral_cuda_nvfp4_native_available(void) {
 }
 
 uint64_t euhedral_cuda_nvfp4_native_scratch_bytes(uint32_t rows, uint32_t in_features, uint32_t out_features) {
-    (void)out_features;
-    return nvfp4n::ActivationLayout(rows, in_features).bytes;
+    return nvfp4n::ActivationLayout(rows, in_features, out_features).bytes;
 }
 
 int euhedral_cuda_linear_nvfp4_native_bf16(const void* input, const void* weights, void* output, void* scratch, uint32_t rows,
@@ -452,7 +455,8 @@ int euhedral_cuda_linear_nvfp4_native_bf16(const void* input, const void* weight
     if (((uintptr_t)input & 15u) != 0 || ((uintptr_t)weights & 15u) != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     if (layout == 1 || in_features % 256u != 0 || out_features % 128u != 0 || ((uintptr_t)scratch & 127u) != 0)
         return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
-    if (scratch == nullptr || scratch_byte_size < nvfp4n::ActivationLayout(rows, in_features).bytes) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    if (scratch == nullptr || scratch_byte_size < nvfp4n::ActivationLayout(rows, in_features, out_features).bytes)
+        return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     if (((uint64_t)rows + 127u) / 128u * (out_features / 128u) > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
     return finish(nvfp4n::run(input, weights, output, scratch, rows, in_features, out_features, state->sms, t_stream, t_pdl != 0,
             state->error_word));

@@ -124,6 +124,18 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// One LOP3: the bitwise function of (a, b, c) whose truth table is LUT (bit i of LUT = f for a, b, c = bits 2, 1, 0 of i).
+// Spelled out because the optimiser does not always merge a mask and a combine into one instruction.
+template <int LUT>
+__device__ __forceinline__ uint32_t lop3(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(d) : "r"(a), "r"(b), "r"(c), "n"(LUT));
+    return d;
+}
+constexpr int kLutAndXor = 0x6A;     // (a & b) ^ c
+constexpr int kLutAndOr = 0xEA;      // (a & b) | c
+constexpr int kLutSelect = 0xE4;     // (a & c) | (b & ~c)
+
 __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));

@@ -52,7 +52,7 @@ struct Geometry {
 // loads fall in distinct banks.
 struct Tile {
     uint32_t stride_codes, stride_scales, stride_x;
-    uint32_t off_scales, off_x, off_partial, off_gather, off_bars, bytes;
+    uint32_t off_scales, off_x, off_zero, off_partial, off_gather, off_bars, bytes;
     __host__ __device__ Tile(uint32_t rt, uint32_t chunks_max, uint32_t rows, uint32_t split) {
         const uint32_t rb = 16u * rt;
         stride_codes = chunks_max * 64u;
@@ -61,7 +61,8 @@ struct Tile {
         stride_x = chunks_max * 256u + 64u;
         off_scales = rb * stride_codes;
         off_x = (off_scales + rb * stride_scales + 127u) & ~127u;
-        off_partial = off_x + rows * stride_x;
+        off_zero = off_x + rows * stride_x;   // 256 zero bytes: the activations of lanes beyond the last row
+        off_partial = off_zero + 256u;
         off_gather = off_partial + 2u * rt * 16u * 8u * 4u;
         off_bars = off_gather + (split > 1u ? split * rb * 8u * 4u : 0u);
         bytes = off_bars + 8u * rt;
@@ -136,6 +137,7 @@ __global__ void __launch_bounds__(64 * RT) gemv_kernel(const uint16_t* __restric
     // The activations may come from the kernel before this one.
     eb::pdl_launch_dependents();
     eb::pdl_wait();
+    if (tid < 64u) reinterpret_cast<uint32_t*>(smem + tile.off_zero)[tid] = 0u;
     for (uint32_t u = tid; u < rows * nc * 16u; u += kThreads) {
         const uint32_t t = u / (nc * 16u), j = u - t * (nc * 16u);
         const uint32_t c = j >> 4, qq = (j >> 2) & 3u, i = j & 3u;
@@ -154,25 +156,26 @@ __global__ void __launch_bounds__(64 * RT) gemv_kernel(const uint16_t* __restric
     const uint32_t rt = warp >> 1, half = warp & 1u;
     const uint32_t first = nc * half / 2u, last = nc * (half + 1u) / 2u;
     if (!eb::mbar_wait(&bars[rt], 0) && lane == 0) atomicOr(error, 1u);
-    const uint8_t* code_g = codes + (rt * 16u + g) * tile.stride_codes + q * 16u;
+    const uint8_t* code_g = codes + (rt * 16u + g) * tile.stride_codes + q * 16u + first * 64u;
     const uint8_t* code_h = code_g + 8u * tile.stride_codes;
-    const uint8_t* scale_g = scales + (rt * 16u + g) * tile.stride_scales + q * 2u;
+    const uint8_t* scale_g = scales + (rt * 16u + g) * tile.stride_scales + q * 2u + first * 8u;
     const uint8_t* scale_h = scale_g + 8u * tile.stride_scales;
-    const uint8_t* x_lane = xs + g * tile.stride_x + q * 16u;
+    // Lanes beyond the last activation row read the zero block and never advance.
     const bool live = g < rows;
+    const uint8_t* x_lane = live ? xs + g * tile.stride_x + q * 16u + first * 256u : smem + tile.off_zero + q * 16u;
+    const uint32_t x_step = live ? 256u : 0u;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     for (uint32_t c = first; c < last; ++c) {
-        const uint4 cg = *reinterpret_cast<const uint4*>(code_g + c * 64u);
-        const uint4 ch = *reinterpret_cast<const uint4*>(code_h + c * 64u);
-        const uint32_t sg = scale_pair(*reinterpret_cast<const uint16_t*>(scale_g + c * 8u));
-        const uint32_t sh = scale_pair(*reinterpret_cast<const uint16_t*>(scale_h + c * 8u));
+        const uint4 cg = *reinterpret_cast<const uint4*>(code_g);
+        const uint4 ch = *reinterpret_cast<const uint4*>(code_h);
+        const uint32_t sg = scale_pair(*reinterpret_cast<const uint16_t*>(scale_g));
+        const uint32_t sh = scale_pair(*reinterpret_cast<const uint16_t*>(scale_h));
         const uint32_t sg_block[2] = {__byte_perm(sg, sg, 0x1010), __byte_perm(sg, sg, 0x3232)};
         const uint32_t sh_block[2] = {__byte_perm(sh, sh, 0x1010), __byte_perm(sh, sh, 0x3232)};
         const uint32_t wg[4] = {cg.x, cg.y, cg.z, cg.w}, wh[4] = {ch.x, ch.y, ch.z, ch.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-            if (live) xv = *reinterpret_cast<const uint4*>(x_lane + c * 256u + i * 64u);
+            const uint4 xv = *reinterpret_cast<const uint4*>(x_lane + i * 64u);
             const uint32_t fg = sg_block[i >> 1], fh = sh_block[i >> 1];
             const uint32_t g0 = eb::bf16x2_mul(raw_pair<0>(wg[i]), fg), h0 = eb::bf16x2_mul(raw_pair<0>(wh[i]), fh);
             const uint32_t g1 = eb::bf16x2_mul(raw_pair<1>(wg[i]), fg), h1 = eb::bf16x2_mul(raw_pair<1>(wh[i]), fh);
@@ -181,6 +184,11 @@ __global__ void __launch_bounds__(64 * RT) gemv_kernel(const uint16_t* __restric
             const uint32_t g3 = eb::bf16x2_mul(raw_pair<3>(wg[i]), fg), h3 = eb::bf16x2_mul(raw_pair<3>(wh[i]), fh);
             eb::mma_bf16_16816(acc, g2, h2, g3, h3, xv.z, xv.w);
         }
+        code_g += 64u;
+        code_h += 64u;
+        scale_g += 8u;
+        scale_h += 8u;
+        x_lane += x_step;
     }
     // partial[warp][row in tile][activation row]
     float* mine = partial + warp * 128u;

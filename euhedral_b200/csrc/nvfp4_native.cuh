@@ -1,20 +1,445 @@
-// Placeholder replaced below.
+// NVFP4 prefill GEMM on sm_100a: both operands NVFP4, tcgen05 block-scaled MMA (kind::mxf4nvf4, one UE4M3 scale per 16
+// values) with the accumulator in tensor memory.
+//
+// Replaces the reference's native route behind euhedral_cuda_linear_nvfp4_native_bf16
+// (native/src/host/nvfp4_linear.c:299-361): its activation quantizer native/src/nvfp4_native/native.cuh:105-168 and its
+// 128x128 warp-MMA tile native/src/nvfp4_native/native.cuh:265-432. Same arithmetic contract: each BF16 activation row
+// becomes two NVFP4 terms (the value and the quantized residual) under one FP32 scale per row; per output the K steps
+// run in increasing order with one MMA per term into the same FP32 accumulator; the result is
+// bf16(acc * row scale * tensor scale).
+//
+// Three launches per call, all on the selected stream, no allocation (everything lives in the caller's scratch):
+//   1. quantize_rows: BF16 rows -> code planes [term][row][K/2], block scales already in the layout tcgen05 wants
+//      (512-byte atoms of 128 rows x 4 scales, byte (r % 32) * 16 + (r / 32) * 4 + s), one FP32 scale per row.
+//   2. repack_weight_scales: the tensor's row-major E4M3 scale plane -> the same atom layout (the scales are 1/9 of
+//      the weight bytes; the codes are consumed in place through a tensor map).
+//   3. gemm: persistent CTAs, one per SM, 128 x 256 output tiles, K in steps of 256 through a 3-stage ring.
+//      warp 0 (one lane) issues the TMA loads (codes as 128-byte-swizzled tiles, scale atoms as bulk copies),
+//      warp 1 (one lane) copies the scale atoms to tensor memory (tcgen05.cp) and issues the MMAs
+//      (M 128, N 256, K 64; two terms x four K blocks per stage) and commits to the ring's and the accumulator's
+//      mbarriers, warps 2..5 read the accumulator back (tcgen05.ld), scale, round and store BF16.
+// Tiles are walked in panels of eight tile columns with the row index fastest, so that CTAs running together share
+// weight tiles and re-read activation tiles from L2. No multicast, no cluster.
 #pragma once
+
+#include <cuda.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+
 #include "common.cuh"
+
 namespace nvfp4n {
+
+constexpr uint32_t kTerms = 2;
+constexpr uint32_t kTileM = 128, kTileN = 256, kStepK = 256, kBlockK = 64;
+constexpr uint32_t kStages = 3;
+constexpr uint32_t kATile = kTileM * 128u;                 // one term's codes of a stage: 128 rows x 128 bytes
+constexpr uint32_t kBTile = kTileN * 128u;
+constexpr uint32_t kAtom = 512u;                           // 128 rows x 4 scales
+constexpr uint32_t kSfaStage = (kStepK / kBlockK) * kTerms * kAtom;
+constexpr uint32_t kSfbStage = (kStepK / kBlockK) * (kTileN / 128u) * kAtom;
+constexpr uint32_t kStageBytes = kTerms * kATile + kBTile + kSfaStage + kSfbStage;
+constexpr uint32_t kBarrierBytes = 128u;
+constexpr uint32_t kSharedBytes = kStages * kStageBytes + kBarrierBytes + 1024u;   // + slack to align to 1024
+constexpr uint32_t kThreads = 192u;
+constexpr uint32_t kTmemColumns = 512u;
+constexpr uint32_t kTmemSfa = 256u, kTmemSfb = 288u;       // column offsets behind the 256 accumulator columns
+constexpr uint32_t kPanel = 8u;                            // tile columns per panel of the tile walk
+
+__host__ __device__ inline uint64_t align256(uint64_t v) { return (v + 255ull) & ~255ull; }
+
+// Caller scratch of one native linear.
 struct ActivationLayout {
-    uint64_t scale_offset, global_offset, bytes;
-    uint32_t pad;
-    __host__ __device__ ActivationLayout(uint32_t rows, uint32_t k) {
+    uint64_t sfa_offset, global_offset, sfb_offset, bytes;
+    uint32_t row_tiles, k_blocks;
+    __host__ __device__ ActivationLayout(uint32_t rows, uint32_t k, uint32_t out_features = 0) {
         const uint64_t kp = ((uint64_t)k + 127u) / 128u * 128u;
-        pad = (rows + 127u) / 128u * 128u;
-        scale_offset = ((uint64_t)rows * 2u * (kp / 2u) + 255u) & ~255ull;
-        global_offset = (scale_offset + (kp / 128u) * 2u * pad * 8ull + 255u) & ~255ull;
-        bytes = global_offset + 4ull * rows;
+        row_tiles = (rows + kTileM - 1u) / kTileM;
+        k_blocks = (uint32_t)(kp / kBlockK);
+        sfa_offset = align256((uint64_t)kTerms * rows * (kp / 2u));
+        global_offset = align256(sfa_offset + (uint64_t)row_tiles * k_blocks * kTerms * kAtom);
+        sfb_offset = align256(global_offset + 4ull * rows);
+        const uint64_t n128 = ((uint64_t)out_features + 255u) / 256u * 2u;
+        bytes = sfb_offset + n128 * k_blocks * kAtom;
     }
 };
-inline cudaError_t initialize() { return cudaSuccess; }
-inline cudaError_t run(const void*, const void*, void*, void*, uint32_t, uint32_t, uint32_t, int, cudaStream_t, bool, uint32_t*) {
-    return cudaErrorNotSupported;
+
+__host__ __device__ inline uint32_t atom_byte(uint32_t row_in_tile, uint32_t scale) {
+    return (row_in_tile & 31u) * 16u + (row_in_tile >> 5) * 4u + scale;
 }
+
+// ---- 1. activation quantizer -----------------------------------------------------------------------------------------
+// One CTA per row. global = amax / (6 * 448) (1 for a zero row); per block of 16: scale = e4m3_satfinite(amax / 6 /
+// global); codes = e2m1_rn(v / (scale * global)), saturating; the next term quantizes v - decoded. All in FP32 with the
+// hardware conversions, in the order of native/src/nvfp4_native/native.cuh:105-127.
+__global__ void __launch_bounds__(128) quantize_rows(const __nv_bfloat16* __restrict__ input, uint8_t* __restrict__ scratch,
+        uint32_t rows, uint32_t k) {
+    const uint32_t row = blockIdx.x;
+    const ActivationLayout layout(rows, k);
+    const uint32_t blocks = k / 16u;
+    const __nv_bfloat16* x = input + (uint64_t)row * k;
+    eb::pdl_launch_dependents();
+    eb::pdl_wait();
+    float amax = 0.0f;
+    for (uint32_t b = threadIdx.x; b < blocks; b += 128u) {
+        const uint4 lo = *reinterpret_cast<const uint4*>(x + 16u * b), hi = *reinterpret_cast<const uint4*>(x + 16u * b + 8u);
+        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            amax = fmaxf(amax, fmaxf(fabsf(eb::bf16_bits_to_float(words[i] & 0xFFFFu)), fabsf(__uint_as_float(words[i] & 0xFFFF0000u))));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    __shared__ float warp_max[4];
+    if ((threadIdx.x & 31u) == 0) warp_max[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = fmaxf(fmaxf(warp_max[0], warp_max[1]), fmaxf(warp_max[2], warp_max[3]));
+    const float global = amax > 0.0f ? __fdiv_rn(amax, 6.0f * 448.0f) : 1.0f;
+    const float inverse_global = __fdiv_rn(1.0f, global);
+    uint8_t* sfa = scratch + layout.sfa_offset;
+    const uint32_t row_tile = row / kTileM, row_in_tile = row % kTileM;
+    for (uint32_t b = threadIdx.x; b < blocks; b += 128u) {
+        float v[16];
+        const uint4 lo = *reinterpret_cast<const uint4*>(x + 16u * b), hi = *reinterpret_cast<const uint4*>(x + 16u * b + 8u);
+        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[2 * i] = eb::bf16_bits_to_float(words[i] & 0xFFFFu);
+            v[2 * i + 1] = __uint_as_float(words[i] & 0xFFFF0000u);
+        }
+#pragma unroll
+        for (uint32_t t = 0; t < kTerms; ++t) {
+            float block_max = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) block_max = fmaxf(block_max, fabsf(v[i]));
+            const __nv_fp8_storage_t scale = __nv_cvt_float_to_fp8(__fmul_rn(__fmul_rn(block_max, 1.0f / 6.0f), inverse_global), __NV_SATFINITE, __NV_E4M3);
+            const float decoded = __half2float(__half(__nv_cvt_fp8_to_halfraw(scale, __NV_E4M3)));
+            const float inverse = decoded > 0.0f ? __fdiv_rn(inverse_global, decoded) : 0.0f;
+            const float step = __fmul_rn(decoded, global);
+            uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const __nv_fp4x2_storage_t pair = __nv_cvt_float2_to_fp4x2(
+                        make_float2(__fmul_rn(v[2 * i], inverse), __fmul_rn(v[2 * i + 1], inverse)), __NV_E2M1, cudaRoundNearest);
+                packed[i >> 2] |= (uint32_t)pair << (8 * (i & 3));
+                const __half2_raw back = __nv_cvt_fp4x2_to_halfraw2(pair, __NV_E2M1);
+                const float2 q = __half22float2(*reinterpret_cast<const __half2*>(&back));
+                v[2 * i] = __fsub_rn(v[2 * i], __fmul_rn(q.x, step));
+                v[2 * i + 1] = __fsub_rn(v[2 * i + 1], __fmul_rn(q.y, step));
+            }
+            *reinterpret_cast<uint2*>(scratch + ((uint64_t)t * rows + row) * (k / 2u) + 8u * b) = make_uint2(packed[0], packed[1]);
+            sfa[((uint64_t)(row_tile * layout.k_blocks + (b >> 2)) * kTerms + t) * kAtom + atom_byte(row_in_tile, b & 3u)] = scale;
+        }
+    }
+    if (threadIdx.x == 0) reinterpret_cast<float*>(scratch + layout.global_offset)[row] = global;
+}
+
+// ---- 2. weight scale repack ---------------------------------------------------------------------------------------------
+// scales[n][K/16] (row-major E4M3 bytes) -> atoms [n / 128][K / 64][512]. One thread per (row, K block): 4 bytes.
+__global__ void __launch_bounds__(256) repack_weight_scales(const uint8_t* __restrict__ scales, uint8_t* __restrict__ atoms,
+        uint32_t n, uint32_t k_blocks, uint32_t n_padded) {
+    const uint64_t index = (uint64_t)blockIdx.x * 256u + threadIdx.x;
+    eb::pdl_launch_dependents();
+    eb::pdl_wait();   // the GEMM of the call before this one may still be reading these atoms
+    const uint32_t row = (uint32_t)(index / k_blocks), j = (uint32_t)(index % k_blocks);
+    if (row >= n_padded) return;
+    const uint32_t word = row < n ? *reinterpret_cast<const uint32_t*>(scales + (uint64_t)row * k_blocks * 4u + 4u * j) : 0u;
+    *reinterpret_cast<uint32_t*>(atoms + ((uint64_t)(row >> 7) * k_blocks + j) * kAtom + atom_byte(row & 127u, 0)) = word;
+}
+
+// ---- 3. the GEMM ----------------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                         eb::smem_u32(dst)),
+            "l"(map), "r"(c0), "r"(c1), "r"(eb::smem_u32(bar))
+            : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+                         eb::smem_u32(dst)),
+            "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(eb::smem_u32(bar))
+            : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows under the 128-byte swizzle: 8-row groups are
+// 1024 bytes apart, descriptor version 1 (sm_100), layout type 2.
+__device__ __forceinline__ uint64_t tile_descriptor(const void* smem_tile) {
+    uint64_t d = 0;
+    d |= (uint64_t)((eb::smem_u32(smem_tile) & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(1024u >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Descriptor of a 512-byte scale atom for tcgen05.cp: 32 rows of 16 bytes, no swizzle, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t atom_descriptor(const void* smem_atom) {
+    uint64_t d = 0;
+    d |= (uint64_t)((eb::smem_u32(smem_atom) & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(128u >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+// kind::mxf4nvf4 instruction descriptor: E2M1 x E2M1, UE4M3 scales, both operands K-major, M 128, N 256.
+constexpr uint32_t kInstruction = (1u << 7) | (1u << 10) | ((kTileN >> 3) << 17) | (0u << 23) | ((kTileM >> 4) << 24);
+
+__device__ __forceinline__ void tmem_copy_atom(uint32_t tmem_address, uint64_t descriptor) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_address), "l"(descriptor) : "memory");
+}
+__device__ __forceinline__ void mma_block_scaled(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+        uint32_t accumulate) {
+    asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%4], [%5], p;\n}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(kInstruction), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+            : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(eb::smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+struct TileWalk {
+    uint32_t tiles_m, tiles_n, total;
+    __device__ TileWalk(uint32_t rows, uint32_t n) : tiles_m((rows + kTileM - 1u) / kTileM), tiles_n((n + kTileN - 1u) / kTileN) {
+        total = tiles_m * tiles_n;
+    }
+    // Panels of kPanel tile columns; inside a panel the row index runs fastest across the panel's columns.
+    __device__ void at(uint32_t tile, uint32_t* tm, uint32_t* tn) const {
+        const uint32_t per_panel = tiles_m * kPanel;
+        const uint32_t panel = tile / per_panel, rest = tile - panel * per_panel;
+        const uint32_t width = min(kPanel, tiles_n - panel * kPanel);
+        *tm = rest / width;
+        *tn = panel * kPanel + rest % width;
+    }
+};
+
+__global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+        const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, const float* __restrict__ row_globals,
+        const float* __restrict__ tensor_global, uint16_t* __restrict__ out, uint32_t rows, uint32_t n, uint32_t k,
+        uint32_t* __restrict__ error) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+    uint64_t* empty = full + kStages;
+    uint64_t* acc_full = empty + kStages;
+    uint64_t* acc_empty = acc_full + 1;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const TileWalk walk(rows, n);
+    const uint32_t k_steps = k / kStepK, k_blocks = k / kBlockK;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            eb::mbar_init(&full[s], 1);
+            eb::mbar_init(&empty[s], 1);
+        }
+        eb::mbar_init(acc_full, 1);
+        eb::mbar_init(acc_empty, 4);
+        eb::mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(eb::smem_u32(tmem_holder)), "r"(kTmemColumns) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem = *tmem_holder;
+    eb::pdl_launch_dependents();
+    eb::pdl_wait();   // the scratch comes from the two launches before this one
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t step = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < walk.total && ok; tile += gridDim.x) {
+                uint32_t tm, tn;
+                walk.at(tile, &tm, &tn);
+                for (uint32_t ks = 0; ks < k_steps; ++ks, ++step) {
+                    const uint32_t s = step % kStages, round = step / kStages;
+                    if (round > 0 && !eb::mbar_wait(&empty[s], (round - 1u) & 1u)) {
+                        atomicOr(error, 8u);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* stage = smem + s * kStageBytes;
+                    eb::mbar_arrive_expect_tx(&full[s], kStageBytes);
+                    tma_load_3d(stage, &map_a, (int)(ks * 128u), (int)(tm * kTileM), 0, &full[s]);
+                    tma_load_3d(stage + kATile, &map_a, (int)(ks * 128u), (int)(tm * kTileM), 1, &full[s]);
+                    tma_load_2d(stage + kTerms * kATile, &map_b, (int)(ks * 128u), (int)(tn * kTileN), &full[s]);
+                    uint8_t* sf = stage + kTerms * kATile + kBTile;
+                    eb::bulk_g2s(sf, sfa + ((uint64_t)tm * k_blocks + ks * 4u) * kTerms * kAtom, kSfaStage, &full[s]);
+                    eb::bulk_g2s(sf + kSfaStage, sfb + ((uint64_t)(2u * tn) * k_blocks + ks * 4u) * kAtom, 4u * kAtom, &full[s]);
+                    eb::bulk_g2s(sf + kSfaStage + 4u * kAtom, sfb + ((uint64_t)(2u * tn + 1u) * k_blocks + ks * 4u) * kAtom, 4u * kAtom, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t step = 0, local = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < walk.total && ok; tile += gridDim.x, ++local) {
+                if (local > 0 && !eb::mbar_wait(acc_empty, (local - 1u) & 1u)) {
+                    atomicOr(error, 8u);
+                    break;
+                }
+                tcgen05_fence_after();
+                for (uint32_t ks = 0; ks < k_steps; ++ks, ++step) {
+                    const uint32_t s = step % kStages, round = step / kStages;
+                    if (!eb::mbar_wait(&full[s], round & 1u)) {
+                        atomicOr(error, 8u);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint8_t* stage = smem + s * kStageBytes;
+                    const uint8_t* sf = stage + kTerms * kATile + kBTile;
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j) {
+                        tmem_copy_atom(tmem + kTmemSfa + (j * 2u) * 4u, atom_descriptor(sf + (j * 2u) * kAtom));
+                        tmem_copy_atom(tmem + kTmemSfa + (j * 2u + 1u) * 4u, atom_descriptor(sf + (j * 2u + 1u) * kAtom));
+                        tmem_copy_atom(tmem + kTmemSfb + j * 8u, atom_descriptor(sf + kSfaStage + j * kAtom));
+                        tmem_copy_atom(tmem + kTmemSfb + j * 8u + 4u, atom_descriptor(sf + kSfaStage + (4u + j) * kAtom));
+                    }
+                    const uint64_t a0 = tile_descriptor(stage), a1 = tile_descriptor(stage + kATile), b = tile_descriptor(stage + kTerms * kATile);
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j) {
+                        // A K block of 64 values is 32 bytes further along the swizzled row: + 2 in descriptor units.
+                        mma_block_scaled(tmem, a0 + 2u * j, b + 2u * j, tmem + kTmemSfa + (j * 2u) * 4u, tmem + kTmemSfb + j * 8u, (ks | j) != 0u);
+                        mma_block_scaled(tmem, a1 + 2u * j, b + 2u * j, tmem + kTmemSfa + (j * 2u + 1u) * 4u, tmem + kTmemSfb + j * 8u, 1u);
+                    }
+                    mma_commit(&empty[s]);
+                }
+                if (ok) mma_commit(acc_full);
+            }
+        }
+    } else {
+        // Epilogue: warp w reads the 32 accumulator rows of lane quarter w % 4.
+        const uint32_t quarter = warp & 3u;
+        const float scale_w = *tensor_global;
+        uint32_t local = 0;
+        for (uint32_t tile = blockIdx.x; tile < walk.total; tile += gridDim.x, ++local) {
+            uint32_t tm, tn;
+            walk.at(tile, &tm, &tn);
+            if (!eb::mbar_wait(acc_full, local & 1u)) {
+                if (lane == 0) atomicOr(error, 8u);
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t row = tm * kTileM + quarter * 32u + lane;
+            const float scale = row < rows ? __fmul_rn(row_globals[row], scale_w) : 0.0f;
+#pragma unroll 1
+            for (uint32_t cb = 0; cb < kTileN / 32u; ++cb) {
+                uint32_t r[32];
+                asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+                        "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+                          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                        : "r"(tmem + ((quarter * 32u) << 16) + cb * 32u));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const uint32_t col = tn * kTileN + cb * 32u;
+                if (row < rows && col < n) {
+                    uint16_t* dst = out + (uint64_t)row * n + col;
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float lo = __fmul_rn(__uint_as_float(r[8 * v + 2 * i]), scale), hi = __fmul_rn(__uint_as_float(r[8 * v + 2 * i + 1]), scale);
+                            packed[i] = (uint32_t)eb::float_to_bf16_bits(lo) | (uint32_t)eb::float_to_bf16_bits(hi) << 16;
+                        }
+                        if (col + 8u * v < n) *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) eb::mbar_arrive(acc_empty);
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+        const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiled encoder() {
+    static EncodeTiled cached = [] {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &query) != cudaSuccess || query != cudaDriverEntryPointSuccess)
+            entry = nullptr;
+        return reinterpret_cast<EncodeTiled>(entry);
+    }();
+    return cached;
+}
+
+inline cudaError_t initialize() {
+    return cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSharedBytes);
+}
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_on(cudaStream_t stream, bool pdl, void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = pdl ? 1u : 0u;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+// Quantize, repack, multiply. Shapes are pre-checked by the caller: k % 256 == 0, out_features % 128 == 0, scratch
+// aligned to 128 bytes and at least ActivationLayout(rows, k, out_features).bytes long.
+inline cudaError_t run(const void* input, const void* weights, void* output, void* scratch, uint32_t rows, uint32_t k, uint32_t out_features,
+        int sms, cudaStream_t stream, bool pdl, uint32_t* error) {
+    const EncodeTiled encode = encoder();
+    if (encode == nullptr) return cudaErrorNotSupported;
+    const ActivationLayout layout(rows, k, out_features);
+    uint8_t* base = static_cast<uint8_t*>(scratch);
+    const uint8_t* w = static_cast<const uint8_t*>(weights);
+    const uint64_t row_bytes = k / 2u;
+    const uint64_t scale_offset = align256((uint64_t)out_features * row_bytes);
+    const uint64_t global_offset = align256(scale_offset + (uint64_t)out_features * (k / 16u));
+    CUtensorMap map_a, map_b;
+    const cuuint32_t ones[3] = {1u, 1u, 1u};
+    const cuuint64_t a_dims[3] = {row_bytes, rows, kTerms}, a_strides[2] = {row_bytes, row_bytes * rows};
+    const cuuint32_t a_box[3] = {128u, kTileM, 1u};
+    const cuuint64_t b_dims[2] = {row_bytes, out_features}, b_strides[1] = {row_bytes};
+    const cuuint32_t b_box[2] = {128u, kTileN};
+    CUresult r = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, a_dims, a_strides, a_box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS)
+        r = encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w), b_dims, b_strides, b_box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    cudaError_t e = launch_on(stream, pdl, quantize_rows, dim3(rows), dim3(128), 0, static_cast<const __nv_bfloat16*>(input), base, rows, k);
+    if (e != cudaSuccess) return e;
+    const uint32_t n_padded = (out_features + 255u) / 256u * 256u;
+    const uint64_t items = (uint64_t)n_padded * layout.k_blocks;
+    e = launch_on(stream, pdl, repack_weight_scales, dim3((unsigned)((items + 255u) / 256u)), dim3(256), 0, w + scale_offset, base + layout.sfb_offset,
+            out_features, layout.k_blocks, n_padded);
+    if (e != cudaSuccess) return e;
+    const uint32_t tiles = ((rows + kTileM - 1u) / kTileM) * ((out_features + kTileN - 1u) / kTileN);
+    const uint32_t grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
+    return launch_on(stream, pdl, gemm_kernel, dim3(grid), dim3(kThreads), kSharedBytes, map_a, map_b, base + layout.sfa_offset,
+            base + layout.sfb_offset, reinterpret_cast<const float*>(base + layout.global_offset), reinterpret_cast<const float*>(w + global_offset),
+            static_cast<uint16_t*>(output), rows, out_features, k, error);
+}
+
 }  // namespace nvfp4n

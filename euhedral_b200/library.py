@@ -6,6 +6,7 @@ no fallback implementation."""
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 PACKAGE = Path(__file__).resolve().parent
@@ -72,7 +73,8 @@ def load(path: Path | None = None) -> C.CDLL:
     global _LIB
     if _LIB is not None and path is None:
         return _LIB
-    target = Path(path) if path else LIBRARY_PATH
+    # EUHEDRAL_CUDA_LIBRARY names another build of the same library (e.g. one compiled with bounds checks).
+    target = Path(path) if path else Path(os.environ.get("EUHEDRAL_CUDA_LIBRARY", LIBRARY_PATH))
     if not target.exists():
         raise LibraryMissing(f"{target} is missing: build it with `python -m euhedral_b200.build`; there is no CPU fallback")
     lib = C.CDLL(str(target))

@@ -1,0 +1,96 @@
+"""NVFP4 prefill route (activation quantizer + tcgen05 block-scaled GEMM) through the C ABI, modelled on the
+reference's native/tests/test_nvfp4_native.py: the output is checked against float64 over the operands the kernel
+really multiplied (the quantized activations read back from the scratch), the quantizer against the CPU restatement."""
+
+import numpy as np
+import pytest
+
+from euhedral_b200 import layouts, library
+from oracle import oracle_c as OC
+from oracle import oracle_np as O
+from tests.gpu_util import Device, random_x
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    device = Device()
+    yield device
+    assert device.gpu.take_device_error() == 0
+    device.release()
+
+
+def run(dev, x_bits, blob, n, k):
+    rows = x_bits.shape[0]
+    lib = dev.gpu.lib
+    need = lib.euhedral_cuda_nvfp4_native_scratch_bytes(rows, k, n)
+    d_x, d_w, d_y, d_s = dev.put(x_bits), dev.put(blob), dev.empty(rows * n * 2), dev.empty(need + 256, fill=0)
+    scratch = (d_s.data_ptr() + 255) & ~255
+    with dev.submit(pdl=True):
+        status = lib.euhedral_cuda_linear_nvfp4_native_bf16(d_x.data_ptr(), d_w.data_ptr(), d_y.data_ptr(), scratch, rows, k, n,
+                                                            blob.size, need)
+    assert status == 0, status
+    y = dev.get(d_y, np.uint16, (rows, n))
+    raw = dev.get(d_s, np.uint8, (need + 256,))[scratch - d_s.data_ptr():]
+    return y, raw
+
+
+def unpack_scratch(raw, rows, k):
+    """(codes [2, rows, k], scales [2, rows, k/16], globals [rows]) from the kernel's scratch layout."""
+    half = k // 2
+    planes = raw[:2 * rows * half].reshape(2, rows, half)
+    codes = np.empty((2, rows, k), dtype=np.uint8)
+    codes[:, :, 0::2] = planes & 15
+    codes[:, :, 1::2] = planes >> 4
+    sfa_offset = layouts.align_up(2 * rows * half, 256)
+    row_tiles, k_blocks = -(-rows // 128), k // 64
+    atoms = raw[sfa_offset:sfa_offset + row_tiles * k_blocks * 2 * 512].reshape(row_tiles, k_blocks, 2, 512)
+    scales = np.zeros((2, rows, k // 16), dtype=np.uint8)
+    for row in range(rows):
+        in_tile = row % 128
+        for t in range(2):
+            for s4 in range(4):
+                scales[t, row, s4::4] = atoms[row // 128, :, t, (in_tile % 32) * 16 + (in_tile // 32) * 4 + s4]
+    global_offset = layouts.align_up(sfa_offset + row_tiles * k_blocks * 2 * 512, 256)
+    g = raw[global_offset:global_offset + 4 * rows].view(np.float32)
+    return codes, scales, g
+
+
+@pytest.mark.parametrize("rows,k,n", [(16, 256, 128), (128, 512, 256), (200, 1024, 384), (300, 5120, 1024)])
+def test_native_matches_float64_over_quantized_operands(dev, rows, k, n):
+    rng = np.random.default_rng(rows + k + n)
+    weights = (rng.standard_normal((n, k)) * rng.uniform(0.01, 1.0, (n, 1))).astype(np.float32)
+    blob = OC.nvfp4_quantize(weights)
+    dense = OC.nvfp4_dense(blob, n, k).astype(np.float64)
+    x = random_x(rng, rows, k)
+    y, raw = run(dev, x, blob, n, k)
+    codes, scales, g = unpack_scratch(raw, rows, k)
+    # the quantizer against its CPU restatement (bit level) and against the activations (reconstruction error)
+    ref_codes, ref_scales, ref_g = O.quantize_activations(x, 2)
+    assert np.array_equal(g, ref_g)
+    assert np.array_equal(scales, ref_scales)
+    assert np.array_equal(codes & 7, ref_codes & 7) and np.array_equal(codes[(codes & 7) > 0], ref_codes[(codes & 7) > 0])
+    quantized = O.activations_dense(codes, scales, g)
+    xf = O.bf16_to_f32(x).astype(np.float64)
+    assert np.linalg.norm(quantized - xf) / np.linalg.norm(xf) < 0.012
+    expect = quantized @ dense.T
+    got = O.bf16_to_f32(y).astype(np.float64)
+    assert np.max(np.abs(got - expect)) <= 2.0 ** -7 * np.max(np.abs(expect))
+    # and against the BF16-activation result: the two-term approximation costs about 1% (reported, loosely bounded)
+    exact = xf @ dense.T
+    assert np.linalg.norm(got - exact) / np.linalg.norm(exact) < 0.03
+
+
+def test_native_route_declines(dev):
+    lib = dev.gpu.lib
+    rows, k, n = 16, 384, 128      # k % 256 != 0
+    blob = OC.nvfp4_quantize(np.ones((n, k), dtype=np.float32))
+    d = dev.empty(1 << 20)
+    assert lib.euhedral_cuda_linear_nvfp4_native_bf16(d.data_ptr(), d.data_ptr(), d.data_ptr(), d.data_ptr(), rows, k, n, blob.size, 1 << 20) == library.ROUTE_UNAVAILABLE
+    dev.gpu.select_exact_numerics(True)
+    try:
+        assert lib.euhedral_cuda_linear_nvfp4_native_bf16(d.data_ptr(), d.data_ptr(), d.data_ptr(), d.data_ptr(), 16, 256, 128, 1, 1) == library.ROUTE_UNAVAILABLE
+    finally:
+        dev.gpu.select_exact_numerics(False)
+    assert lib.euhedral_cuda_nvfp4_native_available() == 1
