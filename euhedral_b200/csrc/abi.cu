@@ -25,6 +25,11 @@ std::atomic<int> g_exact{0};
 
 __device__ uint32_t g_error_word;
 
+// Scratch of euhedral_b200_linear_trellis_bf16_static: lives in the library's own device image, so that entry point
+// needs no allocation by anybody. Every device that loads the library holds these bytes until the process exits.
+constexpr size_t kStaticScratchBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
 constexpr int kMaxDevices = 64;
 struct DeviceState {
     std::once_flag once;
@@ -32,6 +37,7 @@ struct DeviceState {
     int sms = 0;
     int major = 0;
     uint32_t* error_word = nullptr;
+    unsigned char* static_scratch = nullptr;   // device address of g_static_scratch on this device
 };
 DeviceState g_devices[kMaxDevices];
 
@@ -64,6 +70,8 @@ void initialize_device(int device, DeviceState* state) {
         state->major = prop.major;
         e = cudaGetSymbolAddress(reinterpret_cast<void**>(&state->error_word), g_error_word);
     }
+    // In host code the array's name is only a handle; the kernels need its device address on this device.
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&state->static_scratch), g_static_scratch);
     if (e == cudaSuccess) e = allow_big_smem(nvfp4::gemv_kernel<1>);
     if (e == cudaSuccess) e = allow_big_smem(nvfp4::gemv_kernel<2>);
     if (e == cudaSuccess) e = allow_big_smem(nvfp4::gemv_kernel<4>);
@@ -226,6 +234,25 @@ cudaError_t launch_trellis_mma(const uint64_t* a, uint32_t* error) {
     auto out = reinterpret_cast<uint16_t*>(a[5]);
     if (rows <= 8) return launch(trellis::mma_kernel<W, 1>, grid, block, shared, 1u, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
     return launch(trellis::mma_kernel<W, 4>, grid, block, shared, 1u, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
+}
+
+cudaError_t launch_trellis_prepass(const void* x, const void* suh, void* act, int rows, int k, int s, int layout) {
+    return launch(trellis::prepass_kernel, dim3((unsigned)((k + 511) / 512), (unsigned)rows, (unsigned)s), dim3(128), 0, 1u,
+            static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(suh), static_cast<uint16_t*>(act), rows, k, s, layout);
+}
+
+cudaError_t launch_trellis_epilogue(const void* partials, int splits, const void* svh, void* out, int rows, int n) {
+    return launch(trellis::epilogue_kernel, dim3((unsigned)((n + 511) / 512), (unsigned)rows), dim3(128), 0, 1u,
+            static_cast<const float*>(partials), splits, static_cast<const uint16_t*>(svh), static_cast<uint16_t*>(out), rows, n);
+}
+
+cudaError_t launch_trellis_mma_width(int w, const uint64_t* a, uint32_t* error) {
+    switch (w) {
+#define EB_CASE(W) case W: return launch_trellis_mma<W>(a, error);
+        EB_TRELLIS_WIDTHS(EB_CASE)
+#undef EB_CASE
+    }
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace
@@ -498,28 +525,21 @@ int euhedral_cuda_linear_launch(int32_t kernel, uint32_t grid_x, uint32_t grid_y
             const int rows = (int)a[3], k = (int)a[4], s = (int)a[5], layout = (int)a[6];
             if (rows <= 0 || k <= 0 || k % 128 != 0 || s <= 0 || rows > 65535 || s > 65535) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
             if (layout != 0 && layout != 1) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;   // 2 = block FP8: no kernel here
-            return finish(launch(trellis::prepass_kernel, dim3((unsigned)((k + 511) / 512), (unsigned)rows, (unsigned)s), dim3(128), 0, 1u,
-                    reinterpret_cast<const uint16_t*>(a[0]), reinterpret_cast<const uint16_t*>(a[1]), reinterpret_cast<uint16_t*>(a[2]),
-                    rows, k, s, layout));
+            return finish(launch_trellis_prepass(reinterpret_cast<const void*>(a[0]), reinterpret_cast<const void*>(a[1]),
+                    reinterpret_cast<void*>(a[2]), rows, k, s, layout));
         }
         case 1: {   // mma(act, words, ends, svh, partials, out, rows, k, n, w, splits, s)
             const int rows = (int)a[6], k = (int)a[7], n = (int)a[8], w = (int)a[9], splits = (int)a[10], s = (int)a[11];
             if (rows <= 0 || k <= 0 || k % 128 != 0 || n <= 0 || n % 128 != 0 || !trellis_width_valid(w) || splits <= 0
                     || splits > k / 16 || splits > 65535 || s <= 0 || (a[1] & 15u) != 0)
                 return EUHEDRAL_CUDA_INVALID_ARGUMENT;
-            cudaError_t e = cudaErrorInvalidValue;
-            switch (w) {
-#define EB_CASE(W) case W: e = launch_trellis_mma<W>(a, state->error_word); break;
-                EB_TRELLIS_WIDTHS(EB_CASE)
-#undef EB_CASE
-            }
-            return finish(e);
+            return finish(launch_trellis_mma_width(w, a, state->error_word));
         }
         case 4: {   // epilogue(partials, splits, svh, out, rows, n)
             const int splits = (int)a[1], rows = (int)a[4], n = (int)a[5];
             if (splits <= 0 || rows <= 0 || rows > 65535 || n <= 0 || n % 128 != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
-            return finish(launch(trellis::epilogue_kernel, dim3((unsigned)((n + 511) / 512), (unsigned)rows), dim3(128), 0, 1u,
-                    reinterpret_cast<const float*>(a[0]), splits, reinterpret_cast<const uint16_t*>(a[2]), reinterpret_cast<uint16_t*>(a[3]), rows, n));
+            return finish(launch_trellis_epilogue(reinterpret_cast<const void*>(a[0]), splits, reinterpret_cast<const void*>(a[2]),
+                    reinterpret_cast<void*>(a[3]), rows, n));
         }
         case 5: {   // decode_bf16(words, out, k, n, w)
             const int k = (int)a[2], n = (int)a[3], w = (int)a[4];
@@ -554,6 +574,38 @@ int euhedral_b200_take_device_error(uint32_t* word) {
     if (e == cudaSuccess) e = cudaMemcpy(word, state->error_word, 4, cudaMemcpyDeviceToHost);
     if (e == cudaSuccess) e = cudaMemset(state->error_word, 0, 4);
     return e == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)e;
+}
+
+uint64_t euhedral_b200_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+// A whole trellis linear (prepass, tensor-core GEMM, epilogue when the K range is split) whose scratch is the library's
+// own static device array instead of caller memory. Nothing is allocated or freed here, by CUDA or by any library.
+int euhedral_b200_linear_trellis_bf16_static(const void* input, const void* words, const void* suh, const void* svh,
+        const void* segment_ends, void* output, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t tile_words,
+        uint32_t segments, uint32_t splits) {
+    if (input == nullptr || words == nullptr || suh == nullptr || svh == nullptr || segment_ends == nullptr || output == nullptr
+            || rows == 0 || in_features == 0 || in_features % 128u != 0 || out_features == 0 || out_features % 128u != 0
+            || !trellis_width_valid((int)tile_words) || segments == 0 || splits == 0 || splits > in_features / 16u
+            || ((uintptr_t)words & 15u) != 0)
+        return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    // Activations (FP16, every segment) on a 256-byte boundary, then the FP32 partials of every split.
+    const uint64_t activations = ((uint64_t)segments * rows * in_features * 2u + 255u) & ~255ull;
+    const uint64_t partials = splits > 1u ? (uint64_t)splits * rows * out_features * 4u : 0u;
+    if (rows > 65535u || segments > 65535u || splits > 65535u || activations + partials > kStaticScratchBytes)
+        return EUHEDRAL_CUDA_SIZE_OVERFLOW;   // beyond the static scratch: use the table launches with caller scratch
+    DeviceState* state = nullptr;
+    const int status = bind(&state);   // first call on a device: resolves the scratch's device address
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    unsigned char* scratch = state->static_scratch;
+    cudaError_t e = launch_trellis_prepass(input, suh, scratch, (int)rows, (int)in_features, (int)segments, 0);
+    if (e != cudaSuccess) return (int)e;
+    const uint64_t a[12] = {(uint64_t)(uintptr_t)scratch, (uint64_t)(uintptr_t)words, (uint64_t)(uintptr_t)segment_ends,
+            (uint64_t)(uintptr_t)svh, (uint64_t)(uintptr_t)(scratch + activations), (uint64_t)(uintptr_t)output, rows, in_features,
+            out_features, tile_words, splits, segments};
+    e = launch_trellis_mma_width((int)tile_words, a, state->error_word);
+    if (e != cudaSuccess) return (int)e;
+    if (splits > 1u) e = launch_trellis_epilogue(scratch + activations, (int)splits, svh, output, (int)rows, (int)out_features);
+    return finish(e);
 }
 
 int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t* row_tiles,

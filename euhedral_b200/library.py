@@ -57,6 +57,8 @@ SIGNATURES = {
     "euhedral_cuda_linear_launch": (C.c_int, [_i32, _u32, _u32, _u32, _u32, _u32, _u32, _u32, C.POINTER(_u64),
                                               C.POINTER(C.c_uint8), _i32]),
     "euhedral_b200_take_device_error": (C.c_int, [C.POINTER(_u32)]),
+    "euhedral_b200_static_scratch_bytes": (_u64, []),
+    "euhedral_b200_linear_trellis_bf16_static": (C.c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _u32, _u32, _u32, _u32, _u32, _u32]),
     "euhedral_b200_decode_plan": (C.c_int, [C.c_int, _u32, _u32, _u32, C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32),
                                             C.POINTER(_u32)]),
 }

@@ -107,6 +107,24 @@ EUHEDRAL_CUDA_EXPORT int euhedral_b200_take_device_error(uint32_t* word);
 EUHEDRAL_CUDA_EXPORT int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, uint32_t out_features,
         uint32_t* row_tiles, uint32_t* k_slices, uint32_t* ctas, uint32_t* shared_bytes);
 
+/* No counterpart in the reference. A whole trellis linear for callers that cannot provide scratch because they cannot
+ * allocate device memory at the point of the call: a host that only holds the weight and activation addresses it was
+ * given, a plugin running inside somebody else's memory plan, or a step that runs after the process's allocator has
+ * been frozen. The scratch (rotated FP16 activations, then the FP32 partial sums of the K splits) lives in a static
+ * device array inside the library, euhedral_b200_static_scratch_bytes() bytes (8 MiB) on every device that loads the
+ * library, held until the process exits. The call allocates and frees nothing.
+ *   input BF16 [rows][in_features]; words the payload [in/16][out/16][tile_words]; suh FP16 [segments][in]; svh FP16 [out];
+ *   segment_ends int32 [segments]; output BF16 [rows][out]; splits = the K splits (1 = finish in the GEMM kernel).
+ * Needs align256(segments*rows*in*2) + (splits > 1 ? splits*rows*out*4 : 0) <= the static size, else SIZE_OVERFLOW
+ * (use euhedral_cuda_linear_launch with caller scratch). Same results, bit for bit, as the three table launches.
+ * The first call on a device looks the array's device address up; make that call before any stream capture.
+ * Every call uses the same array and leaves its last contents there: calls that overlap on the GPU (two streams, or
+ * two threads) race on it. Nothing in it needs clearing between calls - every byte read was written by the same call. */
+EUHEDRAL_CUDA_EXPORT uint64_t euhedral_b200_static_scratch_bytes(void);
+EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_trellis_bf16_static(const void* input, const void* words, const void* suh,
+        const void* svh, const void* segment_ends, void* output, uint32_t rows, uint32_t in_features, uint32_t out_features,
+        uint32_t tile_words, uint32_t segments, uint32_t splits);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,79 @@
+"""The C ABI library loads without a GPU, exports every symbol include/euhedral_cuda.h declares, and its pure
+host-side entry points (no device work) behave: table names, decode plans, scratch sizes, argument validation."""
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+from euhedral_b200 import layouts, library
+
+HEADER = Path(__file__).resolve().parents[1] / "include" / "euhedral_cuda.h"
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return re.findall(r"EUHEDRAL_CUDA_EXPORT\s+[\w\s\*]+?\b(euhedral_\w+)\s*\(", text)
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    lib = library.load()
+    names = declared_symbols()
+    assert len(names) >= 35
+    for name in names:
+        assert hasattr(lib, name), name
+    assert set(names) == set(library.SIGNATURES), set(names) ^ set(library.SIGNATURES)
+
+
+def test_kernel_table_order_is_the_reference_abi():
+    lib = library.load()
+    # native/src/host/linear_kernels.c:7-24; Java mirror core/.../artifact/format/LinearKernel.java:8-34
+    expect = ["euhedral_trellis_prepass", "euhedral_trellis_mma", "euhedral_trellis_mma_rows", "euhedral_trellis_mma_rows64",
+              "euhedral_trellis_epilogue", "euhedral_trellis_decode_bf16", "euhedral_trellis_epilogue_bf16", "euhedral_trellis_reference",
+              "euhedral_trellis_mma_rows_fp8", "euhedral_trellis_mma_rows64_fp8", "euhedral_nvfp4_embedding"]
+    assert lib.euhedral_cuda_linear_kernel_count() == len(expect)
+    assert [lib.euhedral_cuda_linear_kernel_name(i).decode() for i in range(len(expect))] == expect
+    assert lib.euhedral_cuda_linear_kernel_name(99) is None
+
+
+def test_argument_validation_needs_no_device():
+    lib = library.load()
+    assert lib.euhedral_cuda_linear_nvfp4_bf16(None, None, None, 1, 128, 16, 0) == library.INVALID_ARGUMENT
+    assert lib.euhedral_cuda_linear_nvfp4_bf16(16, 16, 16, 1, 128, 16, 12345) == library.FORMAT_MISMATCH
+    assert lib.euhedral_cuda_linear_q3_bf16(16, 16, 16, 1, 128, 16, 12345) == library.FORMAT_MISMATCH
+    assert lib.euhedral_cuda_linear_q3_bf16(16, 16, 16, 0, 128, 16, 12345) == library.INVALID_ARGUMENT
+    assert lib.euhedral_cuda_stream_select(0) == library.INVALID_ARGUMENT
+    assert lib.euhedral_cuda_set_include_directory(None) == library.INVALID_ARGUMENT
+    assert lib.euhedral_cuda_set_include_directory(b"/usr/include") == 0
+    words, sizes = (C.c_uint64 * 1)(), (C.c_uint8 * 1)()
+    assert lib.euhedral_cuda_linear_launch(99, 1, 1, 1, 1, 1, 1, 0, words, sizes, 0) == library.INVALID_ARGUMENT
+    assert lib.euhedral_cuda_linear_launch(1, 0, 1, 1, 1, 1, 1, 0, words, sizes, 0) == library.INVALID_ARGUMENT
+    assert lib.euhedral_cuda_select_exact_numerics(1) == 0 and lib.euhedral_cuda_select_exact_numerics(0) == 1
+    assert lib.euhedral_b200_static_scratch_bytes() == 8 << 20
+
+
+def test_decode_plans_depend_on_k_only_for_the_k_split():
+    plans = {}
+    for n in (128, 640, 1024, 5120, 17408):
+        for fmt in ("nvfp4", "q3"):
+            plan = library.decode_plan(fmt, 5, 5120, n)
+            plans.setdefault(fmt, set()).add(plan["k_slices"])
+            assert plan["ctas"] == n // (16 * plan["row_tiles"]) * plan["k_slices"]
+            assert plan["shared_bytes"] < 200 * 1024
+    assert all(len(v) == 1 for v in plans.values())      # a row's K order is the same whatever the shard's N
+    assert library.decode_plan("nvfp4", 1, 17408, 5120)["k_slices"] == 8
+    with pytest.raises(ValueError):
+        library.decode_plan("nvfp4", 1, 100, 16)
+    with pytest.raises(ValueError):
+        library.decode_plan("q3", 9, 1024, 16)
+
+
+def test_native_scratch_covers_every_region():
+    lib = library.load()
+    for rows, k, n in ((16, 256, 128), (4096, 5120, 17408), (300, 5120, 1024)):
+        need = lib.euhedral_cuda_nvfp4_native_scratch_bytes(rows, k, n)
+        codes = layouts.align_up(2 * rows * k // 2, 256)
+        atoms_a = -(-rows // 128) * (k // 64) * 2 * 512
+        atoms_b = -(-n // 256) * 2 * (k // 64) * 512
+        assert need == layouts.align_up(layouts.align_up(codes + atoms_a, 256) + 4 * rows, 256) + atoms_b
