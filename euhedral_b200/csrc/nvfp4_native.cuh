@@ -19,7 +19,7 @@
 //      (M 128, N 256, K 64; two terms x four K blocks per stage) and commits to the ring's and the accumulator's
 //      mbarriers, warps 2..5 read the accumulator back (tcgen05.ld), scale, round and store BF16.
 // Tiles are walked in panels of eight tile columns with the row index fastest, so that CTAs running together share
-// weight tiles and re-read activation tiles from L2. No multicast, no cluster.
+// weight tiles and re-read activation tiles from L2. Every CTA issues its own loads; there is no cluster.
 #pragma once
 
 #include <cuda.h>

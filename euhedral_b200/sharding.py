@@ -72,6 +72,9 @@ def gather_columns(local, world_size: int, group=None):
     import torch
     import torch.distributed as dist
     rows, width = local.shape
-    gathered = torch.empty((world_size, rows, width), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(gathered, local.contiguous(), group=group)
-    return gathered.permute(1, 0, 2).reshape(rows, world_size * width)
+    # Gathered as raw bytes: the slices are BF16 bit patterns, and every backend moves uint8.
+    flat = local.contiguous().view(torch.uint8).reshape(rows, -1)
+    gathered = torch.empty((world_size * rows, flat.shape[1]), dtype=torch.uint8, device=local.device)
+    dist.all_gather_into_tensor(gathered, flat, group=group)
+    joined = gathered.reshape(world_size, rows, -1).permute(1, 0, 2).reshape(rows, -1).contiguous()
+    return joined.view(local.dtype).reshape(rows, world_size * width)
