@@ -10,7 +10,7 @@ algorithmic bytes of the step (weight planes + activations + outputs, each byte 
 same measurement for the NVFP4 and trellis layouts and the NVFP4 prefill GEMM.
 
 With --gpus N (launched under torch.distributed.run) every weight matrix is split along N over the ranks, each rank
-runs its slices and the output slices are joined with an NCCL all-gather after every GEMV.
+runs its slices into one packed output buffer, and the slices of a step are joined with one NCCL all-gather.
 
 `--impl reference` times the CPU restatement of the reference's dequant + matmul (oracle/oracle.c) on the host cores.
 """
@@ -179,6 +179,13 @@ class Resident:
                 self.host_inputs[(rows, k)] = host
                 self.inputs[(rows, k)] = host.cuda()
         settings = TrellisSettings.for_device(sms)
+        # Every output slice of a step lives in one packed buffer, so that a multi-GPU step joins them with ONE all-gather.
+        unit = 128 if fmt == "trellis" else 16
+        total = sum(rows * sharding.shard_range(n, world, rank, unit)[1] for name, n, k in LAYER if only in (None, name) for rows in rows_list)
+        self.packed = torch.empty(total, dtype=torch.int16, device="cuda")
+        self.gathered = torch.empty(total * world, dtype=torch.int16, device="cuda") if world > 1 else self.packed
+        self.host_result = torch.empty(total * world, dtype=torch.int16).pin_memory()
+        cursor = 0
         for index, (name, n, k) in enumerate(LAYER):
             if only is not None and name != only:
                 continue
@@ -200,7 +207,8 @@ class Resident:
                 assert TrellisFormat.splits(k, local, splits * (local // 128)) == splits
             for rows in rows_list:
                 launches = []
-                out = torch.empty((rows, local), dtype=torch.int16, device="cuda")
+                out = self.packed[cursor:cursor + rows * local].view(rows, local)
+                cursor += rows * local
                 for copy in range(copies):
                     if fmt == "trellis":
                         tensors = [a.clone() for a in (payload, suh, svh, ends)]
@@ -220,28 +228,29 @@ class Resident:
                 self.calls.append((launches, out, local, n, k, rows))
                 self.bytes_per_step += algorithmic_bytes(fmt, local, k, rows, w)
                 self.h2d += 2 * rows * k
-                self.d2h += 2 * rows * local
+                self.d2h += 2 * rows * local * world
         self.launches_per_step = len(self.calls) * (3 if fmt == "trellis" else 1)
 
-    def step(self, iteration: int, world: int, gathered=None):
+    def step(self, iteration: int, world: int):
         from euhedral_b200 import sharding
         for launches, out, local, n, k, rows in self.calls:
             operator, launch = launches[iteration % self.copies]
             operator.linear(self.gpu, launch)
-            if world > 1:
-                sharding.gather_columns(out, world)
+        if world > 1:
+            sharding.gather_packed(self.packed, self.gathered)
 
-    def step_e2e(self, iteration: int, world: int, host_out):
-        """The same step fed from pinned host memory: every call uploads its activation rows and reads its output back."""
+    def step_e2e(self, iteration: int, world: int):
+        """The same step fed from pinned host memory: every call uploads its activation rows from pinned memory, and the
+        step's whole result (every rank's slices) is read back to pinned memory at the end."""
         from euhedral_b200 import sharding
-        for index, (launches, out, local, n, k, rows) in enumerate(self.calls):
+        for launches, out, local, n, k, rows in self.calls:
             operator, launch = launches[iteration % self.copies]
             host = self.host_inputs[(rows, k)]
             self.gpu.copy_upload_to_device(self.inputs[(rows, k)].data_ptr(), host.data_ptr(), host.numel() * 2)
             operator.linear(self.gpu, launch)
-            if world > 1:
-                sharding.gather_columns(out, world)
-            self.gpu.copy_device_to_readback(host_out[index].data_ptr(), out.data_ptr(), out.numel() * 2)
+        if world > 1:
+            sharding.gather_packed(self.packed, self.gathered)
+        self.gpu.copy_device_to_readback(self.host_result.data_ptr(), self.gathered.data_ptr(), self.gathered.numel() * 2)
 
 
 def timed(torch, dist, world, steps, warmup, body):
@@ -280,8 +289,7 @@ def measure_format(torch, dist, gpu, fmt, rows_list, copies, world, rank, sms, s
         result = {"gbs": total_bytes * steps / seconds / 1e9, "ms_per_step": seconds / steps * 1e3, "bytes_per_step": total_bytes,
                   "launches_per_step": resident.launches_per_step}
         if e2e:
-            host_out = [torch.empty(out.shape, dtype=torch.int16).pin_memory() for _, out, *_ in resident.calls]
-            seconds = timed(torch, dist, world, steps, warmup, lambda i: resident.step_e2e(i, world, host_out))
+            seconds = timed(torch, dist, world, steps, warmup, lambda i: resident.step_e2e(i, world))
             result["e2e_gbs"] = total_bytes * steps / seconds / 1e9
             result["h2d"], result["d2h"] = resident.h2d, resident.d2h
     assert gpu.take_device_error() == 0, "a kernel's bounded wait gave up"
@@ -372,7 +380,7 @@ def run_ours(args):
             "config": {"workload": "Q3 decode GEMV set, one Qwen-27B-shaped layer, M in {1,3}", "layer": [list(s) for s in LAYER],
                        "weights": "N(0, 0.02^2) seeded, rounded as the converter rounds Q3G64_F16S", "activations": "N(0,1) as BF16",
                        "l2": f"weights rotate over {copies} resident copies of the layer ({copies * head['bytes_per_step'] / 2 / 1e6:.0f} MB > 126 MB L2)",
-                       "parallelism": f"n-sharded x{world} + NCCL all-gather" if world > 1 else "single GPU",
+                       "parallelism": f"n-sharded x{world}, one NCCL all-gather of the step's packed output slices" if world > 1 else "single GPU",
                        "launch": "one C-ABI call per GEMV, one stream, programmatic dependent launch"},
             "roofline": {"bound": "hbm", "achieved": head["gbs"], "peak": peak * world, "unit": "GB/s", "frac": head["gbs"] / (peak * world),
                          "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "q3::gemv_kernel (every launch of the timed region)"},

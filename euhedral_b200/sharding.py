@@ -78,3 +78,13 @@ def gather_columns(local, world_size: int, group=None):
     dist.all_gather_into_tensor(gathered, flat, group=group)
     joined = gathered.reshape(world_size, rows, -1).permute(1, 0, 2).reshape(rows, -1).contiguous()
     return joined.view(local.dtype).reshape(rows, world_size * width)
+
+
+def gather_packed(packed, gathered, group=None):
+    """One all-gather of a rank's packed output slices (1-D) into `gathered` (world_size times as long, rank-major): the
+    decode-sized slices of a whole step travel in one collective, because at a few KB each the collective's latency,
+    not its bandwidth, is the cost. Rank r's slice of output j is at r * len(packed) + offset_j."""
+    import torch
+    import torch.distributed as dist
+    dist.all_gather_into_tensor(gathered.view(torch.uint8), packed.view(torch.uint8), group=group)
+    return gathered
