@@ -298,7 +298,7 @@ def measure_format(torch, dist, gpu, fmt, rows_list, copies, world, rank, sms, s
     return result
 
 
-def measure_prefill(torch, gpu, stream, steps, warmup, rows=4096):
+def measure_prefill(torch, gpu, stream, steps, warmup, rows=4096, detail=False):
     """NVFP4 prefill GEMM over the seven layer shapes at `rows` tokens: TFLOP/s of 2 M N K (one logical product)."""
     from euhedral_b200 import layouts, synthetic
     if not gpu.nvfp4_native_available():
@@ -323,7 +323,21 @@ def measure_prefill(torch, gpu, stream, steps, warmup, rows=4096):
             seconds = timed(torch, None, 1, steps, warmup, body)
         except RuntimeError:
             return None
-    return {"rows": rows, "tflops": flops * steps / seconds / 1e12, "ms_per_step": seconds / steps * 1e3}
+    result = {"rows": rows, "tflops": flops * steps / seconds / 1e12, "issued_tflops": 2 * flops * steps / seconds / 1e12,
+              "ms_per_step": seconds / steps * 1e3}
+    if detail:
+        per_shape = {}
+        with torch.cuda.stream(stream), gpu.submit(stream.cuda_stream, pdl=True):
+            for (name, n, k), item in zip(LAYER, tensors):
+                blob, x, y, _, _ = item
+
+                def one(_, item=item):
+                    blob, x, y, n, k = item
+                    gpu.linear_nvfp4_native_bf16(x.data_ptr(), blob.data_ptr(), y.data_ptr(), rows, k, n, blob.numel())
+                t = timed(torch, None, 1, steps, warmup, one)
+                per_shape[name] = round(2 * rows * n * k * steps / t / 1e12, 1)
+        result["per_shape_tflops"] = per_shape
+    return result
 
 
 def run_ours(args):
@@ -341,6 +355,11 @@ def run_ours(args):
     stream = torch.cuda.Stream()
     peak, peak_kind = read_peaks()
     copies = 3
+    if args.prefill_only:
+        r = measure_prefill(torch, gpu, stream, args.steps, args.warmup, rows=args.prefill_only, detail=True)
+        if RANK == 0:
+            print(json.dumps({"prefill_rows": args.prefill_only, **(r or {"unavailable": True})}))
+        return
     if args.only:
         # One matrix alone (profiling and per-shape numbers): FORMAT:NAME:ROWS, e.g. q3:gate:3
         fmt, name, rows = args.only.split(":")
@@ -404,6 +423,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--detail", action="store_true")
+    parser.add_argument("--prefill-only", type=int, default=0, help="time the NVFP4 prefill GEMM over the layer shapes at this many rows")
     parser.add_argument("--only", default=None, help="FORMAT:NAME:ROWS - time one matrix alone, e.g. q3:gate:3")
     args = parser.parse_args()
     if args.impl == "reference":
