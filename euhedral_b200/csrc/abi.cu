@@ -6,7 +6,9 @@
 
 #include <atomic>
 #include <cstring>
+#include <algorithm>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "exact_kernels.cuh"
@@ -62,6 +64,20 @@ cudaError_t allow_trellis_width() {
     return e;
 }
 
+template <class F>
+cudaError_t allow_gemv() {
+    cudaError_t e = cudaSuccess;
+#define EB_ALLOW_GEMV(RT)                                                               \
+    if (e == cudaSuccess) e = allow_big_smem(gemv::kernel<F, RT, 24>);                  \
+    if (e == cudaSuccess) e = allow_big_smem(gemv::kernel<F, RT, 16>);
+    EB_ALLOW_GEMV(1)
+    EB_ALLOW_GEMV(2)
+    EB_ALLOW_GEMV(4)
+    EB_ALLOW_GEMV(8)
+#undef EB_ALLOW_GEMV
+    return e;
+}
+
 void initialize_device(int device, DeviceState* state) {
     cudaDeviceProp prop;
     cudaError_t e = cudaGetDeviceProperties(&prop, device);
@@ -72,12 +88,8 @@ void initialize_device(int device, DeviceState* state) {
     }
     // In host code the array's name is only a handle; the kernels need its device address on this device.
     if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&state->static_scratch), g_static_scratch);
-    if (e == cudaSuccess) e = allow_big_smem(nvfp4::gemv_kernel<1>);
-    if (e == cudaSuccess) e = allow_big_smem(nvfp4::gemv_kernel<2>);
-    if (e == cudaSuccess) e = allow_big_smem(nvfp4::gemv_kernel<4>);
-    if (e == cudaSuccess) e = allow_big_smem(q3::gemv_kernel<1>);
-    if (e == cudaSuccess) e = allow_big_smem(q3::gemv_kernel<2>);
-    if (e == cudaSuccess) e = allow_big_smem(q3::gemv_kernel<4>);
+    if (e == cudaSuccess) e = allow_gemv<nvfp4::Format>();
+    if (e == cudaSuccess) e = allow_gemv<q3::Format>();
     if (e == cudaSuccess) e = allow_big_smem(exact::trellis_linear);
 #define EB_ALLOW(W) if (e == cudaSuccess) e = allow_trellis_width<W>();
     EB_TRELLIS_WIDTHS(EB_ALLOW)
@@ -128,60 +140,162 @@ cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shar
 }
 
 // ---- decode GEMV planning ---------------------------------------------------------------------------------------------
-// K slices per row depend on K only (nvfp4::split_of); the 16-row tiles per CTA on the shape and the SM count: the
-// largest of 4, 2, 1 that divides the rows, fits two CTAs per SM at 8 activation rows, and still gives two CTAs per SM
-// over the whole grid; else the count that gives the most CTAs.
+// K slices per row depend on K only (gemv::split_of). A CTA has one warp per 16-row tile in flight: the largest of 8,
+// 4, 2, 1 warps that still gives two CTAs per SM over the whole grid. If a grid of one tile per warp is resident at
+// once with three CTAs per SM (the ring shrinks from 4 to 2 slots to make room), that grid is launched. Otherwise the
+// grid is the number of clusters the device holds at two CTAs per SM and every cluster takes an even share of the tiles
+// (`span` at most), its warps several tiles each in turn.
+constexpr uint32_t kSpanCap = 32;
+
 struct DecodePlan {
-    uint32_t rt, split, ctas, shared;
+    uint32_t rt, warps_per_sm, span, slots, split, ctas, shared;
 };
 
-template <typename TileT>
+template <class F, int RT, int WARPS_PER_SM>
+int query_clusters(uint32_t shared, uint32_t split) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(split * 4096u);
+    config.blockDim = dim3(32u * RT);
+    config.dynamicSmemBytes = shared;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = split;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemv::kernel<F, RT, WARPS_PER_SM>, &config) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return clusters;
+}
+
+// Clusters of `split` CTAs of this kernel that the current device holds at once; cached per (device, kernel, shape of the CTA).
+// Without a device: three CTAs of eight warps per SM, as far as shared memory allows.
+template <class F>
+uint32_t resident_clusters(uint32_t rt, uint32_t warps_per_sm, uint32_t shared, uint32_t split, int sms) {
+    struct Entry {
+        int device;
+        uint32_t error_bit, rt, warps, shared, split, clusters;
+    };
+    static std::mutex mutex;
+    static std::vector<Entry> cache;
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess) {
+        (void)cudaGetLastError();
+        device = -1;
+    }
+    if (device >= 0) {
+        std::lock_guard<std::mutex> lock(mutex);
+        for (const Entry& e : cache)
+            if (e.device == device && e.error_bit == F::kErrorBit && e.rt == rt && e.warps == warps_per_sm && e.shared == shared && e.split == split)
+                return e.clusters;
+        int found = 0;
+        if (warps_per_sm == 24u)
+            found = rt == 8 ? query_clusters<F, 8, 24>(shared, split) : rt == 4 ? query_clusters<F, 4, 24>(shared, split)
+                    : rt == 2 ? query_clusters<F, 2, 24>(shared, split) : query_clusters<F, 1, 24>(shared, split);
+        else
+            found = rt == 8 ? query_clusters<F, 8, 16>(shared, split) : rt == 4 ? query_clusters<F, 4, 16>(shared, split)
+                    : rt == 2 ? query_clusters<F, 2, 16>(shared, split) : query_clusters<F, 1, 16>(shared, split);
+        if (found > 0) {
+            cache.push_back({device, F::kErrorBit, rt, warps_per_sm, shared, split, (uint32_t)found});
+            return (uint32_t)found;
+        }
+    }
+    const uint32_t per_sm = std::min<uint32_t>(warps_per_sm / rt, (227u * 1024u) / (shared + 1024u));
+    return std::max<uint32_t>(1u, (uint32_t)sms * per_sm / split);
+}
+
+template <class F>
 bool plan_decode(uint32_t rows, uint32_t k, uint32_t n, int sms, DecodePlan* plan) {
-    if (k == 0 || k % 128u != 0 || n == 0 || n % 16u != 0 || rows == 0 || rows > 8u) return false;
-    const uint32_t chunks = k / 128u, split = nvfp4::split_of(k);
+    if (k == 0 || k % 128u != 0 || n == 0 || n % 16u != 0 || rows == 0 || rows > gemv::kMaxRows) return false;
+    const uint32_t chunks = k / 128u, split = gemv::split_of(k);
     const uint32_t chunks_max = (chunks + split - 1u) / split;
-    uint32_t chosen = 0;
-#ifdef EB_FORCE_RT
-    for (uint32_t rt = EB_FORCE_RT; rt >= 1; rt >>= 1) {
-#else
-    for (uint32_t rt = 4; rt >= 1; rt >>= 1) {
-#endif
-        if (n % (16u * rt) != 0 || TileT(rt, chunks_max, 8, split).bytes > 110u * 1024u) continue;
-        chosen = rt;   // the smallest valid tile count survives when none fills the GPU
-        if ((uint64_t)(n / (16u * rt)) * split >= 2ull * (uint64_t)sms) break;
-    }
-    if (chosen == 0) return false;
-    plan->rt = chosen;
+    const uint32_t tiles = n / 16u;
+    uint32_t rt = 8;
+    while (rt > 1u && (uint64_t)((tiles + rt - 1u) / rt) * split < 2ull * (uint64_t)sms) rt >>= 1;
+    plan->rt = rt;
     plan->split = split;
-    plan->ctas = n / (16u * chosen) * split;
-    plan->shared = TileT(chosen, chunks_max, rows, split).bytes;
-    return plan->shared <= (uint32_t)kBigSmem;
+    // One tile per warp, everything resident at once.
+    const uint32_t groups = (tiles + rt - 1u) / rt;
+    for (uint32_t slots = gemv::kMaxSlots; slots >= 2u; --slots) {
+        const uint32_t shared = gemv::Layout<F>(rt, rt, slots, chunks_max, rows, split).bytes;
+        if (shared <= (uint32_t)kBigSmem && groups <= resident_clusters<F>(rt, 24u, shared, split, sms)) {
+            plan->warps_per_sm = 24;
+            plan->span = rt;
+            plan->slots = slots;
+            plan->ctas = groups * split;
+            plan->shared = shared;
+            return true;
+        }
+    }
+    // Even shares over the resident clusters, two CTAs per SM (measured: three CTAs of eight warps, or one of sixteen, are
+    // slower - more CTAs pay more staging, wider CTAs wait longer on their slowest warp). The shared-memory request is
+    // raised to more than a third of an SM so that the hardware cannot stack three CTAs on one SM and leave another with
+    // one. The ring is the deepest that fits. A larger share needs a larger gather buffer, which can lower the resident
+    // count once.
+    const uint32_t two_per_sm = (227u * 1024u) / 3u + 1024u;
+    for (uint32_t slots = gemv::kMaxSlots; slots >= 2u; --slots) {
+        uint32_t span = rt, shared = std::max(two_per_sm / (8u / rt), gemv::Layout<F>(rt, span, slots, chunks_max, rows, split).bytes);
+        if (shared > (uint32_t)kBigSmem) continue;
+        // Every warp takes the same number of tiles, `turns`: the fewest that fit the resident clusters. That usually
+        // leaves a few clusters of slack, which a straggler of the previous launch can hold without delaying this one.
+        // A share is at most kSpanCap tiles (the gather buffer grows with it): very tall tensors run several waves.
+        const uint32_t most_turns = std::max(1u, kSpanCap / rt);
+        uint32_t resident = std::min(groups, resident_clusters<F>(rt, 16u, shared, split, sms));
+        bool fits = true;
+        for (int round = 0; round < 3; ++round) {
+            const uint32_t turns = std::min(most_turns, (tiles + rt * resident - 1u) / (rt * resident));
+            span = rt * turns;
+            shared = std::max(two_per_sm / (8u / rt), gemv::Layout<F>(rt, span, slots, chunks_max, rows, split).bytes);
+            if (shared > (uint32_t)kBigSmem) {
+                fits = false;
+                break;
+            }
+            const uint32_t again = std::min(groups, resident_clusters<F>(rt, 16u, shared, split, sms));
+            if (again >= resident) break;
+            resident = again;
+        }
+        if (!fits) continue;
+        if ((uint64_t)resident * split * rt < 16ull * (uint64_t)sms * 9u / 10u && slots > 2u) continue;   // too few warps per SM
+        plan->warps_per_sm = 16;
+        plan->span = span;
+        plan->slots = slots;
+        plan->ctas = (tiles + span - 1u) / span * split;
+        plan->shared = shared;
+        return true;
+    }
+    return false;
 }
 
-cudaError_t launch_nvfp4(const DecodePlan& p, const void* x, const void* w, void* y, uint32_t rows, uint32_t k, uint32_t n,
+template <class F>
+cudaError_t launch_gemv(const DecodePlan& p, const void* x, const void* w, void* y, uint32_t rows, uint32_t k, uint32_t n,
         uint32_t* error) {
-    const dim3 grid(p.ctas), block(64u * p.rt);
+    const dim3 grid(p.ctas), block(32u * p.rt);
+    CUtensorMap map;
+    if (!gemv::encode_codes<F>(&map, w, n, k)) return cudaErrorNotSupported;
     auto xs = static_cast<const uint16_t*>(x);
     auto ws = static_cast<const uint8_t*>(w);
     auto ys = static_cast<uint16_t*>(y);
-    switch (p.rt) {
-        case 4: return launch(nvfp4::gemv_kernel<4>, grid, block, p.shared, p.split, xs, ws, ys, rows, k, n, p.split, error);
-        case 2: return launch(nvfp4::gemv_kernel<2>, grid, block, p.shared, p.split, xs, ws, ys, rows, k, n, p.split, error);
-        default: return launch(nvfp4::gemv_kernel<1>, grid, block, p.shared, p.split, xs, ws, ys, rows, k, n, p.split, error);
+#define EB_LAUNCH_GEMV(RT, WARPS) \
+    launch(gemv::kernel<F, RT, WARPS>, grid, block, p.shared, p.split, map, xs, ws, ys, rows, k, n, p.split, p.span, p.slots, error)
+    if (p.warps_per_sm == 24u) {
+        switch (p.rt) {
+            case 8: return EB_LAUNCH_GEMV(8, 24);
+            case 4: return EB_LAUNCH_GEMV(4, 24);
+            case 2: return EB_LAUNCH_GEMV(2, 24);
+            default: return EB_LAUNCH_GEMV(1, 24);
+        }
     }
-}
-
-cudaError_t launch_q3(const DecodePlan& p, const void* x, const void* w, void* y, uint32_t rows, uint32_t k, uint32_t n,
-        uint32_t* error) {
-    const dim3 grid(p.ctas), block(64u * p.rt);
-    auto xs = static_cast<const uint16_t*>(x);
-    auto ws = static_cast<const uint8_t*>(w);
-    auto ys = static_cast<uint16_t*>(y);
     switch (p.rt) {
-        case 4: return launch(q3::gemv_kernel<4>, grid, block, p.shared, p.split, xs, ws, ys, rows, k, n, p.split, error);
-        case 2: return launch(q3::gemv_kernel<2>, grid, block, p.shared, p.split, xs, ws, ys, rows, k, n, p.split, error);
-        default: return launch(q3::gemv_kernel<1>, grid, block, p.shared, p.split, xs, ws, ys, rows, k, n, p.split, error);
+        case 8: return EB_LAUNCH_GEMV(8, 16);
+        case 4: return EB_LAUNCH_GEMV(4, 16);
+        case 2: return EB_LAUNCH_GEMV(2, 16);
+        default: return EB_LAUNCH_GEMV(1, 16);
     }
+#undef EB_LAUNCH_GEMV
 }
 
 uint32_t capped_grid(uint64_t count) { return count > 2147483647ull ? 2147483647u : (uint32_t)count; }
@@ -408,12 +522,12 @@ int euhedral_cuda_linear_q3_bf16(const void* input, const void* weights, void* o
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     DecodePlan plan;
     const bool qualified = rows <= 32u && ((uintptr_t)input & 15u) == 0 && ((uintptr_t)weights & 15u) == 0
-            && plan_decode<q3::Tile>(rows < 8u ? rows : 8u, in_features, out_features, state->sms, &plan);
+            && plan_decode<q3::Format>(rows < 8u ? rows : 8u, in_features, out_features, state->sms, &plan);
     if (g_exact.load() || !qualified) return q3_reference(state, input, weights, output, rows, in_features, out_features);
     for (uint32_t first = 0; first < rows; first += 8u) {
         const uint32_t group = rows - first < 8u ? rows - first : 8u;
-        plan_decode<q3::Tile>(group, in_features, out_features, state->sms, &plan);
-        const cudaError_t e = launch_q3(plan, static_cast<const uint16_t*>(input) + (uint64_t)first * in_features, weights,
+        plan_decode<q3::Format>(group, in_features, out_features, state->sms, &plan);
+        const cudaError_t e = launch_gemv<q3::Format>(plan, static_cast<const uint16_t*>(input) + (uint64_t)first * in_features, weights,
                 static_cast<uint16_t*>(output) + (uint64_t)first * out_features, group, in_features, out_features, state->error_word);
         if (e != cudaSuccess) return (int)e;
     }
@@ -444,7 +558,7 @@ int euhedral_cuda_linear_nvfp4_bf16(const void* input, const void* weights, void
     const int status = bind(&state);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     DecodePlan plan;
-    const bool qualified = rows <= 32u && plan_decode<nvfp4::Tile>(rows < 8u ? rows : 8u, in_features, out_features, state->sms, &plan);
+    const bool qualified = rows <= 32u && plan_decode<nvfp4::Format>(rows < 8u ? rows : 8u, in_features, out_features, state->sms, &plan);
     if (g_exact.load() || !qualified) {
         return finish(launch(exact::nvfp4_linear, dim3(capped_grid((uint64_t)rows * out_features)), dim3(128), 0, 1u,
                 static_cast<const uint16_t*>(input), static_cast<const uint8_t*>(weights), static_cast<uint16_t*>(output), rows,
@@ -452,8 +566,8 @@ int euhedral_cuda_linear_nvfp4_bf16(const void* input, const void* weights, void
     }
     for (uint32_t first = 0; first < rows; first += 8u) {
         const uint32_t group = rows - first < 8u ? rows - first : 8u;
-        plan_decode<nvfp4::Tile>(group, in_features, out_features, state->sms, &plan);
-        const cudaError_t e = launch_nvfp4(plan, static_cast<const uint16_t*>(input) + (uint64_t)first * in_features, weights,
+        plan_decode<nvfp4::Format>(group, in_features, out_features, state->sms, &plan);
+        const cudaError_t e = launch_gemv<nvfp4::Format>(plan, static_cast<const uint16_t*>(input) + (uint64_t)first * in_features, weights,
                 static_cast<uint16_t*>(output) + (uint64_t)first * out_features, group, in_features, out_features, state->error_word);
         if (e != cudaSuccess) return (int)e;
     }
@@ -615,10 +729,10 @@ int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, u
     DeviceState* state = nullptr;
     if (bind(&state) == EUHEDRAL_CUDA_SUCCESS) sms = state->sms;
     DecodePlan plan;
-    const bool ok = format == 0 ? plan_decode<nvfp4::Tile>(rows, in_features, out_features, sms, &plan)
-                                : plan_decode<q3::Tile>(rows, in_features, out_features, sms, &plan);
+    const bool ok = format == 0 ? plan_decode<nvfp4::Format>(rows, in_features, out_features, sms, &plan)
+                                : plan_decode<q3::Format>(rows, in_features, out_features, sms, &plan);
     if (!ok) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
-    *row_tiles = plan.rt;
+    *row_tiles = plan.span;
     *k_slices = plan.split;
     *ctas = plan.ctas;
     *shared_bytes = plan.shared;
@@ -626,3 +740,10 @@ int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, u
 }
 
 }  // extern "C"
+
+#ifdef EB_X_TRACE
+extern "C" EUHEDRAL_CUDA_EXPORT int euhedral_b200_debug_trace(void* host, uint64_t bytes) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(host, gemv::g_trace, bytes);
+}
+#endif

@@ -2,6 +2,7 @@
 // programmatic dependent launch, thread-block clusters and warp-level BF16 MMA.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -50,6 +51,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
             : "memory");
     return done != 0;
 }
+__device__ __forceinline__ bool mbar_try_wait_at(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+    return done != 0;
+}
+// Bounded wait on a barrier given by its 32-bit shared address.
+__device__ __forceinline__ bool mbar_wait_at(uint32_t bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+        if (mbar_try_wait_at(bar, parity)) return true;
+    return false;
+}
 // Bounded wait: false when the phase did not complete within kSpinLimit polls.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
@@ -65,6 +83,24 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
             : "memory");
 }
 
+// ---- tiled asynchronous copy global -> shared through a tensor map (TMA) -----------------------------------------
+// c0 is the innermost coordinate: c0 times the element size must be a multiple of 16 bytes. The whole box is written
+// (out-of-range elements as zeros) and signalled on `bar`.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                         smem_u32(dst)),
+            "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+            : "memory");
+}
+
+// The same with destination and barrier given as 32-bit shared addresses, preceded by the barrier's expect_tx.
+__device__ __forceinline__ void tma_load_2d_expect(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+            "l"(map), "r"(c0), "r"(c1), "r"(bar)
+            : "memory");
+}
+
 // ---- cp.async (LDGSTS) for pieces too small or too misaligned for a bulk copy ------------------------------------
 __device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
@@ -76,6 +112,43 @@ __device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's most recent groups are still in flight.
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// cp.async with the destination given as a 32-bit shared address.
+__device__ __forceinline__ void cp_async_4_to(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_8_to(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// ---- shared-memory loads by 32-bit shared address plus a compile-time byte offset (folded into the instruction) -------
+template <int OFFSET>
+__device__ __forceinline__ uint32_t lds_u32(uint32_t address) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(address), "n"(OFFSET));
+    return v;
+}
+template <int OFFSET>
+__device__ __forceinline__ uint32_t lds_u16(uint32_t address) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(address), "n"(OFFSET));
+    return v;
+}
+template <int OFFSET>
+__device__ __forceinline__ uint4 lds_v4(uint32_t address) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address), "n"(OFFSET));
+    return v;
+}
+template <int OFFSET>
+__device__ __forceinline__ float2 lds_f2(uint32_t address) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2+%3];" : "=f"(v.x), "=f"(v.y) : "r"(address), "n"(OFFSET));
+    return v;
+}
 
 // ---- thread-block clusters ---------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -100,6 +173,24 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
     return remote;
 }
+// Global loads of weight bytes. Streamed bytes are read once and bypass L1; small pieces that neighbouring chunks share
+// (scales, overlapping code words) keep the default L1 policy.
+__device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_u32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_u16(const void* p) {
+    uint16_t v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+
 __device__ __forceinline__ void st_cluster_f32(uint32_t address, float value) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(address), "f"(value) : "memory");
 }
@@ -111,8 +202,7 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t address, float value) {
 //   d0, d1: row g, cols 2q, 2q+1   d2, d3: row g+8, cols 2q, 2q+1
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
         uint32_t b1) {
-    asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
             : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -145,6 +235,21 @@ __device__ __forceinline__ uint32_t bf16x2_fma(uint32_t a, uint32_t b, uint32_t 
     uint32_t d;
     asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
+}
+
+// ---- host side: the driver's tensor-map encoder, looked up through the runtime (no link against libcuda) -----------
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+        const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiled encoder() {
+    static EncodeTiled cached = [] {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &query) != cudaSuccess || query != cudaDriverEntryPointSuccess)
+            entry = nullptr;
+        return reinterpret_cast<EncodeTiled>(entry);
+    }();
+    return cached;
 }
 
 }  // namespace eb

@@ -149,12 +149,7 @@ __global__ void __launch_bounds__(256) repack_weight_scales(const uint8_t* __res
 
 // ---- 3. the GEMM ----------------------------------------------------------------------------------------------------------
 
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                         eb::smem_u32(dst)),
-            "l"(map), "r"(c0), "r"(c1), "r"(eb::smem_u32(bar))
-            : "memory");
-}
+using eb::tma_load_2d;
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
                          eb::smem_u32(dst)),
@@ -371,19 +366,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
 // ---- host side ------------------------------------------------------------------------------------------------------------
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-        const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-inline EncodeTiled encoder() {
-    static EncodeTiled cached = [] {
-        void* entry = nullptr;
-        cudaDriverEntryPointQueryResult query;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &query) != cudaSuccess || query != cudaDriverEntryPointSuccess)
-            entry = nullptr;
-        return reinterpret_cast<EncodeTiled>(entry);
-    }();
-    return cached;
-}
+using eb::EncodeTiled;
+using eb::encoder;
 
 inline cudaError_t initialize() {
     return cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSharedBytes);

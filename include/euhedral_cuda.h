@@ -101,8 +101,8 @@ EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_launch(int32_t kernel, uint32_t gr
 /* Reads and clears the current device's kernel error word: nonzero when a bounded wait inside a kernel gave up
  * (bit 0 NVFP4 GEMV, bit 1 Q3 GEMV, bit 2 trellis GEMM, bit 3 NVFP4 prefill GEMM). Synchronizes the device. */
 EUHEDRAL_CUDA_EXPORT int euhedral_b200_take_device_error(uint32_t* word);
-/* The launch geometry chosen for a decode GEMV of this shape: 16-row tiles per CTA, K slices per row (cluster size),
- * CTAs and dynamic shared bytes for `rows` activation rows. format: 0 NVFP4, 1 Q3. Returns 0, or -1 for a shape the
+/* The launch geometry chosen for a decode GEMV of this shape: the most 16-row tiles a CTA takes, K slices per row
+ * (cluster size), CTAs and dynamic shared bytes for `rows` activation rows. format: 0 NVFP4, 1 Q3. Returns 0, or -1 for a shape the
  * decode kernels do not take. */
 EUHEDRAL_CUDA_EXPORT int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, uint32_t out_features,
         uint32_t* row_tiles, uint32_t* k_slices, uint32_t* ctas, uint32_t* shared_bytes);
