@@ -209,7 +209,7 @@ uint32_t resident_clusters(uint32_t rt, uint32_t warps_per_sm, uint32_t shared, 
 }
 
 template <class F>
-bool plan_decode(uint32_t rows, uint32_t k, uint32_t n, int sms, DecodePlan* plan) {
+bool plan_decode_uncached(uint32_t rows, uint32_t k, uint32_t n, int sms, DecodePlan* plan) {
     if (k == 0 || k % 128u != 0 || n == 0 || n % 16u != 0 || rows == 0 || rows > gemv::kMaxRows) return false;
     const uint32_t chunks = k / 128u, split = gemv::split_of(k);
     const uint32_t chunks_max = (chunks + split - 1u) / split;
@@ -220,9 +220,14 @@ bool plan_decode(uint32_t rows, uint32_t k, uint32_t n, int sms, DecodePlan* pla
     plan->split = split;
     // One tile per warp, everything resident at once.
     const uint32_t groups = (tiles + rt - 1u) / rt;
+    // The shared-memory request is raised so that no SM takes more than its even share of the CTAs, rounded up: the
+    // hardware fills the SMs that free up first, and without the cap some end up with twice the work of others.
+    const uint32_t even_share = (groups * split + (uint32_t)sms - 1u) / (uint32_t)sms;
+    const uint32_t capped = (227u * 1024u) / (even_share + 1u) + 1u;
     for (uint32_t slots = gemv::kMaxSlots; slots >= 2u; --slots) {
-        const uint32_t shared = gemv::Layout<F>(rt, rt, slots, chunks_max, rows, split).bytes;
-        if (shared <= (uint32_t)kBigSmem && groups <= resident_clusters<F>(rt, 24u, shared, split, sms)) {
+        const uint32_t needed = gemv::Layout<F>(rt, rt, slots, chunks_max, rows, split).bytes;
+        const uint32_t shared = std::min<uint32_t>(std::max(needed, capped), (uint32_t)kBigSmem);
+        if (needed <= (uint32_t)kBigSmem && groups <= resident_clusters<F>(rt, 24u, shared, split, sms)) {
             plan->warps_per_sm = 24;
             plan->span = rt;
             plan->slots = slots;
@@ -270,12 +275,70 @@ bool plan_decode(uint32_t rows, uint32_t k, uint32_t n, int sms, DecodePlan* pla
     return false;
 }
 
+// The calling thread remembers the last plans it made (a plan costs several occupancy look-ups).
+template <class F>
+bool plan_decode(uint32_t rows, uint32_t k, uint32_t n, int sms, DecodePlan* plan) {
+    struct Cached {
+        int device;
+        uint32_t rows, k, n;
+        bool ok;
+        DecodePlan plan;
+    };
+    constexpr int kCached = 32;
+    thread_local Cached cache[kCached] = {};
+    thread_local int next = 0;
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess) {
+        (void)cudaGetLastError();
+        device = -1;
+    }
+    for (int i = 0; i < kCached; ++i) {
+        const Cached& c = cache[i];
+        if (c.k == k && c.n == n && c.rows == rows && c.device == device && c.k != 0) {
+            *plan = c.plan;
+            return c.ok;
+        }
+    }
+    Cached& slot = cache[next];
+    next = (next + 1) % kCached;
+    slot.device = device;
+    slot.rows = rows;
+    slot.k = k;
+    slot.n = n;
+    slot.ok = plan_decode_uncached<F>(rows, k, n, sms, &slot.plan);
+    if (k == 0) return slot.ok;   // never cached: k == 0 marks an empty slot
+    *plan = slot.plan;
+    return slot.ok;
+}
+
 template <class F>
 cudaError_t launch_gemv(const DecodePlan& p, const void* x, const void* w, void* y, uint32_t rows, uint32_t k, uint32_t n,
         uint32_t* error) {
     const dim3 grid(p.ctas), block(32u * p.rt);
-    CUtensorMap map;
-    if (!gemv::encode_codes<F>(&map, w, n, k)) return cudaErrorNotSupported;
+    // Encoding a tensor map costs about a microsecond of host time: the calling thread keeps the last few it made. A map
+    // holds only the address and the shape, so a stale entry for a reused address is still the right map.
+    struct Cached {
+        const void* weights;
+        uint32_t n, k, format;
+        CUtensorMap map;
+    };
+    constexpr int kCached = 32;
+    thread_local Cached cache[kCached] = {};
+    thread_local int next = 0;
+    const CUtensorMap* found = nullptr;
+    for (int i = 0; i < kCached; ++i)
+        if (cache[i].weights == w && cache[i].n == n && cache[i].k == k && cache[i].format == F::kErrorBit) found = &cache[i].map;
+    if (found == nullptr) {
+        Cached& slot = cache[next];
+        if (!gemv::encode_codes<F>(&slot.map, w, n, k)) return cudaErrorNotSupported;
+        slot.weights = w;
+        slot.n = n;
+        slot.k = k;
+        slot.format = F::kErrorBit;
+        found = &slot.map;
+        next = (next + 1) % kCached;
+    }
+    const CUtensorMap& map = *found;
     auto xs = static_cast<const uint16_t*>(x);
     auto ws = static_cast<const uint8_t*>(w);
     auto ys = static_cast<uint16_t*>(y);
