@@ -340,6 +340,10 @@ def measure_prefill(torch, gpu, stream, steps, warmup, rows=4096, detail=False):
     return result
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one captured gate launch over its algorithmic bytes (profiles/q3_gemv_gate_m3.md).
+Q3_TRAFFIC_RATIO = 36.27 / 36.34
+
+
 def run_ours(args):
     os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "8")
     import torch
@@ -402,7 +406,9 @@ def run_ours(args):
                        "parallelism": f"n-sharded x{world}, one NCCL all-gather of the step's packed output slices" if world > 1 else "single GPU",
                        "launch": "one C-ABI call per GEMV, one stream, programmatic dependent launch"},
             "roofline": {"bound": "hbm", "achieved": head["gbs"], "peak": peak * world, "unit": "GB/s", "frac": head["gbs"] / (peak * world),
-                         "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "q3::gemv_kernel (every launch of the timed region)"},
+                         "traffic": head["bytes_per_step"] * Q3_TRAFFIC_RATIO, "traffic_unit": "bytes per step",
+                         "traffic_note": "ncu dram bytes of the gate launch (36.27 MB read, 36.34 MB algorithmic) scaled to the step's bytes",
+                         "peak_kind": f"of {peak_kind}", "kernel": "gemv::kernel<q3::Format, ...> (every launch of the timed region)"},
             "e2e": {"value": head.get("e2e_gbs"), "unit": "GB/s", "h2d_bytes_per_step": head.get("h2d"), "d2h_bytes_per_step": head.get("d2h")},
             "gpu_launches": head["launches_per_step"] * args.steps,
             "clocks": clocks.summary(),

@@ -148,7 +148,7 @@ cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shar
 constexpr uint32_t kSpanCap = 32;
 
 struct DecodePlan {
-    uint32_t rt, warps_per_sm, span, slots, split, ctas, shared;
+    uint32_t rt, warps_per_sm, span, slots, pair, split, ctas, shared;
 };
 
 template <class F, int RT, int WARPS_PER_SM>
@@ -224,13 +224,16 @@ bool plan_decode_uncached(uint32_t rows, uint32_t k, uint32_t n, int sms, Decode
     // hardware fills the SMs that free up first, and without the cap some end up with twice the work of others.
     const uint32_t even_share = (groups * split + (uint32_t)sms - 1u) / (uint32_t)sms;
     const uint32_t capped = (227u * 1024u) / (even_share + 1u) + 1u;
-    for (uint32_t slots = gemv::kMaxSlots; slots >= 2u; --slots) {
-        const uint32_t needed = gemv::Layout<F>(rt, rt, slots, chunks_max, rows, split).bytes;
+    // Ring shapes from deepest to shallowest: (slots, boxes per slot).
+    const uint32_t shapes[4][2] = {{3u, 2u}, {2u, 2u}, {3u, 1u}, {2u, 1u}};
+    for (const auto& shape : shapes) {
+        const uint32_t needed = gemv::Layout<F>(rt, rt, shape[0], shape[1], chunks_max, rows, split).bytes;
         const uint32_t shared = std::min<uint32_t>(std::max(needed, capped), (uint32_t)kBigSmem);
         if (needed <= (uint32_t)kBigSmem && groups <= resident_clusters<F>(rt, 24u, shared, split, sms)) {
             plan->warps_per_sm = 24;
             plan->span = rt;
-            plan->slots = slots;
+            plan->slots = shape[0];
+            plan->pair = shape[1];
             plan->ctas = groups * split;
             plan->shared = shared;
             return true;
@@ -242,8 +245,9 @@ bool plan_decode_uncached(uint32_t rows, uint32_t k, uint32_t n, int sms, Decode
     // one. The ring is the deepest that fits. A larger share needs a larger gather buffer, which can lower the resident
     // count once.
     const uint32_t two_per_sm = (227u * 1024u) / 3u + 1024u;
-    for (uint32_t slots = gemv::kMaxSlots; slots >= 2u; --slots) {
-        uint32_t span = rt, shared = std::max(two_per_sm / (8u / rt), gemv::Layout<F>(rt, span, slots, chunks_max, rows, split).bytes);
+    for (const auto& shape : shapes) {
+        const uint32_t slots = shape[0], pair = shape[1];
+        uint32_t span = rt, shared = std::max(two_per_sm / (8u / rt), gemv::Layout<F>(rt, span, slots, pair, chunks_max, rows, split).bytes);
         if (shared > (uint32_t)kBigSmem) continue;
         // Every warp takes the same number of tiles, `turns`: the fewest that fit the resident clusters. That usually
         // leaves a few clusters of slack, which a straggler of the previous launch can hold without delaying this one.
@@ -254,7 +258,7 @@ bool plan_decode_uncached(uint32_t rows, uint32_t k, uint32_t n, int sms, Decode
         for (int round = 0; round < 3; ++round) {
             const uint32_t turns = std::min(most_turns, (tiles + rt * resident - 1u) / (rt * resident));
             span = rt * turns;
-            shared = std::max(two_per_sm / (8u / rt), gemv::Layout<F>(rt, span, slots, chunks_max, rows, split).bytes);
+            shared = std::max(two_per_sm / (8u / rt), gemv::Layout<F>(rt, span, slots, pair, chunks_max, rows, split).bytes);
             if (shared > (uint32_t)kBigSmem) {
                 fits = false;
                 break;
@@ -264,10 +268,11 @@ bool plan_decode_uncached(uint32_t rows, uint32_t k, uint32_t n, int sms, Decode
             resident = again;
         }
         if (!fits) continue;
-        if ((uint64_t)resident * split * rt < 16ull * (uint64_t)sms * 9u / 10u && slots > 2u) continue;   // too few warps per SM
+        if ((uint64_t)resident * split * rt < 16ull * (uint64_t)sms * 9u / 10u && !(slots == 2u && pair == 1u)) continue;   // too few warps per SM
         plan->warps_per_sm = 16;
         plan->span = span;
         plan->slots = slots;
+        plan->pair = pair;
         plan->ctas = (tiles + span - 1u) / span * split;
         plan->shared = shared;
         return true;
@@ -343,7 +348,7 @@ cudaError_t launch_gemv(const DecodePlan& p, const void* x, const void* w, void*
     auto ws = static_cast<const uint8_t*>(w);
     auto ys = static_cast<uint16_t*>(y);
 #define EB_LAUNCH_GEMV(RT, WARPS) \
-    launch(gemv::kernel<F, RT, WARPS>, grid, block, p.shared, p.split, map, xs, ws, ys, rows, k, n, p.split, p.span, p.slots, error)
+    launch(gemv::kernel<F, RT, WARPS>, grid, block, p.shared, p.split, map, xs, ws, ys, rows, k, n, p.split, p.span, p.slots, p.pair, error)
     if (p.warps_per_sm == 24u) {
         switch (p.rt) {
             case 8: return EB_LAUNCH_GEMV(8, 24);

@@ -101,6 +101,12 @@ __device__ __forceinline__ void tma_load_2d_expect(uint32_t dst, const CUtensorM
             : "memory");
 }
 
+__device__ __forceinline__ void tma_load_2d_at(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+            "l"(map), "r"(c0), "r"(c1), "r"(bar)
+            : "memory");
+}
+
 // ---- cp.async (LDGSTS) for pieces too small or too misaligned for a bulk copy ------------------------------------
 __device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
@@ -141,6 +147,12 @@ template <int OFFSET>
 __device__ __forceinline__ uint4 lds_v4(uint32_t address) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address), "n"(OFFSET));
+    return v;
+}
+template <int OFFSET>
+__device__ __forceinline__ float4 lds_f4(uint32_t address) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(address), "n"(OFFSET));
     return v;
 }
 template <int OFFSET>
@@ -205,6 +217,13 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
     asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
             : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// D = A * B + C with C in registers of its own (a group's starting value that must survive, or a constant).
+__device__ __forceinline__ void mma_bf16_16816_from(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+        uint32_t b1, const float4& c) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c.x), "f"(c.y), "f"(c.z), "f"(c.w));
 }
 __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
         uint32_t b1) {

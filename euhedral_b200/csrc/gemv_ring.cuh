@@ -9,9 +9,9 @@
 //     at two CTAs per SM, each with an even share of the tiles: no second wave of CTAs, the activation slice is staged
 //     once per CTA, and every SM gets the same work.
 //   * Warp w of RT takes tiles w, w + RT, .. of its CTA and runs its own pipeline over them, one after the other
-//     without draining: a private ring of 2 to 4 shared-memory slots, each slot one box of 16 rows x two 128-value
-//     chunks of code bytes, fetched by a single tiled TMA copy through a tensor map of the code plane (one instruction
-//     per box, completion on the slot's mbarrier). The copy engine moves the code bytes past L1 and the load/store
+//     without draining: a private ring of 2 or 3 shared-memory slots, each slot two boxes of 16 rows x two 128-value
+//     chunks of code bytes, each box fetched by a single tiled TMA copy through a tensor map of the code plane (one
+//     instruction per box, completion of both on the slot's mbarrier). The copy engine moves the code bytes past L1 and the load/store
 //     unit; the warp decodes slot i while slots i+1.. are in flight, and no CTA-wide barrier is taken after the
 //     activations are staged, so the warps of an SM drift apart instead of loading and computing in lock-step.
 //   * The block scales are too small and too misaligned for TMA (a slice may start at any multiple of 4 bytes): a warp
@@ -30,9 +30,10 @@
 //   extra_bytes(chunks)             extra shared bytes next to the activation slice
 //   stage(...)                      CTA-wide staging of the activation slice in the decode's pairing
 //   lane_scale_offset(q)            byte offset of lane q's scales within a chunk's scale bytes
-//   State                           accumulators: chunk<I>(...) consumes chunk I of a box given the shared addresses of
-//                                   the box's codes (row g; row g+8 is 8 ring rows further), of the two rows' scales
-//                                   and of the lane's activations; result(out) yields the lane's four sums; reset()
+//   State                           accumulators: chunk<I>(...) consumes chunk I of a slot given the shared addresses of
+//                                   the slot's codes (row g of box 0; row g+8 is 8 ring rows further, box 1 sixteen),
+//                                   of the two rows' scales and of the lane's activations, and the slot's first
+//                                   chunk index; result(out) yields the lane's four sums; reset()
 //   Finish(w, geo)                  apply(sum) = the value to round to BF16
 #pragma once
 
@@ -40,6 +41,8 @@
 
 namespace gemv {
 
+// Diagnostic build only (-DEB_X_TRACE): thread 0 of every CTA records the global timer at six points of the kernel and
+// its SM, read back through euhedral_b200_debug_trace. The regular build compiles none of it.
 #ifdef EB_X_TRACE
 __device__ unsigned long long g_trace[8192 * 8];
 __device__ __forceinline__ unsigned long long now_ns() {
@@ -55,10 +58,11 @@ __device__ __forceinline__ unsigned long long now_ns() {
 #endif
 
 constexpr uint32_t kChunk = 128;   // K values per chunk
-constexpr uint32_t kBox = 2;       // chunks per ring slot (one TMA box: 16 rows x kBox chunks)
+constexpr uint32_t kBox = 2;       // chunks per TMA box (16 rows x kBox chunks)
+constexpr uint32_t kMaxPair = 2;   // boxes per ring slot, 1 or 2 (chosen by the launcher): one mbarrier wait covers up to four chunks
 constexpr uint32_t kMaxRows = 8;   // activation rows per launch
 constexpr uint32_t kMaxSplit = 8;  // portable cluster size
-constexpr uint32_t kMaxSlots = 4;  // ring slots per warp: 2 to 4, chosen by the launcher
+constexpr uint32_t kMaxSlots = 3;  // ring slots per warp: 2 or 3, chosen by the launcher
 
 // K slices per row (cluster size): a function of K alone.
 __host__ __device__ inline uint32_t split_of(uint32_t k) {
@@ -70,15 +74,15 @@ __host__ __device__ inline uint32_t split_of(uint32_t k) {
 template <class F>
 struct Layout {
     uint32_t stride_x, stride_scales, off_extra, off_gather, off_scales, off_ring, off_bars, bytes;
-    // span: the most 16-row tiles a CTA owns; slots: ring slots per warp.
-    __host__ __device__ Layout(uint32_t rt, uint32_t span, uint32_t slots, uint32_t chunks_max, uint32_t rows, uint32_t split) {
+    // span: the most 16-row tiles a CTA owns; slots: ring slots per warp; pair: boxes per slot.
+    __host__ __device__ Layout(uint32_t rt, uint32_t span, uint32_t slots, uint32_t pair, uint32_t chunks_max, uint32_t rows, uint32_t split) {
         stride_x = chunks_max * 256u + 64u;   // 64 modulo 128: the rows a quarter-warp reads fall in distinct banks
         stride_scales = (chunks_max + 1u) * F::kScaleBytes;   // an odd number of pieces: rows fall in distinct banks
         off_extra = rows * stride_x;
         off_gather = off_extra + F::extra_bytes(chunks_max);
         off_scales = (off_gather + (split > 1u ? (span + split - 1u) / split * split * 16u * rows * 4u : 0u) + 15u) & ~15u;
         off_ring = (off_scales + rt * 2u * 16u * stride_scales + 127u) & ~127u;
-        off_bars = off_ring + rt * slots * 16u * kBox * F::kCodeBytes;
+        off_bars = off_ring + rt * slots * pair * 16u * kBox * F::kCodeBytes;
         bytes = off_bars + rt * slots * 8u;
     }
 };
@@ -101,9 +105,10 @@ inline bool encode_codes(CUtensorMap* map, const void* weights, uint32_t n, uint
 template <class F, int RT, int WARPS_PER_SM>
 __global__ void __launch_bounds__(32 * RT, WARPS_PER_SM / RT) kernel(const __grid_constant__ CUtensorMap codes, const uint16_t* __restrict__ x,
         const uint8_t* __restrict__ w, uint16_t* __restrict__ y, uint32_t rows, uint32_t k, uint32_t n, uint32_t split, uint32_t span,
-        uint32_t slots, uint32_t* __restrict__ error) {
+        uint32_t slots, uint32_t pair, uint32_t* __restrict__ error) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr uint32_t kRb = 16u * RT, kThreads = 32u * RT, kRowBytes = kBox * F::kCodeBytes, kSlotBytes = 16u * kRowBytes;
+    constexpr uint32_t kRb = 16u * RT, kThreads = 32u * RT, kRowBytes = kBox * F::kCodeBytes, kBoxBytes = 16u * kRowBytes;
+    const uint32_t slot_bytes = pair * kBoxBytes, slot_chunks = pair * kBox;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, q = lane & 3u;
     const uint32_t rank = split > 1u ? eb::cluster_rank() : 0u;
     // The clusters share the tensor's 16-row tiles evenly: cluster i of G owns tiles [i T / G, (i + 1) T / G), at most `span`.
@@ -113,11 +118,11 @@ __global__ void __launch_bounds__(32 * RT, WARPS_PER_SM / RT) kernel(const __gri
     const uint32_t chunks = k / kChunk;
     const uint32_t c_begin = (uint32_t)((uint64_t)rank * chunks / split), c_end = (uint32_t)((uint64_t)(rank + 1u) * chunks / split);
     const uint32_t nc = c_end - c_begin, nc_max = (chunks + split - 1u) / split;
-    const uint32_t boxes = (nc + kBox - 1u) / kBox;
-    const Layout<F> layout(RT, span, slots, nc_max, rows, split);
+    const uint32_t boxes = (nc + slot_chunks - 1u) / slot_chunks;   // ring slots (box pairs) per tile
+    const Layout<F> layout(RT, span, slots, pair, nc_max, rows, split);
     const typename F::Geometry geo(n, k);
     const uint32_t smem_a = eb::smem_u32(smem);
-    const uint32_t ring_a = smem_a + layout.off_ring + warp * slots * kSlotBytes;
+    const uint32_t ring_a = smem_a + layout.off_ring + warp * slots * slot_bytes;
     const uint32_t bars_a = smem_a + layout.off_bars + warp * slots * 8u;
     const uint32_t scale_bytes = 16u * layout.stride_scales, scales_a = smem_a + layout.off_scales + warp * 2u * scale_bytes;
     float* gather = reinterpret_cast<float*>(smem + layout.off_gather);
@@ -149,13 +154,18 @@ __global__ void __launch_bounds__(32 * RT, WARPS_PER_SM / RT) kernel(const __gri
         }
         eb::cp_async_commit();
     };
-    // Requests the next box of the sequence into slot `slot`; the slot's previous contents have been consumed by every
-    // lane. A box that reaches past the slice or the row brings bytes that are never decoded (zeros past the row).
+    // Requests the next box pair of the sequence into slot `slot`; the slot's previous contents have been consumed by
+    // every lane. The second box is skipped when the slice ends before it; a box that reaches past the slice or the row
+    // brings bytes that are never decoded (zeros past the row).
     uint32_t ask_box = 0, ask_row = first_row, unasked = total;
     auto request = [&](uint32_t slot) {
-        if (lane == 0)
-            eb::tma_load_2d_expect(ring_a + slot * kSlotBytes, &codes, (int)((c_begin + ask_box * kBox) * F::kCodeBytes), (int)ask_row,
-                    bars_a + slot * 8u, kSlotBytes);
+        if (lane == 0) {
+            const uint32_t first = ask_box * slot_chunks;
+            const bool both = pair == 2u && first + kBox < nc;
+            const uint32_t bar = bars_a + slot * 8u, to = ring_a + slot * slot_bytes;
+            eb::tma_load_2d_expect(to, &codes, (int)((c_begin + first) * F::kCodeBytes), (int)ask_row, bar, both ? slot_bytes : kBoxBytes);
+            if (both) eb::tma_load_2d_at(to + kBoxBytes, &codes, (int)((c_begin + first + kBox) * F::kCodeBytes), (int)ask_row, bar);
+        }
         --unasked;
         if (++ask_box == boxes) {
             ask_box = 0;
@@ -181,7 +191,7 @@ __global__ void __launch_bounds__(32 * RT, WARPS_PER_SM / RT) kernel(const __gri
     const uint32_t x_a = smem_a + (g < rows ? g : rows - 1u) * layout.stride_x + q * 16u;
     const uint32_t t0 = 2u * q;
     typename F::State state(smem_a + layout.off_extra, q);
-    static_assert(kBox == 2, "the box loop below decodes two chunks per box");
+    static_assert(kBox == 2 && kMaxPair == 2, "the slot loop below decodes up to four chunks per slot");
     bool complete = true;
     uint32_t slot = 0, parity = 0, row_g = first_row + g;
     for (uint32_t t = 0; t < tiles; ++t) {
@@ -191,11 +201,15 @@ __global__ void __launch_bounds__(32 * RT, WARPS_PER_SM / RT) kernel(const __gri
         const uint32_t scale_g = scales_a + (t & 1u) * scale_bytes + g * layout.stride_scales + F::lane_scale_offset(q);
         for (uint32_t box = 0; box < boxes; ++box) {
             complete = eb::mbar_wait_at(bars_a + slot * 8u, parity) && complete;
-            // Everything a box needs hangs off four shared addresses; the offsets inside are compile-time constants.
-            const uint32_t code_box = ring_a + slot * kSlotBytes + g * kRowBytes;
-            const uint32_t scale_box = scale_g + box * (kBox * F::kScaleBytes), x_box = x_a + box * (kBox * 256u);
-            state.template chunk<0>(code_box, scale_box, scale_box + 8u * layout.stride_scales, x_box, box);
-            if (box * kBox + 1u < nc) state.template chunk<1>(code_box, scale_box, scale_box + 8u * layout.stride_scales, x_box, box);
+            // Everything a slot needs hangs off four shared addresses; the offsets inside are compile-time constants.
+            const uint32_t code_slot = ring_a + slot * slot_bytes + g * kRowBytes;
+            const uint32_t first = box * slot_chunks, left = min(slot_chunks, nc - first);
+            const uint32_t scale_slot = scale_g + first * F::kScaleBytes, x_slot = x_a + first * 256u;
+            const uint32_t scale_slot_h = scale_slot + 8u * layout.stride_scales;
+            state.template chunk<0>(code_slot, scale_slot, scale_slot_h, x_slot, first);
+            if (left > 1u) state.template chunk<1>(code_slot, scale_slot, scale_slot_h, x_slot, first);
+            if (left > 2u) state.template chunk<2>(code_slot, scale_slot, scale_slot_h, x_slot, first);
+            if (left > 3u) state.template chunk<3>(code_slot, scale_slot, scale_slot_h, x_slot, first);
             __syncwarp();
             if (unasked != 0u) request(slot);
             if (++slot == slots) {

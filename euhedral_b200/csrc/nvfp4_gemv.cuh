@@ -83,9 +83,9 @@ struct Format {
         __device__ State(uint32_t, uint32_t q) : lane_codes(q * 16u) {}
         template <int I>
         __device__ __forceinline__ void chunk(uint32_t code_box, uint32_t scale_g, uint32_t scale_h, uint32_t x_box, uint32_t) {
-            constexpr int kRow8 = 8 * (int)(gemv::kBox * kCodeBytes);
-            const uint4 cg = eb::lds_v4<I * 64>(code_box + lane_codes);
-            const uint4 ch = eb::lds_v4<I * 64 + kRow8>(code_box + lane_codes);
+            constexpr int kRow8 = 8 * (int)(gemv::kBox * kCodeBytes), kAt = (I / 2) * 2 * kRow8 + (I % 2) * (int)kCodeBytes;
+            const uint4 cg = eb::lds_v4<kAt>(code_box + lane_codes);
+            const uint4 ch = eb::lds_v4<kAt + kRow8>(code_box + lane_codes);
             const uint32_t sg = scale_pair(eb::lds_u16<I * 8>(scale_g)), sh = scale_pair(eb::lds_u16<I * 8>(scale_h));
             const uint32_t sg_block[2] = {__byte_perm(sg, sg, 0x1010), __byte_perm(sg, sg, 0x3232)};
             const uint32_t sh_block[2] = {__byte_perm(sh, sh, 0x1010), __byte_perm(sh, sh, 0x3232)};

@@ -98,8 +98,9 @@ __device__ __forceinline__ void decode16(uint32_t a32, uint32_t b16, const Masks
 struct Format {
     using Geometry = q3::Geometry;
     static constexpr uint32_t kCodeBytes = 48, kScaleBytes = 4, kErrorBit = 2;
-    // float [chunk][group][8 activation rows]: minus the biased sum of the group's activations.
-    __host__ __device__ static constexpr uint32_t extra_bytes(uint32_t chunks) { return chunks * 64u; }
+    // float [chunk][group][lane q][4]: minus the biased sum of the group's activations of rows 2q and 2q+1, twice over
+    // (x, y, x, y), which is the accumulator quad lane q starts a group with.
+    __host__ __device__ static constexpr uint32_t extra_bytes(uint32_t chunks) { return chunks * 128u; }
     __device__ static uint32_t lane_scale_offset(uint32_t) { return 0; }
 
     // One unit = 16 consecutive activations of one row, (row, chunk, group, quarter): stored in the decode's pairing for
@@ -131,7 +132,10 @@ struct Format {
             // and the lanes past the end of the loop in its last turn are whole quartets too.
             total = __fadd_rn(total, __shfl_xor_sync(__activemask(), total, 1));
             total = __fadd_rn(total, __shfl_xor_sync(__activemask(), total, 2));
-            if (qq == 0u) bias[(c * 2u + grp) * 8u + t] = -total;
+            if (qq == 0u) {
+                float* quad = bias + ((c * 2u + grp) * 4u + (t >> 1)) * 4u + (t & 1u);
+                quad[0] = quad[2] = -total;
+            }
         }
     }
 
@@ -142,33 +146,33 @@ struct Format {
         Masks masks;
         // Lane q's 48 bits of a group start at 32-bit word {0, 1, 3, 4}[q], at bit 16 of it for odd q.
         __device__ State(uint32_t extra, uint32_t q)
-            : bias_lane(extra + q * 8u), word_offset(((q >> 1) * 3u + (q & 1u)) * 4u), shift((q & 1u) * 16u) {}
+            : bias_lane(extra + q * 16u), word_offset(((q >> 1) * 3u + (q & 1u)) * 4u), shift((q & 1u) * 16u) {}
         template <int I>
-        __device__ __forceinline__ void chunk(uint32_t code_box, uint32_t scale_g, uint32_t scale_h, uint32_t x_box, uint32_t box) {
-            constexpr int kRow8 = 8 * (int)(gemv::kBox * kCodeBytes);
+        __device__ __forceinline__ void chunk(uint32_t code_box, uint32_t scale_g, uint32_t scale_h, uint32_t x_box, uint32_t first_chunk) {
+            constexpr int kRow8 = 8 * (int)(gemv::kBox * kCodeBytes), kAt = (I / 2) * 2 * kRow8 + (I % 2) * (int)kCodeBytes;
             const uint32_t scales_g = eb::lds_u32<I * 4>(scale_g), scales_h = eb::lds_u32<I * 4>(scale_h);
             const float2 sg2 = __half22float2(*reinterpret_cast<const __half2*>(&scales_g));
             const float2 sh2 = __half22float2(*reinterpret_cast<const __half2*>(&scales_h));
-            const uint32_t words = code_box + word_offset, bias_box = bias_lane + box * (gemv::kBox * 64u);
+            const uint32_t words = code_box + word_offset, bias_box = bias_lane + first_chunk * 128u;
             uint32_t ga[2], gb[2], ha[2], hb[2];
-            ga[0] = eb::lds_u32<I * 48>(words);
-            gb[0] = eb::lds_u32<I * 48 + 4>(words);
-            ha[0] = eb::lds_u32<I * 48 + kRow8>(words);
-            hb[0] = eb::lds_u32<I * 48 + kRow8 + 4>(words);
-            ga[1] = eb::lds_u32<I * 48 + 24>(words);
-            gb[1] = eb::lds_u32<I * 48 + 28>(words);
-            ha[1] = eb::lds_u32<I * 48 + kRow8 + 24>(words);
-            hb[1] = eb::lds_u32<I * 48 + kRow8 + 28>(words);
+            ga[0] = eb::lds_u32<kAt>(words);
+            gb[0] = eb::lds_u32<kAt + 4>(words);
+            ha[0] = eb::lds_u32<kAt + kRow8>(words);
+            hb[0] = eb::lds_u32<kAt + kRow8 + 4>(words);
+            ga[1] = eb::lds_u32<kAt + 24>(words);
+            gb[1] = eb::lds_u32<kAt + 28>(words);
+            ha[1] = eb::lds_u32<kAt + kRow8 + 24>(words);
+            hb[1] = eb::lds_u32<kAt + kRow8 + 28>(words);
             const uint4 xv[4] = {eb::lds_v4<I * 256>(x_box), eb::lds_v4<I * 256 + 64>(x_box), eb::lds_v4<I * 256 + 128>(x_box),
                     eb::lds_v4<I * 256 + 192>(x_box)};
-            const float2 bias[2] = {eb::lds_f2<I * 64>(bias_box), eb::lds_f2<I * 64 + 32>(bias_box)};
+            const float4 bias[2] = {eb::lds_f4<I * 128>(bias_box), eb::lds_f4<I * 128 + 64>(bias_box)};
 #pragma unroll
             for (int grp = 0; grp < 2; ++grp) {
                 uint32_t wg[8], wh[8];
                 decode16(__funnelshift_r(ga[grp], gb[grp], shift), gb[grp] >> shift, masks, wg);
                 decode16(__funnelshift_r(ha[grp], hb[grp], shift), hb[grp] >> shift, masks, wh);
-                float sum[4] = {bias[grp].x, bias[grp].y, bias[grp].x, bias[grp].y};
-                eb::mma_bf16_16816(sum, wg[0], wh[0], wg[1], wh[1], xv[2 * grp].x, xv[2 * grp].y);
+                float sum[4];
+                eb::mma_bf16_16816_from(sum, wg[0], wh[0], wg[1], wh[1], xv[2 * grp].x, xv[2 * grp].y, bias[grp]);
                 eb::mma_bf16_16816(sum, wg[2], wh[2], wg[3], wh[3], xv[2 * grp].z, xv[2 * grp].w);
                 eb::mma_bf16_16816(sum, wg[4], wh[4], wg[5], wh[5], xv[2 * grp + 1].x, xv[2 * grp + 1].y);
                 eb::mma_bf16_16816(sum, wg[6], wh[6], wg[7], wh[7], xv[2 * grp + 1].z, xv[2 * grp + 1].w);
