@@ -165,3 +165,28 @@ def test_model_shapes(dev, n, k):
         got = O.bf16_to_f32(run(dev, x, blob, n, k)).astype(np.float64)
         expect = OC.nvfp4_linear(x, blob, n, k).astype(np.float64)   # FP32-accumulated reference
         assert max_relative_error(got, expect) <= 2e-3 + 2.0 ** -8
+
+
+# Shapes that take every launch geometry of the decode kernel: tall tensors on the persistent grid (several tiles per warp
+# in turn, a last cluster with a short share, an odd tile count), one K slice (no cluster) on the persistent grid, two K
+# slices, an odd number of chunks per slice, few rows of tiles.
+GRID_SHAPES = [(17424, 5120), (40000, 1024), (3088, 2048), (2000, 1536), (5120, 17408), (48, 4352), (9232, 8192)]  # (N, K)
+
+
+@pytest.mark.parametrize("n,k", GRID_SHAPES)
+def test_launch_geometries(dev, n, k):
+    plan = library.decode_plan("nvfp4", 5, k, n)
+    assert plan["ctas"] % plan["k_slices"] == 0
+    rng = np.random.default_rng(n * 31 + k)
+    weights = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    blob = OC.nvfp4_quantize(weights)
+    for rows in (1, 2, 5, 8):
+        x = random_x(np.random.default_rng(0xB0 + rows), rows, k)
+        got_bits = run(dev, x, blob, n, k)
+        got = O.bf16_to_f32(got_bits).astype(np.float64)
+        expect = OC.nvfp4_linear(x, blob, n, k).astype(np.float64)
+        assert max_relative_error(got, expect) <= 2e-3 + 2.0 ** -8, (rows, n, k)
+        if rows == 5:   # every row of the call is the one-row call, bit for bit
+            for r in (0, 4):
+                assert np.array_equal(run(dev, x[r:r + 1], blob, n, k)[0], got_bits[r])
+
