@@ -167,12 +167,13 @@ int query_clusters(uint32_t shared, uint32_t split) {
     int clusters = 0;
     if (cudaOccupancyMaxActiveClusters(&clusters, gemv::kernel<F, RT, WARPS_PER_SM>, &config) != cudaSuccess) {
         (void)cudaGetLastError();
-        return 0;
+        return -1;   // no answer
     }
-    return clusters;
+    return clusters;   // 0: this CTA shape cannot be launched as a cluster on this device
 }
 
-// Clusters of `split` CTAs of this kernel that the current device holds at once; cached per (device, kernel, shape of the CTA).
+// Clusters of `split` CTAs of this kernel that the current device holds at once (0: none fit); cached per (device,
+// kernel, shape of the CTA).
 // Without a device: three CTAs of eight warps per SM, as far as shared memory allows.
 template <class F>
 uint32_t resident_clusters(uint32_t rt, uint32_t warps_per_sm, uint32_t shared, uint32_t split, int sms) {
@@ -192,14 +193,14 @@ uint32_t resident_clusters(uint32_t rt, uint32_t warps_per_sm, uint32_t shared, 
         for (const Entry& e : cache)
             if (e.device == device && e.error_bit == F::kErrorBit && e.rt == rt && e.warps == warps_per_sm && e.shared == shared && e.split == split)
                 return e.clusters;
-        int found = 0;
+        int found = -1;
         if (warps_per_sm == 24u)
             found = rt == 8 ? query_clusters<F, 8, 24>(shared, split) : rt == 4 ? query_clusters<F, 4, 24>(shared, split)
                     : rt == 2 ? query_clusters<F, 2, 24>(shared, split) : query_clusters<F, 1, 24>(shared, split);
         else
             found = rt == 8 ? query_clusters<F, 8, 16>(shared, split) : rt == 4 ? query_clusters<F, 4, 16>(shared, split)
                     : rt == 2 ? query_clusters<F, 2, 16>(shared, split) : query_clusters<F, 1, 16>(shared, split);
-        if (found > 0) {
+        if (found >= 0) {
             cache.push_back({device, F::kErrorBit, rt, warps_per_sm, shared, split, (uint32_t)found});
             return (uint32_t)found;
         }
@@ -254,8 +255,8 @@ bool plan_decode_uncached(uint32_t rows, uint32_t k, uint32_t n, int sms, Decode
         // A share is at most kSpanCap tiles (the gather buffer grows with it): very tall tensors run several waves.
         const uint32_t most_turns = std::max(1u, kSpanCap / rt);
         uint32_t resident = std::min(groups, resident_clusters<F>(rt, 16u, shared, split, sms));
-        bool fits = true;
-        for (int round = 0; round < 3; ++round) {
+        bool fits = resident != 0u;
+        for (int round = 0; fits && round < 3; ++round) {
             const uint32_t turns = std::min(most_turns, (tiles + rt * resident - 1u) / (rt * resident));
             span = rt * turns;
             shared = std::max(two_per_sm / (8u / rt), gemv::Layout<F>(rt, span, slots, pair, chunks_max, rows, split).bytes);
@@ -266,6 +267,7 @@ bool plan_decode_uncached(uint32_t rows, uint32_t k, uint32_t n, int sms, Decode
             const uint32_t again = std::min(groups, resident_clusters<F>(rt, 16u, shared, split, sms));
             if (again >= resident) break;
             resident = again;
+            fits = resident != 0u;
         }
         if (!fits) continue;
         if ((uint64_t)resident * split * rt < 16ull * (uint64_t)sms * 9u / 10u && !(slots == 2u && pair == 1u)) continue;   // too few warps per SM
