@@ -51,20 +51,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
             : "memory");
     return done != 0;
 }
+// One poll that lets the hardware park the thread until the phase completes or about `kParkNs` have passed, so that a
+// warp waiting for its copy does not spend issue slots on polling.
+constexpr uint32_t kParkNs = 20000;
+constexpr uint32_t kParkLimit = 1u << 17;   // polls before a parked wait gives up (a couple of seconds)
 __device__ __forceinline__ bool mbar_try_wait_at(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
             "{\n.reg .pred p;\n"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
             "selp.u32 %0, 1, 0, p;\n}"
             : "=r"(done)
-            : "r"(bar), "r"(parity)
+            : "r"(bar), "r"(parity), "r"(kParkNs)
             : "memory");
     return done != 0;
 }
 // Bounded wait on a barrier given by its 32-bit shared address.
 __device__ __forceinline__ bool mbar_wait_at(uint32_t bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+    for (uint32_t spin = 0; spin < kParkLimit; ++spin)
         if (mbar_try_wait_at(bar, parity)) return true;
     return false;
 }
@@ -239,6 +243,19 @@ template <int LUT>
 __device__ __forceinline__ uint32_t lop3(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
     asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(d) : "r"(a), "r"(b), "r"(c), "n"(LUT));
+    return d;
+}
+// A value the compiler must treat as unknown and keep in a register: lane constants (addresses, shift counts, masks)
+// that it would otherwise recompute from the thread index inside the inner loop to save a register.
+__device__ __forceinline__ uint32_t pinned(uint32_t v) {
+    asm volatile("mov.b32 %0, %0;" : "+r"(v));
+    return v;
+}
+// The same with the third operand as an immediate (the instruction takes one).
+template <int LUT, uint32_t C>
+__device__ __forceinline__ uint32_t lop3_imm(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(d) : "r"(a), "r"(b), "n"(C), "n"(LUT));
     return d;
 }
 constexpr int kLutAndXor = 0x6A;     // (a & b) ^ c

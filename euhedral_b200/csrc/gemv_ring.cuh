@@ -188,7 +188,8 @@ __global__ void __launch_bounds__(32 * RT, WARPS_PER_SM / RT) kernel(const __gri
     __syncthreads();
     EB_TRACE(3);
 
-    const uint32_t x_a = smem_a + (g < rows ? g : rows - 1u) * layout.stride_x + q * 16u;
+    const uint32_t x_a = eb::pinned(smem_a + (g < rows ? g : rows - 1u) * layout.stride_x + q * 16u);
+    const uint32_t ring_lane = eb::pinned(ring_a + g * kRowBytes), scale_lane = eb::pinned(g * layout.stride_scales + F::lane_scale_offset(q));
     const uint32_t t0 = 2u * q;
     typename F::State state(smem_a + layout.off_extra, q);
     static_assert(kBox == 2 && kMaxPair == 2, "the slot loop below decodes up to four chunks per slot");
@@ -198,11 +199,11 @@ __global__ void __launch_bounds__(32 * RT, WARPS_PER_SM / RT) kernel(const __gri
         eb::cp_async_wait_group<1>();
         __syncwarp();
         state.reset();
-        const uint32_t scale_g = scales_a + (t & 1u) * scale_bytes + g * layout.stride_scales + F::lane_scale_offset(q);
+        const uint32_t scale_g = scales_a + (t & 1u) * scale_bytes + scale_lane;
         for (uint32_t box = 0; box < boxes; ++box) {
             complete = eb::mbar_wait_at(bars_a + slot * 8u, parity) && complete;
             // Everything a slot needs hangs off four shared addresses; the offsets inside are compile-time constants.
-            const uint32_t code_slot = ring_a + slot * slot_bytes + g * kRowBytes;
+            const uint32_t code_slot = ring_lane + slot * slot_bytes;
             const uint32_t first = box * slot_chunks, left = min(slot_chunks, nc - first);
             const uint32_t scale_slot = scale_g + first * F::kScaleBytes, x_slot = x_a + first * 256u;
             const uint32_t scale_slot_h = scale_slot + 8u * layout.stride_scales;

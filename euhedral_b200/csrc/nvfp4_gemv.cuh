@@ -80,7 +80,7 @@ struct Format {
     struct State {
         float even[4], odd[4];
         uint32_t lane_codes;   // byte offset of the lane's 16 code bytes within a chunk
-        __device__ State(uint32_t, uint32_t q) : lane_codes(q * 16u) {}
+        __device__ State(uint32_t, uint32_t q) : lane_codes(eb::pinned(q * 16u)) {}
         template <int I>
         __device__ __forceinline__ void chunk(uint32_t code_box, uint32_t scale_g, uint32_t scale_h, uint32_t x_box, uint32_t) {
             constexpr int kRow8 = 8 * (int)(gemv::kBox * kCodeBytes), kAt = (I / 2) * 2 * kRow8 + (I % 2) * (int)kCodeBytes;

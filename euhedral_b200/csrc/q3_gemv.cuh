@@ -62,17 +62,11 @@ __device__ __forceinline__ uint32_t pair_x(const uint32_t (&s)[8]) {
 // The bias weight of activation e (0..15) of a lane's 16: 132 where its code is decoded plain, 16 + 4 where times 8.
 __host__ __device__ constexpr bool element_times8(int e) { return e == 1 || e == 3 || e == 6 || e == 8 || e == 11 || e == 14; }
 
-// A value the compiler must keep in a register (LOP3 takes one immediate only; masks and magic are both needed).
-__device__ __forceinline__ uint32_t in_register(uint32_t v) {
-    asm volatile("mov.b32 %0, %0;" : "+r"(v));
-    return v;
-}
-
 struct Masks {
     uint32_t field1, magic1, field8, magic8;
     __device__ Masks()
-        : field1(in_register(0x00070007u)), magic1(in_register(0x43044304u)), field8(in_register(0x00380038u)),
-          magic8(in_register(0x43204320u)) {}
+        : field1(eb::pinned(0x00070007u)), magic1(eb::pinned(0x43044304u)), field8(eb::pinned(0x00380038u)),
+          magic8(eb::pinned(0x43204320u)) {}
 };
 
 // Eight BF16x2 registers for the 16 codes of the 48 bits (a32 | b16 << 32), in pair order: 128 + (code ^ 4) for the
@@ -80,10 +74,10 @@ struct Masks {
 __device__ __forceinline__ void decode16(uint32_t a32, uint32_t b16, const Masks& m, uint32_t (&out)[8]) {
     // Codes 0..4 at bits 0,3,..,12 of the low half and codes 5..9 at the same bits of the high half (bits 15 and 31 hold
     // leftovers that the masks below never select).
-    const uint32_t z = eb::lop3<eb::kLutSelect>(a32, a32 << 1, 0x00007FFFu);
+    const uint32_t z = eb::lop3_imm<eb::kLutSelect, 0x00007FFFu>(a32, a32 << 1);
     // Codes 10..15 start at bit 30: bring them to bit 0, then 10..12 low and 13..15 high.
     const uint32_t y = __funnelshift_r(a32, b16, 30);
-    const uint32_t z2 = eb::lop3<eb::kLutSelect>(y, y << 7, 0x000001FFu);
+    const uint32_t z2 = eb::lop3_imm<eb::kLutSelect, 0x000001FFu>(y, y << 7);
     const uint32_t z6 = z >> 6;
     out[0] = eb::lop3<eb::kLutAndXor>(z, m.field1, m.magic1);
     out[1] = eb::lop3<eb::kLutAndXor>(z, m.field8, m.magic8);
@@ -146,7 +140,7 @@ struct Format {
         Masks masks;
         // Lane q's 48 bits of a group start at 32-bit word {0, 1, 3, 4}[q], at bit 16 of it for odd q.
         __device__ State(uint32_t extra, uint32_t q)
-            : bias_lane(extra + q * 16u), word_offset(((q >> 1) * 3u + (q & 1u)) * 4u), shift((q & 1u) * 16u) {}
+            : bias_lane(eb::pinned(extra + q * 16u)), word_offset(eb::pinned(((q >> 1) * 3u + (q & 1u)) * 4u)), shift(eb::pinned((q & 1u) * 16u)) {}
         template <int I>
         __device__ __forceinline__ void chunk(uint32_t code_box, uint32_t scale_g, uint32_t scale_h, uint32_t x_box, uint32_t first_chunk) {
             constexpr int kRow8 = 8 * (int)(gemv::kBox * kCodeBytes), kAt = (I / 2) * 2 * kRow8 + (I % 2) * (int)kCodeBytes;
@@ -172,10 +166,17 @@ struct Format {
                 decode16(__funnelshift_r(ga[grp], gb[grp], shift), gb[grp] >> shift, masks, wg);
                 decode16(__funnelshift_r(ha[grp], hb[grp], shift), hb[grp] >> shift, masks, wh);
                 float sum[4];
+#ifdef EB_X_NOMMA
+                sum[0] = bias[grp].x + __uint_as_float((wg[0] ^ wg[2] ^ wg[4] ^ wg[6]) & xv[2 * grp].x);
+                sum[1] = bias[grp].y + __uint_as_float((wg[1] ^ wg[3] ^ wg[5] ^ wg[7]) & xv[2 * grp].y);
+                sum[2] = bias[grp].z + __uint_as_float((wh[0] ^ wh[2] ^ wh[4] ^ wh[6]) & xv[2 * grp + 1].x);
+                sum[3] = bias[grp].w + __uint_as_float((wh[1] ^ wh[3] ^ wh[5] ^ wh[7]) & xv[2 * grp + 1].y);
+#else
                 eb::mma_bf16_16816_from(sum, wg[0], wh[0], wg[1], wh[1], xv[2 * grp].x, xv[2 * grp].y, bias[grp]);
                 eb::mma_bf16_16816(sum, wg[2], wh[2], wg[3], wh[3], xv[2 * grp].z, xv[2 * grp].w);
                 eb::mma_bf16_16816(sum, wg[4], wh[4], wg[5], wh[5], xv[2 * grp + 1].x, xv[2 * grp + 1].y);
                 eb::mma_bf16_16816(sum, wg[6], wh[6], wg[7], wh[7], xv[2 * grp + 1].z, xv[2 * grp + 1].w);
+#endif
                 const float sg = grp == 0 ? sg2.x : sg2.y, sh = grp == 0 ? sh2.x : sh2.y;
                 acc[0] = fmaf(sum[0], sg, acc[0]);
                 acc[1] = fmaf(sum[1], sg, acc[1]);
