@@ -166,17 +166,10 @@ struct Format {
                 decode16(__funnelshift_r(ga[grp], gb[grp], shift), gb[grp] >> shift, masks, wg);
                 decode16(__funnelshift_r(ha[grp], hb[grp], shift), hb[grp] >> shift, masks, wh);
                 float sum[4];
-#ifdef EB_X_NOMMA
-                sum[0] = bias[grp].x + __uint_as_float((wg[0] ^ wg[2] ^ wg[4] ^ wg[6]) & xv[2 * grp].x);
-                sum[1] = bias[grp].y + __uint_as_float((wg[1] ^ wg[3] ^ wg[5] ^ wg[7]) & xv[2 * grp].y);
-                sum[2] = bias[grp].z + __uint_as_float((wh[0] ^ wh[2] ^ wh[4] ^ wh[6]) & xv[2 * grp + 1].x);
-                sum[3] = bias[grp].w + __uint_as_float((wh[1] ^ wh[3] ^ wh[5] ^ wh[7]) & xv[2 * grp + 1].y);
-#else
                 eb::mma_bf16_16816_from(sum, wg[0], wh[0], wg[1], wh[1], xv[2 * grp].x, xv[2 * grp].y, bias[grp]);
                 eb::mma_bf16_16816(sum, wg[2], wh[2], wg[3], wh[3], xv[2 * grp].z, xv[2 * grp].w);
                 eb::mma_bf16_16816(sum, wg[4], wh[4], wg[5], wh[5], xv[2 * grp + 1].x, xv[2 * grp + 1].y);
                 eb::mma_bf16_16816(sum, wg[6], wh[6], wg[7], wh[7], xv[2 * grp + 1].z, xv[2 * grp + 1].w);
-#endif
                 const float sg = grp == 0 ? sg2.x : sg2.y, sh = grp == 0 ? sh2.x : sh2.y;
                 acc[0] = fmaf(sum[0], sg, acc[0]);
                 acc[1] = fmaf(sum[1], sg, acc[1]);
