@@ -349,8 +349,15 @@ cudaError_t launch_gemv(const DecodePlan& p, const void* x, const void* w, void*
     auto xs = static_cast<const uint16_t*>(x);
     auto ws = static_cast<const uint8_t*>(w);
     auto ys = static_cast<uint16_t*>(y);
+#ifdef EB_X_TRACE
+    static std::atomic<uint32_t> generation{0};
+    const uint32_t trace_generation = generation.fetch_add(1);
+#define EB_LAUNCH_GEMV(RT, WARPS) \
+    launch(gemv::kernel<F, RT, WARPS>, grid, block, p.shared, p.split, map, xs, ws, ys, rows, k, n, p.split, p.span, p.slots, p.pair, error, trace_generation)
+#else
 #define EB_LAUNCH_GEMV(RT, WARPS) \
     launch(gemv::kernel<F, RT, WARPS>, grid, block, p.shared, p.split, map, xs, ws, ys, rows, k, n, p.split, p.span, p.slots, p.pair, error)
+#endif
     if (p.warps_per_sm == 24u) {
         switch (p.rt) {
             case 8: return EB_LAUNCH_GEMV(8, 24);
@@ -815,5 +822,29 @@ int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, u
 extern "C" EUHEDRAL_CUDA_EXPORT int euhedral_b200_debug_trace(void* host, uint64_t bytes) {
     cudaDeviceSynchronize();
     return (int)cudaMemcpyFromSymbol(host, gemv::g_trace, bytes);
+}
+
+// Launch-period probe: a kernel that idles for `ns` nanoseconds, launched `launches` times on the selected stream with
+// the thread's programmatic-dependent-launch flag.
+__global__ void debug_idle_kernel(unsigned ns, int wait_first, unsigned long long* sink) {
+    if (wait_first) eb::pdl_wait();
+    eb::pdl_launch_dependents();
+    if (!wait_first) eb::pdl_wait();
+    const unsigned long long t0 = gemv::now_ns();
+    unsigned long long t = t0;
+    while (t - t0 < ns) t = gemv::now_ns();
+    if (threadIdx.x == 0 && blockIdx.x == 0) sink[0] = t;
+}
+
+extern "C" EUHEDRAL_CUDA_EXPORT int euhedral_b200_debug_idle(uint32_t ctas, uint32_t threads, uint32_t cluster, uint32_t shared,
+        uint32_t ns, int32_t wait_first, uint32_t launches) {
+    DeviceState* state = nullptr;
+    int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    cudaError_t e = allow_big_smem(debug_idle_kernel);
+    for (uint32_t i = 0; i < launches && e == cudaSuccess; ++i)
+        e = launch(debug_idle_kernel, dim3(ctas), dim3(threads), shared, cluster, ns, (int)wait_first,
+                reinterpret_cast<unsigned long long*>(state->static_scratch));
+    return (int)e;
 }
 #endif

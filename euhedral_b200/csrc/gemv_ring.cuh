@@ -44,14 +44,15 @@ namespace gemv {
 // Diagnostic build only (-DEB_X_TRACE): thread 0 of every CTA records the global timer at six points of the kernel and
 // its SM, read back through euhedral_b200_debug_trace. The regular build compiles none of it.
 #ifdef EB_X_TRACE
-__device__ unsigned long long g_trace[8192 * 8];
+__device__ unsigned long long g_trace[4 * 2048 * 8];
+__device__ unsigned g_trace_launch;   // set by the host before every launch of the diagnostic build
 __device__ __forceinline__ unsigned long long now_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-#define EB_TRACE(slot) if (tid == 0 && blockIdx.x < 8192) g_trace[blockIdx.x * 8 + (slot)] = now_ns()
-#define EB_TRACE_SM() if (tid == 0 && blockIdx.x < 8192) { unsigned sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); g_trace[blockIdx.x * 8 + 7] = sm; }
+#define EB_TRACE(slot) if (tid == 0 && blockIdx.x < 2048) g_trace[((trace_generation & 3u) * 2048 + blockIdx.x) * 8 + (slot)] = now_ns()
+#define EB_TRACE_SM() if (tid == 0 && blockIdx.x < 2048) { unsigned sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); g_trace[((trace_generation & 3u) * 2048 + blockIdx.x) * 8 + 7] = sm; }
 #else
 #define EB_TRACE(slot)
 #define EB_TRACE_SM()
@@ -105,7 +106,11 @@ inline bool encode_codes(CUtensorMap* map, const void* weights, uint32_t n, uint
 template <class F, int RT, int WARPS_PER_SM>
 __global__ void __launch_bounds__(32 * RT, WARPS_PER_SM / RT) kernel(const __grid_constant__ CUtensorMap codes, const uint16_t* __restrict__ x,
         const uint8_t* __restrict__ w, uint16_t* __restrict__ y, uint32_t rows, uint32_t k, uint32_t n, uint32_t split, uint32_t span,
-        uint32_t slots, uint32_t pair, uint32_t* __restrict__ error) {
+        uint32_t slots, uint32_t pair, uint32_t* __restrict__ error
+#ifdef EB_X_TRACE
+        , uint32_t trace_generation
+#endif
+        ) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr uint32_t kRb = 16u * RT, kThreads = 32u * RT, kRowBytes = kBox * F::kCodeBytes, kBoxBytes = 16u * kRowBytes;
     const uint32_t slot_bytes = pair * kBoxBytes, slot_chunks = pair * kBox;
@@ -250,7 +255,10 @@ __global__ void __launch_bounds__(32 * RT, WARPS_PER_SM / RT) kernel(const __gri
     eb::cp_async_wait_all();
     if (!complete && lane == 0) atomicOr(error, F::kErrorBit);
     EB_TRACE(4);
-    if (split == 1u) return;
+    if (split == 1u) {
+        EB_TRACE(6);
+        return;
+    }
     // Every rank adds the slices' sums of the tiles it owns, in rank order.
     eb::cluster_sync();
     EB_TRACE(5);
@@ -262,6 +270,7 @@ __global__ void __launch_bounds__(32 * RT, WARPS_PER_SM / RT) kernel(const __gri
         for (uint32_t s = 1; s < split; ++s) sum += from[s * 16u * rows];
         y[(uint64_t)t * n + row0 + (local * split + rank) * 16u + r] = eb::float_to_bf16_bits(finish.apply(sum));
     }
+    EB_TRACE(6);
 }
 
 }  // namespace gemv
