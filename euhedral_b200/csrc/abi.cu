@@ -423,8 +423,40 @@ cudaError_t launch_trellis_mma(const uint64_t* a, uint32_t* error) {
     auto svh = reinterpret_cast<const uint16_t*>(a[3]);
     auto partials = reinterpret_cast<float*>(a[4]);
     auto out = reinterpret_cast<uint16_t*>(a[5]);
-    if (rows <= 8) return launch(trellis::mma_kernel<W, 1>, grid, block, shared, 1u, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
-    return launch(trellis::mma_kernel<W, 4>, grid, block, shared, 1u, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
+    // The payload as [k / 16][n / 16 * W / 4] 8-byte elements; a box is one ring stage of one 128-column block. The calling
+    // thread keeps the last few maps (encoding costs about a microsecond).
+    struct Cached {
+        const void* words;
+        int k, n, w;
+        CUtensorMap map;
+    };
+    constexpr int kCached = 16;
+    thread_local Cached cache[kCached] = {};
+    thread_local int next = 0;
+    const CUtensorMap* map = nullptr;
+    for (int i = 0; i < kCached; ++i)
+        if (cache[i].words == words && cache[i].k == k && cache[i].n == n && cache[i].w == W) map = &cache[i].map;
+    if (map == nullptr) {
+        const eb::EncodeTiled encode = eb::encoder();
+        if (encode == nullptr) return cudaErrorNotSupported;
+        Cached& slot = cache[next];
+        const cuuint64_t dims[2] = {(cuuint64_t)(n / 16) * (W / 4), (cuuint64_t)(k / 16)}, strides[1] = {(cuuint64_t)(n / 16) * W * 2u};
+        const cuuint32_t box[2] = {2u * W, (cuuint32_t)trellis::kStageTiles}, ones[2] = {1u, 1u};
+        if (encode(&slot.map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint16_t*>(words), dims, strides, box, ones,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+                != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+        slot.words = words;
+        slot.k = k;
+        slot.n = n;
+        slot.w = W;
+        map = &slot.map;
+        next = (next + 1) % kCached;
+    }
+    if (rows <= 8)
+        return launch(trellis::mma_kernel<W, 1>, grid, block, shared, 1u, *map, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
+    return launch(trellis::mma_kernel<W, 4>, grid, block, shared, 1u, *map, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
 }
 
 cudaError_t launch_trellis_prepass(const void* x, const void* suh, void* act, int rows, int k, int s, int layout) {

@@ -134,8 +134,8 @@ __device__ __forceinline__ uint32_t window(const uint32_t* u) {
 // FP32 sums of split blockIdx.y go to partials[split][rows][n]. P = groups of 8 activation rows held at once.
 //   grid (n / 128, splits), block 256, dynamic shared kStages * kStageTiles * 8 * W * 2 bytes (+ barriers).
 template <int W, int P>
-__global__ void __launch_bounds__(256) mma_kernel(const uint16_t* __restrict__ act, const uint16_t* __restrict__ words,
-        const int* __restrict__ ends, const uint16_t* __restrict__ svh, float* __restrict__ partials,
+__global__ void __launch_bounds__(256) mma_kernel(const __grid_constant__ CUtensorMap payload_map, const uint16_t* __restrict__ act,
+        const uint16_t* __restrict__ words, const int* __restrict__ ends, const uint16_t* __restrict__ svh, float* __restrict__ partials,
         uint16_t* __restrict__ out, int rows, int k, int n, int splits, int s, uint32_t* __restrict__ error) {
     extern __shared__ __align__(128) uint8_t smem[];
     using Wd = Width<W>;
@@ -145,13 +145,11 @@ __global__ void __launch_bounds__(256) mma_kernel(const uint16_t* __restrict__ a
     __shared__ __align__(8) uint64_t bars[kStages];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q = lane & 3;
     const int column0 = blockIdx.x * 128;
-    const int tiles = k >> 4, tiles_n = n >> 4;
+    const int tiles = k >> 4;
     const int first = (int)(((long long)blockIdx.y * tiles) / splits), last = (int)(((long long)(blockIdx.y + 1) * tiles) / splits);
     const int count = last - first;
     const int stages_total = (count + kStageTiles - 1) / kStageTiles;
-    const uint8_t* payload = reinterpret_cast<const uint8_t*>(words) + (size_t)(column0 >> 4) * W * 2u;
-    const size_t row_stride = (size_t)tiles_n * W * 2u;
-
+    (void)words;   // read through payload_map
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) eb::mbar_init(&bars[i], 1);
         eb::mbar_fence_init();
@@ -161,14 +159,16 @@ __global__ void __launch_bounds__(256) mma_kernel(const uint16_t* __restrict__ a
     // [first + (gst % stages_total) * kStageTiles, ...) in ring buffer gst % kStages: one bulk copy per tile row.
     const int passes = (rows + 8 * P - 1) / (8 * P);
     const int stream_total = passes * stages_total;
+    // One tiled TMA copy per stage: a box of kStageTiles tile rows x this block's 8 tiles (16 W bytes) of the payload seen
+    // as [k / 16 rows][n / 16 * 2 W bytes]. A last stage that reaches past the split brings rows that are never decoded
+    // (zeros past the tensor); the box is always whole, so is the byte count the barrier expects.
     auto request = [&](int gst) {
         const int base = first + (gst % stages_total) * kStageTiles;
-        const int rows_here = min(kStageTiles, last - base);
-        uint64_t* bar = &bars[gst % kStages];
-        uint8_t* dst = smem + (gst % kStages) * kStageBytes;
-        if (lane == 0) eb::mbar_arrive_expect_tx(bar, (uint32_t)rows_here * kTileRowBytes);
-        __syncwarp();
-        if (lane < rows_here) eb::bulk_g2s(dst + lane * kTileRowBytes, payload + (size_t)(base + lane) * row_stride, kTileRowBytes, bar);
+        if (lane == 0) {
+            uint64_t* bar = &bars[gst % kStages];
+            eb::mbar_arrive_expect_tx(bar, kStageBytes);
+            eb::tma_load_2d(smem + (gst % kStages) * kStageBytes, &payload_map, (column0 >> 4) * (W / 4), base, bar);
+        }
     };
     if (warp == 0)
         for (int gst = 0; gst < min(kStages, stream_total); ++gst) request(gst);
