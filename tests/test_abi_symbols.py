@@ -79,3 +79,27 @@ def test_native_scratch_covers_every_region():
         atoms_a = -(-rows // 128) * (k // 64) * 2 * 512
         atoms_b = -(-n // 256) * 2 * (k // 64) * 512
         assert need == layouts.align_up(layouts.align_up(codes + atoms_a, 256) + 4 * rows, 256) + atoms_b
+
+
+def test_decode_plans_cover_every_tile_within_the_shared_memory_limit():
+    """Host arithmetic only: whatever the shape, the clusters' shares cover all 16-row tiles, a CTA count is a whole
+    number of clusters, the K split depends on K alone and the shared-memory request stays launchable."""
+    rng = __import__("numpy").random.default_rng(7)
+    splits = {}
+    shapes = [(16, 128), (48, 4352), (1024, 5120), (5120, 5120), (17408, 5120), (5120, 17408), (151936, 5120), (248320, 2048),
+              (2000, 1536), (9232, 8192), (640, 14336)]
+    shapes += [(16 * int(rng.integers(1, 3000)), 128 * int(rng.integers(1, 200))) for _ in range(40)]
+    for n, k in shapes:
+        for fmt in ("nvfp4", "q3"):
+            for rows in (1, 3, 8):
+                try:
+                    plan = library.decode_plan(fmt, rows, k, n)
+                except ValueError:
+                    continue   # the scalar kernel takes the shape (activation slice too large for shared memory)
+                clusters, rest = divmod(plan["ctas"], plan["k_slices"])
+                assert rest == 0 and clusters >= 1
+                assert clusters * plan["row_tiles"] >= n // 16
+                assert plan["k_slices"] in (1, 2, 4, 8)
+                assert plan["shared_bytes"] <= 200 * 1024
+                assert splits.setdefault(k, plan["k_slices"]) == plan["k_slices"]
+
