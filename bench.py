@@ -285,10 +285,25 @@ def timed(torch, dist, world, steps, warmup, body):
     return seconds
 
 
-def measure_format(torch, dist, gpu, fmt, rows_list, copies, world, rank, sms, steps, warmup, stream, e2e=False, only=None):
+def measure_format(torch, dist, gpu, fmt, rows_list, copies, world, rank, sms, steps, warmup, stream, e2e=False, only=None, graph=False):
+    """graph=True: the step of every weight copy is captured once into a CUDA graph (plain stream capture of the same
+    C-ABI calls) and the timed region replays the graphs - what the launches cost on the device, without the Python
+    launch planning of the trellis operator (three table launches per linear, tens of microseconds of host time)."""
     resident = Resident(torch, gpu, fmt, rows_list, copies, world, rank, sms, only=only)
     with torch.cuda.stream(stream), gpu.submit(stream.cuda_stream, pdl=True):
-        seconds = timed(torch, dist, world, steps, warmup, lambda i: resident.step(i, world))
+        body = lambda i: resident.step(i, world)
+        if graph:
+            for i in range(copies):
+                body(i)   # plans, tensor maps and occupancy look-ups are made before the capture
+            torch.cuda.synchronize()
+            graphs = []
+            for copy in range(copies):
+                captured = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(captured, stream=stream):
+                    resident.step(copy, world)
+                graphs.append(captured)
+            body = lambda i: graphs[i % copies].replay()
+        seconds = timed(torch, dist, world, steps, warmup, body)
         total_bytes = resident.bytes_per_step
         if world > 1:
             t = torch.tensor([float(total_bytes)], device="cuda", dtype=torch.float64)
@@ -375,7 +390,8 @@ def run_ours(args):
     if args.only:
         # One matrix alone (profiling and per-shape numbers): FORMAT:NAME:ROWS, e.g. q3:gate:3
         fmt, name, rows = args.only.split(":")
-        r = measure_format(torch, dist, gpu, fmt, (int(rows),), 4, world, RANK, sms, args.steps, args.warmup, stream, only=name)
+        r = measure_format(torch, dist, gpu, fmt, (int(rows),), 4, world, RANK, sms, args.steps, args.warmup, stream, only=name,
+                           graph=args.graph)
         if RANK == 0:
             print(json.dumps({"only": args.only, "gbs": r["gbs"], "frac_of_hbm_peak": r["gbs"] / (peak * world), "us_per_launch_set": r["ms_per_step"] * 1e3,
                               "bytes": r["bytes_per_step"]}))
@@ -386,9 +402,10 @@ def run_ours(args):
     if True:
         for fmt, rows_list in (("nvfp4", (1, 5)), ("trellis", (1, 5))):
             try:
-                r = measure_format(torch, dist, gpu, fmt, rows_list, copies, world, RANK, sms, max(3, args.steps // 2), 3, stream)
+                replay = fmt == "trellis" and world == 1
+                r = measure_format(torch, dist, gpu, fmt, rows_list, copies, world, RANK, sms, max(3, args.steps // 2), 3, stream, graph=replay)
                 extra[fmt] = {"rows": list(rows_list), "gbs": round(r["gbs"], 1), "frac_of_hbm_peak": round(r["gbs"] / (peak * world), 4),
-                              "ms_per_step": round(r["ms_per_step"], 4)}
+                              "ms_per_step": round(r["ms_per_step"], 4), "launch": "CUDA graph replay" if replay else "eager calls"}
             except Exception as error:   # reported, never hidden
                 extra[fmt] = {"error": repr(error)}
         if world == 1:
@@ -438,6 +455,7 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--detail", action="store_true")
     parser.add_argument("--prefill-only", type=int, default=0, help="time the NVFP4 prefill GEMM over the layer shapes at this many rows")
+    parser.add_argument("--graph", action="store_true", help="with --only: replay the calls from a captured CUDA graph")
     parser.add_argument("--only", default=None, help="FORMAT:NAME:ROWS - time one matrix alone, e.g. q3:gate:3")
     args = parser.parse_args()
     if args.impl == "reference":

@@ -140,11 +140,10 @@ cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shar
 }
 
 // ---- decode GEMV planning ---------------------------------------------------------------------------------------------
-// K slices per row depend on K only (gemv::split_of). A CTA has one warp per 16-row tile in flight: the largest of 8,
-// 4, 2, 1 warps that still gives two CTAs per SM over the whole grid. If a grid of one tile per warp is resident at
-// once with three CTAs per SM (the ring shrinks from 4 to 2 slots to make room), that grid is launched. Otherwise the
-// grid is the number of clusters the device holds at two CTAs per SM and every cluster takes an even share of the tiles
-// (`span` at most), its warps several tiles each in turn.
+// K slices per row depend on K only (gemv::split_of). A CTA has one warp per 16-row tile in flight (8, 4, 2 or 1 warps).
+// If a grid of one tile per warp is resident at once (the ring shrinks to make room), that grid is launched. Otherwise
+// the grid is the number of clusters the device holds at two CTAs per SM and every cluster takes an even share of the
+// tiles (`span` at most), its warps several tiles each in turn.
 constexpr uint32_t kSpanCap = 32;
 
 struct DecodePlan {
@@ -215,31 +214,52 @@ bool plan_decode_uncached(uint32_t rows, uint32_t k, uint32_t n, int sms, Decode
     const uint32_t chunks = k / 128u, split = gemv::split_of(k);
     const uint32_t chunks_max = (chunks + split - 1u) / split;
     const uint32_t tiles = n / 16u;
+    plan->split = split;
+    // Ring shapes from deepest to shallowest: (slots, boxes per slot).
+    const uint32_t shapes[4][2] = {{3u, 2u}, {2u, 2u}, {3u, 1u}, {2u, 1u}};
+    // First choice: one tile per warp with the whole grid resident at once. Widths (warps per CTA) are tried from the one
+    // whose grid spreads most evenly over the SMs - CTAs over (SMs x the CTAs of the fullest SM); 0.85 counts as even
+    // enough, and of two even widths the wider goes first because it stages the activations fewer times. The shared-
+    // memory request is raised so that no SM takes more than its even share of the CTAs, rounded up: the hardware fills
+    // the SMs that free up first, and without the cap some end up with twice the work of others.
+    uint32_t order[4] = {8u, 4u, 2u, 1u}, evenness[4];
+    for (int i = 0; i < 4; ++i) {
+        const uint64_t ctas = (uint64_t)((tiles + order[i] - 1u) / order[i]) * split;
+        const uint64_t fullest = (ctas + (uint64_t)sms - 1u) / (uint64_t)sms;
+        evenness[i] = std::min<uint32_t>(850u, (uint32_t)(ctas * 1000u / (fullest * (uint64_t)sms)));
+        // Once the grid covers every SM, a CTA with little to stream (warps x chunks) pays too much for staging its
+        // activations (measured on the 5120 x 5120 shape: 2 warps x 10 chunks lose to 4 x 10 despite the more even grid).
+        if (order[i] * chunks_max < 32u && ctas >= (uint64_t)sms) evenness[i] = evenness[i] > 200u ? evenness[i] - 200u : 0u;
+    }
+    for (int i = 1; i < 4; ++i)   // stable insertion sort, most even first
+        for (int j = i; j > 0 && evenness[j] > evenness[j - 1]; --j) {
+            std::swap(evenness[j], evenness[j - 1]);
+            std::swap(order[j], order[j - 1]);
+        }
+    for (uint32_t rt : order) {
+        const uint32_t groups = (tiles + rt - 1u) / rt;
+        const uint32_t even_share = (groups * split + (uint32_t)sms - 1u) / (uint32_t)sms;
+        const uint32_t capped = (227u * 1024u) / (even_share + 1u) + 1u;
+        for (const auto& shape : shapes) {
+            const uint32_t needed = gemv::Layout<F>(rt, rt, shape[0], shape[1], chunks_max, rows, split).bytes;
+            const uint32_t shared = std::min<uint32_t>(std::max(needed, capped), (uint32_t)kBigSmem);
+            if (needed <= (uint32_t)kBigSmem && groups <= resident_clusters<F>(rt, 24u, shared, split, sms)) {
+                plan->rt = rt;
+                plan->warps_per_sm = 24;
+                plan->span = rt;
+                plan->slots = shape[0];
+                plan->pair = shape[1];
+                plan->ctas = groups * split;
+                plan->shared = shared;
+                return true;
+            }
+        }
+    }
+    // Otherwise a persistent grid of the widest CTAs that still give two CTAs per SM.
     uint32_t rt = 8;
     while (rt > 1u && (uint64_t)((tiles + rt - 1u) / rt) * split < 2ull * (uint64_t)sms) rt >>= 1;
     plan->rt = rt;
-    plan->split = split;
-    // One tile per warp, everything resident at once.
     const uint32_t groups = (tiles + rt - 1u) / rt;
-    // The shared-memory request is raised so that no SM takes more than its even share of the CTAs, rounded up: the
-    // hardware fills the SMs that free up first, and without the cap some end up with twice the work of others.
-    const uint32_t even_share = (groups * split + (uint32_t)sms - 1u) / (uint32_t)sms;
-    const uint32_t capped = (227u * 1024u) / (even_share + 1u) + 1u;
-    // Ring shapes from deepest to shallowest: (slots, boxes per slot).
-    const uint32_t shapes[4][2] = {{3u, 2u}, {2u, 2u}, {3u, 1u}, {2u, 1u}};
-    for (const auto& shape : shapes) {
-        const uint32_t needed = gemv::Layout<F>(rt, rt, shape[0], shape[1], chunks_max, rows, split).bytes;
-        const uint32_t shared = std::min<uint32_t>(std::max(needed, capped), (uint32_t)kBigSmem);
-        if (needed <= (uint32_t)kBigSmem && groups <= resident_clusters<F>(rt, 24u, shared, split, sms)) {
-            plan->warps_per_sm = 24;
-            plan->span = rt;
-            plan->slots = shape[0];
-            plan->pair = shape[1];
-            plan->ctas = groups * split;
-            plan->shared = shared;
-            return true;
-        }
-    }
     // Even shares over the resident clusters, two CTAs per SM (measured: three CTAs of eight warps, or one of sixteen, are
     // slower - more CTAs pay more staging, wider CTAs wait longer on their slowest warp). The shared-memory request is
     // raised to more than a third of an SM so that the hardware cannot stack three CTAs on one SM and leave another with
