@@ -187,7 +187,7 @@ class Resident:
             cursor += rows * k
         self.packed_in.copy_(self.host_packed_in)
         self.h2d_bytes = 2 * total_in
-        settings = TrellisSettings.for_device(sms)
+        settings = TrellisSettings.for_device(sms) if TRELLIS_TARGET_PER_SM is None else TrellisSettings(target_ctas=TRELLIS_TARGET_PER_SM * sms)
         # Every output slice of a step lives in one packed buffer, so that a multi-GPU step joins them with ONE all-gather.
         unit = 128 if fmt == "trellis" else 16
         total = sum(rows * sharding.shard_range(n, world, rank, unit)[1] for name, n, k in LAYER if only in (None, name) for rows in rows_list)
@@ -367,7 +367,12 @@ def measure_prefill(torch, gpu, stream, steps, warmup, rows=4096, detail=False):
 Q3_TRAFFIC_RATIO = 36.27 / 36.34
 
 
+TRELLIS_TARGET_PER_SM = None   # --trellis-target-per-sm: K-split target blocks per SM (kernels.trellis.target-blocks); None = the operator's default
+
+
 def run_ours(args):
+    global TRELLIS_TARGET_PER_SM
+    TRELLIS_TARGET_PER_SM = args.trellis_target_per_sm
     os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "8")
     import torch
     dist = None
@@ -455,6 +460,7 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--detail", action="store_true")
     parser.add_argument("--prefill-only", type=int, default=0, help="time the NVFP4 prefill GEMM over the layer shapes at this many rows")
+    parser.add_argument("--trellis-target-per-sm", type=int, default=None, help="K-split target blocks per SM of the trellis operator")
     parser.add_argument("--graph", action="store_true", help="with --only: replay the calls from a captured CUDA graph")
     parser.add_argument("--only", default=None, help="FORMAT:NAME:ROWS - time one matrix alone, e.g. q3:gate:3")
     args = parser.parse_args()
