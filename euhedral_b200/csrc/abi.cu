@@ -217,23 +217,21 @@ bool plan_decode_uncached(uint32_t rows, uint32_t k, uint32_t n, int sms, Decode
     plan->split = split;
     // Ring shapes from deepest to shallowest: (slots, boxes per slot).
     const uint32_t shapes[4][2] = {{3u, 2u}, {2u, 2u}, {3u, 1u}, {2u, 1u}};
-    // First choice: one tile per warp with the whole grid resident at once. Widths (warps per CTA) are tried from the one
-    // whose grid spreads most evenly over the SMs - CTAs over (SMs x the CTAs of the fullest SM); 0.85 counts as even
-    // enough, and of two even widths the wider goes first because it stages the activations fewer times. The shared-
-    // memory request is raised so that no SM takes more than its even share of the CTAs, rounded up: the hardware fills
-    // the SMs that free up first, and without the cap some end up with twice the work of others.
-    uint32_t order[4] = {8u, 4u, 2u, 1u}, evenness[4];
+    // First choice: one tile per warp with the whole grid resident at once. Widths (warps per CTA) are tried in the order
+    // of a cost estimate: the fullest SM gets ceil(CTAs / SMs) CTAs, each worth its warps plus about 1.5 warps for
+    // staging its activation slice (fitted to measurements: 5120 x 5120 runs best as 320 CTAs of 4 warps, 5120 x 17408 as
+    // 640 of 4, 1024 x 5120 as 128 of 2). Of equal estimates the wider goes first. The shared-memory request is raised so
+    // that no SM takes more than its even share of the CTAs, rounded up: the hardware fills the SMs that free up first,
+    // and without the cap some end up with twice the work of others.
+    uint32_t order[4] = {8u, 4u, 2u, 1u}, cost[4];
     for (int i = 0; i < 4; ++i) {
         const uint64_t ctas = (uint64_t)((tiles + order[i] - 1u) / order[i]) * split;
         const uint64_t fullest = (ctas + (uint64_t)sms - 1u) / (uint64_t)sms;
-        evenness[i] = std::min<uint32_t>(850u, (uint32_t)(ctas * 1000u / (fullest * (uint64_t)sms)));
-        // Once the grid covers every SM, a CTA with little to stream (warps x chunks) pays too much for staging its
-        // activations (measured on the 5120 x 5120 shape: 2 warps x 10 chunks lose to 4 x 10 despite the more even grid).
-        if (order[i] * chunks_max < 32u && ctas >= (uint64_t)sms) evenness[i] = evenness[i] > 200u ? evenness[i] - 200u : 0u;
+        cost[i] = (uint32_t)std::min<uint64_t>(fullest * (2u * order[i] + 3u), 1u << 30);
     }
-    for (int i = 1; i < 4; ++i)   // stable insertion sort, most even first
-        for (int j = i; j > 0 && evenness[j] > evenness[j - 1]; --j) {
-            std::swap(evenness[j], evenness[j - 1]);
+    for (int i = 1; i < 4; ++i)   // stable insertion sort, cheapest first
+        for (int j = i; j > 0 && cost[j] < cost[j - 1]; --j) {
+            std::swap(cost[j], cost[j - 1]);
             std::swap(order[j], order[j - 1]);
         }
     for (uint32_t rt : order) {
