@@ -11,9 +11,10 @@
 //   * Warp w of RT takes tiles w, w + RT, .. of its CTA and runs its own pipeline over them, one after the other
 //     without draining: a private ring of 2 or 3 shared-memory slots, each slot two boxes of 16 rows x two 128-value
 //     chunks of code bytes, each box fetched by a single tiled TMA copy through a tensor map of the code plane (one
-//     instruction per box, completion of both on the slot's mbarrier). The copy engine moves the code bytes past L1 and the load/store
-//     unit; the warp decodes slot i while slots i+1.. are in flight, and no CTA-wide barrier is taken after the
-//     activations are staged, so the warps of an SM drift apart instead of loading and computing in lock-step.
+//     instruction per box, completion of both on the slot's mbarrier). The copy engine moves the code bytes past L1
+//     and the load/store unit; the warp decodes slot i while slots i+1.. are in flight, and no CTA-wide barrier is
+//     taken after the activations are staged, so the warps of an SM drift apart instead of loading and computing in
+//     lock-step.
 //   * The block scales are too small and too misaligned for TMA (a slice may start at any multiple of 4 bytes): a warp
 //     brings the scales of a whole tile (16 rows x the slice) into a private double buffer with 4- or 8-byte cp.async
 //     copies, one tile ahead of the tile it is decoding.
@@ -45,7 +46,6 @@ namespace gemv {
 // its SM, read back through euhedral_b200_debug_trace. The regular build compiles none of it.
 #ifdef EB_X_TRACE
 __device__ unsigned long long g_trace[4 * 2048 * 8];
-__device__ unsigned g_trace_launch;   // set by the host before every launch of the diagnostic build
 __device__ __forceinline__ unsigned long long now_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
