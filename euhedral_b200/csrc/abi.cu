@@ -50,7 +50,7 @@ int finish(cudaError_t status) {
     return sync == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)sync;
 }
 
-constexpr int kBigSmem = 200 * 1024;
+constexpr int kBigSmem = 227 * 1024;   // the most dynamic shared memory of a CTA on sm_100
 
 template <typename K>
 cudaError_t allow_big_smem(K kernel) {
@@ -65,18 +65,7 @@ cudaError_t allow_trellis_width() {
 }
 
 template <class F>
-cudaError_t allow_gemv() {
-    cudaError_t e = cudaSuccess;
-#define EB_ALLOW_GEMV(RT)                                                               \
-    if (e == cudaSuccess) e = allow_big_smem(gemv::kernel<F, RT, 24>);                  \
-    if (e == cudaSuccess) e = allow_big_smem(gemv::kernel<F, RT, 16>);
-    EB_ALLOW_GEMV(1)
-    EB_ALLOW_GEMV(2)
-    EB_ALLOW_GEMV(4)
-    EB_ALLOW_GEMV(8)
-#undef EB_ALLOW_GEMV
-    return e;
-}
+cudaError_t allow_gemv();
 
 void initialize_device(int device, DeviceState* state) {
     cudaDeviceProp prop;
@@ -112,9 +101,15 @@ int bind(DeviceState** out) {
     return EUHEDRAL_CUDA_SUCCESS;
 }
 
-// One launch on the selected stream, with the cluster dimension and the programmatic-dependent-launch attribute when asked.
+// One launch on the selected stream, with the cluster dimension when asked. The programmatic-dependent-launch
+// attribute goes only to kernels that execute griddepcontrol.wait before their first dependent read (`overlappable`),
+// and only when a stream is selected: a kernel without the wait that carried the attribute could start before the
+// launch in front of it has written its input (the reference registers such kernels one by one,
+// native/src/host/cuda_kernel_loader.c:302-325).
+enum Overlap { kOrdered = 0, kOverlappable = 1 };
+
 template <typename... Params, typename... Args>
-cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared, unsigned cluster, Args... args) {
+cudaError_t launch(Overlap overlap, void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared, unsigned cluster, Args... args) {
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = block;
@@ -129,7 +124,7 @@ cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shar
         attributes[count].val.clusterDim.z = 1;
         ++count;
     }
-    if (t_pdl) {
+    if (t_pdl && overlap == kOverlappable && t_stream != nullptr) {
         attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attributes[count].val.programmaticStreamSerializationAllowed = 1;
         ++count;
@@ -140,45 +135,46 @@ cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shar
 }
 
 // ---- decode GEMV planning ---------------------------------------------------------------------------------------------
-// K slices per row depend on K only (gemv::split_of). A CTA has one warp per 16-row tile in flight (8, 4, 2 or 1 warps).
-// If a grid of one tile per warp is resident at once (the ring shrinks to make room), that grid is launched. Otherwise
-// the grid is the number of clusters the device holds at two CTAs per SM and every cluster takes an even share of the
-// tiles (`span` at most), its warps several tiles each in turn.
-constexpr uint32_t kSpanCap = 32;
-
+// How K is cut (slices, pieces: gemv::order_of) depends on the format and K only and fixes the summation order. What is
+// chosen here changes no bit of the result: warps per CTA (a multiple of the team size), ring depth, CTAs (one per SM,
+// clusters of `split`), and the shared-memory request.
 struct DecodePlan {
-    uint32_t rt, warps_per_sm, span, slots, pair, split, ctas, shared;
+    gemv::Order order;
+    uint32_t warps, depth, ctas, span, shared;
+    bool tma_scales;
 };
 
-template <class F, int RT, int WARPS_PER_SM>
-int query_clusters(uint32_t shared, uint32_t split) {
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(split * 4096u);
-    config.blockDim = dim3(32u * RT);
-    config.dynamicSmemBytes = shared;
-    cudaLaunchAttribute attribute;
-    attribute.id = cudaLaunchAttributeClusterDimension;
-    attribute.val.clusterDim.x = split;
-    attribute.val.clusterDim.y = 1;
-    attribute.val.clusterDim.z = 1;
-    config.attrs = &attribute;
-    config.numAttrs = 1;
-    int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, gemv::kernel<F, RT, WARPS_PER_SM>, &config) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return -1;   // no answer
+template <class F>
+using GemvKernel = void (*)(const gemv::Group, uint32_t*);
+
+template <class F, int P>
+GemvKernel<F> gemv_kernel_from(uint32_t piece, bool tma_scales) {
+    if constexpr (P > (int)F::kMaxPiece) {
+        return nullptr;
+    } else {
+        if (piece == (uint32_t)P) return tma_scales ? gemv::kernel<F, P, true> : gemv::kernel<F, P, false>;
+        return gemv_kernel_from<F, P + 1>(piece, tma_scales);
     }
-    return clusters;   // 0: this CTA shape cannot be launched as a cluster on this device
+}
+template <class F>
+GemvKernel<F> gemv_kernel(uint32_t piece, bool tma_scales) { return gemv_kernel_from<F, 1>(piece, tma_scales); }
+
+template <class F>
+cudaError_t allow_gemv() {
+    cudaError_t e = cudaSuccess;
+    for (uint32_t piece = 1; piece <= F::kMaxPiece && e == cudaSuccess; ++piece)
+        for (int tma = 0; tma < 2 && e == cudaSuccess; ++tma) e = allow_big_smem(gemv_kernel<F>(piece, tma != 0));
+    return e;
 }
 
-// Clusters of `split` CTAs of this kernel that the current device holds at once (0: none fit); cached per (device,
-// kernel, shape of the CTA).
-// Without a device: three CTAs of eight warps per SM, as far as shared memory allows.
+// Clusters of `split` CTAs of this kernel that the current device holds at once (0: none fit), cached per (device, kernel,
+// shape of the CTA). Without a device: one CTA per SM.
 template <class F>
-uint32_t resident_clusters(uint32_t rt, uint32_t warps_per_sm, uint32_t shared, uint32_t split, int sms) {
+uint32_t resident_clusters(GemvKernel<F> kernel, uint32_t warps, uint32_t shared, uint32_t split, int sms) {
     struct Entry {
         int device;
-        uint32_t error_bit, rt, warps, shared, split, clusters;
+        const void* kernel;
+        uint32_t warps, shared, split, clusters;
     };
     static std::mutex mutex;
     static std::vector<Entry> cache;
@@ -190,217 +186,184 @@ uint32_t resident_clusters(uint32_t rt, uint32_t warps_per_sm, uint32_t shared, 
     if (device >= 0) {
         std::lock_guard<std::mutex> lock(mutex);
         for (const Entry& e : cache)
-            if (e.device == device && e.error_bit == F::kErrorBit && e.rt == rt && e.warps == warps_per_sm && e.shared == shared && e.split == split)
-                return e.clusters;
-        int found = -1;
-        if (warps_per_sm == 24u)
-            found = rt == 8 ? query_clusters<F, 8, 24>(shared, split) : rt == 4 ? query_clusters<F, 4, 24>(shared, split)
-                    : rt == 2 ? query_clusters<F, 2, 24>(shared, split) : query_clusters<F, 1, 24>(shared, split);
-        else
-            found = rt == 8 ? query_clusters<F, 8, 16>(shared, split) : rt == 4 ? query_clusters<F, 4, 16>(shared, split)
-                    : rt == 2 ? query_clusters<F, 2, 16>(shared, split) : query_clusters<F, 1, 16>(shared, split);
-        if (found >= 0) {
-            cache.push_back({device, F::kErrorBit, rt, warps_per_sm, shared, split, (uint32_t)found});
-            return (uint32_t)found;
+            if (e.device == device && e.kernel == (const void*)kernel && e.warps == warps && e.shared == shared && e.split == split) return e.clusters;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(split * 1024u);
+        config.blockDim = dim3(32u * warps);
+        config.dynamicSmemBytes = shared;
+        cudaLaunchAttribute attribute;
+        attribute.id = cudaLaunchAttributeClusterDimension;
+        attribute.val.clusterDim.x = split;
+        attribute.val.clusterDim.y = 1;
+        attribute.val.clusterDim.z = 1;
+        config.attrs = &attribute;
+        config.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) == cudaSuccess) {
+            cache.push_back({device, (const void*)kernel, warps, shared, split, (uint32_t)clusters});
+            return (uint32_t)clusters;
         }
+        (void)cudaGetLastError();
     }
-    const uint32_t per_sm = std::min<uint32_t>(warps_per_sm / rt, (227u * 1024u) / (shared + 1024u));
-    return std::max<uint32_t>(1u, (uint32_t)sms * per_sm / split);
+    return (uint32_t)sms / split;
 }
 
+// tiles: 16-row tiles of all tensors of the launch; widest: of the tallest tensor.
 template <class F>
-bool plan_decode_uncached(uint32_t rows, uint32_t k, uint32_t n, int sms, DecodePlan* plan) {
-    if (k == 0 || k % 128u != 0 || n == 0 || n % 16u != 0 || rows == 0 || rows > gemv::kMaxRows) return false;
-    const uint32_t chunks = k / 128u, split = gemv::split_of(k);
-    const uint32_t chunks_max = (chunks + split - 1u) / split;
-    const uint32_t tiles = n / 16u;
-    plan->split = split;
-    // Ring shapes from deepest to shallowest: (slots, boxes per slot).
-    const uint32_t shapes[4][2] = {{3u, 2u}, {2u, 2u}, {3u, 1u}, {2u, 1u}};
-    // First choice: one tile per warp with the whole grid resident at once. Widths (warps per CTA) are tried in the order
-    // of a cost estimate: the fullest SM gets ceil(CTAs / SMs) CTAs, each worth its warps plus about 1.5 warps for
-    // staging its activation slice (fitted to measurements: 5120 x 5120 runs best as 320 CTAs of 4 warps, 5120 x 17408 as
-    // 640 of 4, 1024 x 5120 as 128 of 2). Of equal estimates the wider goes first. The shared-memory request is raised so
-    // that no SM takes more than its even share of the CTAs, rounded up: the hardware fills the SMs that free up first,
-    // and without the cap some end up with twice the work of others.
-    uint32_t order[4] = {8u, 4u, 2u, 1u}, cost[4];
-    for (int i = 0; i < 4; ++i) {
-        const uint64_t ctas = (uint64_t)((tiles + order[i] - 1u) / order[i]) * split;
-        const uint64_t fullest = (ctas + (uint64_t)sms - 1u) / (uint64_t)sms;
-        cost[i] = (uint32_t)std::min<uint64_t>(fullest * (2u * order[i] + 3u), 1u << 30);
-    }
-    for (int i = 1; i < 4; ++i)   // stable insertion sort, cheapest first
-        for (int j = i; j > 0 && cost[j] < cost[j - 1]; --j) {
-            std::swap(cost[j], cost[j - 1]);
-            std::swap(order[j], order[j - 1]);
-        }
-    // A tensor with fewer than four warps of work per SM (the shards of an 8-GPU job) is bound by latency, not by any
-    // SM's throughput: there the narrowest CTAs that still give two per SM - most often one warp each - spread the
-    // loads over the most SMs (8 GPUs: 143 us per step against 161 us with the estimate above).
-    if ((uint64_t)tiles * split < 4ull * (uint64_t)sms) {
-        uint32_t narrow = 8;
-        while (narrow > 1u && (uint64_t)((tiles + narrow - 1u) / narrow) * split < 2ull * (uint64_t)sms) narrow >>= 1;
-        uint32_t at = 0;
-        while (order[at] != narrow) ++at;
-        for (; at > 0; --at) std::swap(order[at], order[at - 1]);
-    }
-    for (uint32_t rt : order) {
-        const uint32_t groups = (tiles + rt - 1u) / rt;
-        const uint32_t even_share = (groups * split + (uint32_t)sms - 1u) / (uint32_t)sms;
-        const uint32_t capped = (227u * 1024u) / (even_share + 1u) + 1u;
-        for (const auto& shape : shapes) {
-            const uint32_t needed = gemv::Layout<F>(rt, rt, shape[0], shape[1], chunks_max, rows, split).bytes;
-            const uint32_t shared = std::min<uint32_t>(std::max(needed, capped), (uint32_t)kBigSmem);
-            if (needed <= (uint32_t)kBigSmem && groups <= resident_clusters<F>(rt, 24u, shared, split, sms)) {
-                plan->rt = rt;
-                plan->warps_per_sm = 24;
-                plan->span = rt;
-                plan->slots = shape[0];
-                plan->pair = shape[1];
-                plan->ctas = groups * split;
-                plan->shared = shared;
-                return true;
+bool plan_decode(uint32_t rows, uint32_t k, uint32_t tiles, uint32_t widest, int sms, DecodePlan* plan) {
+    if (rows == 0 || rows > gemv::kMaxRows || tiles == 0) return false;
+    const gemv::Order order = gemv::order_of<F>(k);
+    if (!order.ok) return false;
+    plan->order = order;
+    plan->tma_scales = typename F::Geometry(16, k).scale_row_bytes % 16u == 0;
+    const GemvKernel<F> kernel = gemv_kernel<F>(order.piece, plan->tma_scales);
+    if (kernel == nullptr) return false;
+    for (uint32_t warps = gemv::kMaxWarps; warps >= order.team; warps >>= 1) {
+        for (uint32_t depth = 3; depth >= 2; --depth) {
+            // The gather buffer grows with a cluster's share of the tallest tensor, which depends on the cluster count,
+            // which can depend on the shared-memory request: settle in two rounds.
+            uint32_t clusters = std::min<uint32_t>(std::max(1u, (uint32_t)sms / order.split), tiles);
+            uint32_t span = 0, shared = 0;
+            bool fits = true;
+            for (int round = 0; round < 2 && fits; ++round) {
+                span = std::min(widest, (tiles + clusters - 1u) / clusters + 1u);
+                shared = gemv::Layout<F>(order, rows, warps, depth, span).bytes;
+                if (shared > (uint32_t)kBigSmem) {
+                    fits = false;
+                    break;
+                }
+                if (order.split == 1u) break;
+                const uint32_t resident = resident_clusters<F>(kernel, warps, shared, order.split, sms);
+                if (resident == 0u) fits = false;
+                const uint32_t now = std::min(resident, tiles);
+                if (now >= clusters) break;
+                clusters = now;
             }
+            if (!fits) continue;
+            plan->warps = warps;
+            plan->depth = depth;
+            plan->ctas = clusters * order.split;
+            plan->span = span;
+            plan->shared = shared;
+            return true;
         }
-    }
-    // Otherwise a persistent grid of the widest CTAs that still give two CTAs per SM.
-    uint32_t rt = 8;
-    while (rt > 1u && (uint64_t)((tiles + rt - 1u) / rt) * split < 2ull * (uint64_t)sms) rt >>= 1;
-    plan->rt = rt;
-    const uint32_t groups = (tiles + rt - 1u) / rt;
-    // Even shares over the resident clusters, two CTAs per SM (measured: three CTAs of eight warps, or one of sixteen, are
-    // slower - more CTAs pay more staging, wider CTAs wait longer on their slowest warp). The shared-memory request is
-    // raised to more than a third of an SM so that the hardware cannot stack three CTAs on one SM and leave another with
-    // one. The ring is the deepest that fits. A larger share needs a larger gather buffer, which can lower the resident
-    // count once.
-    const uint32_t two_per_sm = (227u * 1024u) / 3u + 1024u;
-    for (const auto& shape : shapes) {
-        const uint32_t slots = shape[0], pair = shape[1];
-        uint32_t span = rt, shared = std::max(two_per_sm / (8u / rt), gemv::Layout<F>(rt, span, slots, pair, chunks_max, rows, split).bytes);
-        if (shared > (uint32_t)kBigSmem) continue;
-        // Every warp takes the same number of tiles, `turns`: the fewest that fit the resident clusters. That usually
-        // leaves a few clusters of slack, which a straggler of the previous launch can hold without delaying this one.
-        // A share is at most kSpanCap tiles (the gather buffer grows with it): very tall tensors run several waves.
-        const uint32_t most_turns = std::max(1u, kSpanCap / rt);
-        uint32_t resident = std::min(groups, resident_clusters<F>(rt, 16u, shared, split, sms));
-        bool fits = resident != 0u;
-        for (int round = 0; fits && round < 3; ++round) {
-            const uint32_t turns = std::min(most_turns, (tiles + rt * resident - 1u) / (rt * resident));
-            span = rt * turns;
-            shared = std::max(two_per_sm / (8u / rt), gemv::Layout<F>(rt, span, slots, pair, chunks_max, rows, split).bytes);
-            if (shared > (uint32_t)kBigSmem) {
-                fits = false;
-                break;
-            }
-            const uint32_t again = std::min(groups, resident_clusters<F>(rt, 16u, shared, split, sms));
-            if (again >= resident) break;
-            resident = again;
-            fits = resident != 0u;
-        }
-        if (!fits) continue;
-        if ((uint64_t)resident * split * rt < 16ull * (uint64_t)sms * 9u / 10u && !(slots == 2u && pair == 1u)) continue;   // too few warps per SM
-        plan->warps_per_sm = 16;
-        plan->span = span;
-        plan->slots = slots;
-        plan->pair = pair;
-        plan->ctas = (tiles + span - 1u) / span * split;
-        plan->shared = shared;
-        return true;
+        if (warps == 1u) break;
     }
     return false;
 }
 
-// The calling thread remembers the last plans it made (a plan costs several occupancy look-ups).
+// The tensor maps of the weight tensors the calling thread used last (encoding three maps costs a few microseconds of
+// host time), with whether the weights are plain device memory: tensor maps address device memory only, so anything else
+// (host-mapped, managed) is kept off this path, as the reference keeps such weights off its TMA kernels
+// (core/.../gpu/ExecutionGpu.java:398-402). A map holds only the address and the shape, so a stale entry for a reused
+// address is still the right map.
 template <class F>
-bool plan_decode(uint32_t rows, uint32_t k, uint32_t n, int sms, DecodePlan* plan) {
-    struct Cached {
-        int device;
-        uint32_t rows, k, n;
-        bool ok;
-        DecodePlan plan;
-    };
-    constexpr int kCached = 32;
-    thread_local Cached cache[kCached] = {};
-    thread_local int next = 0;
-    int device = -1;
-    if (cudaGetDevice(&device) != cudaSuccess) {
-        (void)cudaGetLastError();
-        device = -1;
-    }
-    for (int i = 0; i < kCached; ++i) {
-        const Cached& c = cache[i];
-        if (c.k == k && c.n == n && c.rows == rows && c.device == device && c.k != 0) {
-            *plan = c.plan;
-            return c.ok;
-        }
-    }
-    Cached& slot = cache[next];
-    next = (next + 1) % kCached;
-    slot.device = device;
-    slot.rows = rows;
-    slot.k = k;
-    slot.n = n;
-    slot.ok = plan_decode_uncached<F>(rows, k, n, sms, &slot.plan);
-    if (k == 0) return slot.ok;   // never cached: k == 0 marks an empty slot
-    *plan = slot.plan;
-    return slot.ok;
-}
-
-template <class F>
-cudaError_t launch_gemv(const DecodePlan& p, const void* x, const void* w, void* y, uint32_t rows, uint32_t k, uint32_t n,
-        uint32_t* error) {
-    const dim3 grid(p.ctas), block(32u * p.rt);
-    // Encoding a tensor map costs about a microsecond of host time: the calling thread keeps the last few it made. A map
-    // holds only the address and the shape, so a stale entry for a reused address is still the right map.
+const gemv::Tensor* cached_tensor(const void* w, uint32_t n, uint32_t k, const DecodePlan& plan, bool* device_memory) {
     struct Cached {
         const void* weights;
-        uint32_t n, k, format;
-        CUtensorMap map;
+        uint32_t n, k, format, piece;
+        int device;
+        bool tma_scales, device_memory;
+        gemv::Tensor tensor;
     };
-    constexpr int kCached = 32;
-    thread_local Cached cache[kCached] = {};
-    thread_local int next = 0;
-    const CUtensorMap* found = nullptr;
-    for (int i = 0; i < kCached; ++i)
-        if (cache[i].weights == w && cache[i].n == n && cache[i].k == k && cache[i].format == F::kErrorBit) found = &cache[i].map;
-    if (found == nullptr) {
-        Cached& slot = cache[next];
-        if (!gemv::encode_codes<F>(&slot.map, w, n, k)) return cudaErrorNotSupported;
+    constexpr uint32_t kCached = 512;
+    thread_local std::vector<Cached> cache(kCached);
+    int device = 0;
+    (void)cudaGetDevice(&device);
+    Cached& slot = cache[(uint32_t)(((uintptr_t)w >> 8) * 0x9E3779B1u >> 16) % kCached];
+    if (slot.weights != w || slot.n != n || slot.k != k || slot.format != F::kErrorBit || slot.piece != plan.order.piece
+            || slot.tma_scales != plan.tma_scales || slot.device != device) {
+        cudaPointerAttributes attributes;
+        bool plain = cudaPointerGetAttributes(&attributes, w) == cudaSuccess && attributes.type == cudaMemoryTypeDevice;
+        (void)cudaGetLastError();
+        slot.weights = nullptr;
+        if (plain && !gemv::encode_tensor<F>(&slot.tensor, w, n, k, plan.order, plan.tma_scales)) return nullptr;
         slot.weights = w;
         slot.n = n;
         slot.k = k;
         slot.format = F::kErrorBit;
-        found = &slot.map;
-        next = (next + 1) % kCached;
+        slot.piece = plan.order.piece;
+        slot.tma_scales = plan.tma_scales;
+        slot.device = device;
+        slot.device_memory = plain;
     }
-    const CUtensorMap& map = *found;
-    auto xs = static_cast<const uint16_t*>(x);
-    auto ws = static_cast<const uint8_t*>(w);
-    auto ys = static_cast<uint16_t*>(y);
-#ifdef EB_X_TRACE
-    static std::atomic<uint32_t> generation{0};
-    const uint32_t trace_generation = generation.fetch_add(1);
-#define EB_LAUNCH_GEMV(RT, WARPS) \
-    launch(gemv::kernel<F, RT, WARPS>, grid, block, p.shared, p.split, map, xs, ws, ys, rows, k, n, p.split, p.span, p.slots, p.pair, error, trace_generation)
-#else
-#define EB_LAUNCH_GEMV(RT, WARPS) \
-    launch(gemv::kernel<F, RT, WARPS>, grid, block, p.shared, p.split, map, xs, ws, ys, rows, k, n, p.split, p.span, p.slots, p.pair, error)
-#endif
-    if (p.warps_per_sm == 24u) {
-        switch (p.rt) {
-            case 8: return EB_LAUNCH_GEMV(8, 24);
-            case 4: return EB_LAUNCH_GEMV(4, 24);
-            case 2: return EB_LAUNCH_GEMV(2, 24);
-            default: return EB_LAUNCH_GEMV(1, 24);
+    *device_memory = slot.device_memory;
+    return &slot.tensor;
+}
+
+struct DecodeItem {
+    const void* x;
+    const void* w;
+    void* y;
+    uint32_t n;
+};
+
+// One launch over `count` tensors (at most gemv::kMaxGroup) that share K and the row count. cudaErrorNotSupported when a
+// tensor's weights are not plain device memory (the caller takes the scalar kernel).
+template <class F>
+cudaError_t launch_gemv(const DecodeItem* items, uint32_t count, uint32_t rows, uint32_t k, int sms, uint32_t* error) {
+    uint32_t tiles = 0, widest = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        tiles += items[i].n / 16u;
+        widest = std::max(widest, items[i].n / 16u);
+    }
+    DecodePlan plan;
+    if (!plan_decode<F>(rows, k, tiles, widest, sms, &plan)) return cudaErrorInvalidConfiguration;
+    gemv::Group group = {};
+    uint32_t end = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        bool device_memory = false;
+        const gemv::Tensor* maps = cached_tensor<F>(items[i].w, items[i].n, k, plan, &device_memory);
+        if (maps == nullptr) return cudaErrorInvalidValue;
+        if (!device_memory) return cudaErrorNotSupported;
+        gemv::Tensor& t = group.tensor[i];
+        t = *maps;
+        t.x = static_cast<const uint16_t*>(items[i].x);
+        t.w = static_cast<const uint8_t*>(items[i].w);
+        t.y = static_cast<uint16_t*>(items[i].y);
+        t.n = items[i].n;
+        end += items[i].n / 16u;
+        t.tile_end = end;
+    }
+    group.count = count;
+    group.rows = rows;
+    group.k = k;
+    group.tiles = tiles;
+    group.depth = plan.depth;
+    group.span = plan.span;
+    return launch(kOverlappable, gemv_kernel<F>(plan.order.piece, plan.tma_scales), dim3(plan.ctas), dim3(32u * plan.warps), plan.shared,
+            plan.order.split, group, error);
+}
+
+// A decode call of up to 32 rows over `count` tensors: groups of at most 8 rows (every row is independent of the others),
+// halved again while the activations of a group do not fit beside the rings. False: no decode kernel takes the shape.
+template <class F>
+bool decode_takes(uint32_t k, uint32_t n) {
+    return n != 0 && n % 16u == 0 && k != 0 && k % 128u == 0 && gemv::order_of<F>(k).ok;
+}
+
+template <class F>
+cudaError_t run_decode(DecodeItem* items, uint32_t count, uint32_t rows, uint32_t k, int sms, uint32_t* error) {
+    uint32_t tiles = 0, widest = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        tiles += items[i].n / 16u;
+        widest = std::max(widest, items[i].n / 16u);
+    }
+    uint32_t group = std::min<uint32_t>(rows, gemv::kMaxRows);
+    DecodePlan plan;
+    while (group > 1u && !plan_decode<F>(group, k, tiles, widest, sms, &plan)) group = (group + 1u) / 2u;
+    for (uint32_t first = 0; first < rows; first += group) {
+        const uint32_t now = std::min(group, rows - first);
+        DecodeItem shifted[gemv::kMaxGroup];
+        for (uint32_t i = 0; i < count; ++i) {
+            shifted[i] = items[i];
+            shifted[i].x = static_cast<const uint16_t*>(items[i].x) + (uint64_t)first * k;
+            shifted[i].y = static_cast<uint16_t*>(items[i].y) + (uint64_t)first * items[i].n;
         }
+        const cudaError_t e = launch_gemv<F>(shifted, count, now, k, sms, error);
+        if (e != cudaSuccess) return e;
     }
-    switch (p.rt) {
-        case 8: return EB_LAUNCH_GEMV(8, 16);
-        case 4: return EB_LAUNCH_GEMV(4, 16);
-        case 2: return EB_LAUNCH_GEMV(2, 16);
-        default: return EB_LAUNCH_GEMV(1, 16);
-    }
-#undef EB_LAUNCH_GEMV
+    return cudaSuccess;
 }
 
 uint32_t capped_grid(uint64_t count) { return count > 2147483647ull ? 2147483647u : (uint32_t)count; }
@@ -483,17 +446,17 @@ cudaError_t launch_trellis_mma(const uint64_t* a, uint32_t* error) {
         next = (next + 1) % kCached;
     }
     if (rows <= 8)
-        return launch(trellis::mma_kernel<W, 1>, grid, block, shared, 1u, *map, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
-    return launch(trellis::mma_kernel<W, 4>, grid, block, shared, 1u, *map, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
+        return launch(kOverlappable, trellis::mma_kernel<W, 1>, grid, block, shared, 1u, *map, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
+    return launch(kOverlappable, trellis::mma_kernel<W, 4>, grid, block, shared, 1u, *map, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
 }
 
 cudaError_t launch_trellis_prepass(const void* x, const void* suh, void* act, int rows, int k, int s, int layout) {
-    return launch(trellis::prepass_kernel, dim3((unsigned)((k + 511) / 512), (unsigned)rows, (unsigned)s), dim3(128), 0, 1u,
+    return launch(kOverlappable, trellis::prepass_kernel, dim3((unsigned)((k + 511) / 512), (unsigned)rows, (unsigned)s), dim3(128), 0, 1u,
             static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(suh), static_cast<uint16_t*>(act), rows, k, s, layout);
 }
 
 cudaError_t launch_trellis_epilogue(const void* partials, int splits, const void* svh, void* out, int rows, int n) {
-    return launch(trellis::epilogue_kernel, dim3((unsigned)((n + 511) / 512), (unsigned)rows), dim3(128), 0, 1u,
+    return launch(kOverlappable, trellis::epilogue_kernel, dim3((unsigned)((n + 511) / 512), (unsigned)rows), dim3(128), 0, 1u,
             static_cast<const float*>(partials), splits, static_cast<const uint16_t*>(svh), static_cast<uint16_t*>(out), rows, n);
 }
 
@@ -504,6 +467,35 @@ cudaError_t launch_trellis_mma_width(int w, const uint64_t* a, uint32_t* error) 
 #undef EB_CASE
     }
     return cudaErrorInvalidValue;
+}
+
+// Several decode linears that share K and the row count (the q, k and v projections of a layer, or gate and up) as ONE
+// launch per 8 tensors. Every output is bit for bit what the single-tensor entry point gives.
+template <class F>
+int linear_group(uint32_t count, const void* const* inputs, const void* const* weights, void* const* outputs, uint32_t rows,
+        uint32_t in_features, const uint32_t* out_features, const uint64_t* weights_byte_sizes) {
+    if (count == 0 || inputs == nullptr || weights == nullptr || outputs == nullptr || out_features == nullptr || weights_byte_sizes == nullptr
+            || rows == 0 || in_features == 0)
+        return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    for (uint32_t i = 0; i < count; ++i) {
+        if (inputs[i] == nullptr || weights[i] == nullptr || outputs[i] == nullptr || out_features[i] == 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+        if (typename F::Geometry(out_features[i], in_features).size != weights_byte_sizes[i]) return EUHEDRAL_CUDA_FORMAT_MISMATCH;
+        if (((uintptr_t)inputs[i] & 15u) != 0 || ((uintptr_t)weights[i] & 15u) != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+        if (!decode_takes<F>(in_features, out_features[i])) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    }
+    if (rows > 32u || g_exact.load()) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    DeviceState* state = nullptr;
+    const int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    for (uint32_t first = 0; first < count; first += gemv::kMaxGroup) {
+        const uint32_t now = std::min<uint32_t>(gemv::kMaxGroup, count - first);
+        DecodeItem items[gemv::kMaxGroup];
+        for (uint32_t i = 0; i < now; ++i) items[i] = {inputs[first + i], weights[first + i], outputs[first + i], out_features[first + i]};
+        const cudaError_t e = run_decode<F>(items, now, rows, in_features, state->sms, state->error_word);
+        if (e == cudaErrorNotSupported || e == cudaErrorInvalidConfiguration) return first == 0 ? EUHEDRAL_CUDA_ROUTE_UNAVAILABLE : EUHEDRAL_CUDA_KERNEL_UNAVAILABLE;
+        if (e != cudaSuccess) return (int)e;
+    }
+    return finish(cudaSuccess);
 }
 
 }  // namespace
@@ -637,7 +629,7 @@ static int q3_reference(DeviceState* state, const void* input, const void* weigh
     const uint64_t count = (uint64_t)rows * out_features;
     if (count > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
     const q3::Geometry geo(out_features, in_features);
-    return finish(launch(exact::q3_linear, dim3((unsigned)count), dim3(128), 0, 1u, static_cast<const uint16_t*>(input),
+    return finish(launch(kOrdered, exact::q3_linear, dim3((unsigned)count), dim3(128), 0, 1u, static_cast<const uint16_t*>(input),
             static_cast<const uint8_t*>(weights), static_cast<uint16_t*>(output), rows, in_features, out_features,
             (uint64_t)geo.scale_offset));
 }
@@ -657,18 +649,14 @@ int euhedral_cuda_linear_q3_bf16(const void* input, const void* weights, void* o
     DeviceState* state = nullptr;
     status = bind(&state);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
-    DecodePlan plan;
     const bool qualified = rows <= 32u && ((uintptr_t)input & 15u) == 0 && ((uintptr_t)weights & 15u) == 0
-            && plan_decode<q3::Format>(rows < 8u ? rows : 8u, in_features, out_features, state->sms, &plan);
-    if (g_exact.load() || !qualified) return q3_reference(state, input, weights, output, rows, in_features, out_features);
-    for (uint32_t first = 0; first < rows; first += 8u) {
-        const uint32_t group = rows - first < 8u ? rows - first : 8u;
-        plan_decode<q3::Format>(group, in_features, out_features, state->sms, &plan);
-        const cudaError_t e = launch_gemv<q3::Format>(plan, static_cast<const uint16_t*>(input) + (uint64_t)first * in_features, weights,
-                static_cast<uint16_t*>(output) + (uint64_t)first * out_features, group, in_features, out_features, state->error_word);
-        if (e != cudaSuccess) return (int)e;
+            && decode_takes<q3::Format>(in_features, out_features);
+    if (!g_exact.load() && qualified) {
+        DecodeItem item = {input, weights, output, out_features};
+        const cudaError_t e = run_decode<q3::Format>(&item, 1, rows, in_features, state->sms, state->error_word);
+        if (e != cudaErrorNotSupported && e != cudaErrorInvalidConfiguration) return finish(e);
     }
-    return finish(cudaSuccess);
+    return q3_reference(state, input, weights, output, rows, in_features, out_features);
 }
 
 int euhedral_cuda_linear_q3_reference_bf16(const void* input, const void* weights, void* output, uint32_t rows,
@@ -694,21 +682,14 @@ int euhedral_cuda_linear_nvfp4_bf16(const void* input, const void* weights, void
     DeviceState* state = nullptr;
     const int status = bind(&state);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
-    DecodePlan plan;
-    const bool qualified = rows <= 32u && plan_decode<nvfp4::Format>(rows < 8u ? rows : 8u, in_features, out_features, state->sms, &plan);
-    if (g_exact.load() || !qualified) {
-        return finish(launch(exact::nvfp4_linear, dim3(capped_grid((uint64_t)rows * out_features)), dim3(128), 0, 1u,
-                static_cast<const uint16_t*>(input), static_cast<const uint8_t*>(weights), static_cast<uint16_t*>(output), rows,
-                in_features, out_features));
+    if (!g_exact.load() && rows <= 32u && decode_takes<nvfp4::Format>(in_features, out_features)) {
+        DecodeItem item = {input, weights, output, out_features};
+        const cudaError_t e = run_decode<nvfp4::Format>(&item, 1, rows, in_features, state->sms, state->error_word);
+        if (e != cudaErrorNotSupported && e != cudaErrorInvalidConfiguration) return finish(e);
     }
-    for (uint32_t first = 0; first < rows; first += 8u) {
-        const uint32_t group = rows - first < 8u ? rows - first : 8u;
-        plan_decode<nvfp4::Format>(group, in_features, out_features, state->sms, &plan);
-        const cudaError_t e = launch_gemv<nvfp4::Format>(plan, static_cast<const uint16_t*>(input) + (uint64_t)first * in_features, weights,
-                static_cast<uint16_t*>(output) + (uint64_t)first * out_features, group, in_features, out_features, state->error_word);
-        if (e != cudaSuccess) return (int)e;
-    }
-    return finish(cudaSuccess);
+    return finish(launch(kOrdered, exact::nvfp4_linear, dim3(capped_grid((uint64_t)rows * out_features)), dim3(128), 0, 1u,
+            static_cast<const uint16_t*>(input), static_cast<const uint8_t*>(weights), static_cast<uint16_t*>(output), rows,
+            in_features, out_features));
 }
 
 int euhedral_cuda_nvfp4_native_available(void) {
@@ -736,7 +717,7 @@ int euhedral_cuda_linear_nvfp4_native_bf16(const void* input, const void* weight
     if (scratch == nullptr || scratch_byte_size < nvfp4n::ActivationLayout(rows, in_features, out_features).bytes)
         return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     if (((uint64_t)rows + 127u) / 128u * (out_features / 128u) > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
-    return finish(nvfp4n::run(input, weights, output, scratch, rows, in_features, out_features, state->sms, t_stream, t_pdl != 0,
+    return finish(nvfp4n::run(input, weights, output, scratch, rows, in_features, out_features, state->sms, t_stream, t_pdl != 0 && t_stream != nullptr,
             state->error_word));
 }
 
@@ -797,7 +778,7 @@ int euhedral_cuda_linear_launch(int32_t kernel, uint32_t grid_x, uint32_t grid_y
             if (k <= 0 || k % 16 != 0 || n <= 0 || n % 16 != 0 || !trellis_width_valid(w)) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
             const uint64_t tiles = (uint64_t)(k / 16) * (uint64_t)(n / 16);
             if (tiles > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
-            return finish(launch(trellis::decode_bf16_kernel, dim3((unsigned)tiles), dim3(256), 0, 1u,
+            return finish(launch(kOrdered, trellis::decode_bf16_kernel, dim3((unsigned)tiles), dim3(256), 0, 1u,
                     reinterpret_cast<const uint16_t*>(a[0]), reinterpret_cast<uint16_t*>(a[1]), k, n, w));
         }
         case 7: {   // reference(x, words, suh, svh, ends, s, out, rows, k, n, w)
@@ -806,7 +787,7 @@ int euhedral_cuda_linear_launch(int32_t kernel, uint32_t grid_x, uint32_t grid_y
             const uint64_t grid = (uint64_t)rows * (uint64_t)n;
             if (grid > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
             if ((size_t)k * 4u > (size_t)kBigSmem) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
-            return finish(launch(exact::trellis_linear, dim3((unsigned)grid), dim3(128), (size_t)k * 4u, 1u,
+            return finish(launch(kOrdered, exact::trellis_linear, dim3((unsigned)grid), dim3(128), (size_t)k * 4u, 1u,
                     reinterpret_cast<const uint16_t*>(a[0]), reinterpret_cast<const uint16_t*>(a[1]), reinterpret_cast<const uint16_t*>(a[2]),
                     reinterpret_cast<const uint16_t*>(a[3]), reinterpret_cast<const int*>(a[4]), s, reinterpret_cast<uint16_t*>(a[6]), rows, k, n, w));
         }
@@ -859,52 +840,35 @@ int euhedral_b200_linear_trellis_bf16_static(const void* input, const void* word
     return finish(e);
 }
 
-int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t* row_tiles,
-        uint32_t* k_slices, uint32_t* ctas, uint32_t* shared_bytes) {
-    if (row_tiles == nullptr || k_slices == nullptr || ctas == nullptr || shared_bytes == nullptr) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t* k_slices,
+        uint32_t* pieces, uint32_t* piece_chunks, uint32_t* ctas, uint32_t* shared_bytes) {
+    if (k_slices == nullptr || pieces == nullptr || piece_chunks == nullptr || ctas == nullptr || shared_bytes == nullptr)
+        return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     int sms = 148;
     DeviceState* state = nullptr;
     if (bind(&state) == EUHEDRAL_CUDA_SUCCESS) sms = state->sms;
+    if (out_features == 0 || out_features % 16u != 0 || in_features % 128u != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     DecodePlan plan;
-    const bool ok = format == 0 ? plan_decode<nvfp4::Format>(rows, in_features, out_features, sms, &plan)
-                                : plan_decode<q3::Format>(rows, in_features, out_features, sms, &plan);
+    const uint32_t tiles = out_features / 16u;
+    const bool ok = format == 0 ? plan_decode<nvfp4::Format>(rows, in_features, tiles, tiles, sms, &plan)
+                                : plan_decode<q3::Format>(rows, in_features, tiles, tiles, sms, &plan);
     if (!ok) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
-    *row_tiles = plan.span;
-    *k_slices = plan.split;
+    *k_slices = plan.order.split;
+    *pieces = plan.order.team;
+    *piece_chunks = plan.order.piece;
     *ctas = plan.ctas;
     *shared_bytes = plan.shared;
     return EUHEDRAL_CUDA_SUCCESS;
 }
 
+int euhedral_b200_linear_group_q3_bf16(uint32_t count, const void* const* inputs, const void* const* weights, void* const* outputs,
+        uint32_t rows, uint32_t in_features, const uint32_t* out_features, const uint64_t* weights_byte_sizes) {
+    return linear_group<q3::Format>(count, inputs, weights, outputs, rows, in_features, out_features, weights_byte_sizes);
+}
+
+int euhedral_b200_linear_group_nvfp4_bf16(uint32_t count, const void* const* inputs, const void* const* weights, void* const* outputs,
+        uint32_t rows, uint32_t in_features, const uint32_t* out_features, const uint64_t* weights_byte_sizes) {
+    return linear_group<nvfp4::Format>(count, inputs, weights, outputs, rows, in_features, out_features, weights_byte_sizes);
+}
+
 }  // extern "C"
-
-#ifdef EB_X_TRACE
-extern "C" EUHEDRAL_CUDA_EXPORT int euhedral_b200_debug_trace(void* host, uint64_t bytes) {
-    cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(host, gemv::g_trace, bytes);
-}
-
-// Launch-period probe: a kernel that idles for `ns` nanoseconds, launched `launches` times on the selected stream with
-// the thread's programmatic-dependent-launch flag.
-__global__ void debug_idle_kernel(unsigned ns, int wait_first, unsigned long long* sink) {
-    if (wait_first) eb::pdl_wait();
-    eb::pdl_launch_dependents();
-    if (!wait_first) eb::pdl_wait();
-    const unsigned long long t0 = gemv::now_ns();
-    unsigned long long t = t0;
-    while (t - t0 < ns) t = gemv::now_ns();
-    if (threadIdx.x == 0 && blockIdx.x == 0) sink[0] = t;
-}
-
-extern "C" EUHEDRAL_CUDA_EXPORT int euhedral_b200_debug_idle(uint32_t ctas, uint32_t threads, uint32_t cluster, uint32_t shared,
-        uint32_t ns, int32_t wait_first, uint32_t launches) {
-    DeviceState* state = nullptr;
-    int status = bind(&state);
-    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
-    cudaError_t e = allow_big_smem(debug_idle_kernel);
-    for (uint32_t i = 0; i < launches && e == cudaSuccess; ++i)
-        e = launch(debug_idle_kernel, dim3(ctas), dim3(threads), shared, cluster, ns, (int)wait_first,
-                reinterpret_cast<unsigned long long*>(state->static_scratch));
-    return (int)e;
-}
-#endif

@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 namespace eb {
 
 // Every wait in these kernels gives up after this many polls (each poll itself blocks for a bounded time), raises the
@@ -54,7 +56,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // One poll that lets the hardware park the thread until the phase completes or about `kParkNs` have passed, so that a
 // warp waiting for its copy does not spend issue slots on polling.
 constexpr uint32_t kParkNs = 20000;
-constexpr uint32_t kParkLimit = 1u << 17;   // polls before a parked wait gives up (a couple of seconds)
+constexpr uint32_t kParkLimit = 1u << 15;   // polls before a parked wait gives up (well under a second)
 __device__ __forceinline__ bool mbar_try_wait_at(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
@@ -257,6 +259,15 @@ __device__ __forceinline__ uint32_t lop3_imm(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(d) : "r"(a), "r"(b), "n"(C), "n"(LUT));
     return d;
+}
+// f(integral_constant<int, 0>), .., f(integral_constant<int, N - 1>): a loop whose index is a compile-time constant in
+// every turn (shared-memory offsets become immediates).
+template <int N, int I = 0, class Body>
+__device__ __forceinline__ void static_for(Body&& body) {
+    if constexpr (I < N) {
+        body(std::integral_constant<int, I>{});
+        static_for<N, I + 1>(body);
+    }
 }
 constexpr int kLutAndXor = 0x6A;     // (a & b) ^ c
 constexpr int kLutAndOr = 0xEA;      // (a & b) | c

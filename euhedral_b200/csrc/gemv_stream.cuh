@@ -1,0 +1,329 @@
+// The decode GEMV skeleton shared by the NVFP4 and Q3 formats on sm_100a: y[M, N] = x[M, K] . W^T for 1 to 8 BF16
+// activation rows, for ONE weight tensor or for a GROUP of tensors that share K and the row count (the q, k, v
+// projections of a layer, or gate and up), all in one persistent launch. The format (byte geometry, activation staging,
+// register decode) is a policy class.
+//
+// Summation order (a function of the format and K only, so that every row of a multi-row call, every N-shard of a
+// tensor and every member of a group gives bitwise the result of its own one-row, whole-tensor, single call):
+//   * K is cut into S slices (S = 1 up to K = 6144, then 2, 4, 8) and a slice into T pieces of P or P - 1 chunks of 128
+//     values (T a power of two up to 16). A piece's 16 x pc x 128 products are summed by the tensor core in chunk order.
+//   * The T piece sums of a slice are added in piece order, the S slice sums in slice order.
+//
+// Execution:
+//   * One CTA per SM (a cluster of S CTAs when S > 1, rank r staging and streaming slice r only). The 16-row tiles of
+//     all tensors of the group form one list, cut evenly over the CTAs (clusters): a CTA walks a contiguous run of it.
+//   * A CTA's warps form teams of T; team member j owns piece j of every tile its team takes. A warp streams its pieces
+//     through a private ring of 2 or 3 shared-memory slots. A slot is filled by two tiled TMA copies signalled on one
+//     mbarrier: the piece's code bytes (16 rows x pc chunks) through a tensor map of the code plane, and the piece's
+//     block scales through a tensor map of the scale plane whose box is widened to start on a 16-byte boundary (the
+//     lane indexes from the remainder). The ring runs ahead across tiles and across the tensors of the group. Scale
+//     planes whose row pitch is not a multiple of 16 bytes cannot be described to TMA; their scales come by cp.async.
+//   * Weights do not depend on the kernel before this one: the rings are requested before griddepcontrol.wait.
+//   * A piece is decoded straight-line (every shared-memory offset an immediate) into mma.sync.m16n8k16 (BF16, FP32
+//     accumulate), weights as the 16-row operand and the activation rows as the 8 columns, so that each activation row
+//     is computed independently of the others. Lanes whose column is beyond the last activation row read the last row
+//     again; those sums are never used.
+//   * The team meets on a named barrier per tile; 128 of its threads add the T piece sums in order and either round
+//     and store BF16 (S = 1) or hand the slice sum to the tile's owner rank through distributed shared memory; owners
+//     add the S slice sums in rank order after a cluster barrier at the end of each tensor.
+//
+// A policy F provides:
+//   Geometry(n, k)                  byte geometry of the tensor: row_bytes, scale_row_bytes, scale_offset
+//   kCodeBytes, kScaleBytes         bytes per row and chunk of codes / of scales
+//   kScaleBox                       bytes per row of a slot's scale box (a multiple of 16, >= kMaxPiece * kScaleBytes + 12,
+//                                   an odd multiple of 16 so that the rows of a quarter-warp fall in distinct banks)
+//   kPieceChunks, kMaxPiece         preferred and largest chunks per piece
+//   kErrorBit                       bit of the device error word for a wait that gave up
+//   extra_bytes(chunks)             extra shared bytes next to the activation slice
+//   stage(...)                      CTA-wide staging of the activation slice in the decode's pairing
+//   lane_scale_offset(q)            byte offset of lane q's scales within a chunk's scale bytes
+//   State                           accumulators: chunk<I, PC>(codes, scales, x) consumes chunk I of a piece of PC
+//                                   chunks given the lane's shared addresses; result(out); reset()
+//   Finish(w, geo)                  apply(sum) = the value to round to BF16
+#pragma once
+
+#include "common.cuh"
+
+namespace gemv {
+
+constexpr uint32_t kChunk = 128;    // K values per chunk
+constexpr uint32_t kMaxRows = 8;    // activation rows per launch
+constexpr uint32_t kMaxWarps = 16;  // one CTA per SM
+constexpr uint32_t kMaxGroup = 8;   // tensors per launch
+constexpr uint32_t kPartial = 512;  // bytes of one piece's sums: 16 rows x 8 columns of FP32
+
+// How K is cut: fixes the summation order.
+struct Order {
+    uint32_t chunks, split, team, piece;   // chunks of 128, slices, pieces per slice, chunks of the widest piece
+    bool ok;
+};
+
+template <class F>
+__host__ __device__ inline Order order_of(uint32_t k) {
+    Order o;
+    o.chunks = k / kChunk;
+    o.split = o.chunks <= 48u ? 1u : o.chunks <= 96u ? 2u : o.chunks <= 192u ? 4u : 8u;
+    const uint32_t widest = (o.chunks + o.split - 1u) / o.split, narrowest = o.chunks / o.split;
+    o.team = 1u;
+    while (o.team < kMaxWarps && (widest + o.team - 1u) / o.team > F::kPieceChunks && o.team * 2u <= narrowest) o.team *= 2u;
+    o.piece = (widest + o.team - 1u) / o.team;
+    o.ok = k != 0u && k % kChunk == 0u && o.piece <= F::kMaxPiece;
+    return o;
+}
+
+// One tensor of a group.
+struct alignas(64) Tensor {
+    CUtensorMap codes;         // box: 16 rows x `piece` chunks
+    CUtensorMap codes_narrow;  // box: 16 rows x (piece - 1) chunks
+    CUtensorMap scales;        // box: 16 rows x F::kScaleBox bytes
+    const uint16_t* x;
+    const uint8_t* w;
+    uint16_t* y;
+    uint32_t n;
+    uint32_t tile_end;         // end of this tensor's tiles in the group's list
+};
+
+struct alignas(64) Group {
+    Tensor tensor[kMaxGroup];
+    uint32_t count, rows, k, tiles;   // tensors, activation rows, K, 16-row tiles of all tensors together
+    uint32_t depth, span;             // ring slots per warp; the most tiles of one tensor a cluster takes (S > 1)
+};
+
+// Shared memory of one CTA.
+template <class F>
+struct Layout {
+    uint32_t stride_x, off_extra, off_partials, off_gather, off_slots, off_bars, slot_bytes, code_bytes, bytes;
+    __host__ __device__ Layout(const Order& o, uint32_t rows, uint32_t warps, uint32_t depth, uint32_t span) {
+        const uint32_t widest = (o.chunks + o.split - 1u) / o.split;
+        stride_x = widest * 256u + 64u;   // 64 modulo 128: the rows a quarter-warp reads fall in distinct banks
+        off_extra = rows * stride_x;
+        off_partials = (off_extra + F::extra_bytes(widest) + 127u) & ~127u;
+        off_gather = off_partials + warps * 2u * kPartial;
+        const uint32_t owned = o.split > 1u ? (span + o.split - 1u) / o.split + 1u : 0u;
+        off_slots = (off_gather + owned * o.split * kPartial + 127u) & ~127u;
+        code_bytes = 16u * o.piece * F::kCodeBytes;
+        slot_bytes = code_bytes + 16u * F::kScaleBox;
+        off_bars = off_slots + warps * depth * slot_bytes;
+        bytes = off_bars + warps * depth * 8u;
+    }
+};
+
+// The tensor maps of one weight tensor. Codes: 32-bit elements [n rows][row_bytes / 4], boxes of 16 rows x pc chunks.
+// Scales: bytes [n rows][scale_row_bytes], boxes of 16 rows x kScaleBox bytes (only when the pitch is a multiple of 16).
+template <class F>
+inline bool encode_tensor(Tensor* t, const void* weights, uint32_t n, uint32_t k, const Order& o, bool tma_scales) {
+    const eb::EncodeTiled encode = eb::encoder();
+    if (encode == nullptr) return false;
+    const typename F::Geometry geo(n, k);
+    const cuuint32_t ones[2] = {1u, 1u};
+    const cuuint64_t dims[2] = {geo.row_bytes / 4u, n}, strides[1] = {geo.row_bytes};
+    for (int narrow = 0; narrow < 2; ++narrow) {
+        const uint32_t pc = o.piece - (uint32_t)narrow;
+        if (pc == 0u) {
+            t->codes_narrow = t->codes;
+            continue;
+        }
+        const cuuint32_t box[2] = {pc * F::kCodeBytes / 4u, 16u};
+        if (encode(narrow ? &t->codes_narrow : &t->codes, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(weights), dims, strides, box,
+                    ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+                != CUDA_SUCCESS)
+            return false;
+    }
+    if (!tma_scales) {
+        t->scales = t->codes;
+        return true;
+    }
+    const cuuint64_t sdims[2] = {geo.scale_row_bytes, n}, sstrides[1] = {geo.scale_row_bytes};
+    const cuuint32_t sbox[2] = {F::kScaleBox, 16u};
+    return encode(&t->scales, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(static_cast<const uint8_t*>(weights) + geo.scale_offset),
+                   sdims, sstrides, sbox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+            == CUDA_SUCCESS;
+}
+
+__device__ __forceinline__ void team_sync(uint32_t team, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(team + 1u), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void st_shared_f2(uint32_t address, float a, float b) {
+    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(address), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ float ld_shared_f(uint32_t address) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(address) : "memory");
+    return v;
+}
+
+// Decodes one piece of PC chunks from a filled slot into the lane's four sums.
+template <class F, int P, int PC>
+__device__ __forceinline__ void decode_piece(typename F::template State<P>& state, uint32_t codes, uint32_t scales, uint32_t x, float (&acc)[4]) {
+    state.reset();
+    eb::static_for<PC>([&](auto index) {
+        constexpr int I = decltype(index)::value;
+        state.template chunk<I, PC>(codes, scales, x);
+    });
+    state.result(acc);
+}
+
+template <class F, int P, bool kTmaScales>
+__global__ void __launch_bounds__(32 * kMaxWarps, 1) kernel(const __grid_constant__ Group group, uint32_t* __restrict__ error) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, q = lane & 3u;
+    const uint32_t warps = blockDim.x >> 5, threads = blockDim.x;
+    const uint32_t rows = group.rows, depth = group.depth;
+    const Order order = order_of<F>(group.k);
+    const uint32_t split = order.split, team_size = order.team;
+    const uint32_t teams = warps / team_size, team = warp / team_size, member = warp % team_size, team_tid = tid - team * team_size * 32u;
+    const uint32_t rank = split > 1u ? eb::cluster_rank() : 0u;
+    const uint32_t clusters = gridDim.x / split, cluster = blockIdx.x / split;
+    // This cluster's run of the group's tile list.
+    const uint32_t run_begin = (uint32_t)((uint64_t)cluster * group.tiles / clusters), run_end = (uint32_t)((uint64_t)(cluster + 1u) * group.tiles / clusters);
+    // This rank's slice and this warp's piece of it, in chunks.
+    const uint32_t slice_begin = (uint32_t)((uint64_t)rank * order.chunks / split), slice_end = (uint32_t)((uint64_t)(rank + 1u) * order.chunks / split);
+    const uint32_t slice = slice_end - slice_begin;
+    const uint32_t piece_begin = slice_begin + member * slice / team_size, piece_end = slice_begin + (member + 1u) * slice / team_size;
+    const bool wide = piece_end - piece_begin == (uint32_t)P;
+    const Layout<F> layout(order, rows, warps, depth, group.span);
+    const uint32_t smem_a = eb::smem_u32(smem);
+    const uint32_t slots_a = smem_a + layout.off_slots + warp * depth * layout.slot_bytes;
+    const uint32_t bars_a = smem_a + layout.off_bars + warp * depth * 8u;
+
+    if (lane == 0) {
+        for (uint32_t s = 0; s < depth; ++s) eb::mbar_init(reinterpret_cast<uint64_t*>(smem + layout.off_bars) + warp * depth + s, 1);
+        eb::mbar_fence_init();
+    }
+    __syncwarp();
+    if (split > 1u) eb::cluster_arrive();   // every CTA of the cluster has started before its shared memory is written to
+
+    // Where a piece's bytes sit in the planes: the code box starts at the piece; the scale box starts on the 16-byte
+    // boundary at or before the piece's scales.
+    const uint32_t code_x = piece_begin * (F::kCodeBytes / 4u);
+    const uint32_t scale_byte = piece_begin * F::kScaleBytes, scale_x = scale_byte & ~15u;
+    const uint32_t scale_rem = kTmaScales ? scale_byte - scale_x : 0u;
+    const uint32_t fill_bytes = 16u * (wide ? (uint32_t)P : (uint32_t)P - 1u) * F::kCodeBytes + (kTmaScales ? 16u * F::kScaleBox : 0u);
+
+    // The tiles this warp's team takes: run_begin + team, + teams, ... Two cursors walk them: `ask` requests, `use` decodes.
+    uint32_t ask_tile = run_begin + team, ask_tensor = 0, ask_slot = 0;
+    while (ask_tensor + 1u < group.count && ask_tile >= group.tensor[ask_tensor].tile_end) ++ask_tensor;
+    auto request = [&]() {
+        if (ask_tile < run_end) {
+            const Tensor& t = group.tensor[ask_tensor];
+            const uint32_t first_tile = ask_tensor == 0u ? 0u : group.tensor[ask_tensor - 1u].tile_end;
+            const uint32_t row = (ask_tile - first_tile) * 16u;
+            const uint32_t to = slots_a + ask_slot * layout.slot_bytes, bar = bars_a + ask_slot * 8u;
+            if (lane == 0) {
+                eb::tma_load_2d_expect(to, wide ? &t.codes : &t.codes_narrow, (int)code_x, (int)row, bar, fill_bytes);
+                if (kTmaScales) eb::tma_load_2d_at(to + layout.code_bytes, &t.scales, (int)scale_x, (int)row, bar);
+            }
+            if (!kTmaScales) {
+                // lane l copies row l % 16, every other chunk's scales
+                const typename F::Geometry geo(t.n, group.k);
+                const uint8_t* from = t.w + geo.scale_offset + (uint64_t)(row + (lane & 15u)) * geo.scale_row_bytes + (uint64_t)piece_begin * F::kScaleBytes;
+                const uint32_t into = to + layout.code_bytes + (lane & 15u) * F::kScaleBox;
+                for (uint32_t c = lane >> 4; c < piece_end - piece_begin; c += 2u) {
+                    if (F::kScaleBytes == 8u) eb::cp_async_8_to(into + c * 8u, from + c * 8u);
+                    else eb::cp_async_4_to(into + c * 4u, from + c * 4u);
+                }
+            }
+            ask_tile += teams;
+            while (ask_tensor + 1u < group.count && ask_tile >= group.tensor[ask_tensor].tile_end) ++ask_tensor;
+            if (++ask_slot == depth) ask_slot = 0;
+        }
+        if (!kTmaScales) eb::cp_async_commit();
+    };
+    for (uint32_t s = 0; s < depth; ++s) request();
+
+    // The activations may come from the kernel before this one.
+    eb::pdl_launch_dependents();
+    eb::pdl_wait();
+    if (split > 1u) eb::cluster_wait();
+
+    // Lane constants. Lane (g, q) decodes rows g and g + 8 of a tile; its activations are those of row min(g, rows - 1).
+    const uint32_t x_lane = eb::pinned(smem_a + (g < rows ? g : rows - 1u) * layout.stride_x + q * 16u + (piece_begin - slice_begin) * 256u);
+    const uint32_t code_lane = eb::pinned(g * (wide ? (uint32_t)P : (uint32_t)P - 1u) * F::kCodeBytes);
+    const uint32_t scale_lane = eb::pinned(layout.code_bytes + g * F::kScaleBox + scale_rem + F::lane_scale_offset(q));
+    const uint32_t extra_lane = smem_a + layout.off_extra + (piece_begin - slice_begin) * (F::extra_bytes(2) - F::extra_bytes(1));
+    const uint32_t partial_team = smem_a + layout.off_partials + team * team_size * 2u * kPartial;
+    typename F::template State<P> state(extra_lane, q);
+
+    bool complete = true;
+    uint32_t use_tile = run_begin + team, use_slot = 0, parity = 0, buffer = 0;
+    const uint16_t* staged = nullptr;
+    uint32_t first_tile = 0;
+    for (uint32_t ti = 0; ti < group.count; ++ti) {
+        const Tensor& t = group.tensor[ti];
+        const uint32_t segment_begin = max(run_begin, first_tile), segment_end = min(run_end, t.tile_end);
+        if (segment_begin < segment_end) {   // uniform over the cluster
+            if (t.x != staged) {
+                __syncthreads();   // every warp is done with the activations staged before
+                F::stage(smem, smem + layout.off_extra, t.x, rows, group.k, slice_begin, slice, layout.stride_x, tid, threads);
+                staged = t.x;
+                __syncthreads();
+            }
+            const typename F::Finish finish(t.w, typename F::Geometry(t.n, group.k));
+            for (; use_tile < segment_end; use_tile += teams) {
+                if (!kTmaScales) {
+                    if (depth == 2u) eb::cp_async_wait_group<1>();
+                    else eb::cp_async_wait_group<2>();
+                    __syncwarp();
+                }
+                if (complete) complete = eb::mbar_wait_at(bars_a + use_slot * 8u, parity);   // after one wait gave up, no further wait is taken
+                const uint32_t slot = slots_a + use_slot * layout.slot_bytes;
+                float acc[4];
+                if (P == 1 || wide) decode_piece<F, P, P>(state, slot + code_lane, slot + scale_lane, x_lane, acc);
+                else decode_piece<F, P, (P > 1 ? P - 1 : 1)>(state, slot + code_lane, slot + scale_lane, x_lane, acc);
+                // The piece's sums: [row of the tile][activation row], lane (g, q) holds rows g, g + 8 for columns 2q, 2q + 1.
+                const uint32_t mine = partial_team + (buffer * team_size + member) * kPartial + (g * 8u + 2u * q) * 4u;
+                st_shared_f2(mine, acc[0], acc[1]);
+                st_shared_f2(mine + 256u, acc[2], acc[3]);
+                __syncwarp();   // every lane is done with the slot
+                request();
+                if (++use_slot == depth) {
+                    use_slot = 0;
+                    parity ^= 1u;
+                }
+                if (team_size > 1u) team_sync(team, team_size * 32u);
+                // 128 outputs of the tile (16 rows x 8 columns, columns beyond `rows` unused): the piece sums in order.
+                const uint32_t pieces = partial_team + buffer * team_size * kPartial;
+                for (uint32_t e = team_tid; e < 128u; e += team_size * 32u) {
+                    const uint32_t column = e & 7u, row = e >> 3;
+                    if (column < rows) {
+                        float sum = ld_shared_f(pieces + e * 4u);
+                        for (uint32_t j = 1; j < team_size; ++j) sum = __fadd_rn(sum, ld_shared_f(pieces + j * kPartial + e * 4u));
+                        if (split == 1u) {
+                            t.y[(uint64_t)column * t.n + (use_tile - first_tile) * 16u + row] = eb::float_to_bf16_bits(finish.apply(sum));
+                        } else {
+                            // Tile i of the segment is summed by rank i % S: its gather buffer is [i / S][source rank][row][column].
+                            const uint32_t local = use_tile - segment_begin, owner = local % split;
+                            const uint32_t at = eb::map_to_rank(smem_a + layout.off_gather, owner) + ((local / split) * split + rank) * kPartial + e * 4u;
+                            eb::st_cluster_f32(at, sum);
+                        }
+                    }
+                }
+                buffer ^= 1u;
+            }
+            if (split > 1u) {
+                // Every rank adds the slice sums of the tiles it owns, in rank order.
+                eb::cluster_sync();
+                const uint32_t count = segment_end - segment_begin;
+                const uint32_t owned = count > rank ? (count - rank + split - 1u) / split : 0u;
+                for (uint32_t e = tid; e < owned * 128u; e += threads) {
+                    const uint32_t local = e >> 7, rest = e & 127u, column = rest & 7u, row = rest >> 3;
+                    if (column < rows) {
+                        const uint32_t from = smem_a + layout.off_gather + local * split * kPartial + rest * 4u;
+                        float sum = ld_shared_f(from);
+                        for (uint32_t s = 1; s < split; ++s) sum = __fadd_rn(sum, ld_shared_f(from + s * kPartial));
+                        t.y[(uint64_t)column * t.n + (segment_begin - first_tile + local * split + rank) * 16u + row]
+                                = eb::float_to_bf16_bits(finish.apply(sum));
+                    }
+                }
+                eb::cluster_sync();   // the gather buffers are free for the next tensor
+            }
+        }
+        first_tile = t.tile_end;
+    }
+    if (!kTmaScales) eb::cp_async_wait_all();
+    if (!complete && lane == 0) atomicOr(error, F::kErrorBit);
+}
+
+}  // namespace gemv

@@ -1,4 +1,4 @@
-// NVFP4 policy of the decode GEMV (gemv_ring.cuh): W in the converter's row-split NVFP4 layout (E2M1 codes two per
+// NVFP4 policy of the decode GEMV (gemv_stream.cuh): W in the converter's row-split NVFP4 layout (E2M1 codes two per
 // byte, one E4M3 scale per 16 values, one FP32 scale per tensor).
 //
 // Replaces the reference's decode kernels native/src/nvfp4/kernels.cu:8-36 (body native/src/nvfp4/nvfp4.cuh:97-198)
@@ -16,7 +16,7 @@
 // that are added at the end; the 2^16 and the tensor scale multiply the final sum.
 #pragma once
 
-#include "gemv_ring.cuh"
+#include "gemv_stream.cuh"
 
 namespace nvfp4 {
 
@@ -58,6 +58,9 @@ __device__ __forceinline__ uint32_t scale_pair(uint32_t bits) {
 struct Format {
     using Geometry = nvfp4::Geometry;
     static constexpr uint32_t kCodeBytes = 64, kScaleBytes = 8, kErrorBit = 1;
+    // A piece is at most 4 chunks (4 KB of codes per 16 rows): with sixteen warps and a ring of two slots each that leaves
+    // room for the activations of 5 rows at K = 5120. The scale box, 80 bytes per row, is an odd multiple of 16.
+    static constexpr uint32_t kPieceChunks = 3, kMaxPiece = 4, kScaleBox = 80;
     __host__ __device__ static constexpr uint32_t extra_bytes(uint32_t) { return 0; }
     __device__ static uint32_t lane_scale_offset(uint32_t q) { return 2u * q; }
 
@@ -77,21 +80,24 @@ struct Format {
         }
     }
 
+    template <int P>
     struct State {
         float even[4], odd[4];
         uint32_t lane_codes;   // byte offset of the lane's 16 code bytes within a chunk
         __device__ State(uint32_t, uint32_t q) : lane_codes(eb::pinned(q * 16u)) {}
-        template <int I>
-        __device__ __forceinline__ void chunk(uint32_t code_box, uint32_t scale_g, uint32_t scale_h, uint32_t x_box, uint32_t) {
-            constexpr int kRow8 = 8 * (int)(gemv::kBox * kCodeBytes), kAt = (I / 2) * 2 * kRow8 + (I % 2) * (int)kCodeBytes;
-            const uint4 cg = eb::lds_v4<kAt>(code_box + lane_codes);
-            const uint4 ch = eb::lds_v4<kAt + kRow8>(code_box + lane_codes);
-            const uint32_t sg = scale_pair(eb::lds_u16<I * 8>(scale_g)), sh = scale_pair(eb::lds_u16<I * 8>(scale_h));
+        // codes: shared address of row g of the piece's code box (rows are PC chunks wide, row g + 8 eight rows further);
+        // scales: of the lane's two scale bytes of row g and the piece's first chunk (row g + 8: 8 * kScaleBox further);
+        // x: of the lane's activations of the piece's first chunk.
+        template <int I, int PC>
+        __device__ __forceinline__ void chunk(uint32_t codes, uint32_t scales, uint32_t x) {
+            constexpr int kRow8 = 8 * PC * (int)kCodeBytes, kAt = I * (int)kCodeBytes;
+            const uint4 cg = eb::lds_v4<kAt>(codes + lane_codes);
+            const uint4 ch = eb::lds_v4<kAt + kRow8>(codes + lane_codes);
+            const uint32_t sg = scale_pair(eb::lds_u16<I * 8>(scales)), sh = scale_pair(eb::lds_u16<I * 8 + 8 * (int)kScaleBox>(scales));
             const uint32_t sg_block[2] = {__byte_perm(sg, sg, 0x1010), __byte_perm(sg, sg, 0x3232)};
             const uint32_t sh_block[2] = {__byte_perm(sh, sh, 0x1010), __byte_perm(sh, sh, 0x3232)};
             const uint32_t wg[4] = {cg.x, cg.y, cg.z, cg.w}, wh[4] = {ch.x, ch.y, ch.z, ch.w};
-            const uint4 xv[4] = {eb::lds_v4<I * 256>(x_box), eb::lds_v4<I * 256 + 64>(x_box), eb::lds_v4<I * 256 + 128>(x_box),
-                    eb::lds_v4<I * 256 + 192>(x_box)};
+            const uint4 xv[4] = {eb::lds_v4<I * 256>(x), eb::lds_v4<I * 256 + 64>(x), eb::lds_v4<I * 256 + 128>(x), eb::lds_v4<I * 256 + 192>(x)};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const uint32_t fg = sg_block[i >> 1], fh = sh_block[i >> 1];

@@ -1,4 +1,4 @@
-// Q3G64_F16S policy of the decode GEMV (gemv_ring.cuh): W in the converter's row-split layout (groups of 64 three-bit
+// Q3G64_F16S policy of the decode GEMV (gemv_stream.cuh): W in the converter's row-split layout (groups of 64 three-bit
 // codes in 24 bytes, one FP16 scale per group in a second plane).
 //
 // Replaces the reference's contiguous decode kernels native/src/q3/kernels.cu:11-41 (body
@@ -25,7 +25,7 @@
 //     biased sum of the group's activations, computed once per CTA when the activations are staged.
 #pragma once
 
-#include "gemv_ring.cuh"
+#include "gemv_stream.cuh"
 
 namespace q3 {
 
@@ -92,6 +92,9 @@ __device__ __forceinline__ void decode16(uint32_t a32, uint32_t b16, const Masks
 struct Format {
     using Geometry = q3::Geometry;
     static constexpr uint32_t kCodeBytes = 48, kScaleBytes = 4, kErrorBit = 2;
+    // A piece is at most 5 chunks (3.75 KB of codes per 16 rows). The scale box, 48 bytes per row, covers 5 chunks' scales
+    // plus the 12 bytes a piece can start after a 16-byte boundary, and is an odd multiple of 16.
+    static constexpr uint32_t kPieceChunks = 5, kMaxPiece = 5, kScaleBox = 48;
     // float [chunk][group][lane q][4]: minus the biased sum of the group's activations of rows 2q and 2q+1, twice over
     // (x, y, x, y), which is the accumulator quad lane q starts a group with.
     __host__ __device__ static constexpr uint32_t extra_bytes(uint32_t chunks) { return chunks * 128u; }
@@ -133,21 +136,25 @@ struct Format {
         }
     }
 
+    template <int P>
     struct State {
         float acc[4];
-        uint32_t bias_lane;   // shared address of the bias of activation rows 2q, 2q + 1
+        uint32_t bias_lane;   // shared address of the bias of activation rows 2q, 2q + 1 of the piece's first chunk
         uint32_t word_offset, shift;
         Masks masks;
         // Lane q's 48 bits of a group start at 32-bit word {0, 1, 3, 4}[q], at bit 16 of it for odd q.
         __device__ State(uint32_t extra, uint32_t q)
             : bias_lane(eb::pinned(extra + q * 16u)), word_offset(eb::pinned(((q >> 1) * 3u + (q & 1u)) * 4u)), shift(eb::pinned((q & 1u) * 16u)) {}
-        template <int I>
-        __device__ __forceinline__ void chunk(uint32_t code_box, uint32_t scale_g, uint32_t scale_h, uint32_t x_box, uint32_t first_chunk) {
-            constexpr int kRow8 = 8 * (int)(gemv::kBox * kCodeBytes), kAt = (I / 2) * 2 * kRow8 + (I % 2) * (int)kCodeBytes;
-            const uint32_t scales_g = eb::lds_u32<I * 4>(scale_g), scales_h = eb::lds_u32<I * 4>(scale_h);
+        // codes: shared address of row g of the piece's code box (rows are PC chunks wide, row g + 8 eight rows further);
+        // scales: of the two FP16 scales of row g and the piece's first chunk (row g + 8: 8 * kScaleBox further);
+        // x: of the lane's activations of the piece's first chunk.
+        template <int I, int PC>
+        __device__ __forceinline__ void chunk(uint32_t codes, uint32_t scales, uint32_t x) {
+            constexpr int kRow8 = 8 * PC * (int)kCodeBytes, kAt = I * (int)kCodeBytes;
+            const uint32_t scales_g = eb::lds_u32<I * 4>(scales), scales_h = eb::lds_u32<I * 4 + 8 * (int)kScaleBox>(scales);
             const float2 sg2 = __half22float2(*reinterpret_cast<const __half2*>(&scales_g));
             const float2 sh2 = __half22float2(*reinterpret_cast<const __half2*>(&scales_h));
-            const uint32_t words = code_box + word_offset, bias_box = bias_lane + first_chunk * 128u;
+            const uint32_t words = codes + word_offset;
             uint32_t ga[2], gb[2], ha[2], hb[2];
             ga[0] = eb::lds_u32<kAt>(words);
             gb[0] = eb::lds_u32<kAt + 4>(words);
@@ -157,9 +164,8 @@ struct Format {
             gb[1] = eb::lds_u32<kAt + 28>(words);
             ha[1] = eb::lds_u32<kAt + kRow8 + 24>(words);
             hb[1] = eb::lds_u32<kAt + kRow8 + 28>(words);
-            const uint4 xv[4] = {eb::lds_v4<I * 256>(x_box), eb::lds_v4<I * 256 + 64>(x_box), eb::lds_v4<I * 256 + 128>(x_box),
-                    eb::lds_v4<I * 256 + 192>(x_box)};
-            const float4 bias[2] = {eb::lds_f4<I * 128>(bias_box), eb::lds_f4<I * 128 + 64>(bias_box)};
+            const uint4 xv[4] = {eb::lds_v4<I * 256>(x), eb::lds_v4<I * 256 + 64>(x), eb::lds_v4<I * 256 + 128>(x), eb::lds_v4<I * 256 + 192>(x)};
+            const float4 bias[2] = {eb::lds_f4<I * 128>(bias_lane), eb::lds_f4<I * 128 + 64>(bias_lane)};
 #pragma unroll
             for (int grp = 0; grp < 2; ++grp) {
                 uint32_t wg[8], wh[8];

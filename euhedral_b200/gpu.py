@@ -129,6 +129,19 @@ class CudaGpuMemory:
         self._check("Q3 reference linear", self.lib.euhedral_cuda_linear_q3_reference_bf16(
             input, weights, output, rows, in_features, out_features, weight_bytes))
 
+    def linear_group_bf16(self, fmt: str, inputs, weights, outputs, rows: int, in_features: int, out_features, weight_bytes) -> bool:
+        """Several decode linears that share in_features and the row count (q, k, v of a layer; gate and up) as one
+        launch per 8 tensors; `fmt` is 'q3' or 'nvfp4'. No counterpart in the reference, whose host queues one linear
+        per launch. False when the route declined (nothing ran): queue the linears one by one then."""
+        count = len(weights)
+        entry = self.lib.euhedral_b200_linear_group_q3_bf16 if fmt == "q3" else self.lib.euhedral_b200_linear_group_nvfp4_bf16
+        status = entry(count, (C.c_void_p * count)(*inputs), (C.c_void_p * count)(*weights), (C.c_void_p * count)(*outputs), rows,
+                       in_features, (C.c_uint32 * count)(*out_features), (C.c_uint64 * count)(*weight_bytes))
+        if status == library.ROUTE_UNAVAILABLE:
+            return False
+        self._check(f"{fmt} linear group", status)
+        return True
+
     def nvfp4_native_available(self) -> bool:
         return self.lib.euhedral_cuda_nvfp4_native_available() == 1
 

@@ -60,7 +60,11 @@ SIGNATURES = {
     "euhedral_b200_static_scratch_bytes": (_u64, []),
     "euhedral_b200_linear_trellis_bf16_static": (C.c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _u32, _u32, _u32, _u32, _u32, _u32]),
     "euhedral_b200_decode_plan": (C.c_int, [C.c_int, _u32, _u32, _u32, C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32),
-                                            C.POINTER(_u32)]),
+                                            C.POINTER(_u32), C.POINTER(_u32)]),
+    "euhedral_b200_linear_group_q3_bf16": (C.c_int, [_u32, C.POINTER(_ptr), C.POINTER(_ptr), C.POINTER(_ptr), _u32, _u32,
+                                                     C.POINTER(_u32), C.POINTER(_u64)]),
+    "euhedral_b200_linear_group_nvfp4_bf16": (C.c_int, [_u32, C.POINTER(_ptr), C.POINTER(_ptr), C.POINTER(_ptr), _u32, _u32,
+                                                        C.POINTER(_u32), C.POINTER(_u64)]),
 }
 
 _LIB = None
@@ -90,9 +94,11 @@ def load(path: Path | None = None) -> C.CDLL:
 
 
 def decode_plan(fmt: str, rows: int, k: int, n: int) -> dict:
-    """Launch geometry of a decode GEMV (format 'nvfp4' or 'q3'); host arithmetic only, works without a GPU."""
-    out = [_u32() for _ in range(4)]
+    """How a decode GEMV of this shape runs (format 'nvfp4' or 'q3'); host arithmetic only, works without a GPU.
+    k_slices, pieces and piece_chunks fix the summation order and depend on the format and k alone."""
+    out = [_u32() for _ in range(5)]
     status = load().euhedral_b200_decode_plan(0 if fmt == "nvfp4" else 1, rows, k, n, *[C.byref(v) for v in out])
     if status != 0:
         raise ValueError(f"no decode kernel takes rows={rows} k={k} n={n}")
-    return {"row_tiles": out[0].value, "k_slices": out[1].value, "ctas": out[2].value, "shared_bytes": out[3].value}
+    return {"k_slices": out[0].value, "pieces": out[1].value, "piece_chunks": out[2].value, "ctas": out[3].value,
+            "shared_bytes": out[4].value}

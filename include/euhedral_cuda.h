@@ -101,11 +101,26 @@ EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_launch(int32_t kernel, uint32_t gr
 /* Reads and clears the current device's kernel error word: nonzero when a bounded wait inside a kernel gave up
  * (bit 0 NVFP4 GEMV, bit 1 Q3 GEMV, bit 2 trellis GEMM, bit 3 NVFP4 prefill GEMM). Synchronizes the device. */
 EUHEDRAL_CUDA_EXPORT int euhedral_b200_take_device_error(uint32_t* word);
-/* The launch geometry chosen for a decode GEMV of this shape: the most 16-row tiles a CTA takes, K slices per row
- * (cluster size), CTAs and dynamic shared bytes for `rows` activation rows. format: 0 NVFP4, 1 Q3. Returns 0, or -1 for a shape the
- * decode kernels do not take. */
+/* How a decode GEMV of this shape runs. k_slices (cluster size), pieces (warps that share a 16-row tile's slice) and
+ * piece_chunks (128-value chunks of the widest piece) depend on the format and in_features only and fix the summation
+ * order; ctas and shared_bytes are the launch for `rows` activation rows. format: 0 NVFP4, 1 Q3. Returns 0, or -1 for a
+ * shape the decode kernels do not take. */
 EUHEDRAL_CUDA_EXPORT int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, uint32_t out_features,
-        uint32_t* row_tiles, uint32_t* k_slices, uint32_t* ctas, uint32_t* shared_bytes);
+        uint32_t* k_slices, uint32_t* pieces, uint32_t* piece_chunks, uint32_t* ctas, uint32_t* shared_bytes);
+
+/* No counterpart in the reference (its host calls one linear per launch). `count` decode linears that share in_features
+ * and the row count - the q, k and v projections of a layer, or gate and up - as one launch per 8 tensors: the 16-row
+ * tiles of all tensors form one work list over one persistent grid. inputs[i] BF16 [rows][in_features] (the same address
+ * may repeat), weights[i] a whole tensor of out_features[i] rows and weights_byte_sizes[i] bytes, outputs[i] BF16
+ * [rows][out_features[i]]. Every output is bit for bit what the single-tensor entry point writes. 1..32 rows.
+ * Status codes as the single-tensor entry points; ROUTE_UNAVAILABLE (nothing ran) when a shape or exact numerics
+ * needs the scalar kernel or a tensor is not in device memory: call the single-tensor entry point per tensor then. */
+EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_group_q3_bf16(uint32_t count, const void* const* inputs,
+        const void* const* weights, void* const* outputs, uint32_t rows, uint32_t in_features,
+        const uint32_t* out_features, const uint64_t* weights_byte_sizes);
+EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_group_nvfp4_bf16(uint32_t count, const void* const* inputs,
+        const void* const* weights, void* const* outputs, uint32_t rows, uint32_t in_features,
+        const uint32_t* out_features, const uint64_t* weights_byte_sizes);
 
 /* No counterpart in the reference. A whole trellis linear for callers that cannot provide scratch because they cannot
  * allocate device memory at the point of the call: a host that only holds the weight and activation addresses it was

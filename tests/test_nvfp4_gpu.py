@@ -40,7 +40,7 @@ def run(dev, x_bits, blob, n, k, **select):
 def test_decode_matches_float64(dev, k, n):
     rng = np.random.default_rng(k * 31 + n)
     blob, dense = tensor(rng, n, k)
-    for rows in (1, 2, 3, 5, 8):
+    for rows in (1, 2, 3, 4, 5, 8):
         x = random_x(rng, rows, k)
         got = O.bf16_to_f32(run(dev, x, blob, n, k, row_exact=True)).astype(np.float64)
         expect = O.linear_f64(x, dense)
@@ -54,7 +54,7 @@ def test_rows_are_bitwise_the_one_row_call(dev, k, n):
     blob, _ = tensor(rng, n, k)
     x = random_x(rng, 8, k)
     single = np.concatenate([run(dev, x[r:r + 1], blob, n, k, row_exact=True) for r in range(8)])
-    for rows in (2, 5, 8):
+    for rows in (2, 4, 5, 8):
         assert np.array_equal(run(dev, x[:rows], blob, n, k, row_exact=True), single[:rows])
     many = random_x(rng, 27, k)
     grouped = run(dev, many, blob, n, k, row_exact=True)
@@ -155,12 +155,12 @@ def test_row_shards_equal_the_whole(dev):
         assert np.array_equal(np.concatenate(parts, axis=1), whole)
 
 
-@pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408), (1024, 5120)])
+@pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408), (1024, 5120), (5120, 5120)])
 def test_model_shapes(dev, n, k):
     rng = np.random.default_rng(0xE0)
     weights = (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
     blob = OC.nvfp4_quantize(weights)
-    for rows in (1, 5):
+    for rows in (1, 3, 4, 5):
         x = random_x(np.random.default_rng(0xA0 + rows), rows, k)
         got = O.bf16_to_f32(run(dev, x, blob, n, k)).astype(np.float64)
         expect = OC.nvfp4_linear(x, blob, n, k).astype(np.float64)   # FP32-accumulated reference

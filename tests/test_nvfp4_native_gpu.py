@@ -82,6 +82,60 @@ def test_native_matches_float64_over_quantized_operands(dev, rows, k, n):
     assert np.linalg.norm(got - exact) / np.linalg.norm(exact) < 0.03
 
 
+def unpack_rows(raw, rows, k, sample):
+    """unpack_scratch for the rows in `sample` only: (codes [2, len, k], scales [2, len, k/16], globals [len])."""
+    half = k // 2
+    planes = raw[:2 * rows * half].reshape(2, rows, half)[:, sample]
+    codes = np.empty((2, len(sample), k), dtype=np.uint8)
+    codes[:, :, 0::2] = planes & 15
+    codes[:, :, 1::2] = planes >> 4
+    sfa_offset = layouts.align_up(2 * rows * half, 256)
+    row_tiles, k_blocks = -(-rows // 128), k // 64
+    atoms = raw[sfa_offset:sfa_offset + row_tiles * k_blocks * 2 * 512].reshape(row_tiles, k_blocks, 2, 512)
+    scales = np.zeros((2, len(sample), k // 16), dtype=np.uint8)
+    for i, row in enumerate(sample):
+        in_tile = row % 128
+        for t in range(2):
+            for s4 in range(4):
+                scales[t, i, s4::4] = atoms[row // 128, :, t, (in_tile % 32) * 16 + (in_tile // 32) * 4 + s4]
+    global_offset = layouts.align_up(sfa_offset + row_tiles * k_blocks * 2 * 512, 256)
+    g = raw[global_offset:global_offset + 4 * rows].view(np.float32)[sample]
+    return codes, scales, g
+
+
+# Shapes where every persistent CTA walks many output tiles (the accumulator hand-over between tiles, the stage ring
+# running on across tiles, several panels of the tile walk): the layer's gate and down shapes at 4096 tokens, its q shape
+# at 32768 tokens, a token count that is not a multiple of 128, more tiles than SMs with a narrow last panel, and an
+# output width that is an odd multiple of 128.
+@pytest.mark.parametrize("rows,k,n", [(1024, 512, 4352), (256, 512, 1408), (4096, 5120, 17408), (4096, 17408, 5120), (4100, 5120, 5120),
+                                      (32768, 5120, 5120)])
+def test_native_at_model_shapes(dev, rows, k, n):
+    rng = np.random.default_rng(rows + k + n)
+    weights = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    blob = OC.nvfp4_quantize(weights)
+    del weights
+    x = O.bf16_bits(rng.standard_normal((rows, k), dtype=np.float32))
+    y, raw = run(dev, x, blob, n, k)
+    # 64 token rows spread over the whole range (first and last included), every output column
+    sample = np.unique(np.concatenate([[0, rows - 1, rows // 2], rng.integers(0, rows, 61)]))
+    codes, scales, g = unpack_rows(raw, rows, k, sample)
+    ref_codes, ref_scales, ref_g = O.quantize_activations(x[sample], 2)
+    assert np.array_equal(g, ref_g) and np.array_equal(scales, ref_scales)
+    assert np.array_equal(codes & 7, ref_codes & 7) and np.array_equal(codes[(codes & 7) > 0], ref_codes[(codes & 7) > 0])
+    quantized = O.activations_dense(codes, scales, g)
+    got = O.bf16_to_f32(y[sample]).astype(np.float64)
+    expect = np.empty((len(sample), n), dtype=np.float64)
+    dense = OC.nvfp4_dense(blob, n, k)
+    for first in range(0, n, 2048):
+        expect[:, first:first + 2048] = quantized @ dense[first:first + 2048].astype(np.float64).T
+    del dense
+    top = np.max(np.abs(expect))
+    assert np.max(np.abs(got - expect)) <= (2e-3 + 2.0 ** -8) * top
+    assert np.all(np.abs(got - expect) <= np.abs(expect) * 2.0 ** -7 + top * 1e-3)
+    # untouched rows around the sample were written too: no row of the output kept the fill pattern
+    assert not np.any(np.all(y == 0xA5A5, axis=1))
+
+
 def test_native_route_declines(dev):
     lib = dev.gpu.lib
     rows, k, n = 16, 384, 128      # k % 256 != 0

@@ -54,7 +54,7 @@ def close_to(got_bits, expect):
 def test_decode_matches_float64(dev, k, n):
     rng = np.random.default_rng(k * 17 + n)
     blob, dense = random_tensor(rng, n, k)
-    for rows in (1, 2, 3, 5, 8):
+    for rows in (1, 2, 3, 4, 5, 8):
         x = random_x(rng, rows, k)
         assert close_to(run(dev, x, blob, n, k), O.linear_f64(x, dense)), (rows, k, n)
 
@@ -125,12 +125,12 @@ def test_row_shards_equal_the_whole(dev):
         assert np.array_equal(np.concatenate(parts, axis=1), whole)
 
 
-@pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408), (1024, 5120)])
+@pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408), (1024, 5120), (5120, 5120)])
 def test_model_shapes(dev, n, k):
     rng = np.random.default_rng(0xE1)
     weights = (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
     blob = OC.q3_quantize(weights)
-    for rows in (1, 3):
+    for rows in (1, 3, 4, 5):
         x = random_x(np.random.default_rng(0xA0 + rows), rows, k)
         got = O.bf16_to_f32(run(dev, x, blob, n, k)).astype(np.float64)
         expect = OC.q3_linear(x, blob, n, k).astype(np.float64)

@@ -7,6 +7,7 @@ import pytest
 from euhedral_b200 import layouts, sharding
 from euhedral_b200.formats import LinearLaunch, TensorHandle, TrellisFormat, TrellisSettings
 from euhedral_b200.gpu import KernelArguments
+from oracle import oracle_c as OC
 from oracle import oracle_np as O
 from tests.gpu_util import Device, random_x
 
@@ -102,6 +103,24 @@ def test_tensor_core_route_matches_float64(dev, w, target):
         x = random_x(rng, rows, k)
         expect = O.trellis_linear_f64(x, payload, suh, svh, [256, 512])
         assert within_kernel_tolerance(linear.linear(x), expect), (w, target, rows)
+
+
+# The layer's projection shapes (N x K) at the model's stored widths, one and two segments, through the operator's own
+# launch plan for this device (K splits of 20, 20, 9 and 30 at 148 SMs: a split's tile rows are not a multiple of the 16
+# the streaming stage holds, so stages reach past their split), against the plain-C restatement of the reference's
+# linear (native/src/reference/trellis.cuh:14-55) within the reference's kernel tolerance.
+@pytest.mark.parametrize("n,k", [(5120, 5120), (1024, 5120), (17408, 5120), (5120, 17408)])
+@pytest.mark.parametrize("w", [40, 48, 56, 64])
+def test_layer_shapes(dev, n, k, w):
+    rng = np.random.default_rng(n + k + w)
+    segments = 1 + (w // 8) % 2                       # 40, 56: two segments; 48, 64: one
+    ends = [n] if segments == 1 else [n // 2, n]
+    payload, suh, svh = random_object(rng, k, n, w, segments=segments)
+    linear = DeviceLinear(dev, payload, suh, svh, ends, 8 * dev.gpu.multiprocessor_count())
+    for rows in (1, 5):
+        x = random_x(rng, rows, k)
+        expect = OC.trellis_linear(x, payload, suh, svh, ends).astype(np.float64)
+        assert within_kernel_tolerance(linear.linear(x), expect), (n, k, w, rows)
 
 
 def test_golden_linear_fixture(dev, golden):
