@@ -50,7 +50,8 @@ int finish(cudaError_t status) {
     return sync == cudaSuccess ? EUHEDRAL_CUDA_SUCCESS : (int)sync;
 }
 
-constexpr int kBigSmem = 227 * 1024;   // the most dynamic shared memory of a CTA on sm_100
+constexpr int kBigSmem = 200 * 1024;    // kernels that also hold static shared memory
+constexpr int kGemvSmem = 227 * 1024;   // the most dynamic shared memory of a CTA on sm_100 (the decode GEMV holds no static bytes)
 
 template <typename K>
 cudaError_t allow_big_smem(K kernel) {
@@ -136,7 +137,7 @@ cudaError_t launch(Overlap overlap, void (*kernel)(Params...), dim3 grid, dim3 b
 
 // ---- decode GEMV planning ---------------------------------------------------------------------------------------------
 // How K is cut (slices, pieces: gemv::order_of) depends on the format and K only and fixes the summation order. What is
-// chosen here changes no bit of the result: warps per CTA (a multiple of the team size), ring depth, CTAs (one per SM,
+// chosen here changes no bit of the result: decoding warps per CTA (a multiple of the team size), ring depth, CTAs (one per SM,
 // clusters of `split`), and the shared-memory request.
 struct DecodePlan {
     gemv::Order order;
@@ -163,7 +164,7 @@ template <class F>
 cudaError_t allow_gemv() {
     cudaError_t e = cudaSuccess;
     for (uint32_t piece = 1; piece <= F::kMaxPiece && e == cudaSuccess; ++piece)
-        for (int tma = 0; tma < 2 && e == cudaSuccess; ++tma) e = allow_big_smem(gemv_kernel<F>(piece, tma != 0));
+        for (int tma = 0; tma < 2 && e == cudaSuccess; ++tma) e = cudaFuncSetAttribute(gemv_kernel<F>(piece, tma != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmem);
     return e;
 }
 
@@ -189,7 +190,7 @@ uint32_t resident_clusters(GemvKernel<F> kernel, uint32_t warps, uint32_t shared
             if (e.device == device && e.kernel == (const void*)kernel && e.warps == warps && e.shared == shared && e.split == split) return e.clusters;
         cudaLaunchConfig_t config = {};
         config.gridDim = dim3(split * 1024u);
-        config.blockDim = dim3(32u * warps);
+        config.blockDim = dim3(32u * (warps + (F::kAddingWarp ? 1u : 0u)));   // the decoding warps and the adding warp
         config.dynamicSmemBytes = shared;
         cudaLaunchAttribute attribute;
         attribute.id = cudaLaunchAttributeClusterDimension;
@@ -228,7 +229,7 @@ bool plan_decode(uint32_t rows, uint32_t k, uint32_t tiles, uint32_t widest, int
             for (int round = 0; round < 2 && fits; ++round) {
                 span = std::min(widest, (tiles + clusters - 1u) / clusters + 1u);
                 shared = gemv::Layout<F>(order, rows, warps, depth, span).bytes;
-                if (shared > (uint32_t)kBigSmem) {
+                if (shared > (uint32_t)kGemvSmem) {
                     fits = false;
                     break;
                 }
@@ -331,7 +332,7 @@ cudaError_t launch_gemv(const DecodeItem* items, uint32_t count, uint32_t rows, 
     group.tiles = tiles;
     group.depth = plan.depth;
     group.span = plan.span;
-    return launch(kOverlappable, gemv_kernel<F>(plan.order.piece, plan.tma_scales), dim3(plan.ctas), dim3(32u * plan.warps), plan.shared,
+    return launch(kOverlappable, gemv_kernel<F>(plan.order.piece, plan.tma_scales), dim3(plan.ctas), dim3(32u * (plan.warps + (F::kAddingWarp ? 1u : 0u))), plan.shared,
             plan.order.split, group, error);
 }
 
@@ -711,8 +712,11 @@ int euhedral_cuda_linear_nvfp4_native_bf16(const void* input, const void* weight
         return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     const int layout = nvfp4_layout(out_features, in_features, weights_byte_size);
     if (layout < 0) return EUHEDRAL_CUDA_FORMAT_MISMATCH;
-    if (((uintptr_t)input & 15u) != 0 || ((uintptr_t)weights & 15u) != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
-    if (layout == 1 || in_features % 256u != 0 || out_features % 128u != 0 || ((uintptr_t)scratch & 127u) != 0)
+    // 16-byte vector loads of the input and 16-byte stores of the output; the scratch is cut at multiples of 256 bytes from
+    // its base, so a 16-byte-aligned base (what the reference asks for, native/src/host/nvfp4_linear.c:310) is enough for
+    // every tensor map and bulk copy into it.
+    if (((uintptr_t)input & 15u) != 0 || ((uintptr_t)weights & 15u) != 0 || ((uintptr_t)output & 15u) != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    if (layout == 1 || in_features % 256u != 0 || out_features % 128u != 0 || ((uintptr_t)scratch & 15u) != 0)
         return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
     if (scratch == nullptr || scratch_byte_size < nvfp4n::ActivationLayout(rows, in_features, out_features).bytes)
         return EUHEDRAL_CUDA_INVALID_ARGUMENT;
@@ -731,7 +735,9 @@ int euhedral_cuda_linear_kernel_available(int32_t kernel) {
     if (kernel < 0 || kernel >= kTableCount) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     DeviceState* state = nullptr;
     const int status = bind(&state);
-    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    // 1 available, 0 not carried by this build, negative status otherwise (reference header :449-451): a CUDA error
+    // (no device, a failed initialization) reads as "no kernel".
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status > 0 ? EUHEDRAL_CUDA_KERNEL_UNAVAILABLE : status;
     return kTable[kernel].available;
 }
 
@@ -755,7 +761,8 @@ int euhedral_cuda_linear_launch(int32_t kernel, uint32_t grid_x, uint32_t grid_y
     switch (kernel) {
         case 0: {   // prepass(x, suh, out, rows, k, s, layout)
             const int rows = (int)a[3], k = (int)a[4], s = (int)a[5], layout = (int)a[6];
-            if (rows <= 0 || k <= 0 || k % 128 != 0 || s <= 0 || rows > 65535 || s > 65535) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+            if (rows <= 0 || k <= 0 || k % 128 != 0 || s <= 0 || rows > 65535 || s > 65535 || ((a[0] | a[1] | a[2]) & 7u) != 0)
+                return EUHEDRAL_CUDA_INVALID_ARGUMENT;   // 8-byte vector loads and stores
             if (layout != 0 && layout != 1) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;   // 2 = block FP8: no kernel here
             return finish(launch_trellis_prepass(reinterpret_cast<const void*>(a[0]), reinterpret_cast<const void*>(a[1]),
                     reinterpret_cast<void*>(a[2]), rows, k, s, layout));
@@ -763,13 +770,14 @@ int euhedral_cuda_linear_launch(int32_t kernel, uint32_t grid_x, uint32_t grid_y
         case 1: {   // mma(act, words, ends, svh, partials, out, rows, k, n, w, splits, s)
             const int rows = (int)a[6], k = (int)a[7], n = (int)a[8], w = (int)a[9], splits = (int)a[10], s = (int)a[11];
             if (rows <= 0 || k <= 0 || k % 128 != 0 || n <= 0 || n % 128 != 0 || !trellis_width_valid(w) || splits <= 0
-                    || splits > k / 16 || splits > 65535 || s <= 0 || (a[1] & 15u) != 0)
-                return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+                    || splits > k / 16 || splits > 65535 || s <= 0 || (a[1] & 15u) != 0 || ((a[0] | a[3] | a[5]) & 7u) != 0 || (a[4] & 3u) != 0)
+                return EUHEDRAL_CUDA_INVALID_ARGUMENT;   // activations, svh and output move as 8-byte vectors
             return finish(launch_trellis_mma_width(w, a, state->error_word));
         }
         case 4: {   // epilogue(partials, splits, svh, out, rows, n)
             const int splits = (int)a[1], rows = (int)a[4], n = (int)a[5];
-            if (splits <= 0 || rows <= 0 || rows > 65535 || n <= 0 || n % 128 != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+            if (splits <= 0 || rows <= 0 || rows > 65535 || n <= 0 || n % 128 != 0 || (a[0] & 15u) != 0 || ((a[2] | a[3]) & 7u) != 0)
+                return EUHEDRAL_CUDA_INVALID_ARGUMENT;   // 16-byte loads of the partial sums, 8-byte vectors of svh and output
             return finish(launch_trellis_epilogue(reinterpret_cast<const void*>(a[0]), splits, reinterpret_cast<const void*>(a[2]),
                     reinterpret_cast<void*>(a[3]), rows, n));
         }
@@ -818,7 +826,7 @@ int euhedral_b200_linear_trellis_bf16_static(const void* input, const void* word
     if (input == nullptr || words == nullptr || suh == nullptr || svh == nullptr || segment_ends == nullptr || output == nullptr
             || rows == 0 || in_features == 0 || in_features % 128u != 0 || out_features == 0 || out_features % 128u != 0
             || !trellis_width_valid((int)tile_words) || segments == 0 || splits == 0 || splits > in_features / 16u
-            || ((uintptr_t)words & 15u) != 0)
+            || ((uintptr_t)words & 15u) != 0 || (((uintptr_t)input | (uintptr_t)suh | (uintptr_t)svh | (uintptr_t)output) & 7u) != 0)
         return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     // Activations (FP16, every segment) on a 256-byte boundary, then the FP32 partials of every split.
     const uint64_t activations = ((uint64_t)segments * rows * in_features * 2u + 255u) & ~255ull;

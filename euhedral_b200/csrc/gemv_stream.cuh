@@ -23,9 +23,12 @@
 //     accumulate), weights as the 16-row operand and the activation rows as the 8 columns, so that each activation row
 //     is computed independently of the others. Lanes whose column is beyond the last activation row read the last row
 //     again; those sums are never used.
-//   * The team meets on a named barrier per tile; 128 of its threads add the T piece sums in order and either round
-//     and store BF16 (S = 1) or hand the slice sum to the tile's owner rank through distributed shared memory; owners
-//     add the S slice sums in rank order after a cluster barrier at the end of each tensor.
+//   * The T piece sums of a tile meet in shared memory and are added in piece order, then rounded and stored as BF16
+//     (S = 1) or handed to the tile's owner rank through distributed shared memory; owners add the S slice sums in
+//     rank order after a cluster barrier at the end of each tensor. Who adds is the policy's choice (kAddingWarp):
+//     the team itself after a named barrier per tile (teams of 8: the barrier costs less than the hand-over), or one
+//     extra warp of the CTA that the teams signal through mbarriers, so that no decoding warp ever waits for another
+//     (teams of 16, where the barrier would stop the whole CTA once per tile).
 //
 // A policy F provides:
 //   Geometry(n, k)                  byte geometry of the tensor: row_bytes, scale_row_bytes, scale_offset
@@ -34,6 +37,7 @@
 //                                   an odd multiple of 16 so that the rows of a quarter-warp fall in distinct banks)
 //   kPieceChunks, kMaxPiece         preferred and largest chunks per piece
 //   kErrorBit                       bit of the device error word for a wait that gave up
+//   kAddingWarp                     whether an extra warp adds the piece sums (else the team does, behind a barrier)
 //   extra_bytes(chunks)             extra shared bytes next to the activation slice
 //   stage(...)                      CTA-wide staging of the activation slice in the decode's pairing
 //   lane_scale_offset(q)            byte offset of lane q's scales within a chunk's scale bytes
@@ -92,7 +96,7 @@ struct alignas(64) Group {
 // Shared memory of one CTA.
 template <class F>
 struct Layout {
-    uint32_t stride_x, off_extra, off_partials, off_gather, off_slots, off_bars, slot_bytes, code_bytes, bytes;
+    uint32_t stride_x, off_extra, off_partials, off_gather, off_slots, off_bars, off_sum_bars, slot_bytes, code_bytes, bytes;
     __host__ __device__ Layout(const Order& o, uint32_t rows, uint32_t warps, uint32_t depth, uint32_t span) {
         const uint32_t widest = (o.chunks + o.split - 1u) / o.split;
         stride_x = widest * 256u + 64u;   // 64 modulo 128: the rows a quarter-warp reads fall in distinct banks
@@ -104,7 +108,8 @@ struct Layout {
         code_bytes = 16u * o.piece * F::kCodeBytes;
         slot_bytes = code_bytes + 16u * F::kScaleBox;
         off_bars = off_slots + warps * depth * slot_bytes;
-        bytes = off_bars + warps * depth * 8u;
+        off_sum_bars = off_bars + warps * depth * 8u;   // per team and sum buffer: a full and an empty barrier
+        bytes = off_sum_bars + (F::kAddingWarp ? (warps / o.team) * 2u * 16u : 0u);
     }
 };
 
@@ -166,35 +171,124 @@ __device__ __forceinline__ void decode_piece(typename F::template State<P>& stat
 }
 
 template <class F, int P, bool kTmaScales>
-__global__ void __launch_bounds__(32 * kMaxWarps, 1) kernel(const __grid_constant__ Group group, uint32_t* __restrict__ error) {
+__global__ void __launch_bounds__(32 * (kMaxWarps + (F::kAddingWarp ? 1 : 0)), 1) kernel(const __grid_constant__ Group group, uint32_t* __restrict__ error) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, q = lane & 3u;
-    const uint32_t warps = blockDim.x >> 5, threads = blockDim.x;
+    constexpr bool kAdder = F::kAddingWarp;   // piece sums are added by a warp of their own (the CTA's last) or by the team itself
+    const uint32_t warps = (blockDim.x >> 5) - (kAdder ? 1u : 0u), threads = blockDim.x;   // decoding warps
     const uint32_t rows = group.rows, depth = group.depth;
     const Order order = order_of<F>(group.k);
     const uint32_t split = order.split, team_size = order.team;
-    const uint32_t teams = warps / team_size, team = warp / team_size, member = warp % team_size, team_tid = tid - team * team_size * 32u;
+    const uint32_t teams = warps / team_size;
     const uint32_t rank = split > 1u ? eb::cluster_rank() : 0u;
     const uint32_t clusters = gridDim.x / split, cluster = blockIdx.x / split;
     // This cluster's run of the group's tile list.
     const uint32_t run_begin = (uint32_t)((uint64_t)cluster * group.tiles / clusters), run_end = (uint32_t)((uint64_t)(cluster + 1u) * group.tiles / clusters);
-    // This rank's slice and this warp's piece of it, in chunks.
     const uint32_t slice_begin = (uint32_t)((uint64_t)rank * order.chunks / split), slice_end = (uint32_t)((uint64_t)(rank + 1u) * order.chunks / split);
     const uint32_t slice = slice_end - slice_begin;
-    const uint32_t piece_begin = slice_begin + member * slice / team_size, piece_end = slice_begin + (member + 1u) * slice / team_size;
-    const bool wide = piece_end - piece_begin == (uint32_t)P;
     const Layout<F> layout(order, rows, warps, depth, group.span);
     const uint32_t smem_a = eb::smem_u32(smem);
-    const uint32_t slots_a = smem_a + layout.off_slots + warp * depth * layout.slot_bytes;
-    const uint32_t bars_a = smem_a + layout.off_bars + warp * depth * 8u;
+    // Piece sums travel from a team's warps to the adding warp through two buffers per team, each guarded by a `full`
+    // barrier (one arrival per team member) and an `empty` barrier (one arrival by the adding warp).
+    const uint32_t sums_a = smem_a + layout.off_sum_bars;   // [team][buffer][full, empty]
 
-    if (lane == 0) {
-        for (uint32_t s = 0; s < depth; ++s) eb::mbar_init(reinterpret_cast<uint64_t*>(smem + layout.off_bars) + warp * depth + s, 1);
-        eb::mbar_fence_init();
+    if (warp < warps) {
+        if (lane == 0) {
+            for (uint32_t s = 0; s < depth; ++s) eb::mbar_init(reinterpret_cast<uint64_t*>(smem + layout.off_bars) + warp * depth + s, 1);
+        }
+    } else if (kAdder && lane == 0) {
+        for (uint32_t i = 0; i < teams * 2u; ++i) {
+            eb::mbar_init(reinterpret_cast<uint64_t*>(smem + layout.off_sum_bars) + 2u * i, team_size);
+            eb::mbar_init(reinterpret_cast<uint64_t*>(smem + layout.off_sum_bars) + 2u * i + 1u, 1);
+        }
     }
+    if (lane == 0) eb::mbar_fence_init();
     __syncwarp();
     if (split > 1u) eb::cluster_arrive();   // every CTA of the cluster has started before its shared memory is written to
 
+    bool complete = true;
+    const uint16_t* staged = nullptr;
+    // Stages a tensor's activations when they are not the ones in shared memory already. Taken by every warp of the CTA
+    // at the same points of the tensor loop.
+    auto stage = [&](const Tensor& t) {
+        if (t.x != staged) {
+            __syncthreads();   // every warp is done with the activations staged before
+            F::stage(smem, smem + layout.off_extra, t.x, rows, group.k, slice_begin, slice, layout.stride_x, tid, threads);
+            staged = t.x;
+            __syncthreads();
+        }
+    };
+    // With K slices: every rank adds the slice sums of the tiles it owns, in rank order. Taken by every thread of the cluster.
+    auto join_slices = [&](const Tensor& t, uint32_t first_tile, uint32_t segment_begin, uint32_t segment_end) {
+        const typename F::Finish finish(t.w, typename F::Geometry(t.n, group.k));
+        eb::cluster_sync();
+        const uint32_t count = segment_end - segment_begin;
+        const uint32_t owned = count > rank ? (count - rank + split - 1u) / split : 0u;
+        for (uint32_t e = tid; e < owned * 128u; e += threads) {
+            const uint32_t local = e >> 7, rest = e & 127u, column = rest & 7u, row = rest >> 3;
+            if (column < rows) {
+                const uint32_t from = smem_a + layout.off_gather + local * split * kPartial + rest * 4u;
+                float sum = ld_shared_f(from);
+                for (uint32_t s = 1; s < split; ++s) sum = __fadd_rn(sum, ld_shared_f(from + s * kPartial));
+                t.y[(uint64_t)column * t.n + (segment_begin - first_tile + local * split + rank) * 16u + row] = eb::float_to_bf16_bits(finish.apply(sum));
+            }
+        }
+        eb::cluster_sync();   // the gather buffers are free for the next tensor
+    };
+
+    // Adds the T piece sums of a tile in piece order and rounds to BF16 (one slice) or hands the slice sum to the tile's
+    // owner rank. The tile's 16 x rows outputs are dealt to the calling threads: `e` from `begin` in steps of `step`.
+    auto add_pieces = [&](const Tensor& t, const typename F::Finish& finish, uint32_t pieces, uint32_t row0, uint32_t local, uint32_t begin, uint32_t step) {
+        for (uint32_t e = begin; e < 16u * rows; e += step) {
+            const uint32_t column = e >> 4, row = e & 15u, at = (row * 8u + column) * 4u;
+            float sum = ld_shared_f(pieces + at);
+            for (uint32_t j = 1; j < team_size; ++j) sum = __fadd_rn(sum, ld_shared_f(pieces + j * kPartial + at));
+            if (split == 1u) {
+                t.y[(uint64_t)column * t.n + row0 + row] = eb::float_to_bf16_bits(finish.apply(sum));
+            } else {
+                // Tile i of the segment is summed by rank i % S: its gather buffer is [i / S][source rank][row][column].
+                const uint32_t owner = local % split;
+                eb::st_cluster_f32(eb::map_to_rank(smem_a + layout.off_gather, owner) + ((local / split) * split + rank) * kPartial + at, sum);
+            }
+        }
+    };
+
+    if (kAdder && warp == warps) {
+        // ---- the adding warp: the T piece sums of a tile in piece order, then BF16 (one slice) or the tile's owner rank ----
+        eb::pdl_launch_dependents();
+        eb::pdl_wait();
+        if (split > 1u) eb::cluster_wait();
+        uint32_t first_tile = 0;
+        for (uint32_t ti = 0; ti < group.count; ++ti) {
+            const Tensor& t = group.tensor[ti];
+            const uint32_t segment_begin = max(run_begin, first_tile), segment_end = min(run_end, t.tile_end);
+            if (segment_begin < segment_end) {
+                stage(t);
+                const typename F::Finish finish(t.w, typename F::Geometry(t.n, group.k));
+                for (uint32_t tile = segment_begin; tile < segment_end; ++tile) {
+                    // Tile run_begin + i belongs to team i % teams and is that team's tile number i / teams.
+                    const uint32_t index = tile - run_begin, team = index % teams, turn = index / teams, buffer = turn & 1u;
+                    const uint32_t bars = sums_a + (team * 2u + buffer) * 16u;
+                    if (complete) complete = eb::mbar_wait_at(bars, (turn >> 1) & 1u);
+                    const uint32_t pieces = smem_a + layout.off_partials + (team * 2u + buffer) * team_size * kPartial;
+                    add_pieces(t, finish, pieces, (tile - first_tile) * 16u, tile - segment_begin, lane, 32u);
+                    __syncwarp();
+                    if (lane == 0) eb::mbar_arrive(reinterpret_cast<uint64_t*>(smem + layout.off_sum_bars) + (team * 2u + buffer) * 2u + 1u);
+                }
+                if (split > 1u) join_slices(t, first_tile, segment_begin, segment_end);
+            }
+            first_tile = t.tile_end;
+        }
+        if (!complete && lane == 0) atomicOr(error, F::kErrorBit);
+        return;
+    }
+
+    // ---- a decoding warp: member j of its team owns piece j of the slice for every tile the team takes ----
+    const uint32_t team = warp / team_size, member = warp % team_size;
+    const uint32_t piece_begin = slice_begin + member * slice / team_size, piece_end = slice_begin + (member + 1u) * slice / team_size;
+    const bool wide = piece_end - piece_begin == (uint32_t)P;
+    const uint32_t slots_a = smem_a + layout.off_slots + warp * depth * layout.slot_bytes;
+    const uint32_t bars_a = smem_a + layout.off_bars + warp * depth * 8u;
     // Where a piece's bytes sit in the planes: the code box starts at the piece; the scale box starts on the 16-byte
     // boundary at or before the piece's scales.
     const uint32_t code_x = piece_begin * (F::kCodeBytes / 4u);
@@ -202,14 +296,16 @@ __global__ void __launch_bounds__(32 * kMaxWarps, 1) kernel(const __grid_constan
     const uint32_t scale_rem = kTmaScales ? scale_byte - scale_x : 0u;
     const uint32_t fill_bytes = 16u * (wide ? (uint32_t)P : (uint32_t)P - 1u) * F::kCodeBytes + (kTmaScales ? 16u * F::kScaleBox : 0u);
 
-    // The tiles this warp's team takes: run_begin + team, + teams, ... Two cursors walk them: `ask` requests, `use` decodes.
-    uint32_t ask_tile = run_begin + team, ask_tensor = 0, ask_slot = 0;
-    while (ask_tensor + 1u < group.count && ask_tile >= group.tensor[ask_tensor].tile_end) ++ask_tensor;
+    // The team's tiles: run_begin + team, + teams, ... Two cursors walk them: `ask` requests, `use` decodes.
+    uint32_t ask_tile = run_begin + team, ask_slot = 0, ask_tensor = 0, ask_first = 0, ask_end = group.tensor[0].tile_end;
     auto request = [&]() {
         if (ask_tile < run_end) {
+            while (ask_tile >= ask_end) {   // the next tensor of the group
+                ask_first = ask_end;
+                ask_end = group.tensor[++ask_tensor].tile_end;
+            }
             const Tensor& t = group.tensor[ask_tensor];
-            const uint32_t first_tile = ask_tensor == 0u ? 0u : group.tensor[ask_tensor - 1u].tile_end;
-            const uint32_t row = (ask_tile - first_tile) * 16u;
+            const uint32_t row = (ask_tile - ask_first) * 16u;
             const uint32_t to = slots_a + ask_slot * layout.slot_bytes, bar = bars_a + ask_slot * 8u;
             if (lane == 0) {
                 eb::tma_load_2d_expect(to, wide ? &t.codes : &t.codes_narrow, (int)code_x, (int)row, bar, fill_bytes);
@@ -226,7 +322,6 @@ __global__ void __launch_bounds__(32 * kMaxWarps, 1) kernel(const __grid_constan
                 }
             }
             ask_tile += teams;
-            while (ask_tensor + 1u < group.count && ask_tile >= group.tensor[ask_tensor].tile_end) ++ask_tensor;
             if (++ask_slot == depth) ask_slot = 0;
         }
         if (!kTmaScales) eb::cp_async_commit();
@@ -243,25 +338,20 @@ __global__ void __launch_bounds__(32 * kMaxWarps, 1) kernel(const __grid_constan
     const uint32_t code_lane = eb::pinned(g * (wide ? (uint32_t)P : (uint32_t)P - 1u) * F::kCodeBytes);
     const uint32_t scale_lane = eb::pinned(layout.code_bytes + g * F::kScaleBox + scale_rem + F::lane_scale_offset(q));
     const uint32_t extra_lane = smem_a + layout.off_extra + (piece_begin - slice_begin) * (F::extra_bytes(2) - F::extra_bytes(1));
-    const uint32_t partial_team = smem_a + layout.off_partials + team * team_size * 2u * kPartial;
+    // This lane's place in its team's two sum buffers: [buffer][member][row of the tile][activation row]; lane (g, q) holds
+    // rows g, g + 8 for columns 2q, 2q + 1.
+    const uint32_t sum_lane = smem_a + layout.off_partials + (team * 2u * team_size + member) * kPartial + (g * 8u + 2u * q) * 4u;
+    const uint32_t sum_bars = sums_a + team * 32u;
     typename F::template State<P> state(extra_lane, q);
 
-    bool complete = true;
-    uint32_t use_tile = run_begin + team, use_slot = 0, parity = 0, buffer = 0;
-    const uint16_t* staged = nullptr;
-    uint32_t first_tile = 0;
+    uint32_t use_tile = run_begin + team, use_slot = 0, parity = 0, turn = 0, first_tile = 0;
     for (uint32_t ti = 0; ti < group.count; ++ti) {
         const Tensor& t = group.tensor[ti];
         const uint32_t segment_begin = max(run_begin, first_tile), segment_end = min(run_end, t.tile_end);
         if (segment_begin < segment_end) {   // uniform over the cluster
-            if (t.x != staged) {
-                __syncthreads();   // every warp is done with the activations staged before
-                F::stage(smem, smem + layout.off_extra, t.x, rows, group.k, slice_begin, slice, layout.stride_x, tid, threads);
-                staged = t.x;
-                __syncthreads();
-            }
+            stage(t);
             const typename F::Finish finish(t.w, typename F::Geometry(t.n, group.k));
-            for (; use_tile < segment_end; use_tile += teams) {
+            for (; use_tile < segment_end; use_tile += teams, ++turn) {
                 if (!kTmaScales) {
                     if (depth == 2u) eb::cp_async_wait_group<1>();
                     else eb::cp_async_wait_group<2>();
@@ -272,53 +362,28 @@ __global__ void __launch_bounds__(32 * kMaxWarps, 1) kernel(const __grid_constan
                 float acc[4];
                 if (P == 1 || wide) decode_piece<F, P, P>(state, slot + code_lane, slot + scale_lane, x_lane, acc);
                 else decode_piece<F, P, (P > 1 ? P - 1 : 1)>(state, slot + code_lane, slot + scale_lane, x_lane, acc);
-                // The piece's sums: [row of the tile][activation row], lane (g, q) holds rows g, g + 8 for columns 2q, 2q + 1.
-                const uint32_t mine = partial_team + (buffer * team_size + member) * kPartial + (g * 8u + 2u * q) * 4u;
+                const uint32_t buffer = turn & 1u;
+                // With an adding warp: the sum buffer of this turn was read two turns ago (the first two turns find it free).
+                if (kAdder && complete) complete = eb::mbar_wait_at(sum_bars + buffer * 16u + 8u, ((turn >> 1) & 1u) ^ 1u);
+                const uint32_t mine = sum_lane + buffer * team_size * kPartial;
                 st_shared_f2(mine, acc[0], acc[1]);
                 st_shared_f2(mine + 256u, acc[2], acc[3]);
-                __syncwarp();   // every lane is done with the slot
+                __syncwarp();   // every lane is done with the slot and has written its sums
+                if (kAdder && lane == 0) eb::mbar_arrive_at(sum_bars + buffer * 16u);
                 request();
                 if (++use_slot == depth) {
                     use_slot = 0;
                     parity ^= 1u;
                 }
-                if (team_size > 1u) team_sync(team, team_size * 32u);
-                // 128 outputs of the tile (16 rows x 8 columns, columns beyond `rows` unused): the piece sums in order.
-                const uint32_t pieces = partial_team + buffer * team_size * kPartial;
-                for (uint32_t e = team_tid; e < 128u; e += team_size * 32u) {
-                    const uint32_t column = e & 7u, row = e >> 3;
-                    if (column < rows) {
-                        float sum = ld_shared_f(pieces + e * 4u);
-                        for (uint32_t j = 1; j < team_size; ++j) sum = __fadd_rn(sum, ld_shared_f(pieces + j * kPartial + e * 4u));
-                        if (split == 1u) {
-                            t.y[(uint64_t)column * t.n + (use_tile - first_tile) * 16u + row] = eb::float_to_bf16_bits(finish.apply(sum));
-                        } else {
-                            // Tile i of the segment is summed by rank i % S: its gather buffer is [i / S][source rank][row][column].
-                            const uint32_t local = use_tile - segment_begin, owner = local % split;
-                            const uint32_t at = eb::map_to_rank(smem_a + layout.off_gather, owner) + ((local / split) * split + rank) * kPartial + e * 4u;
-                            eb::st_cluster_f32(at, sum);
-                        }
-                    }
+                if (!kAdder) {
+                    // The team meets on its named barrier; its threads share the tile's outputs. Two buffers: a warp that runs
+                    // ahead writes the other one, and passes the next barrier only after every teammate has finished here.
+                    if (team_size > 1u) team_sync(team, team_size * 32u);
+                    add_pieces(t, finish, smem_a + layout.off_partials + (team * 2u + buffer) * team_size * kPartial, (use_tile - first_tile) * 16u,
+                            use_tile - segment_begin, tid - team * team_size * 32u, team_size * 32u);
                 }
-                buffer ^= 1u;
             }
-            if (split > 1u) {
-                // Every rank adds the slice sums of the tiles it owns, in rank order.
-                eb::cluster_sync();
-                const uint32_t count = segment_end - segment_begin;
-                const uint32_t owned = count > rank ? (count - rank + split - 1u) / split : 0u;
-                for (uint32_t e = tid; e < owned * 128u; e += threads) {
-                    const uint32_t local = e >> 7, rest = e & 127u, column = rest & 7u, row = rest >> 3;
-                    if (column < rows) {
-                        const uint32_t from = smem_a + layout.off_gather + local * split * kPartial + rest * 4u;
-                        float sum = ld_shared_f(from);
-                        for (uint32_t s = 1; s < split; ++s) sum = __fadd_rn(sum, ld_shared_f(from + s * kPartial));
-                        t.y[(uint64_t)column * t.n + (segment_begin - first_tile + local * split + rank) * 16u + row]
-                                = eb::float_to_bf16_bits(finish.apply(sum));
-                    }
-                }
-                eb::cluster_sync();   // the gather buffers are free for the next tensor
-            }
+            if (split > 1u) join_slices(t, first_tile, segment_begin, segment_end);
         }
         first_tile = t.tile_end;
     }

@@ -60,6 +60,7 @@ struct Format {
     static constexpr uint32_t kCodeBytes = 64, kScaleBytes = 8, kErrorBit = 1;
     // A piece is at most 4 chunks (4 KB of codes per 16 rows): with sixteen warps and a ring of two slots each that leaves
     // room for the activations of 5 rows at K = 5120. The scale box, 80 bytes per row, is an odd multiple of 16.
+    static constexpr bool kAddingWarp = true;
     static constexpr uint32_t kPieceChunks = 3, kMaxPiece = 4, kScaleBox = 80;
     __host__ __device__ static constexpr uint32_t extra_bytes(uint32_t) { return 0; }
     __device__ static uint32_t lane_scale_offset(uint32_t q) { return 2u * q; }
@@ -67,16 +68,34 @@ struct Format {
     // x[t][c][i][qq] <- the (x0,x4) (x1,x5) (x2,x6) (x3,x7) pairs of the eight activations 8 i .. 8 i + 7 of quarter qq.
     __device__ static void stage(uint8_t* xs, uint8_t*, const uint16_t* __restrict__ x, uint32_t rows, uint32_t k, uint32_t c_begin,
             uint32_t nc, uint32_t stride_x, uint32_t tid, uint32_t threads) {
-        for (uint32_t u = tid; u < rows * nc * 16u; u += threads) {
-            const uint32_t t = u / (nc * 16u), j = u - t * (nc * 16u);
-            const uint32_t c = j >> 4, qq = (j >> 2) & 3u, i = j & 3u;
-            const uint4 v = *reinterpret_cast<const uint4*>(x + (uint64_t)t * k + (uint64_t)(c_begin + c) * kChunk + qq * 32u + i * 8u);
-            uint4 p;
-            p.x = __byte_perm(v.x, v.z, 0x5410);   // (x0, x4)
-            p.y = __byte_perm(v.x, v.z, 0x7632);   // (x1, x5)
-            p.z = __byte_perm(v.y, v.w, 0x5410);   // (x2, x6)
-            p.w = __byte_perm(v.y, v.w, 0x7632);   // (x3, x7)
-            *reinterpret_cast<uint4*>(xs + t * stride_x + c * 256u + i * 64u + qq * 16u) = p;
+        // A thread takes up to kTurns 16-byte units per pass and issues all their loads before the first store.
+        constexpr uint32_t kTurns = 4;
+        const uint32_t total = rows * nc * 16u;
+        for (uint32_t base = 0; base < total; base += kTurns * threads) {
+            uint4 v[kTurns];
+#pragma unroll
+            for (uint32_t turn = 0; turn < kTurns; ++turn) {
+                const uint32_t u = base + turn * threads + tid;
+                if (u < total) {
+                    const uint32_t t = u / (nc * 16u), j = u - t * (nc * 16u);
+                    const uint32_t c = j >> 4, qq = (j >> 2) & 3u, i = j & 3u;
+                    v[turn] = *reinterpret_cast<const uint4*>(x + (uint64_t)t * k + (uint64_t)(c_begin + c) * kChunk + qq * 32u + i * 8u);
+                }
+            }
+#pragma unroll
+            for (uint32_t turn = 0; turn < kTurns; ++turn) {
+                const uint32_t u = base + turn * threads + tid;
+                if (u < total) {
+                    const uint32_t t = u / (nc * 16u), j = u - t * (nc * 16u);
+                    const uint32_t c = j >> 4, qq = (j >> 2) & 3u, i = j & 3u;
+                    uint4 p;
+                    p.x = __byte_perm(v[turn].x, v[turn].z, 0x5410);   // (x0, x4)
+                    p.y = __byte_perm(v[turn].x, v[turn].z, 0x7632);   // (x1, x5)
+                    p.z = __byte_perm(v[turn].y, v[turn].w, 0x5410);   // (x2, x6)
+                    p.w = __byte_perm(v[turn].y, v[turn].w, 0x7632);   // (x3, x7)
+                    *reinterpret_cast<uint4*>(xs + t * stride_x + c * 256u + i * 64u + qq * 16u) = p;
+                }
+            }
         }
     }
 

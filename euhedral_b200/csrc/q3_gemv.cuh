@@ -94,6 +94,7 @@ struct Format {
     static constexpr uint32_t kCodeBytes = 48, kScaleBytes = 4, kErrorBit = 2;
     // A piece is at most 5 chunks (3.75 KB of codes per 16 rows). The scale box, 48 bytes per row, covers 5 chunks' scales
     // plus the 12 bytes a piece can start after a 16-byte boundary, and is an odd multiple of 16.
+    static constexpr bool kAddingWarp = false;
     static constexpr uint32_t kPieceChunks = 5, kMaxPiece = 5, kScaleBox = 48;
     // float [chunk][group][lane q][4]: minus the biased sum of the group's activations of rows 2q and 2q+1, twice over
     // (x, y, x, y), which is the accumulator quad lane q starts a group with.
@@ -106,32 +107,50 @@ struct Format {
     __device__ static void stage(uint8_t* xs, uint8_t* extra, const uint16_t* __restrict__ x, uint32_t rows, uint32_t k,
             uint32_t c_begin, uint32_t nc, uint32_t stride_x, uint32_t tid, uint32_t threads) {
         float* bias = reinterpret_cast<float*>(extra);
-        // Activation rows beyond `rows` have no bias: their MMA columns are never stored.
-        const uint32_t per_row = nc * 8u;
-        for (uint32_t unit = tid; unit < rows * per_row; unit += threads) {
-            const uint32_t t = unit / per_row, j = unit - t * per_row;
-            const uint32_t c = j >> 3, grp = (j >> 2) & 1u, qq = j & 3u;
-            const uint4* src = reinterpret_cast<const uint4*>(x + (uint64_t)t * k + (uint64_t)(c_begin + c) * kChunk + grp * 64u + qq * 16u);
-            const uint4 v0 = src[0], v1 = src[1];
-            const uint32_t s[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-            uint8_t* dst = xs + t * stride_x + c * 256u + grp * 128u + qq * 16u;
-            *reinterpret_cast<uint4*>(dst) = make_uint4(pair_x<0>(s), pair_x<1>(s), pair_x<2>(s), pair_x<3>(s));
-            *reinterpret_cast<uint4*>(dst + 64u) = make_uint4(pair_x<4>(s), pair_x<5>(s), pair_x<6>(s), pair_x<7>(s));
-            float plain = 0.0f, eighth = 0.0f;
+        // Activation rows beyond `rows` have no bias: their MMA columns are never stored. A thread takes up to kTurns units
+        // per pass and issues the loads of all of them before it touches the first, so that one memory latency covers them.
+        constexpr uint32_t kTurns = 4;
+        const uint32_t per_row = nc * 8u, total = rows * per_row;
+        for (uint32_t base = 0; base < total; base += kTurns * threads) {
+            uint4 v0[kTurns], v1[kTurns];
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                const float value = (e & 1) ? __uint_as_float(s[e >> 1] & 0xFFFF0000u) : eb::bf16_bits_to_float(s[e >> 1] & 0xFFFFu);
-                if (element_times8(e)) eighth = __fadd_rn(eighth, value);
-                else plain = __fadd_rn(plain, value);
+            for (uint32_t turn = 0; turn < kTurns; ++turn) {
+                const uint32_t unit = base + turn * threads + tid;
+                if (unit < total) {
+                    const uint32_t t = unit / per_row, j = unit - t * per_row;
+                    const uint32_t c = j >> 3, grp = (j >> 2) & 1u, qq = j & 3u;
+                    const uint4* src = reinterpret_cast<const uint4*>(x + (uint64_t)t * k + (uint64_t)(c_begin + c) * kChunk + grp * 64u + qq * 16u);
+                    v0[turn] = src[0];
+                    v1[turn] = src[1];
+                }
             }
-            float total = __fmaf_rn(20.0f, eighth, __fmul_rn(132.0f, plain));
-            // The unit count is a multiple of 4 and units of a quartet are neighbouring lanes: a quartet is always whole,
-            // and the lanes past the end of the loop in its last turn are whole quartets too.
-            total = __fadd_rn(total, __shfl_xor_sync(__activemask(), total, 1));
-            total = __fadd_rn(total, __shfl_xor_sync(__activemask(), total, 2));
-            if (qq == 0u) {
-                float* quad = bias + ((c * 2u + grp) * 4u + (t >> 1)) * 4u + (t & 1u);
-                quad[0] = quad[2] = -total;
+#pragma unroll
+            for (uint32_t turn = 0; turn < kTurns; ++turn) {
+                const uint32_t unit = base + turn * threads + tid;
+                if (unit < total) {   // whole quartets of neighbouring lanes take the branch together (the unit count is a multiple of 4)
+                    const uint32_t t = unit / per_row, j = unit - t * per_row;
+                    const uint32_t c = j >> 3, grp = (j >> 2) & 1u, qq = j & 3u;
+                    const uint32_t s[8] = {v0[turn].x, v0[turn].y, v0[turn].z, v0[turn].w, v1[turn].x, v1[turn].y, v1[turn].z, v1[turn].w};
+                    uint8_t* dst = xs + t * stride_x + c * 256u + grp * 128u + qq * 16u;
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(pair_x<0>(s), pair_x<1>(s), pair_x<2>(s), pair_x<3>(s));
+                    *reinterpret_cast<uint4*>(dst + 64u) = make_uint4(pair_x<4>(s), pair_x<5>(s), pair_x<6>(s), pair_x<7>(s));
+                    // Two chains of eight additions in element order (plain elements, elements met times 8), then the lanes
+                    // of the quartet in the order ((q0 + q1) + (q2 + q3)).
+                    float plain = 0.0f, eighth = 0.0f;
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const float value = (e & 1) ? __uint_as_float(s[e >> 1] & 0xFFFF0000u) : eb::bf16_bits_to_float(s[e >> 1] & 0xFFFFu);
+                        if (element_times8(e)) eighth = __fadd_rn(eighth, value);
+                        else plain = __fadd_rn(plain, value);
+                    }
+                    float sum = __fmaf_rn(20.0f, eighth, __fmul_rn(132.0f, plain));
+                    sum = __fadd_rn(sum, __shfl_xor_sync(__activemask(), sum, 1));
+                    sum = __fadd_rn(sum, __shfl_xor_sync(__activemask(), sum, 2));
+                    if (qq == 0u) {
+                        float* quad = bias + ((c * 2u + grp) * 4u + (t >> 1)) * 4u + (t & 1u);
+                        quad[0] = quad[2] = -sum;
+                    }
+                }
             }
         }
     }
@@ -140,11 +159,17 @@ struct Format {
     struct State {
         float acc[4];
         uint32_t bias_lane;   // shared address of the bias of activation rows 2q, 2q + 1 of the piece's first chunk
-        uint32_t word_offset, shift;
+        uint32_t first_word, second_word, select_low, select_high;
         Masks masks;
-        // Lane q's 48 bits of a group start at 32-bit word {0, 1, 3, 4}[q], at bit 16 of it for odd q.
+        // Lane q's 48 bits of a group start at 32-bit word {0, 1, 3, 4}[q] of the group's six, at bit 16 of it for odd q,
+        // and end in the next word. The two words are fetched by two loads whose lane-to-word maps, {0, 2, 3, 5} and
+        // {1, 1, 4, 4}, keep a warp's 32 addresses in 32 distinct banks when the box rows are 4 words apart modulo 32 (a
+        // piece of 3 or 5 chunks): even lanes get their lower word first, odd lanes their upper word. One byte permute
+        // with a lane constant then yields bits 0..31 of the lane's 48, another bits 32..47.
         __device__ State(uint32_t extra, uint32_t q)
-            : bias_lane(eb::pinned(extra + q * 16u)), word_offset(eb::pinned(((q >> 1) * 3u + (q & 1u)) * 4u)), shift(eb::pinned((q & 1u) * 16u)) {}
+            : bias_lane(eb::pinned(extra + q * 16u)), first_word(eb::pinned(((q >> 1) * 3u + (q & 1u) * 2u) * 4u)),
+              second_word(eb::pinned(((q >> 1) * 3u + 1u) * 4u)), select_low(eb::pinned((q & 1u) ? 0x1076u : 0x3210u)),
+              select_high(eb::pinned((q & 1u) ? 0x3232u : 0x7654u)) {}
         // codes: shared address of row g of the piece's code box (rows are PC chunks wide, row g + 8 eight rows further);
         // scales: of the two FP16 scales of row g and the piece's first chunk (row g + 8: 8 * kScaleBox further);
         // x: of the lane's activations of the piece's first chunk.
@@ -154,23 +179,23 @@ struct Format {
             const uint32_t scales_g = eb::lds_u32<I * 4>(scales), scales_h = eb::lds_u32<I * 4 + 8 * (int)kScaleBox>(scales);
             const float2 sg2 = __half22float2(*reinterpret_cast<const __half2*>(&scales_g));
             const float2 sh2 = __half22float2(*reinterpret_cast<const __half2*>(&scales_h));
-            const uint32_t words = codes + word_offset;
-            uint32_t ga[2], gb[2], ha[2], hb[2];
-            ga[0] = eb::lds_u32<kAt>(words);
-            gb[0] = eb::lds_u32<kAt + 4>(words);
-            ha[0] = eb::lds_u32<kAt + kRow8>(words);
-            hb[0] = eb::lds_u32<kAt + kRow8 + 4>(words);
-            ga[1] = eb::lds_u32<kAt + 24>(words);
-            gb[1] = eb::lds_u32<kAt + 28>(words);
-            ha[1] = eb::lds_u32<kAt + kRow8 + 24>(words);
-            hb[1] = eb::lds_u32<kAt + kRow8 + 28>(words);
+            const uint32_t first = codes + first_word, second = codes + second_word;
+            uint32_t ga[2], gb[2], ha[2], hb[2];   // a: the word fetched first, b: second (which is lower depends on the lane)
+            ga[0] = eb::lds_u32<kAt>(first);
+            gb[0] = eb::lds_u32<kAt>(second);
+            ha[0] = eb::lds_u32<kAt + kRow8>(first);
+            hb[0] = eb::lds_u32<kAt + kRow8>(second);
+            ga[1] = eb::lds_u32<kAt + 24>(first);
+            gb[1] = eb::lds_u32<kAt + 24>(second);
+            ha[1] = eb::lds_u32<kAt + kRow8 + 24>(first);
+            hb[1] = eb::lds_u32<kAt + kRow8 + 24>(second);
             const uint4 xv[4] = {eb::lds_v4<I * 256>(x), eb::lds_v4<I * 256 + 64>(x), eb::lds_v4<I * 256 + 128>(x), eb::lds_v4<I * 256 + 192>(x)};
             const float4 bias[2] = {eb::lds_f4<I * 128>(bias_lane), eb::lds_f4<I * 128 + 64>(bias_lane)};
 #pragma unroll
             for (int grp = 0; grp < 2; ++grp) {
                 uint32_t wg[8], wh[8];
-                decode16(__funnelshift_r(ga[grp], gb[grp], shift), gb[grp] >> shift, masks, wg);
-                decode16(__funnelshift_r(ha[grp], hb[grp], shift), hb[grp] >> shift, masks, wh);
+                decode16(__byte_perm(ga[grp], gb[grp], select_low), __byte_perm(ga[grp], gb[grp], select_high), masks, wg);
+                decode16(__byte_perm(ha[grp], hb[grp], select_low), __byte_perm(ha[grp], hb[grp], select_high), masks, wh);
                 float sum[4];
                 eb::mma_bf16_16816_from(sum, wg[0], wh[0], wg[1], wh[1], xv[2 * grp].x, xv[2 * grp].y, bias[grp]);
                 eb::mma_bf16_16816(sum, wg[2], wh[2], wg[3], wh[3], xv[2 * grp].z, xv[2 * grp].w);

@@ -28,6 +28,7 @@ def dev():
 
 
 def single(dev, fmt, d_x, d_w, size, rows, k, n, **select):
+    select.setdefault("row_exact", True)   # 9 rows and more stay on the decode kernel (no native FP4 route)
     d_y = dev.empty(rows * n * 2)
     with dev.submit(**select) as gpu:
         call = gpu.linear_q3_bf16 if fmt == "q3" else gpu.linear_nvfp4_bf16
