@@ -702,13 +702,11 @@ uint64_t euhedral_cuda_nvfp4_native_scratch_bytes(uint32_t rows, uint32_t in_fea
     return nvfp4n::ActivationLayout(rows, in_features, out_features).bytes;
 }
 
-int euhedral_cuda_linear_nvfp4_native_bf16(const void* input, const void* weights, void* output, void* scratch, uint32_t rows,
+// Validation shared by the native entry points; `input` is null for the call that finds the activations quantized already.
+static int native_validate(bool has_input, const void* input, const void* weights, const void* output, const void* scratch, uint32_t rows,
         uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size, uint64_t scratch_byte_size) {
-    DeviceState* state = nullptr;
-    int status = bind(&state);
-    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     if (in_features % 128u != 0 || g_exact.load()) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
-    if (input == nullptr || weights == nullptr || output == nullptr || rows == 0 || in_features == 0 || out_features == 0)
+    if ((has_input && input == nullptr) || weights == nullptr || output == nullptr || rows == 0 || in_features == 0 || out_features == 0)
         return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     const int layout = nvfp4_layout(out_features, in_features, weights_byte_size);
     if (layout < 0) return EUHEDRAL_CUDA_FORMAT_MISMATCH;
@@ -721,7 +719,39 @@ int euhedral_cuda_linear_nvfp4_native_bf16(const void* input, const void* weight
     if (scratch == nullptr || scratch_byte_size < nvfp4n::ActivationLayout(rows, in_features, out_features).bytes)
         return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     if (((uint64_t)rows + 127u) / 128u * (out_features / 128u) > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
+    return EUHEDRAL_CUDA_SUCCESS;
+}
+
+int euhedral_cuda_linear_nvfp4_native_bf16(const void* input, const void* weights, void* output, void* scratch, uint32_t rows,
+        uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size, uint64_t scratch_byte_size) {
+    DeviceState* state = nullptr;
+    int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    status = native_validate(true, input, weights, output, scratch, rows, in_features, out_features, weights_byte_size, scratch_byte_size);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     return finish(nvfp4n::run(input, weights, output, scratch, rows, in_features, out_features, state->sms, t_stream, t_pdl != 0 && t_stream != nullptr,
+            state->error_word));
+}
+
+int euhedral_b200_nvfp4_native_quantize(const void* input, void* scratch, uint32_t rows, uint32_t in_features, uint64_t scratch_byte_size) {
+    DeviceState* state = nullptr;
+    const int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    if (in_features == 0 || in_features % 256u != 0 || g_exact.load() || ((uintptr_t)scratch & 15u) != 0) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    if (input == nullptr || scratch == nullptr || rows == 0 || ((uintptr_t)input & 15u) != 0
+            || scratch_byte_size < nvfp4n::ActivationLayout(rows, in_features, 0).bytes)
+        return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    return finish(nvfp4n::quantize(input, scratch, rows, in_features, t_stream, t_pdl != 0 && t_stream != nullptr));
+}
+
+int euhedral_b200_linear_nvfp4_native_prequantized_bf16(const void* weights, void* output, void* scratch, uint32_t rows, uint32_t in_features,
+        uint32_t out_features, uint64_t weights_byte_size, uint64_t scratch_byte_size) {
+    DeviceState* state = nullptr;
+    int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    status = native_validate(false, nullptr, weights, output, scratch, rows, in_features, out_features, weights_byte_size, scratch_byte_size);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    return finish(nvfp4n::multiply(weights, output, scratch, rows, in_features, out_features, state->sms, t_stream, t_pdl != 0 && t_stream != nullptr,
             state->error_word));
 }
 
@@ -818,25 +848,34 @@ int euhedral_b200_take_device_error(uint32_t* word) {
 
 uint64_t euhedral_b200_static_scratch_bytes(void) { return kStaticScratchBytes; }
 
-// A whole trellis linear (prepass, tensor-core GEMM, epilogue when the K range is split) whose scratch is the library's
-// own static device array instead of caller memory. Nothing is allocated or freed here, by CUDA or by any library.
-int euhedral_b200_linear_trellis_bf16_static(const void* input, const void* words, const void* suh, const void* svh,
-        const void* segment_ends, void* output, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t tile_words,
-        uint32_t segments, uint32_t splits) {
+// A whole trellis linear (prepass, tensor-core GEMM, epilogue when the K range is split) in `scratch`: the three launches
+// the reference's host plans one by one through the kernel table, planned here. Nothing is allocated or freed.
+static int trellis_linear(unsigned char* scratch, uint64_t scratch_bytes, const void* input, const void* words, const void* suh, const void* svh,
+        const void* segment_ends, void* output, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t tile_words, uint32_t segments,
+        uint32_t splits) {
     if (input == nullptr || words == nullptr || suh == nullptr || svh == nullptr || segment_ends == nullptr || output == nullptr
             || rows == 0 || in_features == 0 || in_features % 128u != 0 || out_features == 0 || out_features % 128u != 0
-            || !trellis_width_valid((int)tile_words) || segments == 0 || splits == 0 || splits > in_features / 16u
+            || !trellis_width_valid((int)tile_words) || segments == 0 || splits > in_features / 16u
             || ((uintptr_t)words & 15u) != 0 || (((uintptr_t)input | (uintptr_t)suh | (uintptr_t)svh | (uintptr_t)output) & 7u) != 0)
         return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    DeviceState* state = nullptr;
+    const int status = bind(&state);   // first call on a device: resolves the static scratch's device address
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    if (scratch == nullptr) {
+        scratch = state->static_scratch;
+        scratch_bytes = kStaticScratchBytes;
+    }
+    // splits == 0: the reference's choice for this device, core/.../artifact/format/TrellisFormat.java:369-376 with the
+    // default target of 8 blocks per SM.
+    if (splits == 0u) {
+        const uint32_t blocks = out_features / 128u, wanted = (8u * (uint32_t)state->sms + blocks - 1u) / blocks;
+        splits = std::max(1u, std::min(wanted, in_features / 256u));
+    }
     // Activations (FP16, every segment) on a 256-byte boundary, then the FP32 partials of every split.
     const uint64_t activations = ((uint64_t)segments * rows * in_features * 2u + 255u) & ~255ull;
     const uint64_t partials = splits > 1u ? (uint64_t)splits * rows * out_features * 4u : 0u;
-    if (rows > 65535u || segments > 65535u || splits > 65535u || activations + partials > kStaticScratchBytes)
-        return EUHEDRAL_CUDA_SIZE_OVERFLOW;   // beyond the static scratch: use the table launches with caller scratch
-    DeviceState* state = nullptr;
-    const int status = bind(&state);   // first call on a device: resolves the scratch's device address
-    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
-    unsigned char* scratch = state->static_scratch;
+    if (rows > 65535u || segments > 65535u || splits > 65535u || activations + partials > scratch_bytes || ((uintptr_t)scratch & 15u) != 0)
+        return EUHEDRAL_CUDA_SIZE_OVERFLOW;
     cudaError_t e = launch_trellis_prepass(input, suh, scratch, (int)rows, (int)in_features, (int)segments, 0);
     if (e != cudaSuccess) return (int)e;
     const uint64_t a[12] = {(uint64_t)(uintptr_t)scratch, (uint64_t)(uintptr_t)words, (uint64_t)(uintptr_t)segment_ends,
@@ -846,6 +885,28 @@ int euhedral_b200_linear_trellis_bf16_static(const void* input, const void* word
     if (e != cudaSuccess) return (int)e;
     if (splits > 1u) e = launch_trellis_epilogue(scratch + activations, (int)splits, svh, output, (int)rows, (int)out_features);
     return finish(e);
+}
+
+// The scratch is the library's own static device array instead of caller memory.
+int euhedral_b200_linear_trellis_bf16_static(const void* input, const void* words, const void* suh, const void* svh,
+        const void* segment_ends, void* output, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t tile_words,
+        uint32_t segments, uint32_t splits) {
+    if (splits == 0u) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    return trellis_linear(nullptr, 0, input, words, suh, svh, segment_ends, output, rows, in_features, out_features, tile_words, segments, splits);
+}
+
+uint64_t euhedral_b200_linear_trellis_scratch_bytes(uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t segments, uint32_t splits) {
+    const uint64_t activations = ((uint64_t)segments * rows * in_features * 2u + 255u) & ~255ull;
+    const uint32_t most = splits != 0u ? splits : std::max(1u, in_features / 256u);
+    return activations + (most > 1u ? (uint64_t)most * rows * out_features * 4u : 0u);
+}
+
+int euhedral_b200_linear_trellis_bf16(const void* input, const void* words, const void* suh, const void* svh, const void* segment_ends,
+        void* output, void* scratch, uint64_t scratch_bytes, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t tile_words,
+        uint32_t segments, uint32_t splits) {
+    if (scratch == nullptr) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    return trellis_linear(static_cast<unsigned char*>(scratch), scratch_bytes, input, words, suh, svh, segment_ends, output, rows, in_features,
+            out_features, tile_words, segments, splits);
 }
 
 int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t* k_slices,

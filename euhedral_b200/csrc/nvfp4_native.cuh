@@ -388,10 +388,16 @@ inline cudaError_t launch_on(cudaStream_t stream, bool pdl, void (*kernel)(Param
     return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 
-// Quantize, repack, multiply. Shapes are pre-checked by the caller: k % 256 == 0, out_features % 128 == 0, scratch
-// aligned to 128 bytes and at least ActivationLayout(rows, k, out_features).bytes long.
-inline cudaError_t run(const void* input, const void* weights, void* output, void* scratch, uint32_t rows, uint32_t k, uint32_t out_features,
-        int sms, cudaStream_t stream, bool pdl, uint32_t* error) {
+// The three launches of a native linear. Shapes are pre-checked by the caller: k % 256 == 0, out_features % 128 == 0,
+// scratch aligned to 16 bytes and at least ActivationLayout(rows, k, out_features).bytes long.
+// quantize: BF16 rows -> the activation part of the scratch (code planes, scale atoms, row scales).
+inline cudaError_t quantize(const void* input, void* scratch, uint32_t rows, uint32_t k, cudaStream_t stream, bool pdl) {
+    return launch_on(stream, pdl, quantize_rows, dim3(rows), dim3(128), 0, static_cast<const __nv_bfloat16*>(input), static_cast<uint8_t*>(scratch), rows, k);
+}
+
+// multiply: the weight scale plane -> scale atoms in the scratch, then the GEMM over the quantized activations found there.
+inline cudaError_t multiply(const void* weights, void* output, void* scratch, uint32_t rows, uint32_t k, uint32_t out_features, int sms,
+        cudaStream_t stream, bool pdl, uint32_t* error) {
     const EncodeTiled encode = encoder();
     if (encode == nullptr) return cudaErrorNotSupported;
     const ActivationLayout layout(rows, k, out_features);
@@ -412,11 +418,9 @@ inline cudaError_t run(const void* input, const void* weights, void* output, voi
         r = encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w), b_dims, b_strides, b_box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-    cudaError_t e = launch_on(stream, pdl, quantize_rows, dim3(rows), dim3(128), 0, static_cast<const __nv_bfloat16*>(input), base, rows, k);
-    if (e != cudaSuccess) return e;
     const uint32_t n_padded = (out_features + 255u) / 256u * 256u;
     const uint64_t items = (uint64_t)n_padded * layout.k_blocks;
-    e = launch_on(stream, pdl, repack_weight_scales, dim3((unsigned)((items + 255u) / 256u)), dim3(256), 0, w + scale_offset, base + layout.sfb_offset,
+    cudaError_t e = launch_on(stream, pdl, repack_weight_scales, dim3((unsigned)((items + 255u) / 256u)), dim3(256), 0, w + scale_offset, base + layout.sfb_offset,
             out_features, layout.k_blocks, n_padded);
     if (e != cudaSuccess) return e;
     const uint32_t tiles = ((rows + kTileM - 1u) / kTileM) * ((out_features + kTileN - 1u) / kTileN);
@@ -424,6 +428,12 @@ inline cudaError_t run(const void* input, const void* weights, void* output, voi
     return launch_on(stream, pdl, gemm_kernel, dim3(grid), dim3(kThreads), kSharedBytes, map_a, map_b, base + layout.sfa_offset,
             base + layout.sfb_offset, reinterpret_cast<const float*>(base + layout.global_offset), reinterpret_cast<const float*>(w + global_offset),
             static_cast<uint16_t*>(output), rows, out_features, k, error);
+}
+
+inline cudaError_t run(const void* input, const void* weights, void* output, void* scratch, uint32_t rows, uint32_t k, uint32_t out_features,
+        int sms, cudaStream_t stream, bool pdl, uint32_t* error) {
+    const cudaError_t e = quantize(input, scratch, rows, k, stream, pdl);
+    return e != cudaSuccess ? e : multiply(weights, output, scratch, rows, k, out_features, sms, stream, pdl, error);
 }
 
 }  // namespace nvfp4n

@@ -178,6 +178,33 @@ class CudaGpuMemory:
         self._check("native NVFP4 linear", status)
         return True
 
+    def nvfp4_native_quantize(self, input: int, rows: int, in_features: int, out_features: int) -> bool:
+        """First half of the native route for linears that share their input: quantizes the rows into the shared scratch
+        (sized for the widest linear, `out_features`). No counterpart in the reference. False when the route declined."""
+        need = self.lib.euhedral_cuda_nvfp4_native_scratch_bytes(rows, in_features, out_features)
+        scratch = self.native_scratch(need)
+        status = self.lib.euhedral_b200_nvfp4_native_quantize(input, scratch, rows, in_features, self._native_scratch_bytes)
+        if status == library.ROUTE_UNAVAILABLE:
+            return False
+        self._check("native NVFP4 quantize", status)
+        return True
+
+    def linear_nvfp4_native_prequantized_bf16(self, weights, output, rows, in_features, out_features, weight_bytes) -> bool:
+        """Second half: one linear over the activations quantized into the shared scratch by nvfp4_native_quantize."""
+        status = self.lib.euhedral_b200_linear_nvfp4_native_prequantized_bf16(weights, output, self._native_scratch, rows, in_features,
+                                                                              out_features, weight_bytes, self._native_scratch_bytes)
+        if status == library.ROUTE_UNAVAILABLE:
+            return False
+        self._check("native NVFP4 linear (prequantized)", status)
+        return True
+
+    def linear_trellis_bf16(self, input: int, words: int, suh: int, svh: int, ends: int, output: int, scratch: int, scratch_bytes: int,
+                            rows: int, in_features: int, out_features: int, tile_words: int, segments: int, splits: int = 0) -> None:
+        """A whole trellis linear as one call (prepass, GEMM, epilogue planned inside the library). No counterpart in the
+        reference, whose host queues the three table launches itself; same bits. splits = 0: the device's default."""
+        self._check("trellis linear", self.lib.euhedral_b200_linear_trellis_bf16(
+            input, words, suh, svh, ends, output, scratch, scratch_bytes, rows, in_features, out_features, tile_words, segments, splits))
+
     # ---- the linear kernel table -------------------------------------------------------------------------------------------
     def table_kernel_available(self, kernel: str | int) -> bool:
         index = LINEAR_KERNEL_INDEX[kernel] if isinstance(kernel, str) else kernel

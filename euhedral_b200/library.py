@@ -59,6 +59,10 @@ SIGNATURES = {
     "euhedral_b200_take_device_error": (C.c_int, [C.POINTER(_u32)]),
     "euhedral_b200_static_scratch_bytes": (_u64, []),
     "euhedral_b200_linear_trellis_bf16_static": (C.c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _u32, _u32, _u32, _u32, _u32, _u32]),
+    "euhedral_b200_nvfp4_native_quantize": (C.c_int, [_ptr, _ptr, _u32, _u32, _u64]),
+    "euhedral_b200_linear_nvfp4_native_prequantized_bf16": (C.c_int, [_ptr, _ptr, _ptr, _u32, _u32, _u32, _u64, _u64]),
+    "euhedral_b200_linear_trellis_scratch_bytes": (_u64, [_u32, _u32, _u32, _u32, _u32]),
+    "euhedral_b200_linear_trellis_bf16": (C.c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _u64, _u32, _u32, _u32, _u32, _u32, _u32]),
     "euhedral_b200_decode_plan": (C.c_int, [C.c_int, _u32, _u32, _u32, C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32),
                                             C.POINTER(_u32), C.POINTER(_u32)]),
     "euhedral_b200_linear_group_q3_bf16": (C.c_int, [_u32, C.POINTER(_ptr), C.POINTER(_ptr), C.POINTER(_ptr), _u32, _u32,

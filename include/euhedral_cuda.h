@@ -140,6 +140,29 @@ EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_trellis_bf16_static(const void* in
         const void* svh, const void* segment_ends, void* output, uint32_t rows, uint32_t in_features, uint32_t out_features,
         uint32_t tile_words, uint32_t segments, uint32_t splits);
 
+/* No counterpart in the reference (its native route quantizes inside every call). The two halves of the native route
+ * for linears that share their input - the q, k and v projections, or gate and up: quantize the BF16 rows into the
+ * scratch once, then run each linear on the quantized activations found there. The scratch is sized for the widest of
+ * those linears by euhedral_cuda_nvfp4_native_scratch_bytes; the activation part does not depend on out_features.
+ * quantize + prequantized gives bit for bit what euhedral_cuda_linear_nvfp4_native_bf16 gives. Same status codes. */
+EUHEDRAL_CUDA_EXPORT int euhedral_b200_nvfp4_native_quantize(const void* input, void* scratch, uint32_t rows,
+        uint32_t in_features, uint64_t scratch_byte_size);
+EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_nvfp4_native_prequantized_bf16(const void* weights, void* output,
+        void* scratch, uint32_t rows, uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size,
+        uint64_t scratch_byte_size);
+
+/* No counterpart in the reference, whose Java host plans a trellis linear as three launches through the kernel table
+ * (core/.../artifact/format/TrellisFormat.java:484-567). The same three launches planned here, as one call with caller
+ * scratch of at least euhedral_b200_linear_trellis_scratch_bytes(...) bytes (16-byte aligned): rotated FP16 activations,
+ * then the FP32 partial sums of the K splits. splits = 0 takes the reference's split count for this device (8 blocks per
+ * SM); an N-shard passes the split count of the whole tensor so that it reproduces the whole tensor's bits. Arguments
+ * otherwise as euhedral_b200_linear_trellis_bf16_static; results bit for bit those of the table launches. */
+EUHEDRAL_CUDA_EXPORT uint64_t euhedral_b200_linear_trellis_scratch_bytes(uint32_t rows, uint32_t in_features,
+        uint32_t out_features, uint32_t segments, uint32_t splits);
+EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_trellis_bf16(const void* input, const void* words, const void* suh,
+        const void* svh, const void* segment_ends, void* output, void* scratch, uint64_t scratch_bytes, uint32_t rows,
+        uint32_t in_features, uint32_t out_features, uint32_t tile_words, uint32_t segments, uint32_t splits);
+
 #ifdef __cplusplus
 }
 #endif

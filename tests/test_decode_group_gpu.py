@@ -95,8 +95,12 @@ def test_output_is_within_one_ulp_of_the_rounded_float64_result(dev, fmt, n, k):
         large = np.abs(expect) >= 1e-2 * np.max(np.abs(expect))
         distance = np.abs(got.astype(np.int32) - rounded.astype(np.int32))
         assert np.all(distance[large] <= 1), (fmt, rows, int(distance[large].max()))
-        error = np.max(np.abs(O.bf16_to_f32(got).astype(np.float64) - expect)) / np.max(np.abs(expect))
-        assert error <= 2e-3
+        # ... and almost always the very same bits: what is left of the 2e-3 bound after the output rounding (2^-9 at the
+        # largest output) belongs to the kernel, whose own error is orders of magnitude below it
+        assert np.mean(distance[large] == 0) >= 0.97, (fmt, rows, float(np.mean(distance[large] == 0)))
+        kernel_error = np.max(np.abs(O.bf16_to_f32(got).astype(np.float64) - O.bf16_to_f32(rounded).astype(np.float64))[large]
+                              / np.abs(expect[large]))
+        assert kernel_error <= 2.0 ** -7   # one unit in the last place at most
 
 
 def test_decode_then_scalar_kernel_under_dependent_launch(dev):

@@ -136,6 +136,29 @@ def test_native_at_model_shapes(dev, rows, k, n):
     assert not np.any(np.all(y == 0xA5A5, axis=1))
 
 
+def test_quantize_once_for_linears_that_share_their_input(dev):
+    """quantize + prequantized linears give bit for bit what the whole native call gives."""
+    rng = np.random.default_rng(91)
+    rows, k = 200, 1024
+    x = random_x(rng, rows, k)
+    shapes = (384, 128)
+    blobs = [OC.nvfp4_quantize((rng.standard_normal((n, k)) * 0.02).astype(np.float32)) for n in shapes]
+    whole = [run(dev, x, blob, n, k)[0] for blob, n in zip(blobs, shapes)]
+    lib = dev.gpu.lib
+    need = lib.euhedral_cuda_nvfp4_native_scratch_bytes(rows, k, max(shapes))
+    d_x, d_s = dev.put(x), dev.empty(need, fill=0)
+    d_w = [dev.put(blob) for blob in blobs]
+    d_y = [dev.empty(rows * n * 2) for n in shapes]
+    with dev.submit(pdl=True):
+        assert lib.euhedral_b200_nvfp4_native_quantize(d_x.data_ptr(), d_s.data_ptr(), rows, k, need) == 0
+        for w, y, blob, n in zip(d_w, d_y, blobs, shapes):
+            assert lib.euhedral_b200_linear_nvfp4_native_prequantized_bf16(w.data_ptr(), y.data_ptr(), d_s.data_ptr(), rows, k, n, blob.size, need) == 0
+    for y, n, expect in zip(d_y, shapes, whole):
+        assert np.array_equal(dev.get(y, np.uint16, (rows, n)), expect)
+    assert lib.euhedral_b200_nvfp4_native_quantize(d_x.data_ptr(), d_s.data_ptr(), rows, 384, need) == library.ROUTE_UNAVAILABLE
+    assert lib.euhedral_b200_nvfp4_native_quantize(d_x.data_ptr(), d_s.data_ptr(), rows, k, 16) == library.INVALID_ARGUMENT
+
+
 def test_native_route_declines(dev):
     lib = dev.gpu.lib
     rows, k, n = 16, 384, 128      # k % 256 != 0

@@ -123,6 +123,33 @@ def test_layer_shapes(dev, n, k, w):
         assert within_kernel_tolerance(linear.linear(x), expect), (n, k, w, rows)
 
 
+def test_one_call_linear_is_bitwise_the_table_launches(dev):
+    rng = np.random.default_rng(44)
+    k, n, w = 2048, 512, 48
+    payload, suh, svh = random_object(rng, k, n, w, segments=2)
+    ends = [256, 512]
+    lib = dev.gpu.lib
+    for target, rows in ((8, 3), (140, 5), (140, 1)):
+        table = DeviceLinear(dev, payload, suh, svh, ends, target)
+        x = random_x(rng, rows, k)
+        expect = table.linear(x)
+        splits = TrellisFormat.splits(k, n, target)
+        need = lib.euhedral_b200_linear_trellis_scratch_bytes(rows, k, n, 2, splits)
+        assert need == table.format.scratch_bytes(dev.gpu, rows, k, n, 2)
+        d_x, d_y, d_s = dev.put(x), dev.empty(rows * n * 2), dev.empty(need)
+        with dev.submit(pdl=True) as gpu:
+            gpu.linear_trellis_bf16(d_x.data_ptr(), *[t.data_ptr() for t in table.tensors[:3]], table.tensors[3].data_ptr(), d_y.data_ptr(),
+                                    d_s.data_ptr(), need, rows, k, n, w, 2, splits)
+        assert np.array_equal(dev.get(d_y, np.uint16, (rows, n)), expect)
+    # splits = 0 takes the device's default split count; a scratch that is too small is refused
+    need = lib.euhedral_b200_linear_trellis_scratch_bytes(2, k, n, 2, 0)
+    d_x, d_y, d_s = dev.put(random_x(rng, 2, k)), dev.empty(2 * n * 2), dev.empty(need)
+    t = [h.data_ptr() for h in table.tensors]
+    with dev.submit():
+        assert lib.euhedral_b200_linear_trellis_bf16(d_x.data_ptr(), t[0], t[1], t[2], t[3], d_y.data_ptr(), d_s.data_ptr(), need, 2, k, n, w, 2, 0) == 0
+        assert lib.euhedral_b200_linear_trellis_bf16(d_x.data_ptr(), t[0], t[1], t[2], t[3], d_y.data_ptr(), d_s.data_ptr(), 1024, 2, k, n, w, 2, 0) == -2
+
+
 def test_golden_linear_fixture(dev, golden):
     g = golden("trellis")
     linear = DeviceLinear(dev, g["linear_payload"], g["linear_suh"], g["linear_svh"], [256], 140)
