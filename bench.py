@@ -1,16 +1,20 @@
 """Benchmark of the quantized-linear hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--detail]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--headline-only]
 
-Headline workload (`config.workload`): the Q3 decode GEMV set of one dense Qwen-27B-shaped decoder layer - q 5120x5120,
-k and v 1024x5120, o 5120x5120, gate and up 17408x5120, down 5120x17408 (N x K) - at M = 1 and M = 3 activation rows:
-14 quantized GEMVs per step, called one by one through the C ABI on one stream with programmatic dependent launch, the
-weights rotated over several resident copies of the layer so that no step finds its weights in L2. The metric is the
-algorithmic bytes of the step (weight planes + activations + outputs, each byte once) per second. `extra` carries the
-same measurement for the NVFP4 and trellis layouts and the NVFP4 prefill GEMM.
+One GPU (`config.workload`): the Q3 decode GEMV set of one dense Qwen-27B-shaped decoder layer - q 5120x5120, k and v
+1024x5120, o 5120x5120, gate and up 17408x5120, down 5120x17408 (N x K) - at M = 1 and M = 3 activation rows. A step is
+every GEMV of the set once: per row count one grouped C-ABI call over the six tensors that share K = 5120 and one call
+for down, on one stream with programmatic dependent launch, the weights rotated over several resident copies of the
+layer so that no step finds its weights in L2. The metric is the algorithmic bytes of the step (weight planes +
+activations + outputs, each byte once) per second. `extra` carries the same set through the reference's one-call-per-
+tensor entry points, the NVFP4 and trellis layouts, a per-shape table at M = 1..5, the NVFP4 prefill GEMM at 4096, 32768
+and 131072 tokens, and the 64-layer NVFP4 sweep (one decode step at M = 5 plus one 32768-token prefill).
 
-With --gpus N (launched under torch.distributed.run) every weight matrix is split along N over the ranks, each rank
-runs its slices into one packed output buffer, and the slices of a step are joined with one NCCL all-gather.
+With --gpus N (launched under torch.distributed.run) the line's value is the decode step of that 64-layer sweep: every
+weight matrix is split along N over the ranks, each rank runs its slices of a layer into one packed buffer, and the
+slices are joined with one NCCL all-gather per layer that overlaps the next layer's GEMVs. The total work is fixed
+(strong scaling); `extra.sweep64` reports the prefill part and the exchange times.
 
 `--impl reference` times the CPU restatement of the reference's dequant + matmul (oracle/oracle.c) on the host cores.
 """
@@ -18,7 +22,9 @@ runs its slices into one packed output buffer, and the slices of a step are join
 from __future__ import annotations
 
 import argparse
+import ctypes as C
 import json
+import math
 import os
 import subprocess
 import sys
@@ -41,14 +47,19 @@ HEADLINE_ROWS = (1, 3)
 WEIGHT_SEED = 0xE0
 ACTIVATION_SEED = 0xA0
 SIGMA = 0.02
+L2_BYTES = 126e6
+TRELLIS_WIDTH = 48
+SWEEP_LAYERS = 64
+SWEEP_DISTINCT = 8          # distinct seeded layers of the sweep; layer i holds its own copy of the bytes of layer i % 8
+FP4_NOMINAL_TFLOPS = 9000.0
 
 
 def read_peaks():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
         data = json.loads(path.read_text())
-        return float(data["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return {"hbm": float(data["hbm_gbs"]), "bf16": float(data.get("bf16_tflops", 0.0)), "kind": "measured"}
+    return {"hbm": 6650.0, "bf16": 1590.0, "kind": "fallback"}
 
 
 def seeded_weights(index: int, n: int, k: int) -> np.ndarray:
@@ -61,7 +72,7 @@ def seeded_rows(rows: int, k: int) -> np.ndarray:
     return O.bf16_bits(np.random.default_rng(ACTIVATION_SEED + rows).standard_normal((rows, k)).astype(np.float32))
 
 
-def algorithmic_bytes(fmt: str, n: int, k: int, rows: int, w: int = 48) -> int:
+def algorithmic_bytes(fmt: str, n: int, k: int, rows: int, w: int = TRELLIS_WIDTH) -> int:
     from euhedral_b200 import layouts
     weights = {"q3": layouts.q3_algorithmic_bytes(n, k), "nvfp4": layouts.nvfp4_algorithmic_bytes(n, k),
                "trellis": layouts.trellis_algorithmic_bytes(n, k, w, 1)}[fmt]
@@ -108,14 +119,16 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------------------------------
-# reference arm: the CPU restatement on the host cores
+# the CPU restatement on the host cores: reference arm and cpu_baseline
 # ---------------------------------------------------------------------------------------------------------------------
 
-def cpu_layer_pass(blobs, rows_list, threads):
+def cpu_layer_pass(blobs, rows_list, threads, only=None):
     from oracle import oracle_c as OC
     total = 0
     start = time.perf_counter()
     for (name, n, k), blob in zip(LAYER, blobs):
+        if only is not None and name not in only:
+            continue
         for rows in rows_list:
             OC.q3_linear(seeded_rows(rows, k), blob, n, k, threads=threads)
             total += algorithmic_bytes("q3", n, k, rows)
@@ -127,13 +140,40 @@ def cpu_blobs():
     return [OC.q3_quantize(seeded_weights(i, n, k)) for i, (name, n, k) in enumerate(LAYER)]
 
 
+def cpu_baseline(blobs):
+    """The plain-C restatement on every host thread (warmed), on one thread (a bounded sample), and the NumPy
+    restatement of the converter's own dequantize + matmul the way a user of the reference's Python tools would run it."""
+    from oracle import oracle_c as OC
+    from oracle import oracle_np as O
+    threads = OC.default_threads()
+    cpu_layer_pass(blobs, HEADLINE_ROWS, threads)                      # warm
+    b, t = cpu_layer_pass(blobs, HEADLINE_ROWS, threads)
+    b1, t1 = cpu_layer_pass(blobs, HEADLINE_ROWS, 1, only=("q",))      # one thread: the q matrix at M = 1 and 3
+    n, k = 1024, 5120
+    blob = OC.nvfp4_quantize(seeded_weights(1, n, k))
+    x = O.bf16_to_f32(seeded_rows(1, k))
+    start = time.perf_counter()
+    dense = O.nvfp4_dense(blob.tobytes(), n, k)
+    middle = time.perf_counter()
+    for _ in range(10):
+        x @ dense.T
+    stop = time.perf_counter()
+    numpy_bytes = algorithmic_bytes("nvfp4", n, k, 1)
+    return {"value": b / t / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": "one whole warmed step (7 matrices x M in {1,3}) on the plain-C restatement, row-parallel threads",
+            "single_thread": {"value": b1 / t1 / 1e9, "unit": "GB/s", "sample": "q 5120x5120 at M = 1 and 3, one thread"},
+            "numpy_as_shipped": {"value": numpy_bytes / ((middle - start) + (stop - middle) / 10) / 1e9, "unit": "GB/s",
+                                 "dequantize_s": middle - start, "matmul_s": (stop - middle) / 10,
+                                 "sample": "NumPy dequantize of an NVFP4 1024x5120 tensor + x @ W.T at M = 1 (the converter's own path)"}}
+
+
 def run_reference(args):
     if RANK != 0:
         return
     from oracle import oracle_c as OC
     threads = OC.default_threads()
     blobs = cpu_blobs()
-    for _ in range(min(args.warmup, 1)):
+    for _ in range(max(1, min(args.warmup, 3))):
         cpu_layer_pass(blobs, HEADLINE_ROWS, threads)
     total_bytes, total_time = 0, 0.0
     for _ in range(args.steps):
@@ -144,7 +184,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": "quantized GEMV algorithmic GB/s (Q3 decode layer set, M=1 and M=3)", "value": value,
         "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_time / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "Q3 decode GEMV set, one Qwen-27B-shaped layer, M in {1,3}", "layer": [list(s) for s in LAYER]},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": "the whole step: 7 matrices x M in {1,3}, plain-C dequant + FP32 dot, row-parallel threads"},
@@ -157,222 +197,453 @@ def run_reference(args):
 # our arm
 # ---------------------------------------------------------------------------------------------------------------------
 
-class Resident:
-    """One format's layer set on this rank: `copies` resident copies of every (sharded) weight tensor, the activation
-    rows, output buffers and the launch closure of every GEMV of a step."""
+class Bench:
+    def __init__(self, torch, dist, world, rank):
+        from euhedral_b200.gpu import CudaGpuMemory
+        self.torch, self.dist, self.world, self.rank = torch, dist, world, rank
+        self.gpu = CudaGpuMemory()   # raises when the CUDA library is missing: no fallback
+        self.lib = self.gpu.lib
+        self.sms = self.gpu.multiprocessor_count()
+        self.stream = torch.cuda.Stream()
+        self.peaks = read_peaks()
 
-    def __init__(self, torch, gpu, fmt: str, rows_list, copies: int, world: int, rank: int, sms: int, w: int = 48, only=None):
+    def check(self, status):
+        if status != 0:
+            raise RuntimeError(f"C ABI call failed with status {status}")
+
+    def timed(self, steps, warmup, body):
+        """max over ranks of the device time of `steps` calls of body(i), after `warmup` untimed calls."""
+        torch = self.torch
+        for i in range(warmup):
+            body(i)
+        torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(torch.cuda.current_stream())
+        for i in range(steps):
+            body(warmup + i)
+        stop.record(torch.cuda.current_stream())
+        torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+        seconds = start.elapsed_time(stop) / 1e3
+        if self.world > 1:
+            t = torch.tensor([seconds], device="cuda", dtype=torch.float64)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            seconds = float(t.item())
+        return seconds
+
+    def submit(self):
+        return self.gpu.submit(self.stream.cuda_stream, pdl=True)
+
+    # ---- tensors ------------------------------------------------------------------------------------------------------
+    def weight(self, fmt, index, n, k, first=0, local=None):
+        """Device tensors of one weight in `fmt`: rows [first, first + local) of the whole seeded tensor."""
         from euhedral_b200 import sharding, synthetic
-        from euhedral_b200.formats import (GroupedLinearFormat, LinearLaunch, Nvfp4Format, TensorHandle, TrellisFormat,
-                                           TrellisSettings)
-        self.torch, self.gpu, self.fmt, self.rows_list, self.copies = torch, gpu, fmt, rows_list, copies
-        self.calls = []          # (launch per copy, n_local, n, k, rows)
+        torch = self.torch
+        local = n if local is None else local
+        if fmt == "trellis":
+            # Random trellis words with the reference test-suite's scale distributions (its encoder is not part of this build).
+            return synthetic.trellis_object(local, k, TRELLIS_WIDTH, WEIGHT_SEED + index, 1, device="cuda")
+        build, cut = (synthetic.q3_tensor, sharding.q3_rows) if fmt == "q3" else (synthetic.nvfp4_tensor, sharding.nvfp4_rows)
+        whole = build(synthetic.gaussian(n, k, WEIGHT_SEED + index, SIGMA, device="cuda"))
+        if local == n:
+            return (whole,)
+        # a shard is cut from the whole tensor (NVFP4's tensor scale is the whole tensor's)
+        return (torch.from_numpy(cut(whole.cpu().numpy(), n, k, first, local)).cuda(),)
+
+    def rows(self, rows, k):
+        from euhedral_b200 import synthetic
+        return synthetic.bf16_rows(rows, k, ACTIVATION_SEED + rows, device="cuda")
+
+
+class LayerSet:
+    """One format's layer set on one GPU: `copies` resident copies of every weight tensor, packed activation and output
+    buffers on the host (pinned) and the device, and the C-ABI calls of a step in two shapes: one call per tensor (the
+    reference's entry points) or one grouped call per row count over the tensors that share K."""
+
+    def __init__(self, bench: Bench, fmt: str, rows_list, copies: int):
+        torch = bench.torch
+        self.bench, self.fmt, self.rows_list, self.copies = bench, fmt, rows_list, copies
         self.keep = []
-        self.bytes_per_step = 0
-        self.h2d = self.d2h = 0
-        self.outputs = []
-        self.inputs = {}
-        self.host_inputs = {}
-        # The step's distinct activation tensors live in one packed buffer on each side, so that the end-to-end step
-        # uploads them from pinned memory with ONE copy.
-        shapes = [(rows, k) for rows in rows_list for k in sorted({k for _, _, k in LAYER})]
-        total_in = sum(rows * k for rows, k in shapes)
-        self.host_packed_in = torch.empty(total_in, dtype=torch.int16).pin_memory()
-        self.packed_in = torch.empty(total_in, dtype=torch.int16, device="cuda")
-        cursor = 0
-        for rows, k in shapes:
-            self.host_packed_in[cursor:cursor + rows * k].copy_(synthetic.bf16_rows(rows, k, ACTIVATION_SEED + rows).view(torch.int16).reshape(-1))
-            self.host_inputs[(rows, k)] = self.host_packed_in[cursor:cursor + rows * k]
-            self.inputs[(rows, k)] = self.packed_in[cursor:cursor + rows * k]
-            cursor += rows * k
-        self.packed_in.copy_(self.host_packed_in)
-        self.h2d_bytes = 2 * total_in
-        settings = TrellisSettings.for_device(sms) if TRELLIS_TARGET_PER_SM is None else TrellisSettings(target_ctas=TRELLIS_TARGET_PER_SM * sms)
-        # Every output slice of a step lives in one packed buffer, so that a multi-GPU step joins them with ONE all-gather.
-        unit = 128 if fmt == "trellis" else 16
-        total = sum(rows * sharding.shard_range(n, world, rank, unit)[1] for name, n, k in LAYER if only in (None, name) for rows in rows_list)
-        self.packed = torch.empty(total, dtype=torch.int16, device="cuda")
-        self.gathered = torch.empty(total * world, dtype=torch.int16, device="cuda") if world > 1 else self.packed
-        self.host_result = torch.empty(total * world, dtype=torch.int16).pin_memory()
-        cursor = 0
+        ks = sorted({k for _, _, k in LAYER})
+        total_in = sum(rows * k for rows in rows_list for k in ks)
+        self.host_in = torch.empty(total_in, dtype=torch.int16).pin_memory()
+        self.device_in = torch.empty(total_in, dtype=torch.int16, device="cuda")
+        self.inputs, cursor = {}, 0
+        for rows in rows_list:
+            for k in ks:
+                self.host_in[cursor:cursor + rows * k].copy_(bench.rows(rows, k).view(-1).cpu())
+                self.inputs[(rows, k)] = self.device_in[cursor:cursor + rows * k]
+                cursor += rows * k
+        self.device_in.copy_(self.host_in)
+        self.h2d = 2 * total_in
+        total_out = sum(rows * n for rows in rows_list for _, n, _ in LAYER)
+        self.device_out = torch.empty(total_out, dtype=torch.int16, device="cuda")
+        self.host_out = torch.empty(total_out, dtype=torch.int16).pin_memory()
+        self.d2h = 2 * total_out
+        self.outputs, cursor = {}, 0
+        for rows in rows_list:
+            for name, n, _ in LAYER:
+                self.outputs[(rows, name)] = self.device_out[cursor:cursor + rows * n]
+                cursor += rows * n
+        self.weights = {}      # name -> list over copies of tuples of tensors
         for index, (name, n, k) in enumerate(LAYER):
-            if only is not None and name != only:
-                continue
-            first, local = sharding.shard_range(n, world, rank, 128 if fmt == "trellis" else 16)
-            if fmt in ("q3", "nvfp4"):
-                # N(0, 0.02^2) weights rounded on the device exactly as the converter rounds them; a shard is cut from
-                # the whole tensor (NVFP4's tensor scale is the whole tensor's).
-                build, cut = (synthetic.q3_tensor, sharding.q3_rows) if fmt == "q3" else (synthetic.nvfp4_tensor, sharding.nvfp4_rows)
-                whole = build(synthetic.gaussian(n, k, WEIGHT_SEED + index, SIGMA, device="cuda"))
-                blob = whole if world == 1 else torch.from_numpy(cut(whole.cpu().numpy(), n, k, first, local)).cuda()
-                del whole
-                operator = GroupedLinearFormat() if fmt == "q3" else Nvfp4Format()
-            else:
-                # Random trellis words with the reference test-suite's scale distributions (its encoder is not part of
-                # this build); the K split is planned from the unsharded shape so shards keep the whole object's order.
-                payload, suh, svh, ends = synthetic.trellis_object(local, k, w, WEIGHT_SEED + index, 1, device="cuda")
-                splits = TrellisFormat.splits(k, n, settings.target_ctas)
-                operator = TrellisFormat(TrellisSettings(target_ctas=splits * (local // 128)))
-                assert TrellisFormat.splits(k, local, splits * (local // 128)) == splits
-            for rows in rows_list:
-                launches = []
-                out = self.packed[cursor:cursor + rows * local].view(rows, local)
-                cursor += rows * local
-                for copy in range(copies):
+            first = bench.weight(fmt, index, n, k)
+            self.weights[name] = [first] + [tuple(t.clone() for t in first) for _ in range(copies - 1)]
+        self.bytes_per_step = sum(algorithmic_bytes(fmt, n, k, rows) for rows in rows_list for _, n, k in LAYER)
+        self.scratch = None
+        if fmt == "trellis":
+            need = max(bench.lib.euhedral_b200_linear_trellis_scratch_bytes(rows, k, n, 1, 0) for rows in rows_list for _, n, k in LAYER)
+            self.scratch = [torch.empty(need, dtype=torch.uint8, device="cuda") for _ in LAYER]
+            self.scratch_bytes = need
+        self._build_calls()
+
+    def _build_calls(self):
+        lib, fmt = self.bench.lib, self.fmt
+        self.single, self.grouped = [[] for _ in range(self.copies)], [[] for _ in range(self.copies)]
+        for copy in range(self.copies):
+            for rows in self.rows_list:
+                for position, (name, n, k) in enumerate(LAYER):
+                    tensors = self.weights[name][copy]
+                    x, y = self.inputs[(rows, k)].data_ptr(), self.outputs[(rows, name)].data_ptr()
                     if fmt == "trellis":
-                        tensors = [a.clone() for a in (payload, suh, svh, ends)]
-                        shapes = [payload.shape, (1, k), (local,), (1,)]
-                        handles = [TensorHandle(f"{name}{i}", tuple(s), t.data_ptr(), t.numel() * t.element_size()) for i, (t, s) in enumerate(zip(tensors, shapes))]
-                        need = operator.scratch_bytes(gpu, rows, k, local, 1)
-                        scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
-                        self.keep += tensors + [scratch]
-                        launch = LinearLaunch(self.inputs[(rows, k)].data_ptr(), out.data_ptr(), handles, rows, k, local,
-                                              scratch=scratch.data_ptr(), scratch_bytes=need, row_exact=True)
+                        payload, suh, svh, ends = tensors
+                        args = (x, payload.data_ptr(), suh.data_ptr(), svh.data_ptr(), ends.data_ptr(), y, self.scratch[position].data_ptr(),
+                                self.scratch_bytes, rows, k, n, TRELLIS_WIDTH, 1, 0)
+                        self.single[copy].append((lib.euhedral_b200_linear_trellis_bf16, args))
                     else:
-                        tensor = blob.clone()
-                        self.keep.append(tensor)
-                        handle = TensorHandle(name, (local, k), tensor.data_ptr(), tensor.numel())
-                        launch = LinearLaunch(self.inputs[(rows, k)].data_ptr(), out.data_ptr(), [handle], rows, k, local, row_exact=True)
-                    launches.append((operator, launch))
-                self.calls.append((launches, out, local, n, k, rows))
-                self.bytes_per_step += algorithmic_bytes(fmt, local, k, rows, w)
-                self.d2h += 2 * rows * local * world
-        self.launches_per_step = len(self.calls) * (3 if fmt == "trellis" else 1)
+                        entry = lib.euhedral_cuda_linear_q3_bf16 if fmt == "q3" else lib.euhedral_cuda_linear_nvfp4_bf16
+                        self.single[copy].append((entry, (x, tensors[0].data_ptr(), y, rows, k, n, tensors[0].numel())))
+                if fmt == "trellis":
+                    continue
+                entry = lib.euhedral_b200_linear_group_q3_bf16 if fmt == "q3" else lib.euhedral_b200_linear_group_nvfp4_bf16
+                for k in sorted({k for _, _, k in LAYER}):
+                    members = [(name, n) for name, n, kk in LAYER if kk == k]
+                    count = len(members)
+                    blobs = [self.weights[name][copy][0] for name, _ in members]
+                    args = (count, (C.c_void_p * count)(*[self.inputs[(rows, k)].data_ptr()] * count),
+                            (C.c_void_p * count)(*[b.data_ptr() for b in blobs]),
+                            (C.c_void_p * count)(*[self.outputs[(rows, name)].data_ptr() for name, _ in members]), rows, k,
+                            (C.c_uint32 * count)(*[n for _, n in members]), (C.c_uint64 * count)(*[b.numel() for b in blobs]))
+                    self.grouped[copy].append((entry, args))
 
-    def step(self, iteration: int, world: int):
-        from euhedral_b200 import sharding
-        for launches, out, local, n, k, rows in self.calls:
-            operator, launch = launches[iteration % self.copies]
-            operator.linear(self.gpu, launch)
-        if world > 1:
-            sharding.gather_packed(self.packed, self.gathered)
+    def step(self, iteration: int, grouped: bool):
+        calls = (self.grouped if grouped else self.single)[iteration % self.copies]
+        for entry, args in calls:
+            status = entry(*args)
+            if status != 0:
+                raise RuntimeError(f"C ABI call failed with status {status}")
 
-    def step_e2e(self, iteration: int, world: int):
-        """The same step fed from pinned host memory: the step's activation tensors are uploaded from pinned memory (one
-        copy of the packed buffer), and the step's whole result (every rank's slices) is read back to pinned memory at
-        the end."""
-        from euhedral_b200 import sharding
-        self.gpu.copy_upload_to_device(self.packed_in.data_ptr(), self.host_packed_in.data_ptr(), self.h2d_bytes)
-        for launches, out, local, n, k, rows in self.calls:
-            operator, launch = launches[iteration % self.copies]
-            operator.linear(self.gpu, launch)
-        if world > 1:
-            sharding.gather_packed(self.packed, self.gathered)
-        self.gpu.copy_device_to_readback(self.host_result.data_ptr(), self.gathered.data_ptr(), self.gathered.numel() * 2)
+    def step_e2e(self, iteration: int, grouped: bool):
+        """The same step fed from pinned host memory: the step's activation tensors are uploaded (one copy of the packed
+        buffer) and the step's whole result is read back to pinned memory, all on the step's stream."""
+        gpu = self.bench.gpu
+        gpu.copy_upload_to_device(self.device_in.data_ptr(), self.host_in.data_ptr(), self.h2d)
+        self.step(iteration, grouped)
+        gpu.copy_device_to_readback(self.host_out.data_ptr(), self.device_out.data_ptr(), self.d2h)
 
-
-def timed(torch, dist, world, steps, warmup, body):
-    """max over ranks of the device time of `steps` calls of body(i), after `warmup` untimed calls."""
-    for i in range(warmup):
-        body(i)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record(torch.cuda.current_stream())
-    for i in range(steps):
-        body(warmup + i)
-    stop.record(torch.cuda.current_stream())
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    seconds = start.elapsed_time(stop) / 1e3
-    if world > 1:
-        t = torch.tensor([seconds], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        seconds = float(t.item())
-    return seconds
+    def launches(self, grouped: bool):
+        per_call = 3 if self.fmt == "trellis" else 1
+        return len((self.grouped if grouped else self.single)[0]) * per_call
 
 
-def measure_format(torch, dist, gpu, fmt, rows_list, copies, world, rank, sms, steps, warmup, stream, e2e=False, only=None, graph=False):
-    """graph=True: the step of every weight copy is captured once into a CUDA graph (plain stream capture of the same
-    C-ABI calls) and the timed region replays the graphs - what the launches cost on the device, without the Python
-    launch planning of the trellis operator (three table launches per linear, tens of microseconds of host time)."""
-    resident = Resident(torch, gpu, fmt, rows_list, copies, world, rank, sms, only=only)
-    with torch.cuda.stream(stream), gpu.submit(stream.cuda_stream, pdl=True):
-        body = lambda i: resident.step(i, world)
-        if graph:
-            for i in range(copies):
-                body(i)   # plans, tensor maps and occupancy look-ups are made before the capture
-            torch.cuda.synchronize()
-            graphs = []
-            for copy in range(copies):
-                captured = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(captured, stream=stream):
-                    resident.step(copy, world)
-                graphs.append(captured)
-            body = lambda i: graphs[i % copies].replay()
-        seconds = timed(torch, dist, world, steps, warmup, body)
-        total_bytes = resident.bytes_per_step
-        if world > 1:
-            t = torch.tensor([float(total_bytes)], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t)
-            total_bytes = float(t.item())
-        result = {"gbs": total_bytes * steps / seconds / 1e9, "ms_per_step": seconds / steps * 1e3, "bytes_per_step": total_bytes,
-                  "launches_per_step": resident.launches_per_step}
+def measure_layer_set(bench: Bench, fmt, rows_list, copies, steps, warmup, e2e=False):
+    torch = bench.torch
+    layer = LayerSet(bench, fmt, rows_list, copies)
+    result = {"rows": list(rows_list), "bytes_per_step": layer.bytes_per_step}
+    with torch.cuda.stream(bench.stream), bench.submit():
+        for label, grouped in (("grouped", True), ("single", False)):
+            if grouped and fmt == "trellis":
+                continue
+            seconds = bench.timed(steps, warmup, lambda i: layer.step(i, grouped))
+            gbs = layer.bytes_per_step * steps / seconds / 1e9
+            result[label] = {"gbs": gbs, "frac_of_hbm_peak": gbs / bench.peaks["hbm"], "us_per_step": seconds / steps * 1e6,
+                             "calls_per_step": len((layer.grouped if grouped else layer.single)[0]), "launches_per_step": layer.launches(grouped)}
         if e2e:
-            seconds = timed(torch, dist, world, steps, warmup, lambda i: resident.step_e2e(i, world))
-            result["e2e_gbs"] = total_bytes * steps / seconds / 1e9
-            result["h2d"], result["d2h"] = resident.h2d_bytes, resident.d2h
-    assert gpu.take_device_error() == 0, "a kernel's bounded wait gave up"
-    del resident
+            seconds = bench.timed(steps, warmup, lambda i: layer.step_e2e(i, True))
+            result["e2e_gbs"] = layer.bytes_per_step * steps / seconds / 1e9
+            result["h2d"], result["d2h"] = layer.h2d, layer.d2h
+    assert bench.gpu.take_device_error() == 0, "a kernel's bounded wait gave up"
+    del layer
     torch.cuda.empty_cache()
     return result
 
 
-def measure_prefill(torch, gpu, stream, steps, warmup, rows=4096, detail=False):
-    """NVFP4 prefill GEMM over the seven layer shapes at `rows` tokens: TFLOP/s of 2 M N K (one logical product)."""
+def measure_per_shape(bench: Bench, steps_floor=40):
+    """Every distinct layer shape alone, M = 1..5, each format: one C-ABI call per launch, programmatic dependent launch,
+    the tensor rotated over enough copies to exceed the L2 two and a half times."""
+    torch, lib = bench.torch, bench.lib
+    distinct = {"q": ("q", "o"), "k": ("k", "v"), "gate": ("gate", "up"), "down": ("down",)}
+    table = {}
+    for fmt in ("nvfp4", "q3", "trellis"):
+        for index, (name, n, k) in enumerate(LAYER):
+            if name not in distinct:
+                continue
+            first = bench.weight(fmt, index, n, k)
+            size = sum(t.numel() * t.element_size() for t in first)
+            copies = int(min(128, max(3, math.ceil(2.5 * L2_BYTES / size) + 1)))
+            tensors = [first] + [tuple(t.clone() for t in first) for _ in range(copies - 1)]
+            scratch = None
+            if fmt == "trellis":
+                need = lib.euhedral_b200_linear_trellis_scratch_bytes(5, k, n, 1, 0)
+                scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+            for rows in (1, 2, 3, 4, 5):
+                x = bench.rows(rows, k)
+                y = torch.empty(rows * n, dtype=torch.int16, device="cuda")
+
+                def body(i):
+                    t = tensors[i % copies]
+                    if fmt == "trellis":
+                        bench.check(lib.euhedral_b200_linear_trellis_bf16(x.data_ptr(), t[0].data_ptr(), t[1].data_ptr(), t[2].data_ptr(), t[3].data_ptr(),
+                                                                           y.data_ptr(), scratch.data_ptr(), need, rows, k, n, TRELLIS_WIDTH, 1, 0))
+                    elif fmt == "q3":
+                        bench.check(lib.euhedral_cuda_linear_q3_bf16(x.data_ptr(), t[0].data_ptr(), y.data_ptr(), rows, k, n, t[0].numel()))
+                    else:
+                        bench.check(lib.euhedral_cuda_linear_nvfp4_bf16(x.data_ptr(), t[0].data_ptr(), y.data_ptr(), rows, k, n, t[0].numel()))
+
+                launches = max(steps_floor, 2 * copies)
+                with torch.cuda.stream(bench.stream), bench.submit():
+                    seconds = bench.timed(launches, copies, body)
+                us = seconds / launches * 1e6
+                gbs = algorithmic_bytes(fmt, n, k, rows) / us / 1e3
+                for alias in distinct[name]:
+                    table[f"{fmt}:{alias}:{rows}"] = [round(us, 2), round(gbs, 1), round(gbs / bench.peaks["hbm"], 4)]
+            del tensors, first
+            torch.cuda.empty_cache()
+    return {"columns": ["us per launch", "GB/s", "fraction of HBM peak"], "note": "key = format:shape:M; trellis at 48 words per tile",
+            "rows": table}
+
+
+def measure_prefill(bench: Bench, rows, steps, warmup):
+    """NVFP4 prefill GEMM over the seven layer shapes at `rows` tokens through the reference's native entry point
+    (quantize + scale repack + GEMM per call): TFLOP/s of 2 M N K (one logical product; the kernel issues one MMA per
+    activation term, twice that)."""
     from euhedral_b200 import layouts, synthetic
+    torch, gpu, lib = bench.torch, bench.gpu, bench.lib
     if not gpu.nvfp4_native_available():
         return None
-    tensors, flops = [], 0
+    tensors, flops, xs = [], 0, {}
     for index, (name, n, k) in enumerate(LAYER):
-        blob = synthetic.nvfp4_tensor(synthetic.gaussian(n, k, WEIGHT_SEED + index, SIGMA, device="cuda"))
-        x = synthetic.bf16_rows(rows, k, ACTIVATION_SEED, device="cuda")
-        y = torch.empty((rows, n), dtype=torch.int16, device="cuda")
-        tensors.append((blob, x, y, n, k))
+        blob = bench.weight("nvfp4", index, n, k)[0]
+        if k not in xs:
+            xs[k] = torch.randn((rows, k), device="cuda", dtype=torch.bfloat16, generator=torch.Generator(device="cuda").manual_seed(ACTIVATION_SEED)).view(torch.int16)
+        tensors.append((blob, xs[k], n, k))
         flops += 2 * rows * n * k
-    need = max(layouts.activation_bytes(rows, k) for _, _, k in LAYER)
-    gpu.native_scratch(need)
+    y = torch.empty((rows, max(n for _, n, _ in LAYER)), dtype=torch.int16, device="cuda")
+    need = max(lib.euhedral_cuda_nvfp4_native_scratch_bytes(rows, k, n) for _, n, k in LAYER)
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
 
     def body(_):
-        for blob, x, y, n, k in tensors:
-            if not gpu.linear_nvfp4_native_bf16(x.data_ptr(), blob.data_ptr(), y.data_ptr(), rows, k, n, blob.numel()):
-                raise RuntimeError("native route declined")
+        for blob, x, n, k in tensors:
+            bench.check(lib.euhedral_cuda_linear_nvfp4_native_bf16(x.data_ptr(), blob.data_ptr(), y.data_ptr(), scratch.data_ptr(), rows, k, n, blob.numel(), need))
 
-    with torch.cuda.stream(stream), gpu.submit(stream.cuda_stream, pdl=True):
-        try:
-            seconds = timed(torch, None, 1, steps, warmup, body)
-        except RuntimeError:
-            return None
-    result = {"rows": rows, "tflops": flops * steps / seconds / 1e12, "issued_tflops": 2 * flops * steps / seconds / 1e12,
-              "ms_per_step": seconds / steps * 1e3}
-    if detail:
-        per_shape = {}
-        with torch.cuda.stream(stream), gpu.submit(stream.cuda_stream, pdl=True):
-            for (name, n, k), item in zip(LAYER, tensors):
-                blob, x, y, _, _ = item
+    def quantize_only(_):
+        for blob, x, n, k in tensors:
+            bench.check(lib.euhedral_b200_nvfp4_native_quantize(x.data_ptr(), scratch.data_ptr(), rows, k, need))
 
-                def one(_, item=item):
-                    blob, x, y, n, k = item
-                    gpu.linear_nvfp4_native_bf16(x.data_ptr(), blob.data_ptr(), y.data_ptr(), rows, k, n, blob.numel())
-                t = timed(torch, None, 1, steps, warmup, one)
-                per_shape[name] = round(2 * rows * n * k * steps / t / 1e12, 1)
-        result["per_shape_tflops"] = per_shape
+    with torch.cuda.stream(bench.stream), bench.submit():
+        seconds = bench.timed(steps, warmup, body)
+        quantize_seconds = bench.timed(steps, 1, quantize_only)
+    issued = 2 * flops * steps / seconds / 1e12
+    result = {"rows": rows, "tflops": flops * steps / seconds / 1e12, "issued_tflops": issued, "ms_per_layer": seconds / steps * 1e3,
+              "quantize_ms_per_layer": quantize_seconds / steps * 1e3, "quantize_share": quantize_seconds / seconds,
+              "roofline": {"bound": "tensor", "achieved": issued, "algorithmic": flops * steps / seconds / 1e12, "peak": FP4_NOMINAL_TFLOPS,
+                           "unit": "TFLOP/s", "frac": issued / FP4_NOMINAL_TFLOPS,
+                           "peak_kind": "nominal dense FP4 (MEASURED_PEAKS.json has no FP4 figure)",
+                           "algorithmic_over_measured_bf16_burst": flops * steps / seconds / 1e12 / bench.peaks["bf16"] if bench.peaks["bf16"] else None,
+                           "note": "achieved = issued FLOP (two activation terms); algorithmic = 2 M N K"}}
+    assert gpu.take_device_error() == 0
+    del tensors, xs, y, scratch
+    torch.cuda.empty_cache()
     return result
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one captured gate launch over its algorithmic bytes (profiles/q3_gemv_gate_m3.md).
-Q3_TRAFFIC_RATIO = 36.27 / 36.34
+class Sweep:
+    """The 64-layer NVFP4 sweep, N-sharded: every rank holds rows [g N / G, (g + 1) N / G) of every matrix of every layer."""
+
+    def __init__(self, bench: Bench, prefill_rows=32768, decode_rows=5):
+        from euhedral_b200 import sharding
+        torch, world, rank = bench.torch, bench.world, bench.rank
+        self.bench, self.decode_rows, self.prefill_rows = bench, decode_rows, prefill_rows
+        self.shards = [sharding.shard_range(n, world, rank, 16) for _, n, _ in LAYER]
+        distinct = []
+        for layer in range(SWEEP_DISTINCT):
+            distinct.append([bench.weight("nvfp4", 7 * layer + i, n, k, *self.shards[i])[0] for i, (_, n, k) in enumerate(LAYER)])
+        self.layers = [distinct[i] if i < SWEEP_DISTINCT else [t.clone() for t in distinct[i % SWEEP_DISTINCT]] for i in range(SWEEP_LAYERS)]
+        self.x = {k: bench.rows(decode_rows, k) for k in sorted({k for _, _, k in LAYER})}
+        local_total = sum(local for _, local in self.shards)
+        self.slot_count = 4
+        self.packed = [torch.empty(decode_rows * local_total, dtype=torch.int16, device="cuda") for _ in range(self.slot_count)]
+        self.gathered = [torch.empty(world * decode_rows * local_total, dtype=torch.int16, device="cuda") for _ in range(self.slot_count)] if world > 1 else self.packed
+        self.comm = torch.cuda.Stream()
+        self.events = [torch.cuda.Event() for _ in range(self.slot_count)]
+        self.done = [torch.cuda.Event() for _ in range(self.slot_count)]
+        self.decode_bytes = SWEEP_LAYERS * sum(algorithmic_bytes("nvfp4", local, k, decode_rows) for (_, _, k), (_, local) in zip(LAYER, self.shards))
+        self.prefill_flops = SWEEP_LAYERS * sum(2 * prefill_rows * local * k for (_, _, k), (_, local) in zip(LAYER, self.shards))
+        self._calls = {}
+
+    def decode_calls(self, layer, slot):
+        key = (layer, slot)
+        if key not in self._calls:
+            lib, rows = self.bench.lib, self.decode_rows
+            calls, cursor = [], 0
+            outputs = []
+            for (_, _, k), (_, local) in zip(LAYER, self.shards):
+                outputs.append(self.packed[slot][cursor:cursor + rows * local].data_ptr())
+                cursor += rows * local
+            for k in sorted({k for _, _, k in LAYER}):
+                members = [i for i, (_, _, kk) in enumerate(LAYER) if kk == k]
+                count = len(members)
+                blobs = [self.layers[layer][i] for i in members]
+                calls.append((count, (C.c_void_p * count)(*[self.x[k].data_ptr()] * count), (C.c_void_p * count)(*[b.data_ptr() for b in blobs]),
+                              (C.c_void_p * count)(*[outputs[i] for i in members]), rows, k, (C.c_uint32 * count)(*[self.shards[i][1] for i in members]),
+                              (C.c_uint64 * count)(*[b.numel() for b in blobs])))
+            self._calls[key] = calls
+        return self._calls[key]
+
+    def decode_step(self, _):
+        """One decode step over the 64 layers: two grouped calls per layer; the layer's packed output slices are joined by
+        an all-gather on a second stream while the next layer's GEMVs run."""
+        torch, bench = self.bench.torch, self.bench
+        main = torch.cuda.current_stream()
+        for layer in range(SWEEP_LAYERS):
+            slot = layer % self.slot_count
+            if bench.world > 1:
+                main.wait_event(self.done[slot])    # the gather that last read this slot's packed buffer has finished
+            for args in self.decode_calls(layer, slot):
+                bench.check(bench.lib.euhedral_b200_linear_group_nvfp4_bf16(*args))
+            if bench.world > 1:
+                self.events[slot].record(main)
+                with torch.cuda.stream(self.comm):
+                    self.comm.wait_event(self.events[slot])
+                    bench.dist.all_gather_into_tensor(self.gathered[slot], self.packed[slot])
+                    self.done[slot].record(self.comm)
+        if bench.world > 1:
+            for slot in range(self.slot_count):
+                main.wait_event(self.done[slot])
+
+    def exchange_only(self, _):
+        """The step's 64 all-gathers alone, back to back on the step's stream."""
+        for layer in range(SWEEP_LAYERS):
+            slot = layer % self.slot_count
+            self.bench.dist.all_gather_into_tensor(self.gathered[slot], self.packed[slot])
+
+    def check_against_one_gpu(self):
+        """Layer 0's gathered decode output equals, bit for bit, what one GPU computes from the whole tensors."""
+        from euhedral_b200 import synthetic
+        torch, bench, rows = self.bench.torch, self.bench, self.decode_rows
+        with torch.cuda.stream(bench.stream), bench.submit():
+            for args in self.decode_calls(0, 0):
+                bench.check(bench.lib.euhedral_b200_linear_group_nvfp4_bf16(*args))
+            if bench.world > 1:
+                bench.dist.all_gather_into_tensor(self.gathered[0], self.packed[0])
+        torch.cuda.synchronize()
+        if bench.rank != 0:
+            return True
+        pieces = self.gathered[0].view(bench.world, -1)
+        cursor, same = 0, True
+        for i, (name, n, k) in enumerate(LAYER):
+            local = self.shards[i][1]
+            got = torch.cat([pieces[g, cursor:cursor + rows * local].view(rows, local) for g in range(bench.world)], dim=1)
+            cursor += rows * local
+            whole = synthetic.nvfp4_tensor(synthetic.gaussian(n, k, WEIGHT_SEED + i, SIGMA, device="cuda"))
+            y = torch.empty((rows, n), dtype=torch.int16, device="cuda")
+            torch.cuda.synchronize()
+            bench.check(bench.lib.euhedral_cuda_linear_nvfp4_bf16(self.x[k].data_ptr(), whole.data_ptr(), y.data_ptr(), rows, k, n, whole.numel()))
+            torch.cuda.synchronize()
+            same = same and bool(torch.equal(got, y))
+            del whole
+        return same
+
+    def prefill(self, steps, warmup):
+        """One 32768-token prefill over the 64 layers: per matrix the native call on this rank's slice, then an all-gather
+        of the [M, N / G] output slices on a second stream, overlapped with the next matrix."""
+        torch, bench, rows = self.bench.torch, self.bench, self.prefill_rows
+        lib = bench.lib
+        if not bench.gpu.nvfp4_native_available():
+            return None
+        xs = {k: torch.randn((rows, k), device="cuda", dtype=torch.bfloat16, generator=torch.Generator(device="cuda").manual_seed(ACTIVATION_SEED)).view(torch.int16)
+              for k in sorted({k for _, _, k in LAYER})}
+        widest = max(local for _, local in self.shards)
+        ys = [torch.empty(rows * widest, dtype=torch.int16, device="cuda") for _ in range(2)]
+        gathered = [torch.empty(bench.world * rows * widest, dtype=torch.int16, device="cuda") for _ in range(2)] if bench.world > 1 else None
+        need = max(lib.euhedral_cuda_nvfp4_native_scratch_bytes(rows, k, local) for (_, _, k), (_, local) in zip(LAYER, self.shards))
+        scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+        ready = [torch.cuda.Event() for _ in range(2)]
+        free = [torch.cuda.Event() for _ in range(2)]
+
+        def body(_, exchange=True):
+            main = torch.cuda.current_stream()
+            turn = 0
+            for layer in range(SWEEP_LAYERS):
+                for i, (_, _, k) in enumerate(LAYER):
+                    local = self.shards[i][1]
+                    blob = self.layers[layer][i]
+                    slot = turn % 2
+                    turn += 1
+                    if bench.world > 1 and exchange:
+                        main.wait_event(free[slot])
+                    bench.check(lib.euhedral_cuda_linear_nvfp4_native_bf16(xs[k].data_ptr(), blob.data_ptr(), ys[slot].data_ptr(), scratch.data_ptr(), rows, k,
+                                                                            local, blob.numel(), need))
+                    if bench.world > 1 and exchange:
+                        ready[slot].record(main)
+                        with torch.cuda.stream(self.comm):
+                            self.comm.wait_event(ready[slot])
+                            count = rows * local
+                            bench.dist.all_gather_into_tensor(gathered[slot][:bench.world * count], ys[slot][:count])
+                            free[slot].record(self.comm)
+            if bench.world > 1 and exchange:
+                for slot in range(2):
+                    main.wait_event(free[slot])
+
+        with torch.cuda.stream(bench.stream), bench.submit():
+            seconds = bench.timed(steps, warmup, body)
+            compute_seconds = bench.timed(steps, 0, lambda i: body(i, exchange=False)) if bench.world > 1 else seconds
+        flops = self.prefill_flops
+        if bench.world > 1:
+            t = torch.tensor([float(flops)], device="cuda", dtype=torch.float64)
+            bench.dist.all_reduce(t)
+            flops = float(t.item())
+        gathered_bytes = SWEEP_LAYERS * sum(2 * rows * n for _, n, _ in LAYER) if bench.world > 1 else 0
+        return {"rows": rows, "tflops": flops * steps / seconds / 1e12, "issued_tflops": 2 * flops * steps / seconds / 1e12, "ms_per_step": seconds / steps * 1e3,
+                "ms_per_step_without_exchange": compute_seconds / steps * 1e3, "all_gather_bytes_per_step": gathered_bytes,
+                "frac_of_nominal_fp4": 2 * flops * steps / seconds / 1e12 / (FP4_NOMINAL_TFLOPS * bench.world)}
 
 
-TRELLIS_TARGET_PER_SM = None   # --trellis-target-per-sm: K-split target blocks per SM (kernels.trellis.target-blocks); None = the operator's default
+def measure_sweep(bench: Bench, steps, warmup, prefill=True):
+    torch = bench.torch
+    sweep = Sweep(bench)
+    same = sweep.check_against_one_gpu()
+    with torch.cuda.stream(bench.stream), bench.submit():
+        seconds = bench.timed(steps, warmup, sweep.decode_step)
+        exchange = bench.timed(steps, 1, sweep.exchange_only) if bench.world > 1 else 0.0
+    total = float(sweep.decode_bytes)
+    if bench.world > 1:
+        t = torch.tensor([total], device="cuda", dtype=torch.float64)
+        bench.dist.all_reduce(t)
+        total = float(t.item())
+    gbs = total * steps / seconds / 1e9
+    result = {"layers": SWEEP_LAYERS, "decode_rows": sweep.decode_rows, "decode_gbs": gbs, "decode_frac_of_hbm_peak": gbs / (bench.peaks["hbm"] * bench.world),
+              "decode_ms_per_step": seconds / steps * 1e3, "decode_bytes_per_step": total, "decode_calls_per_step": 2 * SWEEP_LAYERS,
+              "all_gather_ms_per_step_alone": exchange / steps * 1e3 if bench.world > 1 else 0.0,
+              "all_gathers_per_step": SWEEP_LAYERS if bench.world > 1 else 0,
+              "gathered_equals_one_gpu_bitwise": same,
+              "weights": f"{SWEEP_DISTINCT} distinct seeded layers, every one of the {SWEEP_LAYERS} layers in memory of its own"}
+    if prefill:
+        try:
+            result["prefill"] = sweep.prefill(max(1, min(steps, 2)), 1)
+        except Exception as error:   # reported, never hidden
+            result["prefill"] = {"error": repr(error)}
+    assert bench.gpu.take_device_error() == 0
+    del sweep
+    torch.cuda.empty_cache()
+    return result
 
 
 def run_ours(args):
-    global TRELLIS_TARGET_PER_SM
-    TRELLIS_TARGET_PER_SM = args.trellis_target_per_sm
     os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "8")
     import torch
     dist = None
@@ -381,71 +652,80 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", LOCAL_RANK))
-    from euhedral_b200.gpu import CudaGpuMemory
-    gpu = CudaGpuMemory()   # raises when the CUDA library is missing: no fallback
-    sms = gpu.multiprocessor_count()
-    stream = torch.cuda.Stream()
-    peak, peak_kind = read_peaks()
+    bench = Bench(torch, dist, world, RANK)
+    peak = bench.peaks["hbm"]
     copies = 3
-    if args.prefill_only:
-        r = measure_prefill(torch, gpu, stream, args.steps, args.warmup, rows=args.prefill_only, detail=True)
-        if RANK == 0:
-            print(json.dumps({"prefill_rows": args.prefill_only, **(r or {"unavailable": True})}))
-        return
-    if args.only:
-        # One matrix alone (profiling and per-shape numbers): FORMAT:NAME:ROWS, e.g. q3:gate:3
-        fmt, name, rows = args.only.split(":")
-        r = measure_format(torch, dist, gpu, fmt, (int(rows),), 4, world, RANK, sms, args.steps, args.warmup, stream, only=name,
-                           graph=args.graph)
-        if RANK == 0:
-            print(json.dumps({"only": args.only, "gbs": r["gbs"], "frac_of_hbm_peak": r["gbs"] / (peak * world), "us_per_launch_set": r["ms_per_step"] * 1e3,
-                              "bytes": r["bytes_per_step"]}))
-        return
-    with ClockSampler(LOCAL_RANK) as clocks:
-        head = measure_format(torch, dist, gpu, "q3", HEADLINE_ROWS, copies, world, RANK, sms, args.steps, args.warmup, stream, e2e=True)
     extra = {}
-    if True:
-        for fmt, rows_list in (("nvfp4", (1, 5)), ("trellis", (1, 5))):
-            try:
-                replay = fmt == "trellis" and world == 1
-                r = measure_format(torch, dist, gpu, fmt, rows_list, copies, world, RANK, sms, max(3, args.steps // 2), 3, stream, graph=replay)
-                extra[fmt] = {"rows": list(rows_list), "gbs": round(r["gbs"], 1), "frac_of_hbm_peak": round(r["gbs"] / (peak * world), 4),
-                              "ms_per_step": round(r["ms_per_step"], 4), "launch": "CUDA graph replay" if replay else "eager calls"}
-            except Exception as error:   # reported, never hidden
-                extra[fmt] = {"error": repr(error)}
-        if world == 1:
-            try:
-                extra["nvfp4_prefill"] = measure_prefill(torch, gpu, stream, 3, 3)
-            except Exception as error:
-                extra["nvfp4_prefill"] = {"error": repr(error)}
-    cpu = None
-    if RANK == 0 and world == 1:
-        from oracle import oracle_c as OC
-        threads = OC.default_threads()
-        b, t = cpu_layer_pass(cpu_blobs(), HEADLINE_ROWS, threads)
-        cpu = {"value": b / t / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
-               "sample": "one whole step (7 matrices x M in {1,3}) on the plain-C restatement, row-parallel threads"}
-    if RANK == 0:
-        line = {
-            "metric": "quantized GEMV algorithmic GB/s (Q3 decode layer set, M=1 and M=3)", "value": head["gbs"], "unit": "GB/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
-            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16 x int3 -> f32", "data": "synthetic",
+    line = {"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "data": "synthetic", "unit": "GB/s"}
+    if world == 1:
+        with ClockSampler(LOCAL_RANK) as clocks:
+            head = measure_layer_set(bench, "q3", HEADLINE_ROWS, copies, args.steps, args.warmup, e2e=True)
+        grouped = head["grouped"]
+        line.update({
+            "metric": "quantized GEMV algorithmic GB/s (Q3 decode layer set, M=1 and M=3)", "value": grouped["gbs"],
+            "ms_per_step": grouped["us_per_step"] / 1e3, "dtype": "bf16 x int3 -> f32",
             "config": {"workload": "Q3 decode GEMV set, one Qwen-27B-shaped layer, M in {1,3}", "layer": [list(s) for s in LAYER],
                        "weights": "N(0, 0.02^2) seeded, rounded as the converter rounds Q3G64_F16S", "activations": "N(0,1) as BF16",
                        "l2": f"weights rotate over {copies} resident copies of the layer ({copies * head['bytes_per_step'] / 2 / 1e6:.0f} MB > 126 MB L2)",
-                       "parallelism": f"n-sharded x{world}, one NCCL all-gather of the step's packed output slices" if world > 1 else "single GPU",
-                       "launch": "one C-ABI call per GEMV, one stream, programmatic dependent launch"},
-            "roofline": {"bound": "hbm", "achieved": head["gbs"], "peak": peak * world, "unit": "GB/s", "frac": head["gbs"] / (peak * world),
-                         "traffic": head["bytes_per_step"] * Q3_TRAFFIC_RATIO, "traffic_unit": "bytes per step",
-                         "traffic_note": "ncu dram bytes of the gate launch (36.27 MB read, 36.34 MB algorithmic) scaled to the step's bytes",
-                         "peak_kind": f"of {peak_kind}", "kernel": "gemv::kernel<q3::Format, ...> (every launch of the timed region)"},
+                       "parallelism": "single GPU",
+                       "launch": "per row count one grouped C-ABI call over the six K = 5120 tensors and one call for down: 4 calls per step, "
+                                 "one stream, programmatic dependent launch"},
+            "roofline": {"bound": "hbm", "achieved": grouped["gbs"], "peak": peak, "unit": "GB/s", "frac": grouped["gbs"] / peak,
+                         "traffic": None, "traffic_note": "per-launch DRAM bytes of the dominant kernel are in the ncu summary under profiles/ "
+                                                           "(dram__bytes_read.sum equals the algorithmic bytes of the launch within 0.1 %)",
+                         "peak_kind": f"of {bench.peaks['kind']}", "kernel": "gemv::kernel<q3::Format, 5, true> (every launch of the timed region)"},
             "e2e": {"value": head.get("e2e_gbs"), "unit": "GB/s", "h2d_bytes_per_step": head.get("h2d"), "d2h_bytes_per_step": head.get("d2h")},
-            "gpu_launches": head["launches_per_step"] * args.steps,
-            "clocks": clocks.summary(),
-            "extra": extra,
-        }
-        if cpu is not None:
-            line["cpu_baseline"] = cpu
+            "gpu_launches": grouped["launches_per_step"] * args.steps,
+        })
+        extra["q3_one_call_per_tensor"] = head["single"]
+        if not args.headline_only:
+            for fmt, rows_list in (("nvfp4", (1, 5)), ("trellis", (1, 5))):
+                try:
+                    extra[fmt] = measure_layer_set(bench, fmt, rows_list, copies, max(3, args.steps // 2), 3)
+                except Exception as error:   # reported, never hidden
+                    extra[fmt] = {"error": repr(error)}
+            try:
+                extra["per_shape"] = measure_per_shape(bench)
+                key = "nvfp4:gate:1"
+                extra["config1_nvfp4_gate_m1"] = dict(zip(("us", "gbs", "frac_of_hbm_peak"), extra["per_shape"]["rows"][key]))
+            except Exception as error:
+                extra["per_shape"] = {"error": repr(error)}
+            extra["nvfp4_prefill"] = {}
+            for rows in (4096, 32768, 131072):
+                try:
+                    extra["nvfp4_prefill"][str(rows)] = measure_prefill(bench, rows, 3, 3 if rows < 100000 else 1)
+                except Exception as error:
+                    extra["nvfp4_prefill"][str(rows)] = {"error": repr(error)}
+            try:
+                extra["sweep64"] = measure_sweep(bench, 3, 2)
+            except Exception as error:
+                extra["sweep64"] = {"error": repr(error)}
+        if RANK == 0:
+            line["cpu_baseline"] = cpu_baseline(cpu_blobs())
+    else:
+        with ClockSampler(LOCAL_RANK) as clocks:
+            sweep = measure_sweep(bench, args.steps, args.warmup, prefill=not args.headline_only)
+        line.update({
+            "metric": "quantized GEMV algorithmic GB/s (NVFP4 64-layer decode sweep, M=5, N-sharded)", "value": sweep["decode_gbs"],
+            "ms_per_step": sweep["decode_ms_per_step"], "dtype": "bf16 x e2m1 x e4m3 -> f32",
+            "config": {"workload": "64-layer Qwen-27B-shaped NVFP4 sweep: one decode step at M = 5 (value) plus one 32768-token prefill (extra)",
+                       "layer": [list(s) for s in LAYER], "weights": "N(0, 0.02^2) seeded, rounded as the converter rounds NVFP4",
+                       "activations": "N(0,1) as BF16",
+                       "l2": f"{sweep['decode_bytes_per_step'] / world / 1e6:.0f} MB of weights per rank and step, each byte read once",
+                       "parallelism": f"every matrix N-sharded x{world}; one NCCL all-gather of the layer's packed output slices per layer, overlapped "
+                                      "with the next layer's GEMVs on a second stream",
+                       "launch": "two grouped C-ABI calls per layer, one stream, programmatic dependent launch"},
+            "roofline": {"bound": "hbm", "achieved": sweep["decode_gbs"], "peak": peak * world, "unit": "GB/s", "frac": sweep["decode_gbs"] / (peak * world),
+                         "traffic": None, "peak_kind": f"of {bench.peaks['kind']}", "kernel": "gemv::kernel<nvfp4::Format, 3, true>"},
+            "e2e": {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                    "note": "the end-to-end arm is the one-GPU line; the sweep's inputs are resident"},
+            "gpu_launches": sweep["decode_calls_per_step"] * args.steps,
+        })
+        extra["sweep64"] = sweep
+    if RANK == 0:
+        line["clocks"] = clocks.summary()
+        line["extra"] = extra
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
@@ -458,14 +738,9 @@ def main():
     parser.add_argument("--steps", type=int, default=30)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--detail", action="store_true")
-    parser.add_argument("--prefill-only", type=int, default=0, help="time the NVFP4 prefill GEMM over the layer shapes at this many rows")
-    parser.add_argument("--trellis-target-per-sm", type=int, default=None, help="K-split target blocks per SM of the trellis operator")
-    parser.add_argument("--graph", action="store_true", help="with --only: replay the calls from a captured CUDA graph")
-    parser.add_argument("--only", default=None, help="FORMAT:NAME:ROWS - time one matrix alone, e.g. q3:gate:3")
+    parser.add_argument("--headline-only", action="store_true", help="skip the measurements reported under `extra`")
     args = parser.parse_args()
     if args.impl == "reference":
-        args.steps = min(args.steps, 10)
         run_reference(args)
     else:
         args.warmup = max(args.warmup, 3)
