@@ -124,8 +124,8 @@ __global__ void __launch_bounds__(128) quantize_rows(const __nv_bfloat16* __rest
                 packed[i >> 2] |= (uint32_t)pair << (8 * (i & 3));
                 const __half2_raw back = __nv_cvt_fp4x2_to_halfraw2(pair, __NV_E2M1);
                 const float2 q = __half22float2(*reinterpret_cast<const __half2*>(&back));
-                v[2 * i] = __fsub_rn(v[2 * i], __fmul_rn(q.x, step));
-                v[2 * i + 1] = __fsub_rn(v[2 * i + 1], __fmul_rn(q.y, step));
+                v[2 * i] = __fmaf_rn(-q.x, step, v[2 * i]);       // the residual in one rounding, as the reference's build contracts it
+                v[2 * i + 1] = __fmaf_rn(-q.y, step, v[2 * i + 1]);
             }
             *reinterpret_cast<uint2*>(scratch + ((uint64_t)t * rows + row) * (k / 2u) + 8u * b) = make_uint2(packed[0], packed[1]);
             sfa[((uint64_t)(row_tile * layout.k_blocks + (b >> 2)) * kTerms + t) * kAtom + atom_byte(row_in_tile, b & 3u)] = scale;

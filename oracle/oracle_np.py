@@ -7,7 +7,8 @@ source it restates (paths are relative to the reference project root).
 Pinned against: the reference's Python converter and NumPy trellis decoder run on seeded inputs (fixtures under
 tests/golden, produced by tests/golden/make_golden.py) and the reference's own golden files (GPTQ decode fixtures,
 trellis tile fixtures). The prefill activation quantizer (`quantize_activations`) restates CUDA conversion
-intrinsics for which the reference holds no bit-level vector: its parity is UNPINNED at bit level.
+intrinsics for which the reference holds no vector; it is pinned on the GPU instead, bit for bit, against the
+reference's own quantize_rows kernel compiled for sm_100a (oracle/make_ref_quantize.py, tests/test_ref_quantize_gpu.py).
 """
 
 from __future__ import annotations
@@ -493,7 +494,7 @@ def quantize_activations(x_bits: np.ndarray, terms: int = 2):
     """BF16 rows -> (codes u8 [terms, rows, K] one E2M1 code per entry, scales u8 [terms, rows, K/16], globals f32
     [rows]). native/src/nvfp4_native/native.cuh:105-168: global = amax / 2688 (1 when the row is zero); per block of
     16: scale = e4m3_satfinite(amax * (1/6) * (1/global)); code = e2m1_rn_sat(v * ((1/global) / decoded)); the next
-    term quantizes v - q * (decoded * global). All in float32."""
+    term quantizes fma(-q, decoded * global, v). All in float32."""
     x = bf16_to_f32(x_bits)
     rows, k = x.shape
     amax = np.abs(x).max(axis=1)
@@ -515,7 +516,10 @@ def quantize_activations(x_bits: np.ndarray, terms: int = 2):
         mag = e2m1_encode_magnitude(np.abs(scaled))
         sign = (np.signbit(scaled)).astype(np.uint8) << 3  # the hardware conversion keeps the sign of zero
         q = E2M1_MAGNITUDES[mag] * np.where(sign > 0, np.float32(-1), np.float32(1))
-        v = (v - (q * step[..., None]).astype(np.float32)).astype(np.float32)
+        # v - q * step in one rounding (the reference's build contracts the statement into a fused multiply-add); in
+        # float64 the product (3 x 24 bits) and the sum of two values a few binades apart are exact, so rounding the
+        # float64 result to float32 is that single rounding
+        v = (v.astype(np.float64) - q.astype(np.float64) * step[..., None].astype(np.float64)).astype(np.float32)
         codes[t] = (mag | sign).reshape(rows, k)
         scales[t] = sc
     return codes, scales, g
