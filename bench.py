@@ -13,7 +13,8 @@ and 131072 tokens, and the 64-layer NVFP4 sweep (one decode step at M = 5 plus o
 
 With --gpus N (launched under torch.distributed.run) the line's value is the decode step of that 64-layer sweep: every
 weight matrix is split along N over the ranks, each rank runs its slices of a layer into one packed buffer, and the
-slices are joined with one NCCL all-gather per layer that overlaps the next layer's GEMVs. The total work is fixed
+slices of every four layers are joined with one NCCL all-gather that overlaps the next layers' GEMVs; the step is
+replayed from a CUDA graph. The total work is fixed
 (strong scaling); `extra.sweep64` reports the prefill part and the exchange times.
 
 `--impl reference` times the CPU restatement of the reference's dequant + matmul (oracle/oracle.c) on the host cores.
@@ -50,6 +51,7 @@ SIGMA = 0.02
 L2_BYTES = 126e6
 TRELLIS_WIDTH = 48
 SWEEP_LAYERS = 64
+SWEEP_GATHER = 4            # layers whose output slices travel in one all-gather
 SWEEP_DISTINCT = 8          # distinct seeded layers of the sweep; layer i holds its own copy of the bytes of layer i % 8
 FP4_NOMINAL_TFLOPS = 9000.0
 
@@ -474,10 +476,11 @@ class Sweep:
             distinct.append([bench.weight("nvfp4", 7 * layer + i, n, k, *self.shards[i])[0] for i, (_, n, k) in enumerate(LAYER)])
         self.layers = [distinct[i] if i < SWEEP_DISTINCT else [t.clone() for t in distinct[i % SWEEP_DISTINCT]] for i in range(SWEEP_LAYERS)]
         self.x = {k: bench.rows(decode_rows, k) for k in sorted({k for _, _, k in LAYER})}
-        local_total = sum(local for _, local in self.shards)
+        # The output slices of SWEEP_GATHER consecutive layers share one packed buffer and travel in one all-gather.
+        self.layer_outputs = decode_rows * sum(local for _, local in self.shards)
         self.slot_count = 4
-        self.packed = [torch.empty(decode_rows * local_total, dtype=torch.int16, device="cuda") for _ in range(self.slot_count)]
-        self.gathered = [torch.empty(world * decode_rows * local_total, dtype=torch.int16, device="cuda") for _ in range(self.slot_count)] if world > 1 else self.packed
+        self.packed = [torch.empty(SWEEP_GATHER * self.layer_outputs, dtype=torch.int16, device="cuda") for _ in range(self.slot_count)]
+        self.gathered = [torch.empty(world * SWEEP_GATHER * self.layer_outputs, dtype=torch.int16, device="cuda") for _ in range(self.slot_count)] if world > 1 else self.packed
         self.comm = torch.cuda.Stream()
         self.events = [torch.cuda.Event() for _ in range(self.slot_count)]
         self.done = [torch.cuda.Event() for _ in range(self.slot_count)]
@@ -485,11 +488,13 @@ class Sweep:
         self.prefill_flops = SWEEP_LAYERS * sum(2 * prefill_rows * local * k for (_, _, k), (_, local) in zip(LAYER, self.shards))
         self._calls = {}
 
-    def decode_calls(self, layer, slot):
-        key = (layer, slot)
-        if key not in self._calls:
+    def decode_calls(self, layer):
+        """The two grouped C-ABI calls of a layer (K = 5120: six tensors; K = 17408: down), writing into the layer's place
+        in its gather group's packed buffer."""
+        if layer not in self._calls:
             lib, rows = self.bench.lib, self.decode_rows
-            calls, cursor = [], 0
+            slot, place = (layer // SWEEP_GATHER) % self.slot_count, layer % SWEEP_GATHER
+            calls, cursor = [], place * self.layer_outputs
             outputs = []
             for (_, _, k), (_, local) in zip(LAYER, self.shards):
                 outputs.append(self.packed[slot][cursor:cursor + rows * local].data_ptr())
@@ -501,45 +506,60 @@ class Sweep:
                 calls.append((count, (C.c_void_p * count)(*[self.x[k].data_ptr()] * count), (C.c_void_p * count)(*[b.data_ptr() for b in blobs]),
                               (C.c_void_p * count)(*[outputs[i] for i in members]), rows, k, (C.c_uint32 * count)(*[self.shards[i][1] for i in members]),
                               (C.c_uint64 * count)(*[b.numel() for b in blobs])))
-            self._calls[key] = calls
-        return self._calls[key]
+            self._calls[layer] = calls
+        return self._calls[layer]
 
     def decode_step(self, _):
-        """One decode step over the 64 layers: two grouped calls per layer; the layer's packed output slices are joined by
-        an all-gather on a second stream while the next layer's GEMVs run."""
+        """One decode step over the 64 layers: two grouped calls per layer; the packed output slices of every
+        SWEEP_GATHER layers are joined by one all-gather on a second stream while the next layers' GEMVs run."""
+        from euhedral_b200 import sharding
         torch, bench = self.bench.torch, self.bench
         main = torch.cuda.current_stream()
         for layer in range(SWEEP_LAYERS):
-            slot = layer % self.slot_count
-            if bench.world > 1:
+            slot = (layer // SWEEP_GATHER) % self.slot_count
+            if bench.world > 1 and layer % SWEEP_GATHER == 0 and layer >= SWEEP_GATHER * self.slot_count:
                 main.wait_event(self.done[slot])    # the gather that last read this slot's packed buffer has finished
-            for args in self.decode_calls(layer, slot):
+            for args in self.decode_calls(layer):
                 bench.check(bench.lib.euhedral_b200_linear_group_nvfp4_bf16(*args))
-            if bench.world > 1:
+            if bench.world > 1 and layer % SWEEP_GATHER == SWEEP_GATHER - 1:
                 self.events[slot].record(main)
                 with torch.cuda.stream(self.comm):
                     self.comm.wait_event(self.events[slot])
-                    bench.dist.all_gather_into_tensor(self.gathered[slot], self.packed[slot])
+                    sharding.gather_packed(self.packed[slot], self.gathered[slot])
                     self.done[slot].record(self.comm)
         if bench.world > 1:
             for slot in range(self.slot_count):
                 main.wait_event(self.done[slot])
 
+    def captured_step(self):
+        """The same step recorded once into a CUDA graph (plain stream capture of the same C-ABI calls and collectives) and
+        replayed: what the reference's host does with decode steps (docs/kernels/CUDA_GRAPHS.md), and the only way the
+        host keeps up with 128 launches of a few microseconds each."""
+        torch, bench = self.bench.torch, self.bench
+        for _ in range(2):
+            self.decode_step(0)   # plans, tensor maps and the collective's buffers are made before the capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=bench.stream):
+            self.decode_step(0)
+        return graph
+
     def exchange_only(self, _):
-        """The step's 64 all-gathers alone, back to back on the step's stream."""
-        for layer in range(SWEEP_LAYERS):
-            slot = layer % self.slot_count
-            self.bench.dist.all_gather_into_tensor(self.gathered[slot], self.packed[slot])
+        """The step's all-gathers alone, back to back on the step's stream."""
+        from euhedral_b200 import sharding
+        for group in range(SWEEP_LAYERS // SWEEP_GATHER):
+            slot = group % self.slot_count
+            sharding.gather_packed(self.packed[slot], self.gathered[slot])
 
     def check_against_one_gpu(self):
         """Layer 0's gathered decode output equals, bit for bit, what one GPU computes from the whole tensors."""
-        from euhedral_b200 import synthetic
+        from euhedral_b200 import sharding, synthetic
         torch, bench, rows = self.bench.torch, self.bench, self.decode_rows
         with torch.cuda.stream(bench.stream), bench.submit():
-            for args in self.decode_calls(0, 0):
+            for args in self.decode_calls(0):
                 bench.check(bench.lib.euhedral_b200_linear_group_nvfp4_bf16(*args))
             if bench.world > 1:
-                bench.dist.all_gather_into_tensor(self.gathered[0], self.packed[0])
+                sharding.gather_packed(self.packed[0], self.gathered[0])
         torch.cuda.synchronize()
         if bench.rank != 0:
             return True
@@ -561,6 +581,7 @@ class Sweep:
     def prefill(self, steps, warmup):
         """One 32768-token prefill over the 64 layers: per matrix the native call on this rank's slice, then an all-gather
         of the [M, N / G] output slices on a second stream, overlapped with the next matrix."""
+        from euhedral_b200 import sharding
         torch, bench, rows = self.bench.torch, self.bench, self.prefill_rows
         lib = bench.lib
         if not bench.gpu.nvfp4_native_available():
@@ -593,7 +614,7 @@ class Sweep:
                         with torch.cuda.stream(self.comm):
                             self.comm.wait_event(ready[slot])
                             count = rows * local
-                            bench.dist.all_gather_into_tensor(gathered[slot][:bench.world * count], ys[slot][:count])
+                            sharding.gather_packed(ys[slot][:count], gathered[slot][:bench.world * count])
                             free[slot].record(self.comm)
             if bench.world > 1 and exchange:
                 for slot in range(2):
@@ -618,7 +639,9 @@ def measure_sweep(bench: Bench, steps, warmup, prefill=True):
     sweep = Sweep(bench)
     same = sweep.check_against_one_gpu()
     with torch.cuda.stream(bench.stream), bench.submit():
-        seconds = bench.timed(steps, warmup, sweep.decode_step)
+        eager_seconds = bench.timed(max(2, steps // 3), 2, sweep.decode_step)
+        graph = sweep.captured_step()
+        seconds = bench.timed(steps, warmup, lambda _: graph.replay())
         exchange = bench.timed(steps, 1, sweep.exchange_only) if bench.world > 1 else 0.0
     total = float(sweep.decode_bytes)
     if bench.world > 1:
@@ -628,8 +651,10 @@ def measure_sweep(bench: Bench, steps, warmup, prefill=True):
     gbs = total * steps / seconds / 1e9
     result = {"layers": SWEEP_LAYERS, "decode_rows": sweep.decode_rows, "decode_gbs": gbs, "decode_frac_of_hbm_peak": gbs / (bench.peaks["hbm"] * bench.world),
               "decode_ms_per_step": seconds / steps * 1e3, "decode_bytes_per_step": total, "decode_calls_per_step": 2 * SWEEP_LAYERS,
+              "decode_launch": "the step replayed from a CUDA graph captured over the same C-ABI calls and collectives",
+              "decode_ms_per_step_eager_calls": eager_seconds / max(2, steps // 3) * 1e3,
               "all_gather_ms_per_step_alone": exchange / steps * 1e3 if bench.world > 1 else 0.0,
-              "all_gathers_per_step": SWEEP_LAYERS if bench.world > 1 else 0,
+              "all_gathers_per_step": SWEEP_LAYERS // SWEEP_GATHER if bench.world > 1 else 0,
               "gathered_equals_one_gpu_bitwise": same,
               "weights": f"{SWEEP_DISTINCT} distinct seeded layers, every one of the {SWEEP_LAYERS} layers in memory of its own"}
     if prefill:
@@ -713,9 +738,9 @@ def run_ours(args):
                        "layer": [list(s) for s in LAYER], "weights": "N(0, 0.02^2) seeded, rounded as the converter rounds NVFP4",
                        "activations": "N(0,1) as BF16",
                        "l2": f"{sweep['decode_bytes_per_step'] / world / 1e6:.0f} MB of weights per rank and step, each byte read once",
-                       "parallelism": f"every matrix N-sharded x{world}; one NCCL all-gather of the layer's packed output slices per layer, overlapped "
-                                      "with the next layer's GEMVs on a second stream",
-                       "launch": "two grouped C-ABI calls per layer, one stream, programmatic dependent launch"},
+                       "parallelism": f"every matrix N-sharded x{world}; one NCCL all-gather of the packed output slices of every {SWEEP_GATHER} layers, "
+                                      "overlapped with the next layers' GEMVs on a second stream",
+                       "launch": "two grouped C-ABI calls per layer with programmatic dependent launch, the whole step replayed from a CUDA graph"},
             "roofline": {"bound": "hbm", "achieved": sweep["decode_gbs"], "peak": peak * world, "unit": "GB/s", "frac": sweep["decode_gbs"] / (peak * world),
                          "traffic": None, "peak_kind": f"of {bench.peaks['kind']}", "kernel": "gemv::kernel<nvfp4::Format, 3, true>"},
             "e2e": {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
