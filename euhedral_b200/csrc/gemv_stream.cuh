@@ -14,7 +14,9 @@
 //     all tensors of the group form one list, cut evenly over the CTAs (clusters): a CTA walks a contiguous run of it.
 //   * A CTA's warps form teams of T; team member j owns piece j of every tile its team takes. A warp streams its pieces
 //     through a private ring of 2 or 3 shared-memory slots. A slot is filled by two tiled TMA copies signalled on one
-//     mbarrier: the piece's code bytes (16 rows x pc chunks) through a tensor map of the code plane, and the piece's
+//     mbarrier: the piece's code bytes through a tensor map of the code plane - always a box of 16 rows x P chunks, so a
+//     piece of P - 1 chunks brings one chunk it does not decode (the next piece's first, or zeros past the row): rows
+//     of P chunks keep the shared-memory loads of a warp free of bank conflicts for both piece widths - and the piece's
 //     block scales through a tensor map of the scale plane whose box is widened to start on a 16-byte boundary (the
 //     lane indexes from the remainder). The ring runs ahead across tiles and across the tensors of the group. Scale
 //     planes whose row pitch is not a multiple of 16 bytes cannot be described to TMA; their scales come by cp.async.
@@ -41,8 +43,8 @@
 //   extra_bytes(chunks)             extra shared bytes next to the activation slice
 //   stage(...)                      CTA-wide staging of the activation slice in the decode's pairing
 //   lane_scale_offset(q)            byte offset of lane q's scales within a chunk's scale bytes
-//   State                           accumulators: chunk<I, PC>(codes, scales, x) consumes chunk I of a piece of PC
-//                                   chunks given the lane's shared addresses; result(out); reset()
+//   State                           accumulators: chunk<I, W>(codes, scales, x) consumes chunk I of a piece whose box rows
+//                                   are W chunks wide, given the lane's shared addresses; result(out); reset()
 //   Finish(w, geo)                  apply(sum) = the value to round to BF16
 #pragma once
 
@@ -78,7 +80,6 @@ __host__ __device__ inline Order order_of(uint32_t k) {
 // One tensor of a group.
 struct alignas(64) Tensor {
     CUtensorMap codes;         // box: 16 rows x `piece` chunks
-    CUtensorMap codes_narrow;  // box: 16 rows x (piece - 1) chunks
     CUtensorMap scales;        // box: 16 rows x F::kScaleBox bytes
     const uint16_t* x;
     const uint8_t* w;
@@ -113,7 +114,7 @@ struct Layout {
     }
 };
 
-// The tensor maps of one weight tensor. Codes: 32-bit elements [n rows][row_bytes / 4], boxes of 16 rows x pc chunks.
+// The tensor maps of one weight tensor. Codes: 32-bit elements [n rows][row_bytes / 4], boxes of 16 rows x `piece` chunks.
 // Scales: bytes [n rows][scale_row_bytes], boxes of 16 rows x kScaleBox bytes (only when the pitch is a multiple of 16).
 template <class F>
 inline bool encode_tensor(Tensor* t, const void* weights, uint32_t n, uint32_t k, const Order& o, bool tma_scales) {
@@ -122,19 +123,11 @@ inline bool encode_tensor(Tensor* t, const void* weights, uint32_t n, uint32_t k
     const typename F::Geometry geo(n, k);
     const cuuint32_t ones[2] = {1u, 1u};
     const cuuint64_t dims[2] = {geo.row_bytes / 4u, n}, strides[1] = {geo.row_bytes};
-    for (int narrow = 0; narrow < 2; ++narrow) {
-        const uint32_t pc = o.piece - (uint32_t)narrow;
-        if (pc == 0u) {
-            t->codes_narrow = t->codes;
-            continue;
-        }
-        const cuuint32_t box[2] = {pc * F::kCodeBytes / 4u, 16u};
-        if (encode(narrow ? &t->codes_narrow : &t->codes, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(weights), dims, strides, box,
-                    ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
-                != CUDA_SUCCESS)
-            return false;
-    }
+    const cuuint32_t box[2] = {o.piece * F::kCodeBytes / 4u, 16u};
+    if (encode(&t->codes, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(weights), dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+            != CUDA_SUCCESS)
+        return false;
     if (!tma_scales) {
         t->scales = t->codes;
         return true;
@@ -165,7 +158,7 @@ __device__ __forceinline__ void decode_piece(typename F::template State<P>& stat
     state.reset();
     eb::static_for<PC>([&](auto index) {
         constexpr int I = decltype(index)::value;
-        state.template chunk<I, PC>(codes, scales, x);
+        state.template chunk<I, P>(codes, scales, x);   // the box rows are always P chunks wide
     });
     state.result(acc);
 }
@@ -294,7 +287,7 @@ __global__ void __launch_bounds__(32 * (kMaxWarps + (F::kAddingWarp ? 1 : 0)), 1
     const uint32_t code_x = piece_begin * (F::kCodeBytes / 4u);
     const uint32_t scale_byte = piece_begin * F::kScaleBytes, scale_x = scale_byte & ~15u;
     const uint32_t scale_rem = kTmaScales ? scale_byte - scale_x : 0u;
-    const uint32_t fill_bytes = 16u * (wide ? (uint32_t)P : (uint32_t)P - 1u) * F::kCodeBytes + (kTmaScales ? 16u * F::kScaleBox : 0u);
+    const uint32_t fill_bytes = 16u * (uint32_t)P * F::kCodeBytes + (kTmaScales ? 16u * F::kScaleBox : 0u);
 
     // The team's tiles: run_begin + team, + teams, ... Two cursors walk them: `ask` requests, `use` decodes.
     uint32_t ask_tile = run_begin + team, ask_slot = 0, ask_tensor = 0, ask_first = 0, ask_end = group.tensor[0].tile_end;
@@ -308,7 +301,7 @@ __global__ void __launch_bounds__(32 * (kMaxWarps + (F::kAddingWarp ? 1 : 0)), 1
             const uint32_t row = (ask_tile - ask_first) * 16u;
             const uint32_t to = slots_a + ask_slot * layout.slot_bytes, bar = bars_a + ask_slot * 8u;
             if (lane == 0) {
-                eb::tma_load_2d_expect(to, wide ? &t.codes : &t.codes_narrow, (int)code_x, (int)row, bar, fill_bytes);
+                eb::tma_load_2d_expect(to, &t.codes, (int)code_x, (int)row, bar, fill_bytes);
                 if (kTmaScales) eb::tma_load_2d_at(to + layout.code_bytes, &t.scales, (int)scale_x, (int)row, bar);
             }
             if (!kTmaScales) {
@@ -335,7 +328,7 @@ __global__ void __launch_bounds__(32 * (kMaxWarps + (F::kAddingWarp ? 1 : 0)), 1
 
     // Lane constants. Lane (g, q) decodes rows g and g + 8 of a tile; its activations are those of row min(g, rows - 1).
     const uint32_t x_lane = eb::pinned(smem_a + (g < rows ? g : rows - 1u) * layout.stride_x + q * 16u + (piece_begin - slice_begin) * 256u);
-    const uint32_t code_lane = eb::pinned(g * (wide ? (uint32_t)P : (uint32_t)P - 1u) * F::kCodeBytes);
+    const uint32_t code_lane = eb::pinned(g * (uint32_t)P * F::kCodeBytes);
     const uint32_t scale_lane = eb::pinned(layout.code_bytes + g * F::kScaleBox + scale_rem + F::lane_scale_offset(q));
     const uint32_t extra_lane = smem_a + layout.off_extra + (piece_begin - slice_begin) * (F::extra_bytes(2) - F::extra_bytes(1));
     // This lane's place in its team's two sum buffers: [buffer][member][row of the tile][activation row]; lane (g, q) holds

@@ -104,12 +104,12 @@ struct Format {
         float even[4], odd[4];
         uint32_t lane_codes;   // byte offset of the lane's 16 code bytes within a chunk
         __device__ State(uint32_t, uint32_t q) : lane_codes(eb::pinned(q * 16u)) {}
-        // codes: shared address of row g of the piece's code box (rows are PC chunks wide, row g + 8 eight rows further);
+        // codes: shared address of row g of the piece's code box (rows are W chunks wide, row g + 8 eight rows further);
         // scales: of the lane's two scale bytes of row g and the piece's first chunk (row g + 8: 8 * kScaleBox further);
         // x: of the lane's activations of the piece's first chunk.
-        template <int I, int PC>
+        template <int I, int W>
         __device__ __forceinline__ void chunk(uint32_t codes, uint32_t scales, uint32_t x) {
-            constexpr int kRow8 = 8 * PC * (int)kCodeBytes, kAt = I * (int)kCodeBytes;
+            constexpr int kRow8 = 8 * W * (int)kCodeBytes, kAt = I * (int)kCodeBytes;
             const uint4 cg = eb::lds_v4<kAt>(codes + lane_codes);
             const uint4 ch = eb::lds_v4<kAt + kRow8>(codes + lane_codes);
             const uint32_t sg = scale_pair(eb::lds_u16<I * 8>(scales)), sh = scale_pair(eb::lds_u16<I * 8 + 8 * (int)kScaleBox>(scales));

@@ -10,14 +10,16 @@
 //
 // Three launches per call, all on the selected stream, no allocation (everything lives in the caller's scratch):
 //   1. quantize_rows: BF16 rows -> code planes [term][row][K/2], block scales already in the layout tcgen05 wants
-//      (512-byte atoms of 128 rows x 4 scales, byte (r % 32) * 16 + (r / 32) * 4 + s), one FP32 scale per row.
+//      (512-byte atoms of 128 rows x 4 scales, byte (r % 32) * 16 + (r / 32) * 4 + s), one FP32 scale per row. One warp
+//      per row; a lane's unit is a K block of 64 values, whose four scales are one 4-byte store into the atom.
 //   2. repack_weight_scales: the tensor's row-major E4M3 scale plane -> the same atom layout (the scales are 1/9 of
 //      the weight bytes; the codes are consumed in place through a tensor map).
 //   3. gemm: persistent CTAs, one per SM, 128 x 256 output tiles, K in steps of 256 through a 3-stage ring.
 //      warp 0 (one lane) issues the TMA loads (codes as 128-byte-swizzled tiles, scale atoms as bulk copies),
 //      warp 1 (one lane) copies the scale atoms to tensor memory (tcgen05.cp) and issues the MMAs
 //      (M 128, N 256, K 64; two terms x four K blocks per stage) and commits to the ring's and the accumulator's
-//      mbarriers, warps 2..5 read the accumulator back (tcgen05.ld), scale, round and store BF16.
+//      mbarriers, warps 2..9 drain the accumulator into registers (tcgen05.ld), hand it back at once, then scale, round
+//      and store BF16 while the next tile's MMAs already run.
 // Tiles are walked in panels of eight tile columns with the row index fastest, so that CTAs running together share
 // weight tiles and re-read activation tiles from L2. Every CTA issues its own loads; there is no cluster.
 #pragma once
@@ -41,7 +43,7 @@ constexpr uint32_t kSfbStage = (kStepK / kBlockK) * (kTileN / 128u) * kAtom;
 constexpr uint32_t kStageBytes = kTerms * kATile + kBTile + kSfaStage + kSfbStage;
 constexpr uint32_t kBarrierBytes = 128u;
 constexpr uint32_t kSharedBytes = kStages * kStageBytes + kBarrierBytes + 1024u;   // + slack to align to 1024
-constexpr uint32_t kThreads = 192u;
+constexpr uint32_t kThreads = 320u;                         // TMA warp, MMA warp, eight epilogue warps
 constexpr uint32_t kTmemColumns = 512u;
 constexpr uint32_t kTmemSfa = 256u, kTmemSfb = 288u;       // column offsets behind the 256 accumulator columns
 constexpr uint32_t kPanel = 8u;                            // tile columns per panel of the tile walk
@@ -69,69 +71,90 @@ __host__ __device__ inline uint32_t atom_byte(uint32_t row_in_tile, uint32_t sca
 }
 
 // ---- 1. activation quantizer -----------------------------------------------------------------------------------------
-// One CTA per row. global = amax / (6 * 448) (1 for a zero row); per block of 16: scale = e4m3_satfinite(amax / 6 /
-// global); codes = e2m1_rn(v / (scale * global)), saturating; the next term quantizes v - decoded. All in FP32 with the
-// hardware conversions, in the order of native/src/nvfp4_native/native.cuh:105-127.
-__global__ void __launch_bounds__(128) quantize_rows(const __nv_bfloat16* __restrict__ input, uint8_t* __restrict__ scratch,
+// The arithmetic is the reference's, operation for operation (native/src/nvfp4_native/native.cuh:105-127, pinned bit for
+// bit against that kernel compiled for this GPU): global = amax / (6 * 448) (1 for a zero row); per block of 16:
+// scale = e4m3_satfinite(amax * (1/6) * (1/global)); codes = e2m1_rn(v * ((1/global) / scale)), saturating; the next term
+// quantizes fma(-decoded, scale * global, v). All in FP32 with the hardware conversions.
+// The work split is this kernel's own: one warp per row, eight rows per CTA, no shared memory and no CTA barrier. A lane
+// takes whole K blocks of 64 values (128 bytes in): per term it leaves with two 16-byte code stores and ONE 4-byte store
+// of the block's four scales, which is exactly one row's entry of the 512-byte atom tcgen05 reads.
+constexpr uint32_t kQuantizeWarps = 8;
+
+// One block of 16 values: its scale code, its 8 code bytes, and v replaced by the residual.
+__device__ __forceinline__ uint32_t quantize_block(float (&v)[16], float global, float inverse_global, uint2* codes) {
+    float block_max = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) block_max = fmaxf(block_max, fabsf(v[i]));
+    const __nv_fp8_storage_t scale = __nv_cvt_float_to_fp8(__fmul_rn(__fmul_rn(block_max, 1.0f / 6.0f), inverse_global), __NV_SATFINITE, __NV_E4M3);
+    const float decoded = __half2float(__half(__nv_cvt_fp8_to_halfraw(scale, __NV_E4M3)));
+    const float inverse = decoded > 0.0f ? __fdiv_rn(inverse_global, decoded) : 0.0f;
+    const float step = __fmul_rn(decoded, global);
+    uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const __nv_fp4x2_storage_t pair = __nv_cvt_float2_to_fp4x2(
+                make_float2(__fmul_rn(v[2 * i], inverse), __fmul_rn(v[2 * i + 1], inverse)), __NV_E2M1, cudaRoundNearest);
+        packed[i >> 2] |= (uint32_t)pair << (8 * (i & 3));
+        const __half2_raw back = __nv_cvt_fp4x2_to_halfraw2(pair, __NV_E2M1);
+        const float2 q = __half22float2(*reinterpret_cast<const __half2*>(&back));
+        v[2 * i] = __fmaf_rn(-q.x, step, v[2 * i]);       // the residual in one rounding, as the reference's build contracts it
+        v[2 * i + 1] = __fmaf_rn(-q.y, step, v[2 * i + 1]);
+    }
+    *codes = make_uint2(packed[0], packed[1]);
+    return (uint32_t)scale;
+}
+
+__global__ void __launch_bounds__(32 * kQuantizeWarps) quantize_rows(const __nv_bfloat16* __restrict__ input, uint8_t* __restrict__ scratch,
         uint32_t rows, uint32_t k) {
-    const uint32_t row = blockIdx.x;
+    const uint32_t lane = threadIdx.x & 31u, row = blockIdx.x * kQuantizeWarps + (threadIdx.x >> 5);
     const ActivationLayout layout(rows, k);
-    const uint32_t blocks = k / 16u;
-    const __nv_bfloat16* x = input + (uint64_t)row * k;
     eb::pdl_launch_dependents();
     eb::pdl_wait();
+    if (row >= rows) return;
+    const uint4* x = reinterpret_cast<const uint4*>(input + (uint64_t)row * k);   // 8 values per element
+    const uint32_t vectors = k / 8u, blocks64 = k / kBlockK;
     float amax = 0.0f;
-    for (uint32_t b = threadIdx.x; b < blocks; b += 128u) {
-        const uint4 lo = *reinterpret_cast<const uint4*>(x + 16u * b), hi = *reinterpret_cast<const uint4*>(x + 16u * b + 8u);
-        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    for (uint32_t i = lane; i < vectors; i += 32u) {
+        const uint4 w = x[i];
+        const uint32_t words[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-            amax = fmaxf(amax, fmaxf(fabsf(eb::bf16_bits_to_float(words[i] & 0xFFFFu)), fabsf(__uint_as_float(words[i] & 0xFFFF0000u))));
+        for (int j = 0; j < 4; ++j)
+            amax = fmaxf(amax, fmaxf(fabsf(eb::bf16_bits_to_float(words[j] & 0xFFFFu)), fabsf(__uint_as_float(words[j] & 0xFFFF0000u))));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    __shared__ float warp_max[4];
-    if ((threadIdx.x & 31u) == 0) warp_max[threadIdx.x >> 5] = amax;
-    __syncthreads();
-    amax = fmaxf(fmaxf(warp_max[0], warp_max[1]), fmaxf(warp_max[2], warp_max[3]));
     const float global = amax > 0.0f ? __fdiv_rn(amax, 6.0f * 448.0f) : 1.0f;
     const float inverse_global = __fdiv_rn(1.0f, global);
-    uint8_t* sfa = scratch + layout.sfa_offset;
-    const uint32_t row_tile = row / kTileM, row_in_tile = row % kTileM;
-    for (uint32_t b = threadIdx.x; b < blocks; b += 128u) {
-        float v[16];
-        const uint4 lo = *reinterpret_cast<const uint4*>(x + 16u * b), hi = *reinterpret_cast<const uint4*>(x + 16u * b + 8u);
-        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    uint8_t* sfa = scratch + layout.sfa_offset + (uint64_t)(row / kTileM) * layout.k_blocks * kTerms * kAtom + atom_byte(row % kTileM, 0);
+    const uint64_t plane = (uint64_t)rows * (k / 2u);
+    uint8_t* codes_row = scratch + (uint64_t)row * (k / 2u);
+    for (uint32_t b = lane; b < blocks64; b += 32u) {   // the row was just read: these loads hit L1 / L2
+        uint4 raw[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            v[2 * i] = eb::bf16_bits_to_float(words[i] & 0xFFFFu);
-            v[2 * i + 1] = __uint_as_float(words[i] & 0xFFFF0000u);
+        for (int i = 0; i < 8; ++i) raw[i] = x[8u * b + i];
+        uint2 codes[kTerms][4];
+        uint32_t scales[kTerms] = {0u, 0u};
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            const uint32_t words[8] = {raw[2 * s].x, raw[2 * s].y, raw[2 * s].z, raw[2 * s].w, raw[2 * s + 1].x, raw[2 * s + 1].y, raw[2 * s + 1].z, raw[2 * s + 1].w};
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[2 * i] = eb::bf16_bits_to_float(words[i] & 0xFFFFu);
+                v[2 * i + 1] = __uint_as_float(words[i] & 0xFFFF0000u);
+            }
+#pragma unroll
+            for (uint32_t t = 0; t < kTerms; ++t) scales[t] |= quantize_block(v, global, inverse_global, &codes[t][s]) << (8 * s);
         }
 #pragma unroll
         for (uint32_t t = 0; t < kTerms; ++t) {
-            float block_max = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) block_max = fmaxf(block_max, fabsf(v[i]));
-            const __nv_fp8_storage_t scale = __nv_cvt_float_to_fp8(__fmul_rn(__fmul_rn(block_max, 1.0f / 6.0f), inverse_global), __NV_SATFINITE, __NV_E4M3);
-            const float decoded = __half2float(__half(__nv_cvt_fp8_to_halfraw(scale, __NV_E4M3)));
-            const float inverse = decoded > 0.0f ? __fdiv_rn(inverse_global, decoded) : 0.0f;
-            const float step = __fmul_rn(decoded, global);
-            uint32_t packed[2] = {0u, 0u};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const __nv_fp4x2_storage_t pair = __nv_cvt_float2_to_fp4x2(
-                        make_float2(__fmul_rn(v[2 * i], inverse), __fmul_rn(v[2 * i + 1], inverse)), __NV_E2M1, cudaRoundNearest);
-                packed[i >> 2] |= (uint32_t)pair << (8 * (i & 3));
-                const __half2_raw back = __nv_cvt_fp4x2_to_halfraw2(pair, __NV_E2M1);
-                const float2 q = __half22float2(*reinterpret_cast<const __half2*>(&back));
-                v[2 * i] = __fmaf_rn(-q.x, step, v[2 * i]);       // the residual in one rounding, as the reference's build contracts it
-                v[2 * i + 1] = __fmaf_rn(-q.y, step, v[2 * i + 1]);
-            }
-            *reinterpret_cast<uint2*>(scratch + ((uint64_t)t * rows + row) * (k / 2u) + 8u * b) = make_uint2(packed[0], packed[1]);
-            sfa[((uint64_t)(row_tile * layout.k_blocks + (b >> 2)) * kTerms + t) * kAtom + atom_byte(row_in_tile, b & 3u)] = scale;
+            uint4* out = reinterpret_cast<uint4*>(codes_row + t * plane + 32u * b);
+            out[0] = make_uint4(codes[t][0].x, codes[t][0].y, codes[t][1].x, codes[t][1].y);
+            out[1] = make_uint4(codes[t][2].x, codes[t][2].y, codes[t][3].x, codes[t][3].y);
+            *reinterpret_cast<uint32_t*>(sfa + ((uint64_t)b * kTerms + t) * kAtom) = scales[t];
         }
     }
-    if (threadIdx.x == 0) reinterpret_cast<float*>(scratch + layout.global_offset)[row] = global;
+    if (lane == 0) reinterpret_cast<float*>(scratch + layout.global_offset)[row] = global;
 }
 
 // ---- 2. weight scale repack ---------------------------------------------------------------------------------------------
@@ -195,6 +218,18 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// 32 consecutive accumulator columns of the calling warp's 32 lanes (one row per thread) into registers.
+__device__ __forceinline__ void tmem_load_32(uint32_t (&r)[32], uint32_t address) {
+    asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+            "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+              "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+              "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+              "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(address));
+}
+
 struct TileWalk {
     uint32_t tiles_m, tiles_n, total;
     __device__ TileWalk(uint32_t rows, uint32_t n) : tiles_m((rows + kTileM - 1u) / kTileM), tiles_n((n + kTileN - 1u) / kTileN) {
@@ -231,7 +266,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             eb::mbar_init(&empty[s], 1);
         }
         eb::mbar_init(acc_full, 1);
-        eb::mbar_init(acc_empty, 4);
+        eb::mbar_init(acc_empty, 8);
         eb::mbar_fence_init();
     }
     if (warp == 1) {
@@ -311,8 +346,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             }
         }
     } else {
-        // Epilogue: warp w reads the 32 accumulator rows of lane quarter w % 4.
-        const uint32_t quarter = warp & 3u;
+        // Epilogue: warp w may read the 32 accumulator rows of lane quarter w % 4 only; warps 2..5 take columns 0..127 of
+        // their quarter, warps 6..9 columns 128..255. A warp first drains its 32 x 128 block into registers and hands the
+        // accumulator back (the MMA warp starts the next tile while this one is scaled, rounded and stored).
+        const uint32_t quarter = warp & 3u, half = (warp - 2u) >> 2;
         const float scale_w = *tensor_global;
         uint32_t local = 0;
         for (uint32_t tile = blockIdx.x; tile < walk.total; tile += gridDim.x, ++local) {
@@ -323,21 +360,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 break;
             }
             tcgen05_fence_after();
+            uint32_t r[4][32];
+            const uint32_t from = tmem + ((quarter * 32u) << 16) + half * 128u;
+            tmem_load_32(r[0], from);
+            tmem_load_32(r[1], from + 32u);
+            tmem_load_32(r[2], from + 64u);
+            tmem_load_32(r[3], from + 96u);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) eb::mbar_arrive(acc_empty);
             const uint32_t row = tm * kTileM + quarter * 32u + lane;
             const float scale = row < rows ? __fmul_rn(row_globals[row], scale_w) : 0.0f;
-#pragma unroll 1
-            for (uint32_t cb = 0; cb < kTileN / 32u; ++cb) {
-                uint32_t r[32];
-                asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
-                        "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-                          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-                          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-                          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                        : "r"(tmem + ((quarter * 32u) << 16) + cb * 32u));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const uint32_t col = tn * kTileN + cb * 32u;
+#pragma unroll
+            for (uint32_t cb = 0; cb < 4u; ++cb) {
+                const uint32_t col = tn * kTileN + half * 128u + cb * 32u;
                 if (row < rows && col < n) {
                     uint16_t* dst = out + (uint64_t)row * n + col;
 #pragma unroll
@@ -345,16 +382,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                         uint32_t packed[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const float lo = __fmul_rn(__uint_as_float(r[8 * v + 2 * i]), scale), hi = __fmul_rn(__uint_as_float(r[8 * v + 2 * i + 1]), scale);
+                            const float lo = __fmul_rn(__uint_as_float(r[cb][8 * v + 2 * i]), scale), hi = __fmul_rn(__uint_as_float(r[cb][8 * v + 2 * i + 1]), scale);
                             packed[i] = (uint32_t)eb::float_to_bf16_bits(lo) | (uint32_t)eb::float_to_bf16_bits(hi) << 16;
                         }
                         if (col + 8u * v < n) *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     }
                 }
             }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) eb::mbar_arrive(acc_empty);
         }
     }
     tcgen05_fence_before();
@@ -392,7 +426,8 @@ inline cudaError_t launch_on(cudaStream_t stream, bool pdl, void (*kernel)(Param
 // scratch aligned to 16 bytes and at least ActivationLayout(rows, k, out_features).bytes long.
 // quantize: BF16 rows -> the activation part of the scratch (code planes, scale atoms, row scales).
 inline cudaError_t quantize(const void* input, void* scratch, uint32_t rows, uint32_t k, cudaStream_t stream, bool pdl) {
-    return launch_on(stream, pdl, quantize_rows, dim3(rows), dim3(128), 0, static_cast<const __nv_bfloat16*>(input), static_cast<uint8_t*>(scratch), rows, k);
+    return launch_on(stream, pdl, quantize_rows, dim3((rows + kQuantizeWarps - 1u) / kQuantizeWarps), dim3(32u * kQuantizeWarps), 0,
+            static_cast<const __nv_bfloat16*>(input), static_cast<uint8_t*>(scratch), rows, k);
 }
 
 // multiply: the weight scale plane -> scale atoms in the scratch, then the GEMM over the quantized activations found there.

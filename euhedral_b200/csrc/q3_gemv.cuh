@@ -170,12 +170,12 @@ struct Format {
             : bias_lane(eb::pinned(extra + q * 16u)), first_word(eb::pinned(((q >> 1) * 3u + (q & 1u) * 2u) * 4u)),
               second_word(eb::pinned(((q >> 1) * 3u + 1u) * 4u)), select_low(eb::pinned((q & 1u) ? 0x1076u : 0x3210u)),
               select_high(eb::pinned((q & 1u) ? 0x3232u : 0x7654u)) {}
-        // codes: shared address of row g of the piece's code box (rows are PC chunks wide, row g + 8 eight rows further);
+        // codes: shared address of row g of the piece's code box (rows are W chunks wide, row g + 8 eight rows further);
         // scales: of the two FP16 scales of row g and the piece's first chunk (row g + 8: 8 * kScaleBox further);
         // x: of the lane's activations of the piece's first chunk.
-        template <int I, int PC>
+        template <int I, int W>
         __device__ __forceinline__ void chunk(uint32_t codes, uint32_t scales, uint32_t x) {
-            constexpr int kRow8 = 8 * PC * (int)kCodeBytes, kAt = I * (int)kCodeBytes;
+            constexpr int kRow8 = 8 * W * (int)kCodeBytes, kAt = I * (int)kCodeBytes;
             const uint32_t scales_g = eb::lds_u32<I * 4>(scales), scales_h = eb::lds_u32<I * 4 + 8 * (int)kScaleBox>(scales);
             const float2 sg2 = __half22float2(*reinterpret_cast<const __half2*>(&scales_g));
             const float2 sh2 = __half22float2(*reinterpret_cast<const __half2*>(&scales_h));

@@ -176,7 +176,59 @@ def trellis_cases():
     np.savez_compressed(HERE / "trellis.npz", **out)
 
 
+def edrl_fixture():
+    """A small EDRL v2 container written with the reference's own table encoder and offset assignment
+    (tools/euhedral_artifacts/edrl.py; the header is packed as tools/euhedral_artifacts/pipeline.py:90-91 packs it),
+    holding an NVFP4 and a Q3 linear rounded by the reference's converter, a BF16 norm vector and an I32 vector."""
+    import struct
+    from euhedral_artifacts import edrl
+    rng = np.random.default_rng(0xED)
+    payloads, plans = {}, []
+
+    def plan(name, shape, dtype, fmt, layout, blob):
+        payloads[name] = blob
+        plans.append(edrl.ObjectPlan(name=name, shape=tuple(shape), source_dtype=dtype, format_name=fmt, layout=layout,
+                                     byte_size=len(blob), writer=None))
+
+    w4 = (rng.standard_normal((64, 512)) * 0.02).astype(np.float32)
+    buffer = io.BytesIO()
+    nvfp4.quantize_nvfp4_matrix(buffer, 0, matrix_source(w4))
+    plan("model.layers.0.mlp.down_proj.weight", w4.shape, "BF16", "NVFP4", "row-split-k128-v1",
+         buffer.getvalue().ljust(nvfp4.nvfp4_offsets(w4.shape)[2], b"\0"))
+    w3 = (rng.standard_normal((32, 1024)) * 0.02).astype(np.float32)
+    buffer = io.BytesIO()
+    grouped.quantize_matrix(buffer, 0, matrix_source(w3), "Q3G64_F16S")
+    plan("model.layers.0.self_attn.k_proj.weight", w3.shape, "BF16", "Q3G64_F16S", "row-split-k128-v1",
+         buffer.getvalue().ljust(grouped.row_split_size(w3.shape, "Q3G64_F16S"), b"\0"))
+    norm = (rng.standard_normal(1024).astype(np.float32).view(np.uint32) >> 16).astype("<u2")
+    plan("model.norm.weight", (1024,), "BF16", "BF16", "contiguous-le-v1", norm.tobytes())
+    ids = rng.integers(0, 1000, 17).astype("<i4")
+    plan("draft.token_ids", (17,), "INT32", "I32", "contiguous-le-v1", ids.tobytes())
+    metadata = b'{"format":"edrl-fixture","layers":1}'
+    table_size = len(edrl.encode_table(plans))
+    data_base = edrl.HEADER_SIZE + len(metadata) + table_size
+    file_size = edrl.assign_offsets(plans, data_base)
+    table = edrl.encode_table(plans)
+    header = struct.pack(edrl.HEADER_FORMAT, edrl.MAGIC, edrl.VERSION, edrl.HEADER_SIZE, len(metadata), edrl.HEADER_SIZE + len(metadata),
+                         len(plans), 0, data_base)
+    image = bytearray(file_size)
+    image[:len(header)] = header
+    image[edrl.HEADER_SIZE:edrl.HEADER_SIZE + len(metadata)] = metadata
+    image[edrl.HEADER_SIZE + len(metadata):data_base] = table
+    for item in plans:
+        image[item.offset:item.offset + item.byte_size] = payloads[item.name]
+    (HERE / "tiny.edrl").write_bytes(bytes(image))
+    with (HERE / "tiny.edrl").open("rb") as handle:      # the reference's own reader accepts it
+        _, _, objects = edrl.read_table(handle)
+    out = {"nvfp4_weights": w4, "q3_weights": w3, "norm": norm, "ids": ids,
+           "names": np.array([o["name"] for o in objects]), "offsets": np.array([o["offset"] for o in objects], dtype=np.int64),
+           "sizes": np.array([o["bytes"] for o in objects], dtype=np.int64),
+           "formats": np.array([o["format"] for o in objects], dtype=np.int64), "layouts": np.array([o["layout"] for o in objects], dtype=np.int64)}
+    np.savez_compressed(HERE / "edrl.npz", **out)
+
+
 if __name__ == "__main__":
+    edrl_fixture()
     nvfp4_cases()
     q3_cases()
     gptq_fixture_subset()
