@@ -28,6 +28,8 @@
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace nvfp4n {
@@ -51,8 +53,12 @@ constexpr uint32_t kPanel = 8u;                            // tile columns per p
 __host__ __device__ inline uint64_t align256(uint64_t v) { return (v + 255ull) & ~255ull; }
 
 // Caller scratch of one native linear.
+// Calls of at most kSkinnyRows rows (one row tile) may cut K over up to kMaxSplits CTAs per output tile, so that a call
+// with few output tiles still uses every SM; the FP32 partial tiles go to the end of the scratch.
+constexpr uint32_t kSkinnyRows = 64, kMaxSplits = 8;
+
 struct ActivationLayout {
-    uint64_t sfa_offset, global_offset, sfb_offset, bytes;
+    uint64_t sfa_offset, global_offset, sfb_offset, partial_offset, bytes;
     uint32_t row_tiles, k_blocks;
     __host__ __device__ ActivationLayout(uint32_t rows, uint32_t k, uint32_t out_features = 0) {
         const uint64_t kp = ((uint64_t)k + 127u) / 128u * 128u;
@@ -62,7 +68,8 @@ struct ActivationLayout {
         global_offset = align256(sfa_offset + (uint64_t)row_tiles * k_blocks * kTerms * kAtom);
         sfb_offset = align256(global_offset + 4ull * rows);
         const uint64_t n128 = ((uint64_t)out_features + 255u) / 256u * 2u;
-        bytes = sfb_offset + n128 * k_blocks * kAtom;
+        partial_offset = align256(sfb_offset + n128 * k_blocks * kAtom);
+        bytes = rows <= kSkinnyRows && out_features != 0u ? partial_offset + (uint64_t)kMaxSplits * rows * out_features * 4u : partial_offset;
     }
 };
 
@@ -247,8 +254,8 @@ struct TileWalk {
 
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, const float* __restrict__ row_globals,
-        const float* __restrict__ tensor_global, uint16_t* __restrict__ out, uint32_t rows, uint32_t n, uint32_t k,
-        uint32_t* __restrict__ error) {
+        const float* __restrict__ tensor_global, uint16_t* __restrict__ out, float* __restrict__ partials, uint32_t splits, uint32_t rows,
+        uint32_t n, uint32_t k, uint32_t* __restrict__ error) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -259,6 +266,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const TileWalk walk(rows, n);
     const uint32_t k_steps = k / kStepK, k_blocks = k / kBlockK;
+    // A work item is an output tile and one of `splits` ranges of its K steps (one range unless the call is skinny).
+    const uint32_t items = walk.total * splits;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
@@ -284,10 +293,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         if (lane == 0) {
             uint32_t step = 0;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < walk.total && ok; tile += gridDim.x) {
+            for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
                 uint32_t tm, tn;
-                walk.at(tile, &tm, &tn);
-                for (uint32_t ks = 0; ks < k_steps; ++ks, ++step) {
+                walk.at(item / splits, &tm, &tn);
+                const uint32_t split = item % splits, ks_end = (split + 1u) * k_steps / splits;
+                for (uint32_t ks = split * k_steps / splits; ks < ks_end; ++ks, ++step) {
                     const uint32_t s = step % kStages, round = step / kStages;
                     if (round > 0 && !eb::mbar_wait(&empty[s], (round - 1u) & 1u)) {
                         atomicOr(error, 8u);
@@ -310,13 +320,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         if (lane == 0) {
             uint32_t step = 0, local = 0;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < walk.total && ok; tile += gridDim.x, ++local) {
+            for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x, ++local) {
                 if (local > 0 && !eb::mbar_wait(acc_empty, (local - 1u) & 1u)) {
                     atomicOr(error, 8u);
                     break;
                 }
                 tcgen05_fence_after();
-                for (uint32_t ks = 0; ks < k_steps; ++ks, ++step) {
+                const uint32_t split = item % splits, ks_begin = split * k_steps / splits, ks_end = (split + 1u) * k_steps / splits;
+                for (uint32_t ks = ks_begin; ks < ks_end; ++ks, ++step) {
                     const uint32_t s = step % kStages, round = step / kStages;
                     if (!eb::mbar_wait(&full[s], round & 1u)) {
                         atomicOr(error, 8u);
@@ -337,7 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 #pragma unroll
                     for (uint32_t j = 0; j < 4u; ++j) {
                         // A K block of 64 values is 32 bytes further along the swizzled row: + 2 in descriptor units.
-                        mma_block_scaled(tmem, a0 + 2u * j, b + 2u * j, tmem + kTmemSfa + (j * 2u) * 4u, tmem + kTmemSfb + j * 8u, (ks | j) != 0u);
+                        mma_block_scaled(tmem, a0 + 2u * j, b + 2u * j, tmem + kTmemSfa + (j * 2u) * 4u, tmem + kTmemSfb + j * 8u, ((ks - ks_begin) | j) != 0u);
                         mma_block_scaled(tmem, a1 + 2u * j, b + 2u * j, tmem + kTmemSfa + (j * 2u + 1u) * 4u, tmem + kTmemSfb + j * 8u, 1u);
                     }
                     mma_commit(&empty[s]);
@@ -352,9 +363,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         const uint32_t quarter = warp & 3u, half = (warp - 2u) >> 2;
         const float scale_w = *tensor_global;
         uint32_t local = 0;
-        for (uint32_t tile = blockIdx.x; tile < walk.total; tile += gridDim.x, ++local) {
+        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++local) {
             uint32_t tm, tn;
-            walk.at(tile, &tm, &tn);
+            walk.at(item / splits, &tm, &tn);
             if (!eb::mbar_wait(acc_full, local & 1u)) {
                 if (lane == 0) atomicOr(error, 8u);
                 break;
@@ -375,7 +386,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 #pragma unroll
             for (uint32_t cb = 0; cb < 4u; ++cb) {
                 const uint32_t col = tn * kTileN + half * 128u + cb * 32u;
-                if (row < rows && col < n) {
+                if (splits > 1u) {
+                    // the raw FP32 sums of this K range: partials[split][row][n]; finish_splits adds the ranges in order
+                    if (row < rows && col < n) {
+                        float4* dst = reinterpret_cast<float4*>(partials + ((uint64_t)(item % splits) * rows + row) * n + col);
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            if (col + 4u * v < n)
+                                dst[v] = make_float4(__uint_as_float(r[cb][4 * v]), __uint_as_float(r[cb][4 * v + 1]), __uint_as_float(r[cb][4 * v + 2]),
+                                        __uint_as_float(r[cb][4 * v + 3]));
+                    }
+                } else if (row < rows && col < n) {
                     uint16_t* dst = out + (uint64_t)row * n + col;
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
@@ -396,6 +417,29 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
     }
+}
+
+// Skinny calls: out[row][col] = bf16((sum over the K ranges in order) * row scale * tensor scale). One thread per 4 columns.
+__global__ void __launch_bounds__(256) finish_splits(const float* __restrict__ partials, const float* __restrict__ row_globals,
+        const float* __restrict__ tensor_global, uint16_t* __restrict__ out, uint32_t splits, uint32_t rows, uint32_t n) {
+    const uint64_t index = (uint64_t)blockIdx.x * 256u + threadIdx.x;
+    eb::pdl_launch_dependents();
+    eb::pdl_wait();
+    const uint32_t quads = n / 4u;
+    if (index >= (uint64_t)rows * quads) return;
+    const uint32_t row = (uint32_t)(index / quads), col = (uint32_t)(index % quads) * 4u;
+    float4 sum = *reinterpret_cast<const float4*>(partials + (uint64_t)row * n + col);
+    for (uint32_t s = 1; s < splits; ++s) {
+        const float4 part = *reinterpret_cast<const float4*>(partials + ((uint64_t)s * rows + row) * n + col);
+        sum.x = __fadd_rn(sum.x, part.x);
+        sum.y = __fadd_rn(sum.y, part.y);
+        sum.z = __fadd_rn(sum.z, part.z);
+        sum.w = __fadd_rn(sum.w, part.w);
+    }
+    const float scale = __fmul_rn(row_globals[row], *tensor_global);
+    const uint32_t lo = (uint32_t)eb::float_to_bf16_bits(__fmul_rn(sum.x, scale)) | (uint32_t)eb::float_to_bf16_bits(__fmul_rn(sum.y, scale)) << 16;
+    const uint32_t hi = (uint32_t)eb::float_to_bf16_bits(__fmul_rn(sum.z, scale)) | (uint32_t)eb::float_to_bf16_bits(__fmul_rn(sum.w, scale)) << 16;
+    *reinterpret_cast<uint2*>(out + (uint64_t)row * n + col) = make_uint2(lo, hi);
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------------------
@@ -459,10 +503,20 @@ inline cudaError_t multiply(const void* weights, void* output, void* scratch, ui
             out_features, layout.k_blocks, n_padded);
     if (e != cudaSuccess) return e;
     const uint32_t tiles = ((rows + kTileM - 1u) / kTileM) * ((out_features + kTileN - 1u) / kTileN);
-    const uint32_t grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
-    return launch_on(stream, pdl, gemm_kernel, dim3(grid), dim3(kThreads), kSharedBytes, map_a, map_b, base + layout.sfa_offset,
-            base + layout.sfb_offset, reinterpret_cast<const float*>(base + layout.global_offset), reinterpret_cast<const float*>(w + global_offset),
-            static_cast<uint16_t*>(output), rows, out_features, k, error);
+    // The skinny route (the reference's 9..64-row kernel, native/src/nvfp4_native/native.cuh:435-585, cuts K the same way):
+    // few rows make few output tiles; K is cut so that about every SM gets a work item.
+    uint32_t splits = 1;
+    if (rows <= kSkinnyRows && tiles * 2u <= (uint32_t)sms) splits = std::max(1u, std::min(std::min(kMaxSplits, k / kStepK), (uint32_t)sms / tiles));
+    const uint32_t work = tiles * splits, grid = work < (uint32_t)sms ? work : (uint32_t)sms;
+    float* partials = reinterpret_cast<float*>(base + layout.partial_offset);
+    const float* row_globals = reinterpret_cast<const float*>(base + layout.global_offset);
+    const float* tensor_global = reinterpret_cast<const float*>(w + global_offset);
+    e = launch_on(stream, pdl, gemm_kernel, dim3(grid), dim3(kThreads), kSharedBytes, map_a, map_b, base + layout.sfa_offset,
+            base + layout.sfb_offset, row_globals, tensor_global, static_cast<uint16_t*>(output), partials, splits, rows, out_features, k, error);
+    if (e != cudaSuccess || splits == 1u) return e;
+    const uint64_t quads = (uint64_t)rows * (out_features / 4u);
+    return launch_on(stream, pdl, finish_splits, dim3((unsigned)((quads + 255u) / 256u)), dim3(256), 0, partials, row_globals, tensor_global,
+            static_cast<uint16_t*>(output), splits, rows, out_features);
 }
 
 inline cudaError_t run(const void* input, const void* weights, void* output, void* scratch, uint32_t rows, uint32_t k, uint32_t out_features,

@@ -80,7 +80,9 @@ def test_native_scratch_covers_every_region():
         codes = layouts.align_up(2 * rows * k // 2, 256)
         atoms_a = -(-rows // 128) * (k // 64) * 2 * 512
         atoms_b = -(-n // 256) * 2 * (k // 64) * 512
-        assert need == layouts.align_up(layouts.align_up(codes + atoms_a, 256) + 4 * rows, 256) + atoms_b
+        fixed = layouts.align_up(layouts.align_up(layouts.align_up(codes + atoms_a, 256) + 4 * rows, 256) + atoms_b, 256)
+        # calls of at most 64 rows may cut K over up to 8 CTAs per output tile: FP32 partial tiles follow
+        assert need == fixed + (8 * rows * n * 4 if rows <= 64 else 0)
 
 
 def test_decode_plans_stay_launchable_and_cut_k_by_k_alone():

@@ -57,7 +57,10 @@ def unpack_scratch(raw, rows, k):
     return codes, scales, g
 
 
-@pytest.mark.parametrize("rows,k,n", [(16, 256, 128), (128, 512, 256), (200, 1024, 384), (300, 5120, 1024)])
+# The last three are skinny calls (9 to 64 rows: the K steps of an output tile are cut over 8, 7 and 2 CTAs and the ranges'
+# FP32 sums added in order by a second launch).
+@pytest.mark.parametrize("rows,k,n", [(16, 256, 128), (128, 512, 256), (200, 1024, 384), (300, 5120, 1024), (9, 5120, 1024), (33, 17408, 5120),
+                                      (64, 5120, 17408)])
 def test_native_matches_float64_over_quantized_operands(dev, rows, k, n):
     rng = np.random.default_rng(rows + k + n)
     weights = (rng.standard_normal((n, k)) * rng.uniform(0.01, 1.0, (n, 1))).astype(np.float32)
