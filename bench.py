@@ -704,28 +704,34 @@ def run_ours(args):
             "gpu_launches": grouped["launches_per_step"] * args.steps,
         })
         extra["q3_one_call_per_tensor"] = head["single"]
-        if not args.headline_only:
+        wanted = set() if args.headline_only else {name.strip() for name in args.extras.split(",") if name.strip()}
+        if wanted:
             for fmt, rows_list in (("nvfp4", (1, 5)), ("trellis", (1, 5))):
+                if fmt not in wanted:
+                    continue
                 try:
                     extra[fmt] = measure_layer_set(bench, fmt, rows_list, copies, max(3, args.steps // 2), 3)
                 except Exception as error:   # reported, never hidden
                     extra[fmt] = {"error": repr(error)}
-            try:
-                extra["per_shape"] = measure_per_shape(bench)
-                key = "nvfp4:gate:1"
-                extra["config1_nvfp4_gate_m1"] = dict(zip(("us", "gbs", "frac_of_hbm_peak"), extra["per_shape"]["rows"][key]))
-            except Exception as error:
-                extra["per_shape"] = {"error": repr(error)}
-            extra["nvfp4_prefill"] = {}
-            for rows in (4096, 32768, 131072):
+            if "per_shape" in wanted:
                 try:
-                    extra["nvfp4_prefill"][str(rows)] = measure_prefill(bench, rows, 3, 3 if rows < 100000 else 1)
+                    extra["per_shape"] = measure_per_shape(bench)
+                    key = "nvfp4:gate:1"
+                    extra["config1_nvfp4_gate_m1"] = dict(zip(("us", "gbs", "frac_of_hbm_peak"), extra["per_shape"]["rows"][key]))
                 except Exception as error:
-                    extra["nvfp4_prefill"][str(rows)] = {"error": repr(error)}
-            try:
-                extra["sweep64"] = measure_sweep(bench, 3, 2)
-            except Exception as error:
-                extra["sweep64"] = {"error": repr(error)}
+                    extra["per_shape"] = {"error": repr(error)}
+            if "prefill" in wanted:
+                extra["nvfp4_prefill"] = {}
+                for rows in (4096, 32768, 131072):
+                    try:
+                        extra["nvfp4_prefill"][str(rows)] = measure_prefill(bench, rows, 3, 3 if rows < 100000 else 1)
+                    except Exception as error:
+                        extra["nvfp4_prefill"][str(rows)] = {"error": repr(error)}
+            if "sweep64" in wanted:
+                try:
+                    extra["sweep64"] = measure_sweep(bench, 3, 2)
+                except Exception as error:
+                    extra["sweep64"] = {"error": repr(error)}
         if RANK == 0:
             line["cpu_baseline"] = cpu_baseline(cpu_blobs())
     else:
@@ -764,6 +770,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--headline-only", action="store_true", help="skip the measurements reported under `extra`")
+    parser.add_argument("--extras", default="nvfp4,trellis,per_shape,prefill,sweep64",
+                        help="comma-separated measurements to report under `extra` on one GPU (default: all of nvfp4, trellis, per_shape, prefill, sweep64)")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)
