@@ -71,10 +71,15 @@ __device__ __forceinline__ bool mbar_try_wait_at(uint32_t bar, uint32_t parity) 
             : "memory");
     return done != 0;
 }
-// Bounded wait on a barrier given by its 32-bit shared address.
+// Bounded wait on a barrier given by its 32-bit shared address. A poll that fails is followed by a sleep of kNap
+// nanoseconds: the hardware returns from a parked poll long before its time hint, and a warp that polls back to back
+// takes issue slots from the warps whose work it is waiting for.
+template <uint32_t kNap = 64>
 __device__ __forceinline__ bool mbar_wait_at(uint32_t bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < kParkLimit; ++spin)
+    for (uint32_t spin = 0; spin < kParkLimit; ++spin) {
         if (mbar_try_wait_at(bar, parity)) return true;
+        asm volatile("nanosleep.u32 %0;" ::"n"(kNap));
+    }
     return false;
 }
 // Bounded wait: false when the phase did not complete within kSpinLimit polls.

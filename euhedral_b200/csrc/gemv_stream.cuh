@@ -262,7 +262,7 @@ __global__ void __launch_bounds__(32 * (kMaxWarps + (F::kAddingWarp ? 1 : 0)), 1
                     // Tile run_begin + i belongs to team i % teams and is that team's tile number i / teams.
                     const uint32_t index = tile - run_begin, team = index % teams, turn = index / teams, buffer = turn & 1u;
                     const uint32_t bars = sums_a + (team * 2u + buffer) * 16u;
-                    if (complete) complete = eb::mbar_wait_at(bars, (turn >> 1) & 1u);
+                    if (complete) complete = eb::mbar_wait_at<400>(bars, (turn >> 1) & 1u);   // a team needs microseconds per tile: poll rarely
                     const uint32_t pieces = smem_a + layout.off_partials + (team * 2u + buffer) * team_size * kPartial;
                     add_pieces(t, finish, pieces, (tile - first_tile) * 16u, tile - segment_begin, lane, 32u);
                     __syncwarp();

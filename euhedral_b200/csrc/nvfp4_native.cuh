@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(32 * kQuantizeWarps) quantize_rows(const __nv_
     const uint4* x = reinterpret_cast<const uint4*>(input + (uint64_t)row * k);   // 8 values per element
     const uint32_t vectors = k / 8u, blocks64 = k / kBlockK;
     float amax = 0.0f;
+#pragma unroll 4   // four loads in flight per lane: the pass is bound by load latency
     for (uint32_t i = lane; i < vectors; i += 32u) {
         const uint4 w = x[i];
         const uint32_t words[4] = {w.x, w.y, w.z, w.w};
