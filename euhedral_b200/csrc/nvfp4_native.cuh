@@ -82,9 +82,10 @@ __host__ __device__ inline uint32_t atom_byte(uint32_t row_in_tile, uint32_t sca
 // bit against that kernel compiled for this GPU): global = amax / (6 * 448) (1 for a zero row); per block of 16:
 // scale = e4m3_satfinite(amax * (1/6) * (1/global)); codes = e2m1_rn(v * ((1/global) / scale)), saturating; the next term
 // quantizes fma(-decoded, scale * global, v). All in FP32 with the hardware conversions.
-// The work split is this kernel's own: one warp per row, eight rows per CTA, no shared memory and no CTA barrier. A lane
-// takes whole K blocks of 64 values (128 bytes in): per term it leaves with two 16-byte code stores and ONE 4-byte store
-// of the block's four scales, which is exactly one row's entry of the 512-byte atom tcgen05 reads.
+// The work split is this kernel's own: one warp per row, eight rows per CTA, no shared memory and no CTA barrier. Four
+// neighbouring lanes share a K block of 64 values, one 16-value block each; their four scale bytes meet by two shuffles
+// and leave as ONE 4-byte store, which is exactly one row's entry of the 512-byte atom tcgen05 reads; their codes leave
+// as 32 contiguous bytes per term.
 constexpr uint32_t kQuantizeWarps = 8;
 
 // One block of 16 values: its scale code, its 8 code bytes, and v replaced by the residual.
@@ -111,7 +112,7 @@ __device__ __forceinline__ uint32_t quantize_block(float (&v)[16], float global,
     return (uint32_t)scale;
 }
 
-__global__ void __launch_bounds__(32 * kQuantizeWarps) quantize_rows(const __nv_bfloat16* __restrict__ input, uint8_t* __restrict__ scratch,
+__global__ void __launch_bounds__(32 * kQuantizeWarps, 5) quantize_rows(const __nv_bfloat16* __restrict__ input, uint8_t* __restrict__ scratch,
         uint32_t rows, uint32_t k) {
     const uint32_t lane = threadIdx.x & 31u, row = blockIdx.x * kQuantizeWarps + (threadIdx.x >> 5);
     const ActivationLayout layout(rows, k);
@@ -136,30 +137,33 @@ __global__ void __launch_bounds__(32 * kQuantizeWarps) quantize_rows(const __nv_
     uint8_t* sfa = scratch + layout.sfa_offset + (uint64_t)(row / kTileM) * layout.k_blocks * kTerms * kAtom + atom_byte(row % kTileM, 0);
     const uint64_t plane = (uint64_t)rows * (k / 2u);
     uint8_t* codes_row = scratch + (uint64_t)row * (k / 2u);
-    for (uint32_t b = lane; b < blocks64; b += 32u) {   // the row was just read: these loads hit L1 / L2
-        uint4 raw[8];
+    // Four neighbouring lanes share a K block of 64 values, one 16-value block each; a warp covers eight K blocks per turn.
+    const uint32_t sub = lane & 3u;
+    for (uint32_t first = 0; first < blocks64; first += 8u) {   // the row was just read: these loads hit L1 / L2
+        const uint32_t b = first + (lane >> 2);
+        const bool live = b < blocks64;
+        uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
+        if (live) {
+            lo = x[2u * (4u * b + sub)];
+            hi = x[2u * (4u * b + sub) + 1u];
+        }
+        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        float v[16];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) raw[i] = x[8u * b + i];
-        uint2 codes[kTerms][4];
-        uint32_t scales[kTerms] = {0u, 0u};
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-            const uint32_t words[8] = {raw[2 * s].x, raw[2 * s].y, raw[2 * s].z, raw[2 * s].w, raw[2 * s + 1].x, raw[2 * s + 1].y, raw[2 * s + 1].z, raw[2 * s + 1].w};
-            float v[16];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                v[2 * i] = eb::bf16_bits_to_float(words[i] & 0xFFFFu);
-                v[2 * i + 1] = __uint_as_float(words[i] & 0xFFFF0000u);
-            }
-#pragma unroll
-            for (uint32_t t = 0; t < kTerms; ++t) scales[t] |= quantize_block(v, global, inverse_global, &codes[t][s]) << (8 * s);
+        for (int i = 0; i < 8; ++i) {
+            v[2 * i] = eb::bf16_bits_to_float(words[i] & 0xFFFFu);
+            v[2 * i + 1] = __uint_as_float(words[i] & 0xFFFF0000u);
         }
 #pragma unroll
         for (uint32_t t = 0; t < kTerms; ++t) {
-            uint4* out = reinterpret_cast<uint4*>(codes_row + t * plane + 32u * b);
-            out[0] = make_uint4(codes[t][0].x, codes[t][0].y, codes[t][1].x, codes[t][1].y);
-            out[1] = make_uint4(codes[t][2].x, codes[t][2].y, codes[t][3].x, codes[t][3].y);
-            *reinterpret_cast<uint32_t*>(sfa + ((uint64_t)b * kTerms + t) * kAtom) = scales[t];
+            uint2 codes;
+            uint32_t scales = quantize_block(v, global, inverse_global, &codes) << (8u * sub);
+            scales |= __shfl_xor_sync(0xffffffffu, scales, 1);   // the K block's four scale bytes, in every one of the four lanes
+            scales |= __shfl_xor_sync(0xffffffffu, scales, 2);
+            if (live) {
+                *reinterpret_cast<uint2*>(codes_row + t * plane + 32u * b + 8u * sub) = codes;
+                if (sub == 0u) *reinterpret_cast<uint32_t*>(sfa + ((uint64_t)b * kTerms + t) * kAtom) = scales;
+            }
         }
     }
     if (lane == 0) reinterpret_cast<float*>(scratch + layout.global_offset)[row] = global;
