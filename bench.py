@@ -348,8 +348,7 @@ class LayerSet:
         gpu.copy_device_to_readback(self.host_out.data_ptr(), self.device_out.data_ptr(), self.d2h)
 
     def launches(self, grouped: bool):
-        per_call = 3 if self.fmt == "trellis" else 1
-        return len((self.grouped if grouped else self.single)[0]) * per_call
+        return len((self.grouped if grouped else self.single)[0])   # every call is one launch
 
 
 def measure_layer_set(bench: Bench, fmt, rows_list, copies, steps, warmup, e2e=False):

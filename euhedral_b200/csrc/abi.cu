@@ -60,8 +60,8 @@ cudaError_t allow_big_smem(K kernel) {
 
 template <int W>
 cudaError_t allow_trellis_width() {
-    cudaError_t e = allow_big_smem(trellis::mma_kernel<W, 1>);
-    if (e == cudaSuccess) e = allow_big_smem(trellis::mma_kernel<W, 4>);
+    cudaError_t e = allow_big_smem(trellis::linear_kernel<W, 1>);
+    if (e == cudaSuccess) e = allow_big_smem(trellis::linear_kernel<W, 4>);
     return e;
 }
 
@@ -404,19 +404,10 @@ constexpr int kTableCount = (int)(sizeof(kTable) / sizeof(kTable[0]));
 
 bool trellis_width_valid(int w) { return w >= 16 && w <= 128 && w % 8 == 0; }
 
+// The payload as [k / 16][n / 16 * W / 4] 8-byte elements; a box is one streaming stage of one 128-column block. The
+// calling thread keeps the last few maps (encoding costs about a microsecond).
 template <int W>
-cudaError_t launch_trellis_mma(const uint64_t* a, uint32_t* error) {
-    const int rows = (int)a[6], k = (int)a[7], n = (int)a[8], splits = (int)a[10], s = (int)a[11];
-    const dim3 grid((unsigned)(n / 128), (unsigned)splits), block(256);
-    const size_t shared = (size_t)trellis::kStages * trellis::kStageTiles * 8u * W * 2u;
-    auto act = reinterpret_cast<const uint16_t*>(a[0]);
-    auto words = reinterpret_cast<const uint16_t*>(a[1]);
-    auto ends = reinterpret_cast<const int*>(a[2]);
-    auto svh = reinterpret_cast<const uint16_t*>(a[3]);
-    auto partials = reinterpret_cast<float*>(a[4]);
-    auto out = reinterpret_cast<uint16_t*>(a[5]);
-    // The payload as [k / 16][n / 16 * W / 4] 8-byte elements; a box is one ring stage of one 128-column block. The calling
-    // thread keeps the last few maps (encoding costs about a microsecond).
+const CUtensorMap* trellis_payload_map(const uint16_t* words, int k, int n) {
     struct Cached {
         const void* words;
         int k, n, w;
@@ -425,49 +416,73 @@ cudaError_t launch_trellis_mma(const uint64_t* a, uint32_t* error) {
     constexpr int kCached = 16;
     thread_local Cached cache[kCached] = {};
     thread_local int next = 0;
-    const CUtensorMap* map = nullptr;
     for (int i = 0; i < kCached; ++i)
-        if (cache[i].words == words && cache[i].k == k && cache[i].n == n && cache[i].w == W) map = &cache[i].map;
-    if (map == nullptr) {
-        const eb::EncodeTiled encode = eb::encoder();
-        if (encode == nullptr) return cudaErrorNotSupported;
-        Cached& slot = cache[next];
-        const cuuint64_t dims[2] = {(cuuint64_t)(n / 16) * (W / 4), (cuuint64_t)(k / 16)}, strides[1] = {(cuuint64_t)(n / 16) * W * 2u};
-        const cuuint32_t box[2] = {2u * W, (cuuint32_t)trellis::kStageTiles}, ones[2] = {1u, 1u};
-        if (encode(&slot.map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint16_t*>(words), dims, strides, box, ones,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
-                != CUDA_SUCCESS)
-            return cudaErrorInvalidValue;
-        slot.words = words;
-        slot.k = k;
-        slot.n = n;
-        slot.w = W;
-        map = &slot.map;
-        next = (next + 1) % kCached;
-    }
-    if (rows <= 8)
-        return launch(kOverlappable, trellis::mma_kernel<W, 1>, grid, block, shared, 1u, *map, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
-    return launch(kOverlappable, trellis::mma_kernel<W, 4>, grid, block, shared, 1u, *map, act, words, ends, svh, partials, out, rows, k, n, splits, s, error);
+        if (cache[i].words == words && cache[i].k == k && cache[i].n == n && cache[i].w == W) return &cache[i].map;
+    const eb::EncodeTiled encode = eb::encoder();
+    if (encode == nullptr) return nullptr;
+    Cached& slot = cache[next];
+    const cuuint64_t dims[2] = {(cuuint64_t)(n / 16) * (W / 4), (cuuint64_t)(k / 16)}, strides[1] = {(cuuint64_t)(n / 16) * W * 2u};
+    const cuuint32_t box[2] = {2u * W, (cuuint32_t)trellis::kStageTiles}, ones[2] = {1u, 1u};
+    slot.words = nullptr;
+    if (encode(&slot.map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint16_t*>(words), dims, strides, box, ones,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+            != CUDA_SUCCESS)
+        return nullptr;
+    slot.words = words;
+    slot.k = k;
+    slot.n = n;
+    slot.w = W;
+    next = (next + 1) % kCached;
+    return &slot.map;
 }
 
-cudaError_t launch_trellis_prepass(const void* x, const void* suh, void* act, int rows, int k, int s, int layout) {
-    return launch(kOverlappable, trellis::prepass_kernel, dim3((unsigned)((k + 511) / 512), (unsigned)rows, (unsigned)s), dim3(128), 0, 1u,
-            static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(suh), static_cast<uint16_t*>(act), rows, k, s, layout);
+template <int W>
+cudaError_t launch_trellis_linear(const uint16_t* words, const trellis::Job& job, uint32_t* error) {
+    const CUtensorMap* map = trellis_payload_map<W>(words, job.k, job.n);
+    if (map == nullptr) return cudaErrorNotSupported;
+    const dim3 grid((unsigned)(job.n / 128), (unsigned)job.splits), block(trellis::kThreads);
+    const size_t stages = (size_t)trellis::kStages * trellis::kStageTiles * 16u * W;
+    if (job.rows <= 8)
+        return launch(kOverlappable, trellis::linear_kernel<W, 1>, grid, block, stages + trellis::act_bytes(1), 1u, *map, job, error);
+    return launch(kOverlappable, trellis::linear_kernel<W, 4>, grid, block, stages + trellis::act_bytes(4), 1u, *map, job, error);
 }
 
-cudaError_t launch_trellis_epilogue(const void* partials, int splits, const void* svh, void* out, int rows, int n) {
-    return launch(kOverlappable, trellis::epilogue_kernel, dim3((unsigned)((n + 511) / 512), (unsigned)rows), dim3(128), 0, 1u,
-            static_cast<const float*>(partials), splits, static_cast<const uint16_t*>(svh), static_cast<uint16_t*>(out), rows, n);
-}
-
-cudaError_t launch_trellis_mma_width(int w, const uint64_t* a, uint32_t* error) {
+cudaError_t launch_trellis_linear_width(int w, const uint16_t* words, const trellis::Job& job, uint32_t* error) {
     switch (w) {
-#define EB_CASE(W) case W: return launch_trellis_mma<W>(a, error);
+#define EB_CASE(W) case W: return launch_trellis_linear<W>(words, job, error);
         EB_TRELLIS_WIDTHS(EB_CASE)
 #undef EB_CASE
     }
     return cudaErrorInvalidValue;
+}
+
+// Table entry 1: the activations come from the scratch a rotate launch filled; a split K leaves its partials there.
+cudaError_t launch_trellis_mma(const uint64_t* a, uint32_t* error) {
+    trellis::Job job = {};
+    job.activations = reinterpret_cast<const uint16_t*>(a[0]);
+    job.ends = reinterpret_cast<const int*>(a[2]);
+    job.svh = reinterpret_cast<const uint16_t*>(a[3]);
+    job.partials = reinterpret_cast<float*>(a[4]);
+    job.out = reinterpret_cast<uint16_t*>(a[5]);
+    job.rows = (int)a[6];
+    job.k = (int)a[7];
+    job.n = (int)a[8];
+    job.splits = (int)a[10];
+    job.s = (int)a[11];
+    return launch_trellis_linear_width((int)a[9], reinterpret_cast<const uint16_t*>(a[1]), job, error);
+}
+
+cudaError_t launch_trellis_rotate(const void* x, const void* suh, void* act, int rows, int k, int s, int layout) {
+    const long long tasks = (long long)s * rows * (k / 128);
+    return launch(kOverlappable, trellis::rotate_kernel, dim3((unsigned)((tasks + 7) / 8)), dim3(256), 0, 1u,
+            static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(suh), static_cast<uint16_t*>(act), rows, k, s, layout);
+}
+
+cudaError_t launch_trellis_finish(const void* partials, int splits, const void* svh, void* out, int rows, int n) {
+    const long long tasks = (long long)rows * (n / 128);
+    return launch(kOverlappable, trellis::finish_kernel, dim3((unsigned)((tasks + 7) / 8)), dim3(256), 0, 1u,
+            static_cast<const float*>(partials), splits, static_cast<const uint16_t*>(svh), static_cast<uint16_t*>(out), rows, n);
 }
 
 // Several decode linears that share K and the row count (the q, k and v projections of a layer, or gate and up) as ONE
@@ -794,7 +809,7 @@ int euhedral_cuda_linear_launch(int32_t kernel, uint32_t grid_x, uint32_t grid_y
             if (rows <= 0 || k <= 0 || k % 128 != 0 || s <= 0 || rows > 65535 || s > 65535 || ((a[0] | a[1] | a[2]) & 7u) != 0)
                 return EUHEDRAL_CUDA_INVALID_ARGUMENT;   // 8-byte vector loads and stores
             if (layout != 0 && layout != 1) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;   // 2 = block FP8: no kernel here
-            return finish(launch_trellis_prepass(reinterpret_cast<const void*>(a[0]), reinterpret_cast<const void*>(a[1]),
+            return finish(launch_trellis_rotate(reinterpret_cast<const void*>(a[0]), reinterpret_cast<const void*>(a[1]),
                     reinterpret_cast<void*>(a[2]), rows, k, s, layout));
         }
         case 1: {   // mma(act, words, ends, svh, partials, out, rows, k, n, w, splits, s)
@@ -802,13 +817,13 @@ int euhedral_cuda_linear_launch(int32_t kernel, uint32_t grid_x, uint32_t grid_y
             if (rows <= 0 || k <= 0 || k % 128 != 0 || n <= 0 || n % 128 != 0 || !trellis_width_valid(w) || splits <= 0
                     || splits > k / 16 || splits > 65535 || s <= 0 || (a[1] & 15u) != 0 || ((a[0] | a[3] | a[5]) & 7u) != 0 || (a[4] & 3u) != 0)
                 return EUHEDRAL_CUDA_INVALID_ARGUMENT;   // activations, svh and output move as 8-byte vectors
-            return finish(launch_trellis_mma_width(w, a, state->error_word));
+            return finish(launch_trellis_mma(a, state->error_word));
         }
         case 4: {   // epilogue(partials, splits, svh, out, rows, n)
             const int splits = (int)a[1], rows = (int)a[4], n = (int)a[5];
             if (splits <= 0 || rows <= 0 || rows > 65535 || n <= 0 || n % 128 != 0 || (a[0] & 15u) != 0 || ((a[2] | a[3]) & 7u) != 0)
                 return EUHEDRAL_CUDA_INVALID_ARGUMENT;   // 16-byte loads of the partial sums, 8-byte vectors of svh and output
-            return finish(launch_trellis_epilogue(reinterpret_cast<const void*>(a[0]), splits, reinterpret_cast<const void*>(a[2]),
+            return finish(launch_trellis_finish(reinterpret_cast<const void*>(a[0]), splits, reinterpret_cast<const void*>(a[2]),
                     reinterpret_cast<void*>(a[3]), rows, n));
         }
         case 5: {   // decode_bf16(words, out, k, n, w)
@@ -816,7 +831,7 @@ int euhedral_cuda_linear_launch(int32_t kernel, uint32_t grid_x, uint32_t grid_y
             if (k <= 0 || k % 16 != 0 || n <= 0 || n % 16 != 0 || !trellis_width_valid(w)) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
             const uint64_t tiles = (uint64_t)(k / 16) * (uint64_t)(n / 16);
             if (tiles > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
-            return finish(launch(kOrdered, trellis::decode_bf16_kernel, dim3((unsigned)tiles), dim3(256), 0, 1u,
+            return finish(launch(kOrdered, trellis::decode_bf16_kernel, dim3((unsigned)((tiles + 7) / 8)), dim3(256), 0, 1u,
                     reinterpret_cast<const uint16_t*>(a[0]), reinterpret_cast<uint16_t*>(a[1]), k, n, w));
         }
         case 7: {   // reference(x, words, suh, svh, ends, s, out, rows, k, n, w)
@@ -848,8 +863,23 @@ int euhedral_b200_take_device_error(uint32_t* word) {
 
 uint64_t euhedral_b200_static_scratch_bytes(void) { return kStaticScratchBytes; }
 
-// A whole trellis linear (prepass, tensor-core GEMM, epilogue when the K range is split) in `scratch`: the three launches
-// the reference's host plans one by one through the kernel table, planned here. Nothing is allocated or freed.
+// A whole trellis linear as ONE launch. The scratch holds what the K splits exchange: a flag per (column block, split),
+// then the FP32 partials of every split; nothing of it needs clearing (a call's flags carry a tag of its own) and nothing
+// is allocated or freed. With one split the scratch is not touched.
+static std::atomic<unsigned long long> g_trellis_tag{0x9E3779B97F4A7C15ull ^ (unsigned long long)(uintptr_t)&g_trellis_tag};
+
+static uint32_t trellis_default_splits(uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t tile_words, int sms) {
+    const uint32_t groups = rows <= 8u ? 1u : 4u;
+    const uint32_t shared = (uint32_t)trellis::kStages * trellis::kStageTiles * 16u * tile_words + trellis::act_bytes((int)groups) + 1024u + 128u;
+    const uint32_t per_sm = std::max(1u, std::min(groups == 1u ? (uint32_t)trellis::kResident : 2u, (uint32_t)kGemvSmem / shared));
+    const uint32_t blocks = out_features / 128u, tiles = in_features / 16u;
+    return std::max(1u, std::min(per_sm * (uint32_t)sms / blocks, tiles / 20u));
+}
+
+static uint64_t trellis_flag_bytes(uint32_t out_features, uint32_t splits) {
+    return splits > 1u ? ((uint64_t)(out_features / 128u) * splits * 8u + 255u) & ~255ull : 0u;
+}
+
 static int trellis_linear(unsigned char* scratch, uint64_t scratch_bytes, const void* input, const void* words, const void* suh, const void* svh,
         const void* segment_ends, void* output, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t tile_words, uint32_t segments,
         uint32_t splits) {
@@ -865,26 +895,31 @@ static int trellis_linear(unsigned char* scratch, uint64_t scratch_bytes, const 
         scratch = state->static_scratch;
         scratch_bytes = kStaticScratchBytes;
     }
-    // splits == 0: the reference's choice for this device, core/.../artifact/format/TrellisFormat.java:369-376 with the
-    // default target of 8 blocks per SM.
-    if (splits == 0u) {
-        const uint32_t blocks = out_features / 128u, wanted = (8u * (uint32_t)state->sms + blocks - 1u) / blocks;
-        splits = std::max(1u, std::min(wanted, in_features / 256u));
-    }
-    // Activations (FP16, every segment) on a 256-byte boundary, then the FP32 partials of every split.
-    const uint64_t activations = ((uint64_t)segments * rows * in_features * 2u + 255u) & ~255ull;
+    // splits == 0: as many as give every SM its full set of resident CTAs once (one wave), each with 20 tile rows or more.
+    // (The reference's host aims at 8 blocks per SM, core/.../artifact/format/TrellisFormat.java:369-376; a caller that
+    // wants that count passes it.)
+    if (splits == 0u) splits = trellis_default_splits(rows, in_features, out_features, tile_words, state->sms);
+    const uint64_t flags = trellis_flag_bytes(out_features, splits);
     const uint64_t partials = splits > 1u ? (uint64_t)splits * rows * out_features * 4u : 0u;
-    if (rows > 65535u || segments > 65535u || splits > 65535u || activations + partials > scratch_bytes || ((uintptr_t)scratch & 15u) != 0)
+    if (rows > 65535u || segments > 65535u || splits > 65535u || flags + partials > scratch_bytes || ((uintptr_t)scratch & 15u) != 0)
         return EUHEDRAL_CUDA_SIZE_OVERFLOW;
-    cudaError_t e = launch_trellis_prepass(input, suh, scratch, (int)rows, (int)in_features, (int)segments, 0);
-    if (e != cudaSuccess) return (int)e;
-    const uint64_t a[12] = {(uint64_t)(uintptr_t)scratch, (uint64_t)(uintptr_t)words, (uint64_t)(uintptr_t)segment_ends,
-            (uint64_t)(uintptr_t)svh, (uint64_t)(uintptr_t)(scratch + activations), (uint64_t)(uintptr_t)output, rows, in_features,
-            out_features, tile_words, splits, segments};
-    e = launch_trellis_mma_width((int)tile_words, a, state->error_word);
-    if (e != cudaSuccess) return (int)e;
-    if (splits > 1u) e = launch_trellis_epilogue(scratch + activations, (int)splits, svh, output, (int)rows, (int)out_features);
-    return finish(e);
+    trellis::Job job = {};
+    job.x = static_cast<const uint16_t*>(input);
+    job.suh = static_cast<const uint16_t*>(suh);
+    job.ends = static_cast<const int*>(segment_ends);
+    job.svh = static_cast<const uint16_t*>(svh);
+    job.out = static_cast<uint16_t*>(output);
+    if (splits > 1u) {
+        job.flags = reinterpret_cast<unsigned long long*>(scratch);
+        job.partials = reinterpret_cast<float*>(scratch + flags);
+        job.tag = g_trellis_tag.fetch_add(0x9E3779B97F4A7C15ull, std::memory_order_relaxed);
+    }
+    job.rows = (int)rows;
+    job.k = (int)in_features;
+    job.n = (int)out_features;
+    job.splits = (int)splits;
+    job.s = (int)segments;
+    return finish(launch_trellis_linear_width((int)tile_words, static_cast<const uint16_t*>(words), job, state->error_word));
 }
 
 // The scratch is the library's own static device array instead of caller memory.
@@ -896,17 +931,18 @@ int euhedral_b200_linear_trellis_bf16_static(const void* input, const void* word
 }
 
 uint64_t euhedral_b200_linear_trellis_scratch_bytes(uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t segments, uint32_t splits) {
-    const uint64_t activations = ((uint64_t)segments * rows * in_features * 2u + 255u) & ~255ull;
+    (void)segments;
     const uint32_t most = splits != 0u ? splits : std::max(1u, in_features / 256u);
-    return activations + (most > 1u ? (uint64_t)most * rows * out_features * 4u : 0u);
+    return most > 1u ? trellis_flag_bytes(out_features, most) + (uint64_t)most * rows * out_features * 4u : 0u;
 }
 
 int euhedral_b200_linear_trellis_bf16(const void* input, const void* words, const void* suh, const void* svh, const void* segment_ends,
         void* output, void* scratch, uint64_t scratch_bytes, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t tile_words,
         uint32_t segments, uint32_t splits) {
-    if (scratch == nullptr) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
-    return trellis_linear(static_cast<unsigned char*>(scratch), scratch_bytes, input, words, suh, svh, segment_ends, output, rows, in_features,
-            out_features, tile_words, segments, splits);
+    if (scratch == nullptr && splits != 1u) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    alignas(16) static unsigned char unused[16];   // one split: the scratch is never dereferenced
+    return trellis_linear(scratch != nullptr ? static_cast<unsigned char*>(scratch) : unused, scratch_bytes, input, words, suh, svh,
+            segment_ends, output, rows, in_features, out_features, tile_words, segments, splits);
 }
 
 int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t* k_slices,

@@ -247,6 +247,16 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// D[16x8] = A[16x32] * B[32x8] + C, unsigned bytes in, 32-bit integers out. Lane (g = lane / 4, q = lane % 4) owns
+//   a0: row g, k 4q..4q+3   a1: row g+8, k 4q..4q+3   a2: row g, k 16+4q..   a3: row g+8, k 16+4q..
+//   b0: k 4q..4q+3, col g   b1: k 16+4q.., col g        d0, d1: row g, cols 2q, 2q+1   d2, d3: row g+8, cols 2q, 2q+1
+__device__ __forceinline__ void mma_u8_16832_from(uint32_t (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+        uint32_t b1, uint32_t c) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
+}
+
 // One LOP3: the bitwise function of (a, b, c) whose truth table is LUT (bit i of LUT = f for a, b, c = bits 2, 1, 0 of i).
 // Spelled out because the optimiser does not always merge a mask and a combine into one instruction.
 template <int LUT>

@@ -1,17 +1,30 @@
-// Trellis (trellis-tile16-v1) linear for decode-sized row counts on sm_100a, as three stream-ordered launches behind
-// the reference's table launcher euhedral_cuda_linear_launch (native/src/host/linear_kernels.c:7-24):
-//   prepass  (table entry 0, native/src/trellis/prepass.cuh:17-81):  act[g][r] = fp16(H128(bf16 x[r] * fp16 suh[g]))
-//   mma      (table entry 1, native/src/trellis/mma.cuh:434-455):    z = act . Q per K split (FP16 x FP16 -> FP32)
-//   epilogue (table entry 4, native/src/trellis/epilogue.cuh:13-41): y = bf16(svh * H128(sum of the splits in order))
-// plus decode_bf16 (table entry 5, native/src/trellis/decode.cuh:15-29). Arguments, scratch layout (activations then
-// FP32 partials [split][row][n]) and the split ranges [i T / S, (i + 1) T / S) of the T = k / 16 tile rows are the
-// reference's, because its Java host plans them (core/.../artifact/format/TrellisFormat.java:484-567).
+// Trellis (trellis-tile16-v1) linear for decode-sized row counts on sm_100a.
 //
-// The mma kernel: a CTA owns 128 output columns (8 tiles of 16) and one K split; warp i owns tile column i. The CTA
-// streams its tile rows through a ring of stages in shared memory with bulk asynchronous copies (the 8 tiles of a tile
-// row are contiguous in the payload), all requested before griddepcontrol.wait. A lane decodes its eight consecutive
-// positions of a tile - exactly its m16n8k16 A fragment - from the ring words in registers and issues one MMA per
-// group of 8 activation rows, k16 tiles in increasing order, so a row's bits depend on its own data and the K range only.
+// What the format and the reference's host fix (native/src/host/linear_kernels.c:7-24 names the table entries; the Java
+// host plans them, core/.../artifact/format/TrellisFormat.java:484-567):
+//   entry 0 "prepass":  act[g][r] = fp16(H128(bf16 x[r] * fp16 suh[g])), FP16 in the MMA fragment order of the scratch
+//   entry 1 "mma":      z = act . Q over K split i = tile rows [i T / S, (i + 1) T / S), FP16 x FP16 -> FP32
+//   entry 4 "epilogue": y = bf16(svh * H128(sum of the splits in split order))
+//   entry 5 "decode":   the rotated weight as BF16 [n][k]
+// and the scratch layout between them (activations, then FP32 partials [split][row][n]).
+//
+// How it runs here: ONE kernel does a whole linear. A CTA owns 128 output columns and one K split.
+//   * Warp 8 only requests payload: one tiled TMA copy per stage (16 tile rows x the CTA's 8 tiles), a ring of stages
+//     with a full and an empty mbarrier each, so the eight decoding warps drift apart by up to a ring instead of meeting
+//     at a CTA barrier every stage.
+//   * Warps 0-7 each own one tile column. The rotated activations of the CTA's K range are made here, as many tile rows at
+//     a time as fit (all of them for the usual split), straight into shared memory (from x and suh, or copied from the scratch when the caller ran entry 0), in the
+//     order the decode below wants them; nothing goes through global memory between "prepass" and "mma".
+//   * A lane decodes its eight consecutive trellis states from registers; the byte sums of the codebook hash are taken by
+//     the tensor core (two m16n8k32 u8 MMAs against a 0/1 selector, accumulator preset to the FP16 bit pattern 0x6400),
+//     which also hands each lane the values in the order of its FP16 A fragment; the 16 k of a tile reach the FP16 MMA in
+//     a fixed permutation that the activations in shared memory follow.
+//   * The K splits meet without a second launch and without a counter that would need clearing: a CTA stores its FP32
+//     partials, publishes a flag holding this call's tag, and reads the flags of its column block; whoever sees all of
+//     them set adds the partials in split order, rotates, scales and writes BF16. Two CTAs that finish together may both
+//     do that; they write the same bits.
+// Table entries 0, 1, 4 stay callable one by one (their outputs and the scratch layout are the contract); entry 1 is the
+// same kernel reading the activations from the scratch and leaving the partials to entry 4.
 #pragma once
 
 #include "common.cuh"
@@ -19,63 +32,48 @@
 
 namespace trellis {
 
-// x bf16 [rows][k], suh f16 [s][k] -> out [s][rows][k]: layout 0 = FP16 in MMA fragment order (in each group of 16,
-// elements 2q, 2q+1, 2q+8, 2q+9 contiguous at 4q), layout 1 = BF16 in column order. One warp per 128-column block.
-//   grid (ceil(k / 512), rows, s), block 128.
-__global__ void __launch_bounds__(128) prepass_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ suh,
-        uint16_t* __restrict__ out, int rows, int k, int s, int layout) {
-    const int lane = threadIdx.x & 31, r = blockIdx.y, seg = blockIdx.z;
-    const int block = blockIdx.x * 4 + (threadIdx.x >> 5);
-    eb::pdl_launch_dependents();
-    eb::pdl_wait();
-    if (block * 128 >= k) return;
-    const size_t column = (size_t)block * 128 + lane * 4;
-    const uint2 xb = *reinterpret_cast<const uint2*>(x + (size_t)r * k + column);
-    const uint2 sb = *reinterpret_cast<const uint2*>(suh + (size_t)seg * k + column);
-    float v[4];
-    v[0] = __fmul_rn(eb::bf16_bits_to_float(xb.x & 0xFFFFu), __half2float(__ushort_as_half((unsigned short)(sb.x & 0xFFFFu))));
-    v[1] = __fmul_rn(eb::bf16_bits_to_float(xb.x >> 16), __half2float(__ushort_as_half((unsigned short)(sb.x >> 16))));
-    v[2] = __fmul_rn(eb::bf16_bits_to_float(xb.y & 0xFFFFu), __half2float(__ushort_as_half((unsigned short)(sb.y & 0xFFFFu))));
-    v[3] = __fmul_rn(eb::bf16_bits_to_float(xb.y >> 16), __half2float(__ushort_as_half((unsigned short)(sb.y >> 16))));
-    hadamard128_warp(v, lane);
-    uint16_t* row = out + ((size_t)seg * rows + r) * k;
-    if (layout == 0) {
+// The stored tile widths (16-bit words per tile): X(w) for each.
+#define EB_TRELLIS_WIDTHS(X) X(16) X(24) X(32) X(40) X(48) X(56) X(64) X(72) X(80) X(88) X(96) X(104) X(112) X(120) X(128)
+
+constexpr int kStageTiles = 16;                       // tile rows (k16 steps) per streaming stage
+constexpr int kStages = 3;
+constexpr int kResident = 3;                          // CTAs of up to 8 rows an SM holds (72 registers a thread)
+constexpr int kUnroll = 8;                            // tiles decoded per trip of the inner loop
+constexpr int kChunkLimit = 512;                      // most tile rows whose activations are in shared memory at once
+constexpr int kDecodeWarps = 8;                       // one per tile column of the CTA's 128 output columns
+constexpr int kThreads = 32 * (kDecodeWarps + 1);     // and the warp that requests the payload
+// Shared memory for the activations of a chunk: the live rows only, each chunk * 32 + 32 bytes long (32 modulo 128: the
+// 8 rows x 4 quads of one load tile the banks). 8 rows get 64 tile rows, 5 rows 96, one row 512; 32 rows get 32.
+__host__ __device__ constexpr uint32_t act_bytes(int groups) { return groups == 1 ? 8u * (64u * 32u + 32u) : 32u * (32u * 32u + 32u); }
+__host__ __device__ inline int chunk_tiles(int groups, int live) {
+    const int fit = (int)((act_bytes(groups) / (uint32_t)live - 32u) / 32u) & ~7;
+    return fit < kChunkLimit ? fit : kChunkLimit;
+}
+constexpr uint32_t kWaitFailed = 4u;                  // error bit: a stage did not arrive (or was never freed)
+
+// ---- pieces shared by the one-kernel linear and the table entries -------------------------------------------------------
+
+// One warp: 128 columns of x (BF16) times suh (FP16), rotated; the lane keeps columns 4 lane .. 4 lane + 3.
+__device__ __forceinline__ void rotate128(const uint16_t* __restrict__ x, const uint16_t* __restrict__ suh, int lane, float (&v)[4]) {
+    const uint2 xb = *reinterpret_cast<const uint2*>(x + 4 * lane);
+    const uint2 sb = *reinterpret_cast<const uint2*>(suh + 4 * lane);
+    const uint32_t xw[2] = {xb.x, xb.y}, sw[2] = {sb.x, sb.y};
 #pragma unroll
-        for (int pair = 0; pair < 2; ++pair) {
-            const int e = (lane * 4 + pair * 2) & 15;
-            const size_t at = (column & ~(size_t)15) + 4 * ((e & 7) >> 1) + 2 * (e >> 3);
-            const uint32_t bits = (uint32_t)__half_as_ushort(__float2half_rn(v[2 * pair]))
-                    | (uint32_t)__half_as_ushort(__float2half_rn(v[2 * pair + 1])) << 16;
-            *reinterpret_cast<uint32_t*>(row + at) = bits;
-        }
-    } else {
-        const uint32_t lo = (uint32_t)eb::float_to_bf16_bits(v[0]) | (uint32_t)eb::float_to_bf16_bits(v[1]) << 16;
-        const uint32_t hi = (uint32_t)eb::float_to_bf16_bits(v[2]) | (uint32_t)eb::float_to_bf16_bits(v[3]) << 16;
-        *reinterpret_cast<uint2*>(row + column) = make_uint2(lo, hi);
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t xs = (xw[j >> 1] >> (16 * (j & 1))) & 0xFFFFu, ss = (sw[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+        v[j] = __fmul_rn(eb::bf16_bits_to_float(xs), __half2float(__ushort_as_half((unsigned short)ss)));
     }
+    hadamard128_warp(v, lane);
 }
 
-// partials f32 [splits][rows][n] summed in split order, H128 per 128 columns, * f32(fp16 svh), BF16.
-//   grid (ceil(n / 512), rows), block 128.
-__global__ void __launch_bounds__(128) epilogue_kernel(const float* __restrict__ partials, int splits,
-        const uint16_t* __restrict__ svh, uint16_t* __restrict__ out, int rows, int n) {
-    const int lane = threadIdx.x & 31, r = blockIdx.y;
-    const int block = blockIdx.x * 4 + (threadIdx.x >> 5);
-    eb::pdl_launch_dependents();
-    eb::pdl_wait();
-    if (block * 128 >= n) return;
-    const size_t column = (size_t)block * 128 + lane * 4;
-    float4 sum = *reinterpret_cast<const float4*>(partials + (size_t)r * n + column);
-    for (int i = 1; i < splits; ++i) {
-        const float4 part = *reinterpret_cast<const float4*>(partials + ((size_t)i * rows + r) * n + column);
-        sum.x = __fadd_rn(sum.x, part.x);
-        sum.y = __fadd_rn(sum.y, part.y);
-        sum.z = __fadd_rn(sum.z, part.z);
-        sum.w = __fadd_rn(sum.w, part.w);
-    }
-    float v[4] = {sum.x, sum.y, sum.z, sum.w};
+__device__ __forceinline__ uint32_t half_pair(float low, float high) {
+    return (uint32_t)__half_as_ushort(__float2half_rn(low)) | (uint32_t)__half_as_ushort(__float2half_rn(high)) << 16;
+}
+
+// One warp: the lane's four sums of a 128-column block -> rotated, times svh (FP16), BF16 to out.
+__device__ __forceinline__ void finish128(float (&v)[4], const uint16_t* __restrict__ svh, uint16_t* __restrict__ out, int lane) {
     hadamard128_warp(v, lane);
-    const uint2 sb = *reinterpret_cast<const uint2*>(svh + column);
+    const uint2 sb = *reinterpret_cast<const uint2*>(svh + 4 * lane);
     const uint32_t sw[2] = {sb.x, sb.y};
     uint32_t bits[4];
 #pragma unroll
@@ -83,147 +81,307 @@ __global__ void __launch_bounds__(128) epilogue_kernel(const float* __restrict__
         const float scale = __half2float(__ushort_as_half((unsigned short)(sw[j >> 1] >> (16 * (j & 1)))));
         bits[j] = eb::float_to_bf16_bits(__fmul_rn(scale, v[j]));
     }
-    *reinterpret_cast<uint2*>(out + (size_t)r * n + column) = make_uint2(bits[0] | bits[1] << 16, bits[2] | bits[3] << 16);
+    *reinterpret_cast<uint2*>(out + 4 * lane) = make_uint2(bits[0] | bits[1] << 16, bits[2] | bits[3] << 16);
 }
 
-// Payload -> BF16 rotated weight [n][k] (row-major weights of a BF16 linear). One CTA per tile, one thread per position.
-//   grid (k / 16) * (n / 16), block 256.
-__global__ void __launch_bounds__(256) decode_bf16_kernel(const uint16_t* __restrict__ words, uint16_t* __restrict__ out,
-        int k, int n, int w) {
-    const int tiles_n = n >> 4;
-    const int ti = blockIdx.x / tiles_n, tj = blockIdx.x % tiles_n;
-    const int p = threadIdx.x;
-    const float value = __half2float(__ushort_as_half(value_bits(window_of_tile(words + (size_t)blockIdx.x * w, w, p))));
-    const int lane = p >> 3, j = p & 7;
-    const int kk = 2 * (lane & 3) + 8 * ((j >> 1) & 1) + (j & 1), nn = (lane >> 2) + 8 * (j >> 2);
-    out[(size_t)(tj * 16 + nn) * k + ti * 16 + kk] = eb::float_to_bf16_bits(value);
+// One warp: partials[i * stride + 4 lane ..] of splits i = 0 .. splits - 1 added in that order (read past L1: other SMs
+// wrote them), then finish128.
+__device__ __forceinline__ void add_and_finish128(const float* __restrict__ partials, size_t stride, int splits,
+        const uint16_t* __restrict__ svh, uint16_t* __restrict__ out, int lane) {
+    float4 sum = __ldcg(reinterpret_cast<const float4*>(partials) + lane);
+    for (int i = 1; i < splits; ++i) {
+        const float4 part = __ldcg(reinterpret_cast<const float4*>(partials + (size_t)i * stride) + lane);
+        sum.x = __fadd_rn(sum.x, part.x);
+        sum.y = __fadd_rn(sum.y, part.y);
+        sum.z = __fadd_rn(sum.z, part.z);
+        sum.w = __fadd_rn(sum.w, part.w);
+    }
+    float v[4] = {sum.x, sum.y, sum.z, sum.w};
+    finish128(v, svh, out, lane);
 }
 
-// ---- the tensor-core GEMM -------------------------------------------------------------------------------------------
+// ---- table entries 0, 4, 5 as launches of their own --------------------------------------------------------------------
 
-// The stored tile widths (16-bit words per tile): X(w) for each.
-#define EB_TRELLIS_WIDTHS(X) X(16) X(24) X(32) X(40) X(48) X(56) X(64) X(72) X(80) X(88) X(96) X(104) X(112) X(120) X(128)
-
-constexpr int kStageTiles = 16;   // tile rows (k16 steps) per ring stage
-constexpr int kStages = 3;
-
-// Per-width constants of a lane's eight windows: window j starts offset(j) bits after window 0, whatever the lane
-// (8 * lane is 0 or 8 modulo 16 and the half-step layout adds its extra bit on odd positions only).
-template <int W>
-struct Width {
-    static constexpr int kWords32 = W / 2, kBits = W / 16;
-    static constexpr bool kHalf = (W & 15) == 8;
-    __host__ __device__ static constexpr int offset(int j) { return kBits * j + (kHalf ? (j + 1) / 2 : 0); }
-    // Window 0 starts up to 31 bits into the first word; window 7 ends offset(7) + 16 bits later.
-    static constexpr int kWords = (31 + offset(7) + 16 + 31) / 32;
-};
-
-// Window j of words normalised so that window 0 starts at the top bit of u[0].
-template <int W, int J>
-__device__ __forceinline__ uint32_t window(const uint32_t* u) {
-    constexpr int o = Width<W>::offset(J), i = o >> 5, b = o & 31;
-    if constexpr (b <= 16) {
-        return (u[i] >> (16 - b)) & 0xFFFFu;
+// x bf16 [rows][k], suh f16 [s][k] -> out [s][rows][k]. layout 0: FP16 in the scratch's fragment order (of every 16 columns,
+// columns 2q, 2q+1, 2q+8, 2q+9 sit together at 4q); layout 1: BF16 in column order. A warp per (segment, row, 128 columns).
+//   grid ceil(s * rows * (k / 128) / 8), block 256.
+__global__ void __launch_bounds__(256) rotate_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ suh,
+        uint16_t* __restrict__ out, int rows, int k, int s, int layout) {
+    const int lane = threadIdx.x & 31, blocks = k >> 7;
+    const long long task = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    eb::pdl_launch_dependents();
+    eb::pdl_wait();
+    if (task >= (long long)s * rows * blocks) return;
+    const int block = (int)(task % blocks), row = (int)((task / blocks) % rows), seg = (int)(task / ((long long)blocks * rows));
+    float v[4];
+    rotate128(x + (size_t)row * k + (size_t)block * 128, suh + (size_t)seg * k + (size_t)block * 128, lane, v);
+    uint16_t* to = out + ((size_t)seg * rows + row) * k + (size_t)block * 128;
+    if (layout == 0) {
+        const int a = lane & 3;   // the lane's columns are 4a .. 4a+3 of group lane / 4: (4a, 4a+1) and (4a+2, 4a+3) are pairs
+        uint32_t* group = reinterpret_cast<uint32_t*>(to + 16 * (lane >> 2));
+        group[4 * (a & 1) + (a >> 1)] = half_pair(v[0], v[1]);
+        group[4 * (a & 1) + (a >> 1) + 2] = half_pair(v[2], v[3]);
     } else {
-        return __funnelshift_l(u[i + 1], u[i], b) >> 16;
+        *reinterpret_cast<uint2*>(to + 4 * lane) = make_uint2(
+                (uint32_t)eb::float_to_bf16_bits(v[0]) | (uint32_t)eb::float_to_bf16_bits(v[1]) << 16,
+                (uint32_t)eb::float_to_bf16_bits(v[2]) | (uint32_t)eb::float_to_bf16_bits(v[3]) << 16);
     }
 }
 
-// act f16 [s][rows][k] in fragment order; words [k/16][n/16][W]; ends the exclusive column ends of the s segments;
-// svh f16 [n]. splits == 1: out (BF16 [rows][n]) is written here with the output Hadamard applied; otherwise the raw
-// FP32 sums of split blockIdx.y go to partials[split][rows][n]. P = groups of 8 activation rows held at once.
-//   grid (n / 128, splits), block 256, dynamic shared kStages * kStageTiles * 8 * W * 2 bytes (+ barriers).
+// partials f32 [splits][rows][n] -> out bf16 [rows][n]. A warp per (row, 128 columns).
+//   grid ceil(rows * (n / 128) / 8), block 256.
+__global__ void __launch_bounds__(256) finish_kernel(const float* __restrict__ partials, int splits, const uint16_t* __restrict__ svh,
+        uint16_t* __restrict__ out, int rows, int n) {
+    const int lane = threadIdx.x & 31, blocks = n >> 7;
+    const long long task = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    eb::pdl_launch_dependents();
+    eb::pdl_wait();
+    if (task >= (long long)rows * blocks) return;
+    const size_t at = (size_t)(task / blocks) * n + (size_t)(task % blocks) * 128;
+    add_and_finish128(partials + at, (size_t)rows * n, splits, svh + (size_t)(task % blocks) * 128, out + at, lane);
+}
+
+// Payload -> BF16 rotated weight [n][k] (row-major weights of a BF16 linear). A warp per tile, a lane per eight positions.
+//   grid ceil((k / 16) * (n / 16) / 8), block 256.
+__global__ void __launch_bounds__(256) decode_bf16_kernel(const uint16_t* __restrict__ words, uint16_t* __restrict__ out,
+        int k, int n, int w) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+    const long long tile = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (tile >= (long long)(k >> 4) * (n >> 4)) return;
+    const int ti = (int)(tile / (n >> 4)), tj = (int)(tile % (n >> 4));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float value = __half2float(__ushort_as_half(value_bits(window_of_tile(words + (size_t)tile * w, w, 8 * lane + j))));
+        const int kk = 2 * q + 8 * ((j >> 1) & 1) + (j & 1), nn = g + 8 * (j >> 2);
+        out[(size_t)(tj * 16 + nn) * k + ti * 16 + kk] = eb::float_to_bf16_bits(value);
+    }
+}
+
+// ---- the linear ------------------------------------------------------------------------------------------------------
+
+// The 16 k of a tile enter the FP16 MMA in this order of its k index c: k = 2 (c % 4) + (c % 8) / 4 + 8 (c / 8). It is
+// where the u8 MMA's output lands: lane (g, q) gets the sums of columns 2q and 2q + 1 of its 8, and column 4 b + q' is the
+// product lane (g, q') put into its A register pair b. With it, lane q of a quad reads its B fragment of a tile as one
+// 8-byte load when the activations of 16 k are stored as k = 0 2 8 10 | 4 6 12 14 | 1 3 9 11 | 5 7 13 15.
+
+// How one lane reads its eight states out of a tile's ring of W 16-bit words.
+template <int W>
+struct Lane {
+    static constexpr int kRingWords = W / 2;                // 32-bit words of a tile
+    static constexpr int kStep = W / 16;                    // whole bits from one position's window to the next
+    static constexpr bool kHalfStep = (W % 16) == 8;        // and one more bit before every odd position
+    __host__ __device__ static constexpr int start(int j) { return kStep * j + (kHalfStep ? (j + 1) / 2 : 0); }   // window j after window 0
+    // The first window starts up to 31 bits into the first word; the last one ends start(7) + 16 bits after that.
+    static constexpr int kWords = (31 + start(7) + 16 + 31) / 32;
+
+    uint32_t at[kWords];   // byte offsets of the lane's ring words inside a tile
+    uint32_t shift;        // bits in front of its first window in the first of them
+    uint32_t select[2];    // B operand of the byte-sum MMA: ones where this lane's column takes its k group
+
+    __device__ __forceinline__ void init(int lane) {
+        int bit = window_end(lane * 8, W) - 16;             // tail-biting: the first windows start before the ring's bit 0
+        if (bit < 0) bit += kRingWords * 32;
+        shift = (uint32_t)bit & 31u;
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) at[i] = 4u * (uint32_t)(((bit >> 5) + i) % kRingWords);
+        const int g = lane >> 2, q = lane & 3;
+        select[0] = g == q ? 0x01010101u : 0u;
+        select[1] = g == q + 4 ? 0x01010101u : 0u;
+    }
+
+    // State of window J, the words already shifted so that window 0 starts at the top bit of u[0].
+    template <int J>
+    __device__ __forceinline__ static uint32_t state(const uint32_t (&u)[kWords + 1]) {
+        constexpr int o = start(J), i = o >> 5, b = o & 31;
+        if constexpr (b == 0) {
+            return u[i] >> 16;
+        } else if constexpr (b == 16) {
+            return u[i] & 0xFFFFu;
+        } else if constexpr (b < 16) {
+            return (u[i] >> (16 - b)) & 0xFFFFu;
+        } else {
+            return __funnelshift_l(u[i + 1], u[i], b) >> 16;
+        }
+    }
+
+    // The lane's FP16 A fragment of the tile OFFSET bytes after shared address `tile`.
+    template <int OFFSET>
+    __device__ __forceinline__ void fragment(uint32_t tile, uint32_t (&a)[4]) const {
+        uint32_t u[kWords + 1];
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) u[i] = eb::lds_u32<OFFSET>(tile + at[i]);
+        u[kWords] = 0u;
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) u[i] = __funnelshift_l(u[i + 1], u[i], shift);
+        constexpr uint32_t kHash = 0x83DCD12Du;
+        const uint32_t p0 = state<0>(u) * kHash, p1 = state<1>(u) * kHash, p2 = state<2>(u) * kHash, p3 = state<3>(u) * kHash;
+        const uint32_t p4 = state<4>(u) * kHash, p5 = state<5>(u) * kHash, p6 = state<6>(u) * kHash, p7 = state<7>(u) * kHash;
+        // Positions 0..3 are tile row g (k = 2q, 2q+1, 2q+8, 2q+9), 4..7 the same k of row g + 8.
+        uint32_t low[4], high[4];
+        eb::mma_u8_16832_from(low, p0, p4, p1, p5, select[0], select[1], 0x6400u);    // k = 2q' and 2q'+1 of every lane q'
+        eb::mma_u8_16832_from(high, p2, p6, p3, p7, select[0], select[1], 0x6400u);   // k = 2q'+8 and 2q'+9
+        const __half2 slope = __half2half2(__ushort_as_half((unsigned short)0x1EEE)), offset = __half2half2(__ushort_as_half((unsigned short)0xC931));
+        const uint32_t packed[4] = {__byte_perm(low[0], low[1], 0x5410), __byte_perm(low[2], low[3], 0x5410),
+                __byte_perm(high[0], high[1], 0x5410), __byte_perm(high[2], high[3], 0x5410)};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 value = __hfma2(*reinterpret_cast<const __half2*>(&packed[i]), slope, offset);
+            a[i] = *reinterpret_cast<const uint32_t*>(&value);
+        }
+    }
+};
+
+// What a launch of the linear works on. `activations` (the scratch's fragment-order FP16 [s][rows][k], written by a
+// rotate launch) or, when it is null, x and suh. `flags` null: the partials of a split K are left for a finish launch.
+struct Job {
+    const uint16_t* activations;
+    const uint16_t* x;
+    const uint16_t* suh;
+    const int* ends;              // exclusive column ends of the s segments
+    const uint16_t* svh;
+    float* partials;              // [splits][rows][n], used when splits > 1
+    uint16_t* out;                // bf16 [rows][n]
+    unsigned long long* flags;    // [n / 128][splits]
+    unsigned long long tag;       // this call's flag value
+    int rows, k, n, splits, s;
+};
+
+__device__ __forceinline__ void decoders_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kDecodeWarps) : "memory"); }
+
+// P = groups of 8 activation rows held at once (rows beyond 8 P take another pass over the payload).
+//   grid (n / 128, splits), block kThreads, dynamic shared kStages * kStageTiles * 16 W + act_bytes(P) bytes.
 template <int W, int P>
-__global__ void __launch_bounds__(256) mma_kernel(const __grid_constant__ CUtensorMap payload_map, const uint16_t* __restrict__ act,
-        const uint16_t* __restrict__ words, const int* __restrict__ ends, const uint16_t* __restrict__ svh, float* __restrict__ partials,
-        uint16_t* __restrict__ out, int rows, int k, int n, int splits, int s, uint32_t* __restrict__ error) {
+__global__ void __launch_bounds__(kThreads, P == 1 ? kResident : 2) linear_kernel(const __grid_constant__ CUtensorMap payload_map,
+        const __grid_constant__ Job job, uint32_t* __restrict__ error) {
     extern __shared__ __align__(128) uint8_t smem[];
-    using Wd = Width<W>;
-    constexpr uint32_t kTileRowBytes = 8u * W * 2u;                 // 8 tiles of one tile row
-    constexpr uint32_t kStageBytes = kStageTiles * kTileRowBytes;
-    __shared__ float tile_out[8][128];
-    __shared__ __align__(8) uint64_t bars[kStages];
+    constexpr uint32_t kTileBytes = 2u * W, kTileRowBytes = 8u * kTileBytes, kStageBytes = kStageTiles * kTileRowBytes;
+    __shared__ __align__(8) uint64_t full[kStages], empty[kStages];
+    __shared__ int last_arrival;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q = lane & 3;
-    const int column0 = blockIdx.x * 128;
+    const int rows = job.rows, k = job.k, n = job.n, splits = job.splits;
+    const int column0 = blockIdx.x * 128, split = blockIdx.y;
     const int tiles = k >> 4;
-    const int first = (int)(((long long)blockIdx.y * tiles) / splits), last = (int)(((long long)(blockIdx.y + 1) * tiles) / splits);
-    const int count = last - first;
-    const int stages_total = (count + kStageTiles - 1) / kStageTiles;
-    (void)words;   // read through payload_map
+    const int first = (int)(((long long)split * tiles) / splits), last = (int)(((long long)(split + 1) * tiles) / splits);
+    const int stages = (last - first + kStageTiles - 1) / kStageTiles;
+    const int passes = (rows + 8 * P - 1) / (8 * P);
     if (tid == 0) {
-        for (int i = 0; i < kStages; ++i) eb::mbar_init(&bars[i], 1);
+        for (int i = 0; i < kStages; ++i) {
+            eb::mbar_init(&full[i], 1);
+            eb::mbar_init(&empty[i], kDecodeWarps);
+        }
         eb::mbar_fence_init();
     }
     __syncthreads();
-    // Streaming stage number gst (over all passes over the activation rows) holds the tile rows
-    // [first + (gst % stages_total) * kStageTiles, ...) in ring buffer gst % kStages: one bulk copy per tile row.
-    const int passes = (rows + 8 * P - 1) / (8 * P);
-    const int stream_total = passes * stages_total;
-    // One tiled TMA copy per stage: a box of kStageTiles tile rows x this block's 8 tiles (16 W bytes) of the payload seen
-    // as [k / 16 rows][n / 16 * 2 W bytes]. A last stage that reaches past the split brings rows that are never decoded
-    // (zeros past the tensor); the box is always whole, so is the byte count the barrier expects.
-    auto request = [&](int gst) {
-        const int base = first + (gst % stages_total) * kStageTiles;
-        if (lane == 0) {
-            uint64_t* bar = &bars[gst % kStages];
-            eb::mbar_arrive_expect_tx(bar, kStageBytes);
-            eb::tma_load_2d(smem + (gst % kStages) * kStageBytes, &payload_map, (column0 >> 4) * (W / 4), base, bar);
-        }
-    };
-    if (warp == 0)
-        for (int gst = 0; gst < min(kStages, stream_total); ++gst) request(gst);
-
-    // Segment of this column block: the first whose end is beyond it.
-    int seg = 0;
-    while (seg + 1 < s && column0 >= ends[seg]) ++seg;
-
-    // This lane's ring words of a tile and the bit where its first window starts in the first of them.
-    int at = window_end(lane * 8, W) - 16;
-    if (at < 0) at += Wd::kWords32 * 32;
-    const int shift = at & 31;
-    int word[Wd::kWords];
-#pragma unroll
-    for (int i = 0; i < Wd::kWords; ++i) word[i] = ((at >> 5) + i) % Wd::kWords32;
-
     eb::pdl_launch_dependents();
-    eb::pdl_wait();   // the activations come from the prepass launch
 
-    for (int row_base = 0; row_base < rows; row_base += 8 * P) {
+    if (warp == kDecodeWarps) {
+        // Stage number i over all passes holds tile rows [first + (i % stages) * 16, ..) in ring buffer i % kStages. The box is
+        // always whole (rows past the tensor arrive as zeros, rows past the split are not decoded), so is the byte count.
+        if (lane == 0) {
+            const int total = passes * stages;
+            for (int i = 0; i < total; ++i) {
+                const int slot = i % kStages;
+                if (i >= kStages && !eb::mbar_wait(&empty[slot], (uint32_t)(i / kStages - 1) & 1u)) {
+                    atomicOr(error, kWaitFailed);
+                    break;
+                }
+                eb::mbar_arrive_expect_tx(&full[slot], kStageBytes);
+                eb::tma_load_2d(smem + slot * kStageBytes, &payload_map, (column0 >> 4) * (W / 4), first + (i % stages) * kStageTiles, &full[slot]);
+            }
+        }
+        return;
+    }
+
+    uint8_t* act = smem + kStages * kStageBytes;   // [live rows][stride]: tile row t of the chunk at 32 (t - 8 block0)
+    int seg = 0;   // the segment of this column block: the first whose end lies beyond it
+    while (seg + 1 < job.s && column0 >= job.ends[seg]) ++seg;
+    Lane<W> decoder;
+    decoder.init(lane);
+    const uint32_t ring = eb::smem_u32(smem) + warp * kTileBytes;
+    bool alive = true;   // false once a stage failed to arrive: no further waits, the error bit is set
+
+    eb::pdl_wait();   // x, or the activations of a rotate launch, come from the launch before
+
+    for (int pass = 0; pass < passes; ++pass) {
+        const int row_base = pass * 8 * P, live = min(8 * P, rows - row_base);
+        const int chunk = chunk_tiles(P, live);
+        const uint32_t stride = (uint32_t)chunk * 32u + 32u;
+        // Lane (g, q) reads activation row 8 p + g; a row that is not there reads the last one (its sums are never stored).
+        uint32_t act_lane[P];
+#pragma unroll
+        for (int p = 0; p < P; ++p) act_lane[p] = eb::smem_u32(act) + (uint32_t)min(8 * p + g, live - 1) * stride + q * 8u;
         float acc[P][4];
 #pragma unroll
         for (int p = 0; p < P; ++p) acc[p][0] = acc[p][1] = acc[p][2] = acc[p][3] = 0.0f;
-        // Lane's activations of k16 tile ti for row (row_base + 8 p + g): 8 bytes at a_lane + 16 * ti (+ 8 p rows).
-        const uint16_t* a_lane = act + ((size_t)seg * rows + row_base + g) * k + 4 * q;
-        const int pass = row_base / (8 * P);
-        for (int st = 0; st < stages_total; ++st) {
-            const int gst = pass * stages_total + st;   // stage number over all passes
-            if (!eb::mbar_wait(&bars[gst % kStages], (uint32_t)(gst / kStages) & 1u) && lane == 0) atomicOr(error, 4u);
-            const uint8_t* stage = smem + (gst % kStages) * kStageBytes + warp * (W * 2u);
-            const int base = first + st * kStageTiles;
-            const int rows_here = min(kStageTiles, last - base);
-            for (int t = 0; t < rows_here; ++t) {
-                const uint32_t* ring = reinterpret_cast<const uint32_t*>(stage + t * kTileRowBytes);
-                uint32_t u[Wd::kWords + 1];
-#pragma unroll
-                for (int i = 0; i < Wd::kWords; ++i) u[i] = ring[word[i]];
-                u[Wd::kWords] = 0u;
-#pragma unroll
-                for (int i = 0; i < Wd::kWords; ++i) u[i] = __funnelshift_l(u[i + 1], u[i], shift);
-                const uint32_t a0 = value_pair(window<W, 0>(u), window<W, 1>(u));
-                const uint32_t a2 = value_pair(window<W, 2>(u), window<W, 3>(u));
-                const uint32_t a1 = value_pair(window<W, 4>(u), window<W, 5>(u));
-                const uint32_t a3 = value_pair(window<W, 6>(u), window<W, 7>(u));
-                const int ti = base + t;
-#pragma unroll
-                for (int p = 0; p < P; ++p) {
-                    uint2 xv = make_uint2(0u, 0u);
-                    if (row_base + 8 * p + g < rows) xv = *reinterpret_cast<const uint2*>(a_lane + (size_t)(8 * p) * k + (size_t)ti * 16);
-                    eb::mma_f16_16816(acc[p], a0, a1, a2, a3, xv.x, xv.y);
+        for (int c0 = first; c0 < last;) {
+            const int c1 = min(last, (c0 / chunk + 1) * chunk);
+            const int block0 = c0 >> 3, blocks = ((c1 + 7) >> 3) - block0;
+            decoders_sync();   // nobody reads the chunk before any more
+            for (int task = warp; task < live * blocks; task += kDecodeWarps) {
+                const int r = task % live, block = block0 + task / live;
+                uint8_t* to = act + r * stride + (block - block0) * 256 + (lane >> 2) * 32;   // this lane's group of 16 k
+                const int a = lane & 3;
+                if (job.activations == nullptr) {
+                    float v[4];
+                    rotate128(job.x + (size_t)(row_base + r) * k + (size_t)block * 128, job.suh + (size_t)seg * k + (size_t)block * 128, lane, v);
+                    // the lane's k are 4a .. 4a+3 of its group: (4a, 4a+2) are neighbours in the order above, (4a+1, 4a+3) 8 further
+                    uint32_t* pair = reinterpret_cast<uint32_t*>(to) + 2 * (a & 1) + (a >> 1);
+                    pair[0] = half_pair(v[0], v[2]);
+                    pair[4] = half_pair(v[1], v[3]);
+                } else {
+                    // the scratch holds k = 2a, 2a+1, 2a+8, 2a+9 of the group at 4a
+                    const uint2 from = *reinterpret_cast<const uint2*>(
+                            job.activations + ((size_t)seg * rows + row_base + r) * k + (size_t)block * 128 + 4 * lane);
+                    uint16_t* half = reinterpret_cast<uint16_t*>(to) + 4 * (a >> 1) + (a & 1);
+                    half[0] = (uint16_t)(from.x & 0xFFFFu);
+                    half[8] = (uint16_t)(from.x >> 16);
+                    half[2] = (uint16_t)(from.y & 0xFFFFu);
+                    half[10] = (uint16_t)(from.y >> 16);
                 }
             }
-            __syncthreads();   // every warp is done with this stage's buffer
-            // Refill the buffer with the stage kStages ahead (wrapping into the next pass over the rows).
-            if (warp == 0 && gst + kStages < stream_total) request(gst + kStages);
+            decoders_sync();
+            for (int t0 = c0; t0 < c1;) {   // the pieces of the chunk that lie in one stage
+                const int stage = (t0 - first) / kStageTiles, stage_end = first + (stage + 1) * kStageTiles;
+                const int t1 = min(c1, stage_end), number = pass * stages + stage, slot = number % kStages;
+                if (alive && !eb::mbar_wait(&full[slot], (uint32_t)(number / kStages) & 1u)) {
+                    alive = false;
+                    if (lane == 0) atomicOr(error, kWaitFailed);
+                }
+                uint32_t tile = ring + slot * kStageBytes + (t0 - first - stage * kStageTiles) * kTileRowBytes;
+                const uint32_t b_offset = (uint32_t)(t0 - 8 * block0) * 32u;
+                uint32_t b_at[P];
+#pragma unroll
+                for (int p = 0; p < P; ++p) b_at[p] = act_lane[p] + b_offset;
+                auto one = [&](auto index) {   // tile `index` after the current one
+                    constexpr int kAhead = decltype(index)::value;
+                    uint32_t a[4];
+                    decoder.template fragment<kAhead * kTileRowBytes>(tile, a);
+#pragma unroll
+                    for (int p = 0; p < P; ++p) {
+                        const float2 b = eb::lds_f2<kAhead * 32>(b_at[p]);
+                        eb::mma_f16_16816(acc[p], a[0], a[1], a[2], a[3], __float_as_uint(b.x), __float_as_uint(b.y));
+                    }
+                };
+                int t = t0;
+                for (; t + kUnroll <= t1; t += kUnroll) {
+                    eb::static_for<kUnroll>(one);
+                    tile += kUnroll * kTileRowBytes;
+#pragma unroll
+                    for (int p = 0; p < P; ++p) b_at[p] += 32u * kUnroll;
+                }
+                for (; t < t1; ++t) {
+                    one(std::integral_constant<int, 0>{});
+                    tile += kTileRowBytes;
+#pragma unroll
+                    for (int p = 0; p < P; ++p) b_at[p] += 32u;
+                }
+                if (t1 == stage_end || t1 == last) {   // done with the stage's buffer
+                    __syncwarp();
+                    if (lane == 0) eb::mbar_arrive(&empty[slot]);
+                }
+                t0 = t1;
+            }
+            c0 = c1;
         }
         // acc[p][i]: column g (i < 2) or g + 8 of this warp's 16, row row_base + 8 p + 2 q + (i & 1).
         if (splits > 1) {
@@ -232,30 +390,48 @@ __global__ void __launch_bounds__(256) mma_kernel(const __grid_constant__ CUtens
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int row = row_base + 8 * p + 2 * q + (i & 1);
-                    if (row < rows)
-                        partials[((size_t)blockIdx.y * rows + row) * n + column0 + warp * 16 + g + 8 * (i >> 1)] = acc[p][i];
+                    if (row < rows) job.partials[((size_t)split * rows + row) * n + column0 + warp * 16 + g + 8 * (i >> 1)] = acc[p][i];
                 }
         } else {
+            // One split: rotate and scale here. The sums of 8 rows x 128 columns meet in the activation buffer, which nobody
+            // reads any more; warp w finishes row w of the 8.
+            float(*tile_out)[128] = reinterpret_cast<float(*)[128]>(act);
 #pragma unroll
             for (int p = 0; p < P; ++p) {
-                __syncthreads();
+                decoders_sync();
 #pragma unroll
                 for (int i = 0; i < 4; ++i) tile_out[2 * q + (i & 1)][warp * 16 + g + 8 * (i >> 1)] = acc[p][i];
-                __syncthreads();
-                // Warp `warp` finishes row `warp` of the 8: Hadamard in registers, svh, BF16.
+                decoders_sync();
                 const int row = row_base + 8 * p + warp;
-                float v[4] = {tile_out[warp][lane * 4], tile_out[warp][lane * 4 + 1], tile_out[warp][lane * 4 + 2], tile_out[warp][lane * 4 + 3]};
-                hadamard128_warp(v, lane);
                 if (row < rows) {
-                    const uint2 sb = *reinterpret_cast<const uint2*>(svh + column0 + lane * 4);
-                    const uint32_t sw[2] = {sb.x, sb.y};
-                    uint32_t bits[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        bits[j] = eb::float_to_bf16_bits(__fmul_rn(__half2float(__ushort_as_half((unsigned short)(sw[j >> 1] >> (16 * (j & 1))))), v[j]));
-                    *reinterpret_cast<uint2*>(out + (size_t)row * n + column0 + lane * 4) = make_uint2(bits[0] | bits[1] << 16, bits[2] | bits[3] << 16);
+                    float v[4] = {tile_out[warp][lane * 4], tile_out[warp][lane * 4 + 1], tile_out[warp][lane * 4 + 2], tile_out[warp][lane * 4 + 3]};
+                    finish128(v, job.svh + column0, job.out + (size_t)row * n + column0, lane);
                 }
             }
+        }
+    }
+
+    if (splits > 1 && job.flags != nullptr) {
+        decoders_sync();   // every thread's partials are stored; the fence of thread 0 below orders them before the flag
+        if (warp == 0) {
+            volatile unsigned long long* flags = job.flags + (size_t)blockIdx.x * splits;
+            if (lane == 0) {
+                __threadfence();
+                flags[split] = job.tag;
+            }
+            __syncwarp();
+            __threadfence();   // sequentially consistent: of two CTAs that finish together at least one sees the other's flag
+            bool all = true;   // the lanes read the block's flags side by side
+            for (int i = lane; i < splits; i += 32) all = all && flags[i] == job.tag;
+            all = __all_sync(0xFFFFFFFFu, all);
+            __threadfence();
+            if (lane == 0) last_arrival = all ? 1 : 0;
+        }
+        decoders_sync();
+        if (last_arrival != 0) {
+            for (int row = warp; row < rows; row += kDecodeWarps)
+                add_and_finish128(job.partials + (size_t)row * n + column0, (size_t)rows * n, splits, job.svh + column0,
+                        job.out + (size_t)row * n + column0, lane);
         }
     }
 }

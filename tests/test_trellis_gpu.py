@@ -51,6 +51,16 @@ class DeviceLinear:
             self.format.linear(gpu, launch)
         return self.dev.get(d_y, np.uint16, (rows, self.n))
 
+    def one_call(self, x_bits, splits, **select):
+        """The same linear as ONE launch (euhedral_b200_linear_trellis_bf16) with the split count given."""
+        rows = x_bits.shape[0]
+        need = self.dev.gpu.lib.euhedral_b200_linear_trellis_scratch_bytes(rows, self.k, self.n, len(self.ends), splits)
+        d_x, d_y, d_s = self.dev.put(x_bits), self.dev.empty(rows * self.n * 2), self.dev.empty(max(need, 256), fill=0xA5)
+        with self.dev.submit(**select) as gpu:
+            gpu.linear_trellis_bf16(d_x.data_ptr(), *[t.data_ptr() for t in self.tensors[:3]], self.tensors[3].data_ptr(), d_y.data_ptr(),
+                                    d_s.data_ptr(), need, rows, self.k, self.n, self.w, len(self.ends), splits)
+        return self.dev.get(d_y, np.uint16, (rows, self.n))
+
 
 def within_kernel_tolerance(got_bits, expect):
     """native/tests/test_trellis.py:157-165."""
@@ -117,25 +127,32 @@ def test_layer_shapes(dev, n, k, w):
     ends = [n] if segments == 1 else [n // 2, n]
     payload, suh, svh = random_object(rng, k, n, w, segments=segments)
     linear = DeviceLinear(dev, payload, suh, svh, ends, 8 * dev.gpu.multiprocessor_count())
+    splits = TrellisFormat.splits(k, n, 8 * dev.gpu.multiprocessor_count())
     for rows in (1, 5):
         x = random_x(rng, rows, k)
         expect = OC.trellis_linear(x, payload, suh, svh, ends).astype(np.float64)
-        assert within_kernel_tolerance(linear.linear(x), expect), (n, k, w, rows)
+        got = linear.linear(x)
+        assert within_kernel_tolerance(got, expect), (n, k, w, rows)
+        assert np.array_equal(linear.one_call(x, splits, pdl=True), got), (n, k, w, rows)   # one launch, the same bits
 
 
 def test_one_call_linear_is_bitwise_the_table_launches(dev):
+    """The one-launch linear (activations rotated inside the kernel, splits joined by whoever finishes last) against the
+    three table launches a host plans one by one."""
     rng = np.random.default_rng(44)
     k, n, w = 2048, 512, 48
     payload, suh, svh = random_object(rng, k, n, w, segments=2)
     ends = [256, 512]
     lib = dev.gpu.lib
-    for target, rows in ((8, 3), (140, 5), (140, 1)):
+    for target, rows in ((8, 3), (140, 5), (140, 1), (1, 7), (1, 20), (30, 13), (64, 40)):
         table = DeviceLinear(dev, payload, suh, svh, ends, target)
         x = random_x(rng, rows, k)
         expect = table.linear(x)
         splits = TrellisFormat.splits(k, n, target)
+        assert np.array_equal(table.one_call(x, splits), expect), (target, rows)
         need = lib.euhedral_b200_linear_trellis_scratch_bytes(rows, k, n, 2, splits)
-        assert need == table.format.scratch_bytes(dev.gpu, rows, k, n, 2)
+        # a flag per block and split, then the partials; nothing with one split
+        assert need == (((n // 128 * splits * 8 + 255) & ~255) + splits * rows * n * 4 if splits > 1 else 0)
         d_x, d_y, d_s = dev.put(x), dev.empty(rows * n * 2), dev.empty(need)
         with dev.submit(pdl=True) as gpu:
             gpu.linear_trellis_bf16(d_x.data_ptr(), *[t.data_ptr() for t in table.tensors[:3]], table.tensors[3].data_ptr(), d_y.data_ptr(),
