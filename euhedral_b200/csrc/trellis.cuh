@@ -281,7 +281,8 @@ __global__ void __launch_bounds__(kThreads, P == 1 ? kResident : 2) linear_kerne
             const int total = passes * stages;
             for (int i = 0; i < total; ++i) {
                 const int slot = i % kStages;
-                if (i >= kStages && !eb::mbar_wait(&empty[slot], (uint32_t)(i / kStages - 1) & 1u)) {
+                // a stage lasts microseconds: the poll sleeps between tries and leaves the issue slots to the decoding warps
+                if (i >= kStages && !eb::mbar_wait_at<256>(eb::smem_u32(&empty[slot]), (uint32_t)(i / kStages - 1) & 1u)) {
                     atomicOr(error, kWaitFailed);
                     break;
                 }

@@ -200,8 +200,9 @@ class CudaGpuMemory:
 
     def linear_trellis_bf16(self, input: int, words: int, suh: int, svh: int, ends: int, output: int, scratch: int, scratch_bytes: int,
                             rows: int, in_features: int, out_features: int, tile_words: int, segments: int, splits: int = 0) -> None:
-        """A whole trellis linear as one call (prepass, GEMM, epilogue planned inside the library). No counterpart in the
-        reference, whose host queues the three table launches itself; same bits. splits = 0: the device's default."""
+        """A whole trellis linear as one launch (activations rotated and K splits joined inside the kernel). No counterpart
+        in the reference, whose host queues three table launches; same bits for the same split count. splits = 0: the
+        device's one-wave default."""
         self._check("trellis linear", self.lib.euhedral_b200_linear_trellis_bf16(
             input, words, suh, svh, ends, output, scratch, scratch_bytes, rows, in_features, out_features, tile_words, segments, splits))
 

@@ -125,16 +125,16 @@ EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_group_nvfp4_bf16(uint32_t count, c
 /* No counterpart in the reference. A whole trellis linear for callers that cannot provide scratch because they cannot
  * allocate device memory at the point of the call: a host that only holds the weight and activation addresses it was
  * given, a plugin running inside somebody else's memory plan, or a step that runs after the process's allocator has
- * been frozen. The scratch (rotated FP16 activations, then the FP32 partial sums of the K splits) lives in a static
+ * been frozen. The scratch (a flag per column block and K split, then the FP32 partial sums of the splits) lives in a static
  * device array inside the library, euhedral_b200_static_scratch_bytes() bytes (8 MiB) on every device that loads the
  * library, held until the process exits. The call allocates and frees nothing.
  *   input BF16 [rows][in_features]; words the payload [in/16][out/16][tile_words]; suh FP16 [segments][in]; svh FP16 [out];
- *   segment_ends int32 [segments]; output BF16 [rows][out]; splits = the K splits (1 = finish in the GEMM kernel).
- * Needs align256(segments*rows*in*2) + (splits > 1 ? splits*rows*out*4 : 0) <= the static size, else SIZE_OVERFLOW
- * (use euhedral_cuda_linear_launch with caller scratch). Same results, bit for bit, as the three table launches.
+ *   segment_ends int32 [segments]; output BF16 [rows][out]; splits = the K splits (1: nothing is exchanged).
+ * Needs splits > 1 ? align256(out/128*splits*8) + splits*rows*out*4 : 0 <= the static size, else SIZE_OVERFLOW
+ * (use euhedral_b200_linear_trellis_bf16 with caller scratch). Same results, bit for bit, as the three table launches.
  * The first call on a device looks the array's device address up; make that call before any stream capture.
  * Every call uses the same array and leaves its last contents there: calls that overlap on the GPU (two streams, or
- * two threads) race on it. Nothing in it needs clearing between calls - every byte read was written by the same call. */
+ * two threads) race on it. Nothing in it needs clearing between calls - a flag counts only when it holds the call's own tag. */
 EUHEDRAL_CUDA_EXPORT uint64_t euhedral_b200_static_scratch_bytes(void);
 EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_trellis_bf16_static(const void* input, const void* words, const void* suh,
         const void* svh, const void* segment_ends, void* output, uint32_t rows, uint32_t in_features, uint32_t out_features,
@@ -152,11 +152,13 @@ EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_nvfp4_native_prequantized_bf16(con
         uint64_t scratch_byte_size);
 
 /* No counterpart in the reference, whose Java host plans a trellis linear as three launches through the kernel table
- * (core/.../artifact/format/TrellisFormat.java:484-567). The same three launches planned here, as one call with caller
- * scratch of at least euhedral_b200_linear_trellis_scratch_bytes(...) bytes (16-byte aligned): rotated FP16 activations,
- * then the FP32 partial sums of the K splits. splits = 0 takes the reference's split count for this device (8 blocks per
- * SM); an N-shard passes the split count of the whole tensor so that it reproduces the whole tensor's bits. Arguments
- * otherwise as euhedral_b200_linear_trellis_bf16_static; results bit for bit those of the table launches. */
+ * (core/.../artifact/format/TrellisFormat.java:484-567). Here the whole linear is ONE launch: the activations are rotated
+ * inside the kernel, and the CTA that finishes a column block last adds the K splits in split order, rotates, scales and
+ * writes BF16. Caller scratch of at least euhedral_b200_linear_trellis_scratch_bytes(...) bytes (16-byte aligned, contents
+ * arbitrary, 0 bytes with one split): a 64-bit flag per column block and split, then the FP32 partial sums of the splits.
+ * splits = 0 takes this device's one-wave split count; with the reference host's count (TrellisFormat.java:369-376) the
+ * result is bit for bit that of the three table launches; an N-shard passes the split count of the whole tensor so that
+ * it reproduces the whole tensor's bits. Arguments otherwise as euhedral_b200_linear_trellis_bf16_static. */
 EUHEDRAL_CUDA_EXPORT uint64_t euhedral_b200_linear_trellis_scratch_bytes(uint32_t rows, uint32_t in_features,
         uint32_t out_features, uint32_t segments, uint32_t splits);
 EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_trellis_bf16(const void* input, const void* words, const void* suh,
