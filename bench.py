@@ -377,10 +377,13 @@ def measure_per_shape(bench: Bench, steps_floor=40):
     """Every distinct layer shape alone, M = 1..5, each format: one C-ABI call per launch, programmatic dependent launch,
     the tensor rotated over enough copies to exceed the L2 two and a half times."""
     torch, lib = bench.torch, bench.lib
-    distinct = {"q": ("q", "o"), "k": ("k", "v"), "gate": ("gate", "up"), "down": ("down",)}
+    distinct = {"q": ("q", "o"), "k": ("k", "v"), "gate": ("gate", "up"), "down": ("down",),
+                "query_key_value": ("query_key_value",), "gate_up": ("gate_up",)}
+    # ... and the fused objects the reference's converter emits and its host calls as one tensor
+    shapes = list(LAYER) + [("query_key_value", 7168, 5120), ("gate_up", 34816, 5120)]
     table = {}
     for fmt in ("nvfp4", "q3", "trellis"):
-        for index, (name, n, k) in enumerate(LAYER):
+        for index, (name, n, k) in enumerate(shapes):
             if name not in distinct:
                 continue
             first = bench.weight(fmt, index, n, k)
@@ -445,19 +448,37 @@ def measure_prefill(bench: Bench, rows, steps, warmup):
         for blob, x, n, k in tensors:
             bench.check(lib.euhedral_b200_nvfp4_native_quantize(x.data_ptr(), scratch.data_ptr(), rows, k, need))
 
+    # The same layer as the reference's host calls it: the fused objects its converter emits (query_key_value as one tensor
+    # of 7168 rows, gate_up as one of 34816 rows through the paired SwiGLU region), four calls instead of seven.
+    x5, x17 = xs[5120], xs[17408]
+    fused = [(lib.euhedral_cuda_linear_nvfp4_native_bf16, bench.weight("nvfp4", 16, 7168, 5120)[0], x5, 7168, 5120),
+             (lib.euhedral_cuda_linear_nvfp4_native_bf16, tensors[3][0], x5, 5120, 5120),
+             (lib.euhedral_cuda_nvfp4_native_gate_up_swiglu_bf16, bench.weight("nvfp4", 17, 34816, 5120)[0], x5, 34816, 5120),
+             (lib.euhedral_cuda_linear_nvfp4_native_bf16, tensors[6][0], x17, 5120, 17408)]
+    fused_need = max(lib.euhedral_cuda_nvfp4_native_scratch_bytes(rows, k, n) for _, _, _, n, k in fused)
+    fused_scratch = torch.empty(fused_need, dtype=torch.uint8, device="cuda")
+
+    def fused_body(_):
+        for entry, blob, x, n, k in fused:
+            bench.check(entry(x.data_ptr(), blob.data_ptr(), y.data_ptr(), fused_scratch.data_ptr(), rows, k, n, blob.numel(), fused_need))
+
     with torch.cuda.stream(bench.stream), bench.submit():
         seconds = bench.timed(steps, warmup, body)
         quantize_seconds = bench.timed(steps, 1, quantize_only)
+        fused_seconds = bench.timed(steps, 1, fused_body)
     issued = 2 * flops * steps / seconds / 1e12
     result = {"rows": rows, "tflops": flops * steps / seconds / 1e12, "issued_tflops": issued, "ms_per_layer": seconds / steps * 1e3,
               "quantize_ms_per_layer": quantize_seconds / steps * 1e3, "quantize_share": quantize_seconds / seconds,
+              "fused_objects": {"calls": "query_key_value 7168x5120, o, gate_up 34816x5120 with SwiGLU in the epilogue, down",
+                                "ms_per_layer": fused_seconds / steps * 1e3, "issued_tflops": 2 * flops * steps / fused_seconds / 1e12,
+                                "frac_of_nominal_fp4": 2 * flops * steps / fused_seconds / 1e12 / FP4_NOMINAL_TFLOPS},
               "roofline": {"bound": "tensor", "achieved": issued, "algorithmic": flops * steps / seconds / 1e12, "peak": FP4_NOMINAL_TFLOPS,
                            "unit": "TFLOP/s", "frac": issued / FP4_NOMINAL_TFLOPS,
                            "peak_kind": "nominal dense FP4 (MEASURED_PEAKS.json has no FP4 figure)",
                            "algorithmic_over_measured_bf16_burst": flops * steps / seconds / 1e12 / bench.peaks["bf16"] if bench.peaks["bf16"] else None,
                            "note": "achieved = issued FLOP (two activation terms); algorithmic = 2 M N K"}}
     assert gpu.take_device_error() == 0
-    del tensors, xs, y, scratch
+    del tensors, xs, y, scratch, fused, fused_scratch
     torch.cuda.empty_cache()
     return result
 

@@ -748,6 +748,22 @@ int euhedral_cuda_linear_nvfp4_native_bf16(const void* input, const void* weight
             state->error_word));
 }
 
+// The paired gate/up region (native/src/host/nvfp4_linear.c:288-295): `weights` is a gate/up object of `outputs` rows, gate
+// rows first; the output is [rows][outputs / 2], bf16(silu(gate) * up) with gate and up rounded to BF16 first. An output
+// tile here is 128 columns wide (the reference's: 64), so outputs / 2 must be a multiple of 128, else ROUTE_UNAVAILABLE.
+int euhedral_cuda_nvfp4_native_gate_up_swiglu_bf16(const void* input, const void* weights, void* output, void* scratch, uint32_t rows,
+        uint32_t width, uint32_t outputs, uint64_t weight_bytes, uint64_t scratch_byte_size) {
+    DeviceState* state = nullptr;
+    int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    if (outputs % 2u != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    status = native_validate(true, input, weights, output, scratch, rows, width, outputs, weight_bytes, scratch_byte_size);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    if (outputs % 256u != 0) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    return finish(nvfp4n::run(input, weights, output, scratch, rows, width, outputs, state->sms, t_stream, t_pdl != 0 && t_stream != nullptr,
+            state->error_word, true));
+}
+
 int euhedral_b200_nvfp4_native_quantize(const void* input, void* scratch, uint32_t rows, uint32_t in_features, uint64_t scratch_byte_size) {
     DeviceState* state = nullptr;
     const int status = bind(&state);

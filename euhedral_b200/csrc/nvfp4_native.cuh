@@ -244,7 +244,7 @@ __device__ __forceinline__ void tmem_load_32(uint32_t (&r)[32], uint32_t address
 
 struct TileWalk {
     uint32_t tiles_m, tiles_n, total;
-    __device__ TileWalk(uint32_t rows, uint32_t n) : tiles_m((rows + kTileM - 1u) / kTileM), tiles_n((n + kTileN - 1u) / kTileN) {
+    __device__ TileWalk(uint32_t rows, uint32_t n, uint32_t tile_columns) : tiles_m((rows + kTileM - 1u) / kTileM), tiles_n((n + tile_columns - 1u) / tile_columns) {
         total = tiles_m * tiles_n;
     }
     // Panels of kPanel tile columns; inside a panel the row index runs fastest across the panel's columns.
@@ -260,7 +260,7 @@ struct TileWalk {
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, const float* __restrict__ row_globals,
         const float* __restrict__ tensor_global, uint16_t* __restrict__ out, float* __restrict__ partials, uint32_t splits, uint32_t rows,
-        uint32_t n, uint32_t k, uint32_t* __restrict__ error) {
+        uint32_t n, uint32_t k, uint32_t pair_tiles, uint32_t* __restrict__ error) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -269,7 +269,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     uint64_t* acc_empty = acc_full + 1;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 1);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const TileWalk walk(rows, n);
+    // pair_tiles != 0: the gate/up region. `n` is the output width (half of the weight rows); an output tile of 128 columns
+    // takes the 128 gate rows at its own place and the 128 up rows pair_tiles * 128 further down as the halves of its B tile.
+    const bool paired = pair_tiles != 0u;
+    const TileWalk walk(rows, n, paired ? 128u : kTileN);
     const uint32_t k_steps = k / kStepK, k_blocks = k / kBlockK;
     // A work item is an output tile and one of `splits` ranges of its K steps (one range unless the call is skinny).
     const uint32_t items = walk.total * splits;
@@ -313,11 +316,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                     eb::mbar_arrive_expect_tx(&full[s], kStageBytes);
                     tma_load_3d(stage, &map_a, (int)(ks * 128u), (int)(tm * kTileM), 0, &full[s]);
                     tma_load_3d(stage + kATile, &map_a, (int)(ks * 128u), (int)(tm * kTileM), 1, &full[s]);
-                    tma_load_2d(stage + kTerms * kATile, &map_b, (int)(ks * 128u), (int)(tn * kTileN), &full[s]);
+                    // the B tile's two halves of 128 weight rows, as 128-row tiles of the weight matrix
+                    const uint32_t low = paired ? tn : 2u * tn, high = paired ? pair_tiles + tn : 2u * tn + 1u;
+                    tma_load_2d(stage + kTerms * kATile, &map_b, (int)(ks * 128u), (int)(low * 128u), &full[s]);
+                    tma_load_2d(stage + kTerms * kATile + kBTile / 2u, &map_b, (int)(ks * 128u), (int)(high * 128u), &full[s]);
                     uint8_t* sf = stage + kTerms * kATile + kBTile;
                     eb::bulk_g2s(sf, sfa + ((uint64_t)tm * k_blocks + ks * 4u) * kTerms * kAtom, kSfaStage, &full[s]);
-                    eb::bulk_g2s(sf + kSfaStage, sfb + ((uint64_t)(2u * tn) * k_blocks + ks * 4u) * kAtom, 4u * kAtom, &full[s]);
-                    eb::bulk_g2s(sf + kSfaStage + 4u * kAtom, sfb + ((uint64_t)(2u * tn + 1u) * k_blocks + ks * 4u) * kAtom, 4u * kAtom, &full[s]);
+                    eb::bulk_g2s(sf + kSfaStage, sfb + ((uint64_t)low * k_blocks + ks * 4u) * kAtom, 4u * kAtom, &full[s]);
+                    eb::bulk_g2s(sf + kSfaStage + 4u * kAtom, sfb + ((uint64_t)high * k_blocks + ks * 4u) * kAtom, 4u * kAtom, &full[s]);
                 }
             }
         }
@@ -377,17 +383,47 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             }
             tcgen05_fence_after();
             uint32_t r[4][32];
-            const uint32_t from = tmem + ((quarter * 32u) << 16) + half * 128u;
+            // plain: 128 consecutive columns; paired: 64 gate columns (r[0], r[1]) and the 64 up columns that match them (r[2], r[3])
+            const uint32_t from = tmem + ((quarter * 32u) << 16) + (paired ? half * 64u : half * 128u);
+            const uint32_t other = paired ? from + 128u : from + 64u;
             tmem_load_32(r[0], from);
             tmem_load_32(r[1], from + 32u);
-            tmem_load_32(r[2], from + 64u);
-            tmem_load_32(r[3], from + 96u);
+            tmem_load_32(r[2], other);
+            tmem_load_32(r[3], other + 32u);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) eb::mbar_arrive(acc_empty);
             const uint32_t row = tm * kTileM + quarter * 32u + lane;
             const float scale = row < rows ? __fmul_rn(row_globals[row], scale_w) : 0.0f;
+            if (paired) {
+                // out[row][col] = bf16(silu(gate) * up) with gate and up rounded to BF16 first (the reference's region:
+                // native/src/nvfp4_native/native.cuh:390-413, same expression, same expf and division)
+#pragma unroll
+                for (uint32_t cb = 0; cb < 2u; ++cb) {
+                    const uint32_t col = tn * 128u + half * 64u + cb * 32u;
+                    if (row >= rows || col >= n) continue;
+                    uint16_t* dst = out + (uint64_t)row * n + col;
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            float value[2];
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int c = 8 * v + 2 * i + e;
+                                const float gate = eb::bf16_bits_to_float(eb::float_to_bf16_bits(__fmul_rn(__uint_as_float(r[cb][c]), scale)));
+                                const float up = eb::bf16_bits_to_float(eb::float_to_bf16_bits(__fmul_rn(__uint_as_float(r[cb + 2][c]), scale)));
+                                value[e] = __fmul_rn(__fdiv_rn(gate, __fadd_rn(1.0f, expf(-gate))), up);
+                            }
+                            packed[i] = (uint32_t)eb::float_to_bf16_bits(value[0]) | (uint32_t)eb::float_to_bf16_bits(value[1]) << 16;
+                        }
+                        if (col + 8u * v < n) *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    }
+                }
+                continue;
+            }
 #pragma unroll
             for (uint32_t cb = 0; cb < 4u; ++cb) {
                 const uint32_t col = tn * kTileN + half * 128u + cb * 32u;
@@ -480,8 +516,9 @@ inline cudaError_t quantize(const void* input, void* scratch, uint32_t rows, uin
 }
 
 // multiply: the weight scale plane -> scale atoms in the scratch, then the GEMM over the quantized activations found there.
+// paired: the weights are a gate/up object (gate rows first); the output is [rows][out_features / 2] SwiGLU values.
 inline cudaError_t multiply(const void* weights, void* output, void* scratch, uint32_t rows, uint32_t k, uint32_t out_features, int sms,
-        cudaStream_t stream, bool pdl, uint32_t* error) {
+        cudaStream_t stream, bool pdl, uint32_t* error, bool paired = false) {
     const EncodeTiled encode = encoder();
     if (encode == nullptr) return cudaErrorNotSupported;
     const ActivationLayout layout(rows, k, out_features);
@@ -495,7 +532,7 @@ inline cudaError_t multiply(const void* weights, void* output, void* scratch, ui
     const cuuint64_t a_dims[3] = {row_bytes, rows, kTerms}, a_strides[2] = {row_bytes, row_bytes * rows};
     const cuuint32_t a_box[3] = {128u, kTileM, 1u};
     const cuuint64_t b_dims[2] = {row_bytes, out_features}, b_strides[1] = {row_bytes};
-    const cuuint32_t b_box[2] = {128u, kTileN};
+    const cuuint32_t b_box[2] = {128u, 128u};   // half a B tile: the kernel places the two halves itself
     CUresult r = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, a_dims, a_strides, a_box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r == CUDA_SUCCESS)
@@ -507,17 +544,18 @@ inline cudaError_t multiply(const void* weights, void* output, void* scratch, ui
     cudaError_t e = launch_on(stream, pdl, repack_weight_scales, dim3((unsigned)((items + 255u) / 256u)), dim3(256), 0, w + scale_offset, base + layout.sfb_offset,
             out_features, layout.k_blocks, n_padded);
     if (e != cudaSuccess) return e;
-    const uint32_t tiles = ((rows + kTileM - 1u) / kTileM) * ((out_features + kTileN - 1u) / kTileN);
+    const uint32_t pair_tiles = paired ? out_features / 256u : 0u, width = paired ? out_features / 2u : out_features;
+    const uint32_t tiles = ((rows + kTileM - 1u) / kTileM) * (paired ? pair_tiles : (out_features + kTileN - 1u) / kTileN);
     // The skinny route (the reference's 9..64-row kernel, native/src/nvfp4_native/native.cuh:435-585, cuts K the same way):
     // few rows make few output tiles; K is cut so that about every SM gets a work item.
     uint32_t splits = 1;
-    if (rows <= kSkinnyRows && tiles * 2u <= (uint32_t)sms) splits = std::max(1u, std::min(std::min(kMaxSplits, k / kStepK), (uint32_t)sms / tiles));
+    if (!paired && rows <= kSkinnyRows && tiles * 2u <= (uint32_t)sms) splits = std::max(1u, std::min(std::min(kMaxSplits, k / kStepK), (uint32_t)sms / tiles));
     const uint32_t work = tiles * splits, grid = work < (uint32_t)sms ? work : (uint32_t)sms;
     float* partials = reinterpret_cast<float*>(base + layout.partial_offset);
     const float* row_globals = reinterpret_cast<const float*>(base + layout.global_offset);
     const float* tensor_global = reinterpret_cast<const float*>(w + global_offset);
     e = launch_on(stream, pdl, gemm_kernel, dim3(grid), dim3(kThreads), kSharedBytes, map_a, map_b, base + layout.sfa_offset,
-            base + layout.sfb_offset, row_globals, tensor_global, static_cast<uint16_t*>(output), partials, splits, rows, out_features, k, error);
+            base + layout.sfb_offset, row_globals, tensor_global, static_cast<uint16_t*>(output), partials, splits, rows, width, k, pair_tiles, error);
     if (e != cudaSuccess || splits == 1u) return e;
     const uint64_t quads = (uint64_t)rows * (out_features / 4u);
     return launch_on(stream, pdl, finish_splits, dim3((unsigned)((quads + 255u) / 256u)), dim3(256), 0, partials, row_globals, tensor_global,
@@ -525,9 +563,9 @@ inline cudaError_t multiply(const void* weights, void* output, void* scratch, ui
 }
 
 inline cudaError_t run(const void* input, const void* weights, void* output, void* scratch, uint32_t rows, uint32_t k, uint32_t out_features,
-        int sms, cudaStream_t stream, bool pdl, uint32_t* error) {
+        int sms, cudaStream_t stream, bool pdl, uint32_t* error, bool paired = false) {
     const cudaError_t e = quantize(input, scratch, rows, k, stream, pdl);
-    return e != cudaSuccess ? e : multiply(weights, output, scratch, rows, k, out_features, sms, stream, pdl, error);
+    return e != cudaSuccess ? e : multiply(weights, output, scratch, rows, k, out_features, sms, stream, pdl, error, paired);
 }
 
 }  // namespace nvfp4n

@@ -178,6 +178,18 @@ class CudaGpuMemory:
         self._check("native NVFP4 linear", status)
         return True
 
+    def nvfp4_native_gate_up_swiglu_bf16(self, input, weights, output, rows, width, outputs, weight_bytes) -> bool:
+        """The paired gate/up region (CudaGpuMemory.nvfp4NativeGateUpSwigluBf16): `weights` holds `outputs` rows, gate rows
+        first; `output` gets [rows][outputs / 2] SwiGLU values. False when the route declined."""
+        need = self.lib.euhedral_cuda_nvfp4_native_scratch_bytes(rows, width, outputs)
+        scratch = self.native_scratch(need)
+        status = self.lib.euhedral_cuda_nvfp4_native_gate_up_swiglu_bf16(input, weights, output, scratch, rows, width, outputs, weight_bytes,
+                                                                         self._native_scratch_bytes)
+        if status == library.ROUTE_UNAVAILABLE:
+            return False
+        self._check("native NVFP4 gate/up SwiGLU", status)
+        return True
+
     def nvfp4_native_quantize(self, input: int, rows: int, in_features: int, out_features: int) -> bool:
         """First half of the native route for linears that share their input: quantizes the rows into the shared scratch
         (sized for the widest linear, `out_features`). No counterpart in the reference. False when the route declined."""

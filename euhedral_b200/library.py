@@ -51,6 +51,7 @@ SIGNATURES = {
     "euhedral_cuda_nvfp4_native_available": (C.c_int, []),
     "euhedral_cuda_nvfp4_native_scratch_bytes": (_u64, [_u32, _u32, _u32]),
     "euhedral_cuda_linear_nvfp4_native_bf16": (C.c_int, [_ptr, _ptr, _ptr, _ptr, _u32, _u32, _u32, _u64, _u64]),
+    "euhedral_cuda_nvfp4_native_gate_up_swiglu_bf16": (C.c_int, [_ptr, _ptr, _ptr, _ptr, _u32, _u32, _u32, _u64, _u64]),
     "euhedral_cuda_linear_kernel_count": (C.c_int, []),
     "euhedral_cuda_linear_kernel_name": (C.c_char_p, [C.c_int]),
     "euhedral_cuda_linear_kernel_available": (C.c_int, [_i32]),

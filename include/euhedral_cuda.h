@@ -83,6 +83,12 @@ EUHEDRAL_CUDA_EXPORT uint64_t euhedral_cuda_nvfp4_native_scratch_bytes(uint32_t 
 EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_nvfp4_native_bf16(const void* input, const void* weights, void* output,
         void* scratch, uint32_t rows, uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size,
         uint64_t scratch_byte_size);
+/* The paired gate/up region on the native route (reference native/include/euhedral_cuda.h:168-172): `weights` is a
+ * gate/up object of `outputs` weight rows, gate rows first; output BF16 [rows][outputs / 2] = silu(gate) * up with gate and
+ * up rounded to BF16 before the SwiGLU. Scratch as for a linear of `outputs` columns. -1 for odd `outputs`; -5 unless
+ * outputs / 2 is a multiple of 128 (an output tile here is 128 columns wide). */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_nvfp4_native_gate_up_swiglu_bf16(const void* input, const void* weights, void* output,
+        void* scratch, uint32_t rows, uint32_t width, uint32_t outputs, uint64_t weight_bytes, uint64_t scratch_byte_size);
 
 /* ---- the shared linear kernel table (trellis launches) ------------------------------------------------------------ */
 

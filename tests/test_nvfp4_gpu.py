@@ -155,7 +155,9 @@ def test_row_shards_equal_the_whole(dev):
         assert np.array_equal(np.concatenate(parts, axis=1), whole)
 
 
-@pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408), (1024, 5120), (5120, 5120)])
+# The last two are the fused objects the reference's converter emits and its host calls as one tensor: query_key_value
+# (5120 + 1024 + 1024 rows) and gate_up (2 x 17408 rows), tools/euhedral_artifacts/trellis.py:128-146.
+@pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408), (1024, 5120), (5120, 5120), (7168, 5120), (34816, 5120)])
 def test_model_shapes(dev, n, k):
     rng = np.random.default_rng(0xE0)
     weights = (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))

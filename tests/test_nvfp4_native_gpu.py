@@ -174,3 +174,45 @@ def test_native_route_declines(dev):
     finally:
         dev.gpu.select_exact_numerics(False)
     assert lib.euhedral_cuda_nvfp4_native_available() == 1
+
+
+# The paired gate/up region (the reference's euhedral_cuda_nvfp4_native_gate_up_swiglu_bf16, native/src/nvfp4_native/
+# native.cuh:390-413): gate and up are the BF16 values the plain native linear gives for the same fused tensor, bit for
+# bit (same accumulators, same scaling and rounding); the SwiGLU on top is FP32 with expf and a division, so the BF16
+# result is compared with a float32 NumPy evaluation: equal almost everywhere, one unit in the last place at most.
+@pytest.mark.parametrize("rows,k,outputs", [(200, 1024, 768), (9, 1024, 512), (300, 5120, 34816)])
+def test_gate_up_swiglu_region(dev, rows, k, outputs):
+    rng = np.random.default_rng(rows + outputs)
+    blob = OC.nvfp4_quantize((rng.standard_normal((outputs, k)) * 0.05).astype(np.float32))
+    x = random_x(rng, rows, k)
+    full, _ = run(dev, x, blob, outputs, k)
+    half = outputs // 2
+    lib = dev.gpu.lib
+    need = lib.euhedral_cuda_nvfp4_native_scratch_bytes(rows, k, outputs)
+    d_x, d_w, d_y, d_s = dev.put(x), dev.put(blob), dev.empty(rows * half * 2), dev.empty(need)
+    with dev.submit(pdl=True):
+        assert lib.euhedral_cuda_nvfp4_native_gate_up_swiglu_bf16(d_x.data_ptr(), d_w.data_ptr(), d_y.data_ptr(), d_s.data_ptr(), rows, k,
+                                                                  outputs, blob.size, need) == 0
+        assert lib.euhedral_cuda_nvfp4_native_gate_up_swiglu_bf16(d_x.data_ptr(), d_w.data_ptr(), d_y.data_ptr(), d_s.data_ptr(), rows, k,
+                                                                  outputs - 1, blob.size, need) == library.INVALID_ARGUMENT
+    got = dev.get(d_y, np.uint16, (rows, half))
+    gate, up = O.bf16_to_f32(full[:, :half]), O.bf16_to_f32(full[:, half:])
+    one = np.float32(1.0)
+    value = (gate / (one + np.exp(-gate, dtype=np.float32))).astype(np.float32) * up
+    expect = O.bf16_bits(value.astype(np.float32))
+    distance = np.abs(got.astype(np.int32) - expect.astype(np.int32))
+    assert distance.max() <= 1, int(distance.max())
+    assert np.mean(distance == 0) >= 0.995, float(np.mean(distance == 0))
+    assert got.any()
+
+
+def test_gate_up_swiglu_needs_whole_tiles(dev):
+    rng = np.random.default_rng(5)
+    k, outputs, rows = 1024, 384, 16          # 192 outputs: not a multiple of the 128-column tile
+    blob = OC.nvfp4_quantize((rng.standard_normal((outputs, k)) * 0.05).astype(np.float32))
+    lib = dev.gpu.lib
+    need = lib.euhedral_cuda_nvfp4_native_scratch_bytes(rows, k, outputs)
+    d_x, d_w, d_y, d_s = dev.put(random_x(rng, rows, k)), dev.put(blob), dev.empty(rows * outputs), dev.empty(need)
+    with dev.submit():
+        assert lib.euhedral_cuda_nvfp4_native_gate_up_swiglu_bf16(d_x.data_ptr(), d_w.data_ptr(), d_y.data_ptr(), d_s.data_ptr(), rows, k,
+                                                                  outputs, blob.size, need) == library.ROUTE_UNAVAILABLE
