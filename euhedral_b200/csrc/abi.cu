@@ -708,6 +708,11 @@ int euhedral_cuda_linear_nvfp4_bf16(const void* input, const void* weights, void
             in_features, out_features));
 }
 
+// Process-wide: native calls of 512 rows and more run on CTA pairs (tcgen05 cta_group::2). Off unless selected.
+static std::atomic<bool> g_native_pairs{false};
+
+void euhedral_b200_select_native_pairs(int enabled) { g_native_pairs.store(enabled != 0); }
+
 int euhedral_cuda_nvfp4_native_available(void) {
     DeviceState* state = nullptr;
     return bind(&state) == EUHEDRAL_CUDA_SUCCESS ? 1 : 0;
@@ -745,7 +750,7 @@ int euhedral_cuda_linear_nvfp4_native_bf16(const void* input, const void* weight
     status = native_validate(true, input, weights, output, scratch, rows, in_features, out_features, weights_byte_size, scratch_byte_size);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     return finish(nvfp4n::run(input, weights, output, scratch, rows, in_features, out_features, state->sms, t_stream, t_pdl != 0 && t_stream != nullptr,
-            state->error_word));
+            state->error_word, false, g_native_pairs.load()));
 }
 
 // The paired gate/up region (native/src/host/nvfp4_linear.c:288-295): `weights` is a gate/up object of `outputs` rows, gate
@@ -761,7 +766,7 @@ int euhedral_cuda_nvfp4_native_gate_up_swiglu_bf16(const void* input, const void
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     if (outputs % 256u != 0) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
     return finish(nvfp4n::run(input, weights, output, scratch, rows, width, outputs, state->sms, t_stream, t_pdl != 0 && t_stream != nullptr,
-            state->error_word, true));
+            state->error_word, true, g_native_pairs.load()));
 }
 
 int euhedral_b200_nvfp4_native_quantize(const void* input, void* scratch, uint32_t rows, uint32_t in_features, uint64_t scratch_byte_size) {
@@ -783,7 +788,7 @@ int euhedral_b200_linear_nvfp4_native_prequantized_bf16(const void* weights, voi
     status = native_validate(false, nullptr, weights, output, scratch, rows, in_features, out_features, weights_byte_size, scratch_byte_size);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     return finish(nvfp4n::multiply(weights, output, scratch, rows, in_features, out_features, state->sms, t_stream, t_pdl != 0 && t_stream != nullptr,
-            state->error_word));
+            state->error_word, false, g_native_pairs.load()));
 }
 
 // ---- kernel table -------------------------------------------------------------------------------------------------------

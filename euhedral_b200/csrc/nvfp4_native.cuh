@@ -242,6 +242,44 @@ __device__ __forceinline__ void tmem_load_32(uint32_t (&r)[32], uint32_t address
             : "r"(address));
 }
 
+// A thread's row of an epilogue block, scaled, rounded to BF16 and stored 16 bytes at a time from column col0.
+// plain: r holds 4 x 32 consecutive columns. paired (the gate/up region): r[0], r[1] are 64 gate columns, r[2], r[3] the 64
+// up columns that match them; out[row][col] = bf16(silu(gate) * up) with gate and up rounded to BF16 first (the reference's
+// region, native/src/nvfp4_native/native.cuh:390-413: the same expression, expf and division).
+__device__ __forceinline__ void store_block(const uint32_t (&r)[4][32], uint16_t* __restrict__ out, uint32_t row, uint32_t rows, uint32_t n,
+        uint32_t col0, float scale, bool paired) {
+    if (row >= rows) return;
+#pragma unroll
+    for (uint32_t cb = 0; cb < 4u; ++cb) {
+        if (paired && cb >= 2u) break;
+        const uint32_t col = col0 + cb * 32u;
+        if (col >= n) continue;
+        uint16_t* dst = out + (uint64_t)row * n + col;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float value[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int c = 8 * v + 2 * i + e;
+                    const float first = __fmul_rn(__uint_as_float(r[cb][c]), scale);
+                    if (paired) {
+                        const float gate = eb::bf16_bits_to_float(eb::float_to_bf16_bits(first));
+                        const float up = eb::bf16_bits_to_float(eb::float_to_bf16_bits(__fmul_rn(__uint_as_float(r[(cb + 2u) & 3u][c]), scale)));
+                        value[e] = __fmul_rn(__fdiv_rn(gate, __fadd_rn(1.0f, expf(-gate))), up);
+                    } else {
+                        value[e] = first;
+                    }
+                }
+                packed[i] = (uint32_t)eb::float_to_bf16_bits(value[0]) | (uint32_t)eb::float_to_bf16_bits(value[1]) << 16;
+            }
+            if (col + 8u * v < n) *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+    }
+}
+
 struct TileWalk {
     uint32_t tiles_m, tiles_n, total;
     __device__ TileWalk(uint32_t rows, uint32_t n, uint32_t tile_columns) : tiles_m((rows + kTileM - 1u) / kTileM), tiles_n((n + tile_columns - 1u) / tile_columns) {
@@ -396,39 +434,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             if (lane == 0) eb::mbar_arrive(acc_empty);
             const uint32_t row = tm * kTileM + quarter * 32u + lane;
             const float scale = row < rows ? __fmul_rn(row_globals[row], scale_w) : 0.0f;
-            if (paired) {
-                // out[row][col] = bf16(silu(gate) * up) with gate and up rounded to BF16 first (the reference's region:
-                // native/src/nvfp4_native/native.cuh:390-413, same expression, same expf and division)
+            if (splits > 1u) {
+                // the raw FP32 sums of this K range: partials[split][row][n]; finish_splits adds the ranges in order
 #pragma unroll
-                for (uint32_t cb = 0; cb < 2u; ++cb) {
-                    const uint32_t col = tn * 128u + half * 64u + cb * 32u;
-                    if (row >= rows || col >= n) continue;
-                    uint16_t* dst = out + (uint64_t)row * n + col;
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint32_t packed[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            float value[2];
-#pragma unroll
-                            for (int e = 0; e < 2; ++e) {
-                                const int c = 8 * v + 2 * i + e;
-                                const float gate = eb::bf16_bits_to_float(eb::float_to_bf16_bits(__fmul_rn(__uint_as_float(r[cb][c]), scale)));
-                                const float up = eb::bf16_bits_to_float(eb::float_to_bf16_bits(__fmul_rn(__uint_as_float(r[cb + 2][c]), scale)));
-                                value[e] = __fmul_rn(__fdiv_rn(gate, __fadd_rn(1.0f, expf(-gate))), up);
-                            }
-                            packed[i] = (uint32_t)eb::float_to_bf16_bits(value[0]) | (uint32_t)eb::float_to_bf16_bits(value[1]) << 16;
-                        }
-                        if (col + 8u * v < n) *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    }
-                }
-                continue;
-            }
-#pragma unroll
-            for (uint32_t cb = 0; cb < 4u; ++cb) {
-                const uint32_t col = tn * kTileN + half * 128u + cb * 32u;
-                if (splits > 1u) {
-                    // the raw FP32 sums of this K range: partials[split][row][n]; finish_splits adds the ranges in order
+                for (uint32_t cb = 0; cb < 4u; ++cb) {
+                    const uint32_t col = tn * kTileN + half * 128u + cb * 32u;
                     if (row < rows && col < n) {
                         float4* dst = reinterpret_cast<float4*>(partials + ((uint64_t)(item % splits) * rows + row) * n + col);
 #pragma unroll
@@ -437,19 +447,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                                 dst[v] = make_float4(__uint_as_float(r[cb][4 * v]), __uint_as_float(r[cb][4 * v + 1]), __uint_as_float(r[cb][4 * v + 2]),
                                         __uint_as_float(r[cb][4 * v + 3]));
                     }
-                } else if (row < rows && col < n) {
-                    uint16_t* dst = out + (uint64_t)row * n + col;
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint32_t packed[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float lo = __fmul_rn(__uint_as_float(r[cb][8 * v + 2 * i]), scale), hi = __fmul_rn(__uint_as_float(r[cb][8 * v + 2 * i + 1]), scale);
-                            packed[i] = (uint32_t)eb::float_to_bf16_bits(lo) | (uint32_t)eb::float_to_bf16_bits(hi) << 16;
-                        }
-                        if (col + 8u * v < n) *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    }
                 }
+            } else {
+                store_block(r, out, row, rows, n, paired ? tn * 128u + half * 64u : tn * kTileN + half * 128u, scale, paired);
             }
         }
     }
@@ -457,6 +457,209 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
+    }
+}
+
+// ---- the same GEMM on CTA pairs -----------------------------------------------------------------------------------------
+// Two CTAs of a cluster share an output tile of 256 rows x 256 columns: each holds its own 128 activation rows (both
+// terms) and HALF of the weight tile (128 weight rows), and one thread of the even CTA issues tcgen05.mma.cta_group::2
+// (M 256, N 256, K 64), which reads both CTAs' shared memory and accumulates each CTA's 128 rows in its own tensor
+// memory. A stage is 56 KB per CTA instead of 72 KB for the same FLOP, so four stages fit and the ring carries 22 % fewer
+// bytes per MMA. Measured on B200 it is 6-9 % SLOWER than gemm_kernel (4.1 against 4.5 PFLOP/s issued on the gate shape,
+// three stages or four alike), so it runs only when the caller selects it. Every CTA issues its own plain TMA loads into its own shared memory (no load names another CTA); the odd
+// CTA's MMA warp only relays "my stage has landed" to a barrier of the even CTA; tcgen05.commit signals the ring's and the
+// accumulator's barriers of both CTAs. Weight scale atoms (all 256 columns) are loaded by both.
+constexpr uint32_t kPairStages = 4;
+constexpr uint32_t kPairBTile = 128u * 128u;
+constexpr uint32_t kPairStageBytes = kTerms * kATile + kPairBTile + kSfaStage + kSfbStage;
+constexpr uint32_t kPairShared = kPairStages * kPairStageBytes + 256u + 1024u;
+constexpr uint32_t kPairInstruction = (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | (0u << 23) | ((256u >> 4) << 24);
+
+__device__ __forceinline__ void pair_copy_atom(uint32_t tmem_address, uint64_t descriptor) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_address), "l"(descriptor) : "memory");
+}
+__device__ __forceinline__ void pair_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+            "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%4], [%5], p;\n}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(kPairInstruction), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+            : "memory");
+}
+// Arrives (once the MMAs issued so far are done) on the barrier at this shared address in both CTAs of the pair.
+__device__ __forceinline__ void pair_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(eb::smem_u32(bar)),
+            "h"((uint16_t)3)
+            : "memory");
+}
+__device__ __forceinline__ void arrive_at_rank(uint64_t* bar, uint32_t rank) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(eb::map_to_rank(eb::smem_u32(bar), rank)) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+        const __grid_constant__ CUtensorMap map_b, const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb,
+        const float* __restrict__ row_globals, const float* __restrict__ tensor_global, uint16_t* __restrict__ out, uint32_t rows, uint32_t n,
+        uint32_t k, uint32_t pair_tiles, uint32_t* __restrict__ error) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);
+    uint64_t* empty = full + kPairStages;
+    uint64_t* peer_full = empty + kPairStages;   // even CTA: the odd CTA's stage has landed
+    uint64_t* acc_full = peer_full + kPairStages;
+    uint64_t* acc_empty = acc_full + 1;          // even CTA: both CTAs' epilogue warps have drained the accumulator
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t rank = eb::cluster_rank(), pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    // pair_tiles != 0: the gate/up region; the even CTA's half of the weight tile is the gate rows, the odd CTA's the up rows.
+    const bool paired = pair_tiles != 0u;
+    const uint32_t tiles_m = (rows + 255u) / 256u, tiles_n = paired ? pair_tiles : (n + 255u) / 256u, items = tiles_m * tiles_n;
+    const uint32_t row_tiles = (rows + kTileM - 1u) / kTileM;
+    const uint32_t k_steps = k / kStepK, k_blocks = k / kBlockK;
+    // Panels of kPanel tile columns; inside a panel the row index runs fastest across the panel's columns.
+    auto place = [&](uint32_t item, uint32_t* tm, uint32_t* tn) {
+        const uint32_t per_panel = tiles_m * kPanel, panel = item / per_panel, rest = item - panel * per_panel;
+        const uint32_t width = min(kPanel, tiles_n - panel * kPanel);
+        *tm = rest / width;
+        *tn = panel * kPanel + rest % width;
+    };
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kPairStages; ++s) {
+            eb::mbar_init(&full[s], 1);
+            eb::mbar_init(&empty[s], 1);
+            eb::mbar_init(&peer_full[s], 1);
+        }
+        eb::mbar_init(acc_full, 1);
+        eb::mbar_init(acc_empty, 16);
+        eb::mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(eb::smem_u32(tmem_holder)), "r"(kTmemColumns) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    eb::cluster_sync();   // both CTAs' barriers exist before anything arrives on them from the other CTA
+    tcgen05_fence_after();
+    const uint32_t tmem = *tmem_holder;
+    eb::pdl_launch_dependents();
+    eb::pdl_wait();   // the scratch comes from the two launches before this one
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t step = 0;
+            bool ok = true;
+            for (uint32_t item = pair; item < items && ok; item += pairs) {
+                uint32_t tm, tn;
+                place(item, &tm, &tn);
+                const uint32_t row_tile = 2u * tm + rank;                      // this CTA's 128 rows
+                const uint32_t weight_tile = paired ? (rank == 0u ? tn : pair_tiles + tn) : 2u * tn + rank;   // its 128 weight rows
+                const uint32_t low = paired ? tn : 2u * tn, high = paired ? pair_tiles + tn : 2u * tn + 1u;
+                const uint32_t scale_tile = min(row_tile, row_tiles - 1u);     // a CTA without rows multiplies zeros by some tile's scales
+                for (uint32_t ks = 0; ks < k_steps; ++ks, ++step) {
+                    const uint32_t s = step % kPairStages, round = step / kPairStages;
+                    if (round > 0 && !eb::mbar_wait(&empty[s], (round - 1u) & 1u)) {
+                        atomicOr(error, 8u);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* stage = smem + s * kPairStageBytes;
+                    eb::mbar_arrive_expect_tx(&full[s], kPairStageBytes);
+                    tma_load_3d(stage, &map_a, (int)(ks * 128u), (int)(row_tile * kTileM), 0, &full[s]);
+                    tma_load_3d(stage + kATile, &map_a, (int)(ks * 128u), (int)(row_tile * kTileM), 1, &full[s]);
+                    tma_load_2d(stage + kTerms * kATile, &map_b, (int)(ks * 128u), (int)(weight_tile * 128u), &full[s]);
+                    uint8_t* sf = stage + kTerms * kATile + kPairBTile;
+                    eb::bulk_g2s(sf, sfa + ((uint64_t)scale_tile * k_blocks + ks * 4u) * kTerms * kAtom, kSfaStage, &full[s]);
+                    eb::bulk_g2s(sf + kSfaStage, sfb + ((uint64_t)low * k_blocks + ks * 4u) * kAtom, 4u * kAtom, &full[s]);
+                    eb::bulk_g2s(sf + kSfaStage + 4u * kAtom, sfb + ((uint64_t)high * k_blocks + ks * 4u) * kAtom, 4u * kAtom, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank != 0u) {
+            // the odd CTA: tell the even one about every stage that has landed here
+            uint32_t step = 0;
+            bool ok = true;
+            for (uint32_t item = pair; item < items && ok; item += pairs)
+                for (uint32_t ks = 0; ks < k_steps; ++ks, ++step) {
+                    const uint32_t s = step % kPairStages, round = step / kPairStages;
+                    if (!eb::mbar_wait(&full[s], round & 1u)) {
+                        atomicOr(error, 8u);
+                        ok = false;
+                        break;
+                    }
+                    arrive_at_rank(&peer_full[s], 0u);
+                }
+        } else if (lane == 0) {
+            uint32_t step = 0, local = 0;
+            bool ok = true;
+            for (uint32_t item = pair; item < items && ok; item += pairs, ++local) {
+                if (local > 0 && !eb::mbar_wait(acc_empty, (local - 1u) & 1u)) {
+                    atomicOr(error, 8u);
+                    break;
+                }
+                tcgen05_fence_after();
+                for (uint32_t ks = 0; ks < k_steps; ++ks, ++step) {
+                    const uint32_t s = step % kPairStages, round = step / kPairStages;
+                    if (!eb::mbar_wait(&full[s], round & 1u) || !eb::mbar_wait(&peer_full[s], round & 1u)) {
+                        atomicOr(error, 8u);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint8_t* stage = smem + s * kPairStageBytes;
+                    const uint8_t* sf = stage + kTerms * kATile + kPairBTile;
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j) {
+                        pair_copy_atom(tmem + kTmemSfa + (j * 2u) * 4u, atom_descriptor(sf + (j * 2u) * kAtom));
+                        pair_copy_atom(tmem + kTmemSfa + (j * 2u + 1u) * 4u, atom_descriptor(sf + (j * 2u + 1u) * kAtom));
+                        pair_copy_atom(tmem + kTmemSfb + j * 8u, atom_descriptor(sf + kSfaStage + j * kAtom));
+                        pair_copy_atom(tmem + kTmemSfb + j * 8u + 4u, atom_descriptor(sf + kSfaStage + (4u + j) * kAtom));
+                    }
+                    const uint64_t a0 = tile_descriptor(stage), a1 = tile_descriptor(stage + kATile), b = tile_descriptor(stage + kTerms * kATile);
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j) {
+                        pair_mma(tmem, a0 + 2u * j, b + 2u * j, tmem + kTmemSfa + (j * 2u) * 4u, tmem + kTmemSfb + j * 8u, (ks | j) != 0u);
+                        pair_mma(tmem, a1 + 2u * j, b + 2u * j, tmem + kTmemSfa + (j * 2u + 1u) * 4u, tmem + kTmemSfb + j * 8u, 1u);
+                    }
+                    pair_commit(&empty[s]);
+                }
+                if (ok) pair_commit(acc_full);
+            }
+        }
+    } else {
+        // Epilogue, in both CTAs, each over its own 128 rows: as in gemm_kernel.
+        const uint32_t quarter = warp & 3u, half = (warp - 2u) >> 2;
+        const float scale_w = *tensor_global;
+        uint32_t local = 0;
+        for (uint32_t item = pair; item < items; item += pairs, ++local) {
+            uint32_t tm, tn;
+            place(item, &tm, &tn);
+            if (!eb::mbar_wait(acc_full, local & 1u)) {
+                if (lane == 0) atomicOr(error, 8u);
+                break;
+            }
+            tcgen05_fence_after();
+            uint32_t r[4][32];
+            const uint32_t from = tmem + ((quarter * 32u) << 16) + (paired ? half * 64u : half * 128u);
+            const uint32_t other = paired ? from + 128u : from + 64u;
+            tmem_load_32(r[0], from);
+            tmem_load_32(r[1], from + 32u);
+            tmem_load_32(r[2], other);
+            tmem_load_32(r[3], other + 32u);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) arrive_at_rank(acc_empty, 0u);
+            const uint32_t row = (2u * tm + rank) * kTileM + quarter * 32u + lane;
+            const float scale = row < rows ? __fmul_rn(row_globals[row], scale_w) : 0.0f;
+            store_block(r, out, row, rows, n, paired ? tn * 128u + half * 64u : tn * kTileN + half * 128u, scale, paired);
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    eb::cluster_sync();   // neither CTA leaves while the other may still read its shared memory or arrive on its barriers
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
     }
 }
 
@@ -489,8 +692,11 @@ using eb::EncodeTiled;
 using eb::encoder;
 
 inline cudaError_t initialize() {
-    return cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSharedBytes);
+    const cudaError_t e = cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSharedBytes);
+    return e != cudaSuccess ? e : cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairShared);
 }
+
+constexpr uint32_t kPairRows = 512;   // fewer rows than this always run on single CTAs
 
 template <typename... Params, typename... Args>
 inline cudaError_t launch_on(cudaStream_t stream, bool pdl, void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared, Args... args) {
@@ -517,8 +723,9 @@ inline cudaError_t quantize(const void* input, void* scratch, uint32_t rows, uin
 
 // multiply: the weight scale plane -> scale atoms in the scratch, then the GEMM over the quantized activations found there.
 // paired: the weights are a gate/up object (gate rows first); the output is [rows][out_features / 2] SwiGLU values.
+// pairs: calls of kPairRows rows and more run on CTA pairs (gemm_pair_kernel).
 inline cudaError_t multiply(const void* weights, void* output, void* scratch, uint32_t rows, uint32_t k, uint32_t out_features, int sms,
-        cudaStream_t stream, bool pdl, uint32_t* error, bool paired = false) {
+        cudaStream_t stream, bool pdl, uint32_t* error, bool paired = false, bool pairs = false) {
     const EncodeTiled encode = encoder();
     if (encode == nullptr) return cudaErrorNotSupported;
     const ActivationLayout layout(rows, k, out_features);
@@ -554,6 +761,12 @@ inline cudaError_t multiply(const void* weights, void* output, void* scratch, ui
     float* partials = reinterpret_cast<float*>(base + layout.partial_offset);
     const float* row_globals = reinterpret_cast<const float*>(base + layout.global_offset);
     const float* tensor_global = reinterpret_cast<const float*>(w + global_offset);
+    if (pairs && rows >= kPairRows) {
+        const uint32_t pair_items = ((rows + 255u) / 256u) * (paired ? pair_tiles : (out_features + 255u) / 256u);
+        const uint32_t ctas = 2u * std::max(1u, std::min((uint32_t)sms / 2u, pair_items));
+        return launch_on(stream, pdl, gemm_pair_kernel, dim3(ctas), dim3(kThreads), kPairShared, map_a, map_b, base + layout.sfa_offset,
+                base + layout.sfb_offset, row_globals, tensor_global, static_cast<uint16_t*>(output), rows, width, k, pair_tiles, error);
+    }
     e = launch_on(stream, pdl, gemm_kernel, dim3(grid), dim3(kThreads), kSharedBytes, map_a, map_b, base + layout.sfa_offset,
             base + layout.sfb_offset, row_globals, tensor_global, static_cast<uint16_t*>(output), partials, splits, rows, width, k, pair_tiles, error);
     if (e != cudaSuccess || splits == 1u) return e;
@@ -563,9 +776,9 @@ inline cudaError_t multiply(const void* weights, void* output, void* scratch, ui
 }
 
 inline cudaError_t run(const void* input, const void* weights, void* output, void* scratch, uint32_t rows, uint32_t k, uint32_t out_features,
-        int sms, cudaStream_t stream, bool pdl, uint32_t* error, bool paired = false) {
+        int sms, cudaStream_t stream, bool pdl, uint32_t* error, bool paired = false, bool pairs = false) {
     const cudaError_t e = quantize(input, scratch, rows, k, stream, pdl);
-    return e != cudaSuccess ? e : multiply(weights, output, scratch, rows, k, out_features, sms, stream, pdl, error, paired);
+    return e != cudaSuccess ? e : multiply(weights, output, scratch, rows, k, out_features, sms, stream, pdl, error, paired, pairs);
 }
 
 }  // namespace nvfp4n

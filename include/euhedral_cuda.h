@@ -157,6 +157,11 @@ EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_nvfp4_native_prequantized_bf16(con
         void* scratch, uint32_t rows, uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size,
         uint64_t scratch_byte_size);
 
+/* No counterpart in the reference. Process-wide switch of the native route: when enabled, calls of 512 rows and more run
+ * the GEMM on CTA pairs (tcgen05 cta_group::2: an output tile of 256 x 256 per pair, half of the weight tile per CTA);
+ * the results are bit for bit those of the single-CTA kernel. Off by default: on B200 the pairs measured 4-7 % slower. */
+EUHEDRAL_CUDA_EXPORT void euhedral_b200_select_native_pairs(int enabled);
+
 /* No counterpart in the reference, whose Java host plans a trellis linear as three launches through the kernel table
  * (core/.../artifact/format/TrellisFormat.java:484-567). Here the whole linear is ONE launch: the activations are rotated
  * inside the kernel, and the CTA that finishes a column block last adds the K splits in split order, rotates, scales and

@@ -180,7 +180,7 @@ def test_native_route_declines(dev):
 # native.cuh:390-413): gate and up are the BF16 values the plain native linear gives for the same fused tensor, bit for
 # bit (same accumulators, same scaling and rounding); the SwiGLU on top is FP32 with expf and a division, so the BF16
 # result is compared with a float32 NumPy evaluation: equal almost everywhere, one unit in the last place at most.
-@pytest.mark.parametrize("rows,k,outputs", [(200, 1024, 768), (9, 1024, 512), (300, 5120, 34816)])
+@pytest.mark.parametrize("rows,k,outputs", [(200, 1024, 768), (9, 1024, 512), (300, 5120, 34816), (700, 5120, 34816), (1000, 1024, 768)])
 def test_gate_up_swiglu_region(dev, rows, k, outputs):
     rng = np.random.default_rng(rows + outputs)
     blob = OC.nvfp4_quantize((rng.standard_normal((outputs, k)) * 0.05).astype(np.float32))
@@ -216,3 +216,37 @@ def test_gate_up_swiglu_needs_whole_tiles(dev):
     with dev.submit():
         assert lib.euhedral_cuda_nvfp4_native_gate_up_swiglu_bf16(d_x.data_ptr(), d_w.data_ptr(), d_y.data_ptr(), d_s.data_ptr(), rows, k,
                                                                   outputs, blob.size, need) == library.ROUTE_UNAVAILABLE
+
+
+def test_cta_pairs_give_the_single_cta_bits(dev):
+    """With euhedral_b200_select_native_pairs(1), calls of 512 rows and more run on CTA pairs (tcgen05 cta_group::2): the
+    plain linear at shapes with many tiles per pair, a last pair whose odd CTA has no rows, K = 17408, and the gate/up
+    SwiGLU region give bit for bit what the single-CTA kernel gives."""
+    rng = np.random.default_rng(17)
+    lib = dev.gpu.lib
+    for rows, k, n in ((1100, 1024, 1280), (4096, 5120, 17408), (600, 17408, 5120)):
+        blob = OC.nvfp4_quantize((rng.standard_normal((n, k)) * 0.03).astype(np.float32))
+        x = random_x(rng, rows, k)
+        single, _ = run(dev, x, blob, n, k)
+        lib.euhedral_b200_select_native_pairs(1)
+        try:
+            pairs, _ = run(dev, x, blob, n, k)
+        finally:
+            lib.euhedral_b200_select_native_pairs(0)
+        assert np.array_equal(pairs, single), (rows, k, n)
+    rows, k, outputs = 700, 1024, 1536
+    blob = OC.nvfp4_quantize((rng.standard_normal((outputs, k)) * 0.05).astype(np.float32))
+    need = lib.euhedral_cuda_nvfp4_native_scratch_bytes(rows, k, outputs)
+    d_x, d_w, d_s = dev.put(random_x(rng, rows, k)), dev.put(blob), dev.empty(need)
+    results = []
+    for enabled in (0, 1):
+        d_y = dev.empty(rows * outputs)
+        lib.euhedral_b200_select_native_pairs(enabled)
+        try:
+            with dev.submit(pdl=True):
+                assert lib.euhedral_cuda_nvfp4_native_gate_up_swiglu_bf16(d_x.data_ptr(), d_w.data_ptr(), d_y.data_ptr(), d_s.data_ptr(), rows, k,
+                                                                          outputs, blob.size, need) == 0
+        finally:
+            lib.euhedral_b200_select_native_pairs(0)
+        results.append(dev.get(d_y, np.uint16, (rows, outputs // 2)))
+    assert np.array_equal(results[0], results[1]) and results[0].any()
