@@ -170,26 +170,49 @@ def cpu_baseline(blobs):
 
 
 def run_reference(args):
+    """The CPU restatement of the path on all host threads, on the metric and config of the repo's own arm at this N:
+    one GPU: the Q3 layer set at M = 1 and 3 (a whole step per step); more: the NVFP4 decode sweep at M = 5, each step a
+    bounded sample of it (one of the 64 layers: the seven matrices once)."""
     if RANK != 0:
         return
     from oracle import oracle_c as OC
     threads = OC.default_threads()
-    blobs = cpu_blobs()
+    sweep = args.gpus > 1
+    if sweep:
+        blobs = [OC.nvfp4_quantize(seeded_weights(i, n, k)) for i, (name, n, k) in enumerate(LAYER)]
+
+        def one_pass():
+            total, start = 0, time.perf_counter()
+            for (name, n, k), blob in zip(LAYER, blobs):
+                OC.nvfp4_linear(seeded_rows(5, k), blob, n, k, threads=threads)
+                total += algorithmic_bytes("nvfp4", n, k, 5)
+            return total, time.perf_counter() - start
+    else:
+        blobs = cpu_blobs()
+
+        def one_pass():
+            return cpu_layer_pass(blobs, HEADLINE_ROWS, threads)
     for _ in range(max(1, min(args.warmup, 3))):
-        cpu_layer_pass(blobs, HEADLINE_ROWS, threads)
+        one_pass()
     total_bytes, total_time = 0, 0.0
     for _ in range(args.steps):
-        b, t = cpu_layer_pass(blobs, HEADLINE_ROWS, threads)
+        b, t = one_pass()
         total_bytes += b
         total_time += t
     value = total_bytes / total_time / 1e9
+    if sweep:
+        metric = "quantized GEMV algorithmic GB/s (NVFP4 64-layer decode sweep, M=5, N-sharded)"
+        config = {"workload": "64-layer Qwen-27B-shaped NVFP4 sweep: one decode step at M = 5", "layer": [list(s) for s in LAYER]}
+        sample = "one of the 64 layers per step (the rate does not depend on the layer): 7 NVFP4 matrices at M = 5, plain-C dequant + FP32 dot, row-parallel threads"
+    else:
+        metric = "quantized GEMV algorithmic GB/s (Q3 decode layer set, M=1 and M=3)"
+        config = {"workload": "Q3 decode GEMV set, one Qwen-27B-shaped layer, M in {1,3}", "layer": [list(s) for s in LAYER]}
+        sample = "the whole step: 7 matrices x M in {1,3}, plain-C dequant + FP32 dot, row-parallel threads"
     line = {
-        "impl": "reference", "metric": "quantized GEMV algorithmic GB/s (Q3 decode layer set, M=1 and M=3)", "value": value,
+        "impl": "reference", "metric": metric, "value": value,
         "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_time / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "Q3 decode GEMV set, one Qwen-27B-shaped layer, M in {1,3}", "layer": [list(s) for s in LAYER]},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
-                         "sample": "the whole step: 7 matrices x M in {1,3}, plain-C dequant + FP32 dot, row-parallel threads"},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
@@ -663,6 +686,19 @@ def measure_sweep(bench: Bench, steps, warmup, prefill=True):
         graph = sweep.captured_step()
         seconds = bench.timed(steps, warmup, lambda _: graph.replay())
         exchange = bench.timed(steps, 1, sweep.exchange_only) if bench.world > 1 else 0.0
+        # End to end: the step's activations come from pinned host memory and the outputs of the step's last gather group
+        # (every rank's slices of its last four layers) go back to pinned host memory, on the step's stream.
+        host_x = {k: x.cpu().pin_memory() for k, x in sweep.x.items()}
+        last = sweep.gathered[(SWEEP_LAYERS // SWEEP_GATHER - 1) % sweep.slot_count]
+        host_out = torch.empty(last.shape, dtype=last.dtype).pin_memory()
+
+        def end_to_end(_):
+            for k, x in sweep.x.items():
+                x.copy_(host_x[k], non_blocking=True)
+            graph.replay()
+            host_out.copy_(last, non_blocking=True)
+
+        e2e_seconds = bench.timed(steps, warmup, end_to_end)
     total = float(sweep.decode_bytes)
     if bench.world > 1:
         t = torch.tensor([total], device="cuda", dtype=torch.float64)
@@ -675,6 +711,8 @@ def measure_sweep(bench: Bench, steps, warmup, prefill=True):
               "decode_ms_per_step_eager_calls": eager_seconds / max(2, steps // 3) * 1e3,
               "all_gather_ms_per_step_alone": exchange / steps * 1e3 if bench.world > 1 else 0.0,
               "all_gathers_per_step": SWEEP_LAYERS // SWEEP_GATHER if bench.world > 1 else 0,
+              "e2e_gbs": total * steps / e2e_seconds / 1e9, "e2e_h2d_bytes_per_step": sum(x.numel() * 2 for x in host_x.values()),
+              "e2e_d2h_bytes_per_step": host_out.numel() * 2,
               "gathered_equals_one_gpu_bitwise": same,
               "weights": f"{SWEEP_DISTINCT} distinct seeded layers, every one of the {SWEEP_LAYERS} layers in memory of its own"}
     if prefill:
@@ -769,8 +807,10 @@ def run_ours(args):
                        "launch": "two grouped C-ABI calls per layer with programmatic dependent launch, the whole step replayed from a CUDA graph"},
             "roofline": {"bound": "hbm", "achieved": sweep["decode_gbs"], "peak": peak * world, "unit": "GB/s", "frac": sweep["decode_gbs"] / (peak * world),
                          "traffic": None, "peak_kind": f"of {bench.peaks['kind']}", "kernel": "gemv::kernel<nvfp4::Format, 3, true>"},
-            "e2e": {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-                    "note": "the end-to-end arm is the one-GPU line; the sweep's inputs are resident"},
+            "e2e": {"value": sweep["e2e_gbs"], "unit": "GB/s", "h2d_bytes_per_step": sweep["e2e_h2d_bytes_per_step"],
+                    "d2h_bytes_per_step": sweep["e2e_d2h_bytes_per_step"],
+                    "note": "per rank and step: the activations uploaded from pinned host memory, the graph replayed, the gathered outputs "
+                            "of the last four layers read back to pinned host memory"},
             "gpu_launches": sweep["decode_calls_per_step"] * args.steps,
         })
         extra["sweep64"] = sweep
