@@ -1,6 +1,6 @@
 """Generates the golden vectors under tests/golden from the reference itself.
 
-Run where the reference checkout is mounted (argument 1 or $EUHEDRAL_REFERENCE, default /root/reference):
+Run where the reference checkout is mounted (argument 1 or $EUHEDRAL_REFERENCE name its root):
 
     python tests/golden/make_golden.py [reference_root]
 
