@@ -79,6 +79,7 @@ void initialize_device(int device, DeviceState* state) {
     // In host code the array's name is only a handle; the kernels need its device address on this device.
     if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&state->static_scratch), g_static_scratch);
     if (e == cudaSuccess) e = allow_gemv<nvfp4::Format>();
+    if (e == cudaSuccess) e = allow_gemv<nvfp4::FormatSd4>();
     if (e == cudaSuccess) e = allow_gemv<q3::Format>();
     if (e == cudaSuccess) e = allow_big_smem(exact::trellis_linear);
 #define EB_ALLOW(W) if (e == cudaSuccess) e = allow_trellis_width<W>();
@@ -514,6 +515,20 @@ int linear_group(uint32_t count, const void* const* inputs, const void* const* w
     return finish(cudaSuccess);
 }
 
+// The decode kernel of the layout (plain or table-indexed scales) when it takes the shape, else the scalar kernel.
+template <class F, bool kTable>
+int nvfp4_decode(DeviceState* state, const void* input, const void* weights, void* output, uint32_t rows, uint32_t in_features,
+        uint32_t out_features) {
+    if (!g_exact.load() && rows <= 32u && decode_takes<F>(in_features, out_features)) {
+        DecodeItem item = {input, weights, output, out_features};
+        const cudaError_t e = run_decode<F>(&item, 1, rows, in_features, state->sms, state->error_word);
+        if (e != cudaErrorNotSupported && e != cudaErrorInvalidConfiguration) return finish(e);
+    }
+    return finish(launch(kOrdered, exact::nvfp4_linear<kTable>, dim3(capped_grid((uint64_t)rows * out_features)), dim3(128), 0, 1u,
+            static_cast<const uint16_t*>(input), static_cast<const uint8_t*>(weights), static_cast<uint16_t*>(output), rows,
+            in_features, out_features));
+}
+
 }  // namespace
 
 extern "C" {
@@ -694,18 +709,11 @@ int euhedral_cuda_linear_nvfp4_bf16(const void* input, const void* weights, void
     const int layout = nvfp4_layout(out_features, in_features, weights_byte_size);
     if (layout < 0) return EUHEDRAL_CUDA_FORMAT_MISMATCH;
     if (in_features % 32u != 0 || ((uintptr_t)input & 15u) != 0 || ((uintptr_t)weights & 15u) != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
-    if (layout == 1) return EUHEDRAL_CUDA_KERNEL_UNAVAILABLE;   // table-indexed scales (SD4): no kernel in this build
     DeviceState* state = nullptr;
     const int status = bind(&state);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
-    if (!g_exact.load() && rows <= 32u && decode_takes<nvfp4::Format>(in_features, out_features)) {
-        DecodeItem item = {input, weights, output, out_features};
-        const cudaError_t e = run_decode<nvfp4::Format>(&item, 1, rows, in_features, state->sms, state->error_word);
-        if (e != cudaErrorNotSupported && e != cudaErrorInvalidConfiguration) return finish(e);
-    }
-    return finish(launch(kOrdered, exact::nvfp4_linear, dim3(capped_grid((uint64_t)rows * out_features)), dim3(128), 0, 1u,
-            static_cast<const uint16_t*>(input), static_cast<const uint8_t*>(weights), static_cast<uint16_t*>(output), rows,
-            in_features, out_features));
+    return layout == 1 ? nvfp4_decode<nvfp4::FormatSd4, true>(state, input, weights, output, rows, in_features, out_features)
+                       : nvfp4_decode<nvfp4::Format, false>(state, input, weights, output, rows, in_features, out_features);
 }
 
 // Process-wide: native calls of 512 rows and more run on CTA pairs (tcgen05 cta_group::2). Off unless selected.
@@ -724,7 +732,7 @@ uint64_t euhedral_cuda_nvfp4_native_scratch_bytes(uint32_t rows, uint32_t in_fea
 
 // Validation shared by the native entry points; `input` is null for the call that finds the activations quantized already.
 static int native_validate(bool has_input, const void* input, const void* weights, const void* output, const void* scratch, uint32_t rows,
-        uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size, uint64_t scratch_byte_size) {
+        uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size, uint64_t scratch_byte_size, bool* table_scales) {
     if (in_features % 128u != 0 || g_exact.load()) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
     if ((has_input && input == nullptr) || weights == nullptr || output == nullptr || rows == 0 || in_features == 0 || out_features == 0)
         return EUHEDRAL_CUDA_INVALID_ARGUMENT;
@@ -734,8 +742,8 @@ static int native_validate(bool has_input, const void* input, const void* weight
     // its base, so a 16-byte-aligned base (what the reference asks for, native/src/host/nvfp4_linear.c:310) is enough for
     // every tensor map and bulk copy into it.
     if (((uintptr_t)input & 15u) != 0 || ((uintptr_t)weights & 15u) != 0 || ((uintptr_t)output & 15u) != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
-    if (layout == 1 || in_features % 256u != 0 || out_features % 128u != 0 || ((uintptr_t)scratch & 15u) != 0)
-        return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    *table_scales = layout == 1;   // SD4: the scale repack looks the indices up in the tensor's table
+    if (in_features % 256u != 0 || out_features % 128u != 0 || ((uintptr_t)scratch & 15u) != 0) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
     if (scratch == nullptr || scratch_byte_size < nvfp4n::ActivationLayout(rows, in_features, out_features).bytes)
         return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     if (((uint64_t)rows + 127u) / 128u * (out_features / 128u) > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
@@ -747,10 +755,11 @@ int euhedral_cuda_linear_nvfp4_native_bf16(const void* input, const void* weight
     DeviceState* state = nullptr;
     int status = bind(&state);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
-    status = native_validate(true, input, weights, output, scratch, rows, in_features, out_features, weights_byte_size, scratch_byte_size);
+    bool table_scales = false;
+    status = native_validate(true, input, weights, output, scratch, rows, in_features, out_features, weights_byte_size, scratch_byte_size, &table_scales);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     return finish(nvfp4n::run(input, weights, output, scratch, rows, in_features, out_features, state->sms, t_stream, t_pdl != 0 && t_stream != nullptr,
-            state->error_word, false, g_native_pairs.load()));
+            state->error_word, false, g_native_pairs.load(), table_scales));
 }
 
 // The paired gate/up region (native/src/host/nvfp4_linear.c:288-295): `weights` is a gate/up object of `outputs` rows, gate
@@ -762,11 +771,12 @@ int euhedral_cuda_nvfp4_native_gate_up_swiglu_bf16(const void* input, const void
     int status = bind(&state);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     if (outputs % 2u != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
-    status = native_validate(true, input, weights, output, scratch, rows, width, outputs, weight_bytes, scratch_byte_size);
+    bool table_scales = false;
+    status = native_validate(true, input, weights, output, scratch, rows, width, outputs, weight_bytes, scratch_byte_size, &table_scales);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     if (outputs % 256u != 0) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
     return finish(nvfp4n::run(input, weights, output, scratch, rows, width, outputs, state->sms, t_stream, t_pdl != 0 && t_stream != nullptr,
-            state->error_word, true, g_native_pairs.load()));
+            state->error_word, true, g_native_pairs.load(), table_scales));
 }
 
 int euhedral_b200_nvfp4_native_quantize(const void* input, void* scratch, uint32_t rows, uint32_t in_features, uint64_t scratch_byte_size) {
@@ -785,10 +795,12 @@ int euhedral_b200_linear_nvfp4_native_prequantized_bf16(const void* weights, voi
     DeviceState* state = nullptr;
     int status = bind(&state);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
-    status = native_validate(false, nullptr, weights, output, scratch, rows, in_features, out_features, weights_byte_size, scratch_byte_size);
+    bool table_scales = false;
+    status = native_validate(false, nullptr, weights, output, scratch, rows, in_features, out_features, weights_byte_size, scratch_byte_size,
+            &table_scales);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     return finish(nvfp4n::multiply(weights, output, scratch, rows, in_features, out_features, state->sms, t_stream, t_pdl != 0 && t_stream != nullptr,
-            state->error_word, false, g_native_pairs.load()));
+            state->error_word, false, g_native_pairs.load(), table_scales));
 }
 
 // ---- kernel table -------------------------------------------------------------------------------------------------------
@@ -994,6 +1006,10 @@ int euhedral_b200_linear_group_q3_bf16(uint32_t count, const void* const* inputs
 
 int euhedral_b200_linear_group_nvfp4_bf16(uint32_t count, const void* const* inputs, const void* const* weights, void* const* outputs,
         uint32_t rows, uint32_t in_features, const uint32_t* out_features, const uint64_t* weights_byte_sizes) {
+    // plain or table-indexed scales, told apart by the first tensor's byte size; a group holds one layout
+    if (count != 0 && out_features != nullptr && weights_byte_sizes != nullptr && out_features[0] != 0
+            && nvfp4_layout(out_features[0], in_features, weights_byte_sizes[0]) == 1)
+        return linear_group<nvfp4::FormatSd4>(count, inputs, weights, outputs, rows, in_features, out_features, weights_byte_sizes);
     return linear_group<nvfp4::Format>(count, inputs, weights, outputs, rows, in_features, out_features, weights_byte_sizes);
 }
 

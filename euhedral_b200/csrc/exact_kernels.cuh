@@ -33,13 +33,17 @@ __device__ __forceinline__ float e4m3(uint32_t code) {
 }
 
 // NVFP4: partial = fma(x, e2m1 * e4m3, partial); (tree sum) * global; BF16. Grid-stride over rows * n outputs.
+// kTable: the block scales are 4-bit indices (two per byte, the even block in the low nibble) into the tensor's table of
+// 16 E4M3 codes (layout row-split-k128-sd4-v1; the reference's twin kernels, native/src/nvfp4/scale_table.cuh:4-15).
+template <bool kTable>
 __global__ void __launch_bounds__(128) nvfp4_linear(const uint16_t* __restrict__ x, const uint8_t* __restrict__ w,
         uint16_t* __restrict__ y, uint32_t rows, uint32_t k, uint32_t n) {
     __shared__ float scratch[128];
     const uint64_t kp = ((uint64_t)k + 127u) / 128u * 128u;
-    const uint64_t row_bytes = kp / 2u, row_scales = kp / 16u;
+    const uint64_t row_bytes = kp / 2u, row_scales = kTable ? kp / 32u : kp / 16u;
     const uint64_t scale_offset = ((uint64_t)n * row_bytes + 255u) & ~255ull;
-    const uint64_t global_offset = (scale_offset + (uint64_t)n * row_scales + 255u) & ~255ull;
+    const uint64_t table_offset = (scale_offset + (uint64_t)n * row_scales + 255u) & ~255ull;
+    const uint64_t global_offset = kTable ? table_offset + 16u : table_offset;
     const float global = *reinterpret_cast<const float*>(w + global_offset);
     const uint64_t count = (uint64_t)rows * n;
     for (uint64_t index = blockIdx.x; index < count; index += gridDim.x) {
@@ -47,8 +51,14 @@ __global__ void __launch_bounds__(128) nvfp4_linear(const uint16_t* __restrict__
         float partial = 0.0f;
         for (uint32_t i = threadIdx.x; i < k; i += 128u) {
             const uint32_t code = (w[(uint64_t)col * row_bytes + i / 2u] >> ((i & 1u) * 4u)) & 15u;
-            const float scale = e4m3(w[scale_offset + (uint64_t)col * row_scales + i / 16u]);
-            partial = __fmaf_rn(eb::bf16_bits_to_float(x[(uint64_t)row * k + i]), __fmul_rn(e2m1(code), scale), partial);
+            uint32_t scale_code;
+            if (kTable) {
+                const uint32_t block = i / 16u;
+                scale_code = w[table_offset + ((w[scale_offset + (uint64_t)col * row_scales + block / 2u] >> ((block & 1u) * 4u)) & 15u)];
+            } else {
+                scale_code = w[scale_offset + (uint64_t)col * row_scales + i / 16u];
+            }
+            partial = __fmaf_rn(eb::bf16_bits_to_float(x[(uint64_t)row * k + i]), __fmul_rn(e2m1(code), e4m3(scale_code)), partial);
         }
         const float total = tree128(partial, scratch);
         if (threadIdx.x == 0) y[index] = eb::float_to_bf16_bits(__fmul_rn(total, global));

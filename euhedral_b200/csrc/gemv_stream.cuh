@@ -43,7 +43,7 @@
 //   extra_bytes(chunks)             extra shared bytes next to the activation slice
 //   stage(...)                      CTA-wide staging of the activation slice in the decode's pairing
 //   lane_scale_offset(q)            byte offset of lane q's scales within a chunk's scale bytes
-//   State                           accumulators: chunk<I, W>(codes, scales, x) consumes chunk I of a piece whose box rows
+//   State                           accumulators: tensor(w, geo) at the start of every tensor; chunk<I, W>(codes, scales, x) consumes chunk I of a piece whose box rows
 //                                   are W chunks wide, given the lane's shared addresses; result(out); reset()
 //   Finish(w, geo)                  apply(sum) = the value to round to BF16
 #pragma once
@@ -344,6 +344,7 @@ __global__ void __launch_bounds__(32 * (kMaxWarps + (F::kAddingWarp ? 1 : 0)), 1
         if (segment_begin < segment_end) {   // uniform over the cluster
             stage(t);
             const typename F::Finish finish(t.w, typename F::Geometry(t.n, group.k));
+            state.tensor(t.w, typename F::Geometry(t.n, group.k));   // what the decode keeps per tensor (a scale table, if the format has one)
             for (; use_tile < segment_end; use_tile += teams, ++turn) {
                 if (!kTmaScales) {
                     if (depth == 2u) eb::cp_async_wait_group<1>();

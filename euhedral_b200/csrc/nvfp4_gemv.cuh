@@ -55,15 +55,64 @@ __device__ __forceinline__ uint32_t scale_pair(uint32_t bits) {
     return eb::bf16x2_mul(unit, 0x76807680u);                  // * 2^110
 }
 
-struct Format {
+// Byte geometry of a tensor whose block scales are 4-bit indices into a table of 16 E4M3 codes (layout
+// row-split-k128-sd4-v1, tools/euhedral_artifacts/nvfp4.py:60-69): the index plane is half the scale plane (two indices
+// per byte, the even block in the low nibble), then the table, then the FP32 tensor scale.
+struct GeometrySd4 {
+    uint64_t row_bytes, scale_row_bytes, scale_offset, table_offset, global_offset, size;
+    __host__ __device__ GeometrySd4(uint32_t rows, uint32_t k) {
+        const uint64_t kp = ((uint64_t)k + 127u) / 128u * 128u;
+        row_bytes = kp / 2u;
+        scale_row_bytes = kp / 32u;
+        scale_offset = align256((uint64_t)rows * row_bytes);
+        table_offset = align256(scale_offset + (uint64_t)rows * scale_row_bytes);
+        global_offset = table_offset + 16u;
+        size = table_offset + 20u;
+    }
+};
+
+// Where a lane's block scales come from. Plain: two E4M3 bytes per lane and chunk, read as they are.
+struct PlainScales {
     using Geometry = nvfp4::Geometry;
-    static constexpr uint32_t kCodeBytes = 64, kScaleBytes = 8, kErrorBit = 1;
+    static constexpr uint32_t kScaleBytes = 8, kScaleBox = 80;   // 80 bytes per row: an odd multiple of 16
+    __device__ static uint32_t lane_scale_offset(uint32_t q) { return 2u * q; }
+    __device__ __forceinline__ void tensor(const uint8_t*, const Geometry&) {}
+    // The lane's two E4M3 bytes (low byte: its first block of 16) of chunk I at shared address `scales` + OFFSET rows' bytes.
+    template <int I, int OFFSET>
+    __device__ __forceinline__ uint32_t read(uint32_t scales) const { return eb::lds_u16<I * 8 + OFFSET>(scales); }
+};
+
+// Table-indexed (SD4): one byte per lane and chunk holds the two 4-bit indices; the tensor's 16 codes sit in four
+// registers and one byte permute per half of the table plus a select on each index's top bit looks both up at once
+// (the reference's twin kernels look four up at a time the same way, native/src/nvfp4/scale_table.cuh:4-15).
+struct TableScales {
+    using Geometry = GeometrySd4;
+    static constexpr uint32_t kScaleBytes = 4, kScaleBox = 48;
+    __device__ static uint32_t lane_scale_offset(uint32_t q) { return q; }
+    uint4 table;
+    __device__ __forceinline__ void tensor(const uint8_t* w, const Geometry& geo) { table = *reinterpret_cast<const uint4*>(w + geo.table_offset); }
+    template <int I, int OFFSET>
+    __device__ __forceinline__ uint32_t read(uint32_t scales) const {
+        uint32_t pair;
+        asm volatile("ld.shared.u8 %0, [%1 + %2];" : "=r"(pair) : "r"(scales), "n"(I * 4 + OFFSET));
+        const uint32_t within = pair & 0x77u;   // per nibble: which of the eight codes of a table half
+        const uint32_t low = __byte_perm(table.x, table.y, within), high = __byte_perm(table.z, table.w, within);
+        // byte 0 all ones when index 0 is 8 or more, byte 1 when index 1 is: a byte of ones (selector 4) or of zeros (0)
+        const uint32_t upper = __byte_perm(0u, 0xFFFFFFFFu, (pair >> 1) & 0x44u);
+        return eb::lop3<eb::kLutSelect>(high, low, upper) & 0xFFFFu;
+    }
+};
+
+template <class Scales>
+struct FormatOf {
+    using Geometry = typename Scales::Geometry;
+    static constexpr uint32_t kCodeBytes = 64, kScaleBytes = Scales::kScaleBytes, kErrorBit = 1;
     // A piece is at most 4 chunks (4 KB of codes per 16 rows): with sixteen warps and a ring of two slots each that leaves
     // room for the activations of 5 rows at K = 5120. The scale box, 80 bytes per row, is an odd multiple of 16.
     static constexpr bool kAddingWarp = true;
-    static constexpr uint32_t kPieceChunks = 3, kMaxPiece = 4, kScaleBox = 80;
+    static constexpr uint32_t kPieceChunks = 3, kMaxPiece = 4, kScaleBox = Scales::kScaleBox;
     __host__ __device__ static constexpr uint32_t extra_bytes(uint32_t) { return 0; }
-    __device__ static uint32_t lane_scale_offset(uint32_t q) { return 2u * q; }
+    __device__ static uint32_t lane_scale_offset(uint32_t q) { return Scales::lane_scale_offset(q); }
 
     // x[t][c][i][qq] <- the (x0,x4) (x1,x5) (x2,x6) (x3,x7) pairs of the eight activations 8 i .. 8 i + 7 of quarter qq.
     __device__ static void stage(uint8_t* xs, uint8_t*, const uint16_t* __restrict__ x, uint32_t rows, uint32_t k, uint32_t c_begin,
@@ -103,7 +152,9 @@ struct Format {
     struct State {
         float even[4], odd[4];
         uint32_t lane_codes;   // byte offset of the lane's 16 code bytes within a chunk
+        Scales source;         // what turns the slot's scale bytes into E4M3 codes (per tensor: the table, if any)
         __device__ State(uint32_t, uint32_t q) : lane_codes(eb::pinned(q * 16u)) {}
+        __device__ __forceinline__ void tensor(const uint8_t* w, const Geometry& geo) { source.tensor(w, geo); }
         // codes: shared address of row g of the piece's code box (rows are W chunks wide, row g + 8 eight rows further);
         // scales: of the lane's two scale bytes of row g and the piece's first chunk (row g + 8: 8 * kScaleBox further);
         // x: of the lane's activations of the piece's first chunk.
@@ -112,7 +163,7 @@ struct Format {
             constexpr int kRow8 = 8 * W * (int)kCodeBytes, kAt = I * (int)kCodeBytes;
             const uint4 cg = eb::lds_v4<kAt>(codes + lane_codes);
             const uint4 ch = eb::lds_v4<kAt + kRow8>(codes + lane_codes);
-            const uint32_t sg = scale_pair(eb::lds_u16<I * 8>(scales)), sh = scale_pair(eb::lds_u16<I * 8 + 8 * (int)kScaleBox>(scales));
+            const uint32_t sg = scale_pair(source.template read<I, 0>(scales)), sh = scale_pair(source.template read<I, 8 * (int)kScaleBox>(scales));
             const uint32_t sg_block[2] = {__byte_perm(sg, sg, 0x1010), __byte_perm(sg, sg, 0x3232)};
             const uint32_t sh_block[2] = {__byte_perm(sh, sh, 0x1010), __byte_perm(sh, sh, 0x3232)};
             const uint32_t wg[4] = {cg.x, cg.y, cg.z, cg.w}, wh[4] = {ch.x, ch.y, ch.z, ch.w};
@@ -145,5 +196,8 @@ struct Format {
         __device__ __forceinline__ float apply(float sum) const { return sum * 65536.0f * global; }
     };
 };
+
+using Format = FormatOf<PlainScales>;      // row-split-k128-v1
+using FormatSd4 = FormatOf<TableScales>;   // row-split-k128-sd4-v1
 
 }  // namespace nvfp4

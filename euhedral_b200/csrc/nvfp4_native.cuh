@@ -171,14 +171,23 @@ __global__ void __launch_bounds__(32 * kQuantizeWarps, 5) quantize_rows(const __
 
 // ---- 2. weight scale repack ---------------------------------------------------------------------------------------------
 // scales[n][K/16] (row-major E4M3 bytes) -> atoms [n / 128][K / 64][512]. One thread per (row, K block): 4 bytes.
-__global__ void __launch_bounds__(256) repack_weight_scales(const uint8_t* __restrict__ scales, uint8_t* __restrict__ atoms,
-        uint32_t n, uint32_t k_blocks, uint32_t n_padded) {
+// table != nullptr (layout row-split-k128-sd4-v1): `scales` holds 4-bit indices, two per byte with the even block in the
+// low nibble, into the tensor's 16 E4M3 codes at `table`; the atoms get the codes, so the GEMM is the same for both layouts.
+__global__ void __launch_bounds__(256) repack_weight_scales(const uint8_t* __restrict__ scales, const uint8_t* __restrict__ table,
+        uint8_t* __restrict__ atoms, uint32_t n, uint32_t k_blocks, uint32_t n_padded) {
     const uint64_t index = (uint64_t)blockIdx.x * 256u + threadIdx.x;
     eb::pdl_launch_dependents();
     eb::pdl_wait();   // the GEMM of the call before this one may still be reading these atoms
     const uint32_t row = (uint32_t)(index / k_blocks), j = (uint32_t)(index % k_blocks);
     if (row >= n_padded) return;
-    const uint32_t word = row < n ? *reinterpret_cast<const uint32_t*>(scales + (uint64_t)row * k_blocks * 4u + 4u * j) : 0u;
+    uint32_t word = 0u;
+    if (row < n && table == nullptr) {
+        word = *reinterpret_cast<const uint32_t*>(scales + (uint64_t)row * k_blocks * 4u + 4u * j);
+    } else if (row < n) {
+        const uint32_t pairs = *reinterpret_cast<const uint16_t*>(scales + (uint64_t)row * k_blocks * 2u + 2u * j);   // four indices
+#pragma unroll
+        for (uint32_t i = 0; i < 4u; ++i) word |= (uint32_t)table[(pairs >> (4u * i)) & 15u] << (8u * i);
+    }
     *reinterpret_cast<uint32_t*>(atoms + ((uint64_t)(row >> 7) * k_blocks + j) * kAtom + atom_byte(row & 127u, 0)) = word;
 }
 
@@ -725,15 +734,17 @@ inline cudaError_t quantize(const void* input, void* scratch, uint32_t rows, uin
 // paired: the weights are a gate/up object (gate rows first); the output is [rows][out_features / 2] SwiGLU values.
 // pairs: calls of kPairRows rows and more run on CTA pairs (gemm_pair_kernel).
 inline cudaError_t multiply(const void* weights, void* output, void* scratch, uint32_t rows, uint32_t k, uint32_t out_features, int sms,
-        cudaStream_t stream, bool pdl, uint32_t* error, bool paired = false, bool pairs = false) {
+        cudaStream_t stream, bool pdl, uint32_t* error, bool paired = false, bool pairs = false, bool table_scales = false) {
     const EncodeTiled encode = encoder();
     if (encode == nullptr) return cudaErrorNotSupported;
     const ActivationLayout layout(rows, k, out_features);
     uint8_t* base = static_cast<uint8_t*>(scratch);
     const uint8_t* w = static_cast<const uint8_t*>(weights);
     const uint64_t row_bytes = k / 2u;
+    // plain: scale bytes, then the FP32 tensor scale; table-indexed: index bytes, then 16 table codes and the tensor scale
     const uint64_t scale_offset = align256((uint64_t)out_features * row_bytes);
-    const uint64_t global_offset = align256(scale_offset + (uint64_t)out_features * (k / 16u));
+    const uint64_t table_offset = align256(scale_offset + (uint64_t)out_features * (k / (table_scales ? 32u : 16u)));
+    const uint64_t global_offset = table_scales ? table_offset + 16u : table_offset;
     CUtensorMap map_a, map_b;
     const cuuint32_t ones[3] = {1u, 1u, 1u};
     const cuuint64_t a_dims[3] = {row_bytes, rows, kTerms}, a_strides[2] = {row_bytes, row_bytes * rows};
@@ -748,8 +759,8 @@ inline cudaError_t multiply(const void* weights, void* output, void* scratch, ui
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     const uint32_t n_padded = (out_features + 255u) / 256u * 256u;
     const uint64_t items = (uint64_t)n_padded * layout.k_blocks;
-    cudaError_t e = launch_on(stream, pdl, repack_weight_scales, dim3((unsigned)((items + 255u) / 256u)), dim3(256), 0, w + scale_offset, base + layout.sfb_offset,
-            out_features, layout.k_blocks, n_padded);
+    cudaError_t e = launch_on(stream, pdl, repack_weight_scales, dim3((unsigned)((items + 255u) / 256u)), dim3(256), 0, w + scale_offset,
+            table_scales ? w + table_offset : static_cast<const uint8_t*>(nullptr), base + layout.sfb_offset, out_features, layout.k_blocks, n_padded);
     if (e != cudaSuccess) return e;
     const uint32_t pair_tiles = paired ? out_features / 256u : 0u, width = paired ? out_features / 2u : out_features;
     const uint32_t tiles = ((rows + kTileM - 1u) / kTileM) * (paired ? pair_tiles : (out_features + kTileN - 1u) / kTileN);
@@ -776,9 +787,9 @@ inline cudaError_t multiply(const void* weights, void* output, void* scratch, ui
 }
 
 inline cudaError_t run(const void* input, const void* weights, void* output, void* scratch, uint32_t rows, uint32_t k, uint32_t out_features,
-        int sms, cudaStream_t stream, bool pdl, uint32_t* error, bool paired = false, bool pairs = false) {
+        int sms, cudaStream_t stream, bool pdl, uint32_t* error, bool paired = false, bool pairs = false, bool table_scales = false) {
     const cudaError_t e = quantize(input, scratch, rows, k, stream, pdl);
-    return e != cudaSuccess ? e : multiply(weights, output, scratch, rows, k, out_features, sms, stream, pdl, error, paired, pairs);
+    return e != cudaSuccess ? e : multiply(weights, output, scratch, rows, k, out_features, sms, stream, pdl, error, paired, pairs, table_scales);
 }
 
 }  // namespace nvfp4n

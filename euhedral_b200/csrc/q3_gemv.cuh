@@ -170,6 +170,7 @@ struct Format {
             : bias_lane(eb::pinned(extra + q * 16u)), first_word(eb::pinned(((q >> 1) * 3u + (q & 1u) * 2u) * 4u)),
               second_word(eb::pinned(((q >> 1) * 3u + 1u) * 4u)), select_low(eb::pinned((q & 1u) ? 0x1076u : 0x3210u)),
               select_high(eb::pinned((q & 1u) ? 0x3232u : 0x7654u)) {}
+        __device__ __forceinline__ void tensor(const uint8_t*, const Geometry&) {}   // nothing is kept per tensor
         // codes: shared address of row g of the piece's code box (rows are W chunks wide, row g + 8 eight rows further);
         // scales: of the two FP16 scales of row g and the piece's first chunk (row g + 8: 8 * kScaleBox further);
         // x: of the lane's activations of the piece's first chunk.

@@ -52,10 +52,15 @@ class TrellisSettings:
 
 
 class Nvfp4Format:
-    """NVFP4 / row-split-k128-v1 (Nvfp4Format.java:160-202)."""
+    """NVFP4 in its plain layout (row-split-k128-v1) or with table-indexed block scales (row-split-k128-sd4-v1); the
+    library tells them apart by the tensor's byte size (Nvfp4Format.java:20-60,160-202)."""
+
+    def __init__(self, sd4: bool = False):
+        self.sd4 = sd4
 
     def byte_size(self, shape) -> int:
-        return layouts.nvfp4_byte_size(shape[0], shape[1])
+        size = layouts.nvfp4_sd4_byte_size if self.sd4 else layouts.nvfp4_byte_size
+        return size(shape[0], shape[1])
 
     def accepts_byte_size(self, shape, byte_size: int) -> bool:
         return byte_size == self.byte_size(shape)

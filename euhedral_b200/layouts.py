@@ -38,9 +38,14 @@ def nvfp4_byte_size(n: int, k: int) -> int:
     return nvfp4_trailer_offset(n, k) + 4
 
 
+def nvfp4_sd4_table_offset(n: int, k: int) -> int:
+    """Table-indexed variant (row-split-k128-sd4-v1): the index plane (4 bits per block) starts where the scale plane
+    would; the 16 E4M3 codes of the table and then the FP32 tensor scale follow it (nvfp4_linear.c:79-91)."""
+    return align_up(nvfp4_scale_offset(n, k) + n * padded_k(k) // 32, 256)
+
+
 def nvfp4_sd4_byte_size(n: int, k: int) -> int:
-    """Size of the table-indexed variant; used only to tell the layouts apart by size (nvfp4_linear.c:79-91)."""
-    return align_up(nvfp4_scale_offset(n, k) + n * padded_k(k) // 32, 256) + 20
+    return nvfp4_sd4_table_offset(n, k) + 20
 
 
 def nvfp4_algorithmic_bytes(n: int, k: int) -> int:

@@ -35,6 +35,20 @@ def nvfp4_rows(blob: np.ndarray, n: int, k: int, first: int, rows: int) -> np.nd
     return out
 
 
+def nvfp4_sd4_rows(blob: np.ndarray, n: int, k: int, first: int, rows: int) -> np.ndarray:
+    """The same for the table-indexed layout: code rows, index rows, and the tensor's table and FP32 scale."""
+    blob = np.ascontiguousarray(blob, dtype=np.uint8)
+    kp = layouts.padded_k(k)
+    row_bytes, row_indices = kp // 2, kp // 32
+    out = np.zeros(layouts.nvfp4_sd4_byte_size(rows, k), dtype=np.uint8)
+    out[:rows * row_bytes] = blob[first * row_bytes:(first + rows) * row_bytes]
+    src, dst = layouts.nvfp4_scale_offset(n, k), layouts.nvfp4_scale_offset(rows, k)
+    out[dst:dst + rows * row_indices] = blob[src + first * row_indices:src + (first + rows) * row_indices]
+    src, dst = layouts.nvfp4_sd4_table_offset(n, k), layouts.nvfp4_sd4_table_offset(rows, k)
+    out[dst:dst + 20] = blob[src:src + 20]
+    return out
+
+
 def q3_rows(blob: np.ndarray, n: int, k: int, first: int, rows: int) -> np.ndarray:
     blob = np.ascontiguousarray(blob, dtype=np.uint8)
     groups = layouts.q3_groups(k)

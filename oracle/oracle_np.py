@@ -172,6 +172,68 @@ def nvfp4_dense(blob: bytes, n: int, k: int) -> np.ndarray:
     return nvfp4_dequantize(codes, scales, g)[:, :k]
 
 
+# NVFP4 with table-indexed block scales (layout row-split-k128-sd4-v1): the scale plane holds 4-bit indices, two per byte
+# with the even block in the low nibble, into 16 E4M3 codes that follow the index plane; then the FP32 tensor scale.
+
+def nvfp4_sd4_offsets(n: int, k: int) -> tuple[int, int, int]:
+    """(index plane offset, table offset, byte size). tools/euhedral_artifacts/nvfp4.py:60-69,
+    native/src/host/nvfp4_linear.c:79-91."""
+    kp = align_up(k, 128)
+    index_off = align_up(n * kp // 2, 256)
+    table_off = align_up(index_off + n * kp // 32, 256)
+    return index_off, table_off, table_off + 16 + 4
+
+
+def nvfp4_sd4_to_plain(blob: bytes, n: int, k: int) -> bytes:
+    """The same tensor in the plain layout (every block's table entry written out as its E4M3 scale byte,
+    tools/euhedral_artifacts/nvfp4.py:217-223), so that every function above applies to it. The values are the same bit
+    for bit: a block's scale IS its table entry."""
+    kp = align_up(k, 128)
+    index_off, table_off, size = nvfp4_sd4_offsets(n, k)
+    assert len(blob) == size, (len(blob), size)
+    raw = np.frombuffer(bytes(blob), dtype=np.uint8)
+    packed = raw[index_off:index_off + n * kp // 32].reshape(n, kp // 32)
+    indices = np.empty((n, kp // 16), dtype=np.uint8)
+    indices[:, 0::2] = packed & 15
+    indices[:, 1::2] = packed >> 4
+    scales = raw[table_off:table_off + 16][indices]
+    scale_off, global_off, plain_size = nvfp4_offsets(n, k)
+    plain = bytearray(plain_size)
+    plain[:n * kp // 2] = raw[:n * kp // 2].tobytes()
+    plain[scale_off:scale_off + scales.size] = scales.tobytes()
+    plain[global_off:global_off + 4] = raw[table_off + 16:table_off + 20].tobytes()
+    return bytes(plain)
+
+
+def nvfp4_sd4_dense(blob: bytes, n: int, k: int) -> np.ndarray:
+    return nvfp4_dense(nvfp4_sd4_to_plain(blob, n, k), n, k)
+
+
+def nvfp4_sd4_from_plain(blob: bytes, n: int, k: int, rng) -> bytes:
+    """A valid table-indexed tensor for kernel tests, made from a plain one without the converter's table search: sixteen of
+    the scale codes the tensor uses become the table (the smallest, the largest and random ones between), every block takes
+    the nearest table entry; the E2M1 codes stay. Not what the converter would choose - the kernels only decode."""
+    kp = align_up(k, 128)
+    scale_off, global_off, _ = nvfp4_offsets(n, k)
+    raw = np.frombuffer(bytes(blob), dtype=np.uint8)
+    scales = raw[scale_off:scale_off + n * kp // 16].reshape(n, kp // 16)
+    used = np.unique(scales)
+    if len(used) > 16:
+        inner = rng.choice(used[1:-1], size=14, replace=False)
+        table = np.sort(np.concatenate([[used[0], used[-1]], inner])).astype(np.uint8)
+    else:
+        table = np.sort(np.concatenate([used, np.setdiff1d(np.arange(127, dtype=np.uint8), used)[:16 - len(used)]])).astype(np.uint8)
+    values = e4m3_value(table)
+    nearest = np.abs(e4m3_value(scales)[..., None] - values[None, None, :]).argmin(axis=2).astype(np.uint8)
+    index_off, table_off, size = nvfp4_sd4_offsets(n, k)
+    out = bytearray(size)
+    out[:n * kp // 2] = raw[:n * kp // 2].tobytes()
+    out[index_off:index_off + n * kp // 32] = (nearest[:, 0::2] | (nearest[:, 1::2] << 4)).astype(np.uint8).tobytes()
+    out[table_off:table_off + 16] = table.tobytes()
+    out[table_off + 16:table_off + 20] = raw[global_off:global_off + 4].tobytes()
+    return bytes(out)
+
+
 def nvfp4_unscaled(blob: bytes, n: int, k: int):
     """(e2m1 * e4m3 per weight as float32 [n, k] - exact -, global): what the kernels sum before applying the global
     scale to the sum (native/src/nvfp4/nvfp4.cuh:97-198, native/src/reference/kernels.cu:125-149)."""

@@ -89,6 +89,36 @@ def nvfp4_cases():
     np.savez_compressed(HERE / "nvfp4.npz", **out)
 
 
+def sd4_cases():
+    """NVFP4 with table-indexed scales, written by the reference's converter (table search included), and its values."""
+    rng = np.random.default_rng(0xD4)
+    out = {}
+    weights = {
+        "gauss": (rng.standard_normal((24, 256)) * 0.02).astype(np.float32),
+        "spread": (rng.standard_normal((16, 384)) * np.exp(rng.uniform(-6.0, 1.0, (16, 1)))).astype(np.float32),
+        "padded": (rng.standard_normal((8, 200)) * 0.02).astype(np.float32),
+    }
+    for name, w in weights.items():
+        buffer = io.BytesIO()
+        nvfp4.quantize_nvfp4_sd4_matrix(buffer, 0, matrix_source(w))
+        n, k = w.shape
+        kp = (k + 127) // 128 * 128
+        index_off, table_off, size = nvfp4.nvfp4_sd4_offsets((n, k))
+        blob = buffer.getvalue().ljust(size, b"\0")
+        raw = np.frombuffer(blob, dtype=np.uint8)
+        packed = raw[:n * kp // 2].reshape(n, kp // 2)
+        indices = raw[index_off:index_off + n * kp // 32].reshape(n, kp // 32)
+        table = raw[table_off:table_off + 16]
+        g = np.frombuffer(blob[table_off + 16:table_off + 20], dtype="<f4")[0]
+        out[f"{name}_weights"] = w
+        out[f"{name}_blob"] = raw.copy()
+        out[f"{name}_dense"] = nvfp4.dequantize_nvfp4_rows(packed, nvfp4.expand_nvfp4_sd4(indices, table), np.float32(g))
+    shapes = np.array([(3, 1024), (17408, 5120), (5120, 17408), (1024, 5120), (32, 640), (7, 200)])
+    out["offset_shapes"] = shapes
+    out["offsets"] = np.array([nvfp4.nvfp4_sd4_offsets((int(n), int(k))) for n, k in shapes], dtype=np.int64)
+    np.savez_compressed(HERE / "nvfp4_sd4.npz", **out)
+
+
 def q3_cases():
     rng = np.random.default_rng(0xE1)
     out = {}
@@ -230,6 +260,7 @@ def edrl_fixture():
 if __name__ == "__main__":
     edrl_fixture()
     nvfp4_cases()
+    sd4_cases()
     q3_cases()
     gptq_fixture_subset()
     trellis_cases()

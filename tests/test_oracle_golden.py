@@ -127,3 +127,25 @@ def test_activation_quantizer_properties():
     codes, scales, g = O.quantize_activations(zero)
     assert g[0] == 1.0 and not codes.any() and not scales.any()
     assert O.activation_layout(4096, 5120)[2] == O.activation_layout(4096, 5120)[1] + 4 * 4096
+
+
+@pytest.mark.parametrize("case", ["gauss", "spread", "padded"])
+def test_nvfp4_sd4_layout_and_values(golden, case):
+    """Table-indexed NVFP4 (row-split-k128-sd4-v1) as the reference's converter writes it: geometry, and the dense values
+    through the oracle's table lookup, bit for bit."""
+    g = golden("nvfp4_sd4")
+    w = g[f"{case}_weights"]
+    n, k = w.shape
+    blob = g[f"{case}_blob"].tobytes()
+    assert len(blob) == O.nvfp4_sd4_offsets(n, k)[2]
+    dense = O.nvfp4_sd4_dense(blob, n, k)
+    assert np.array_equal(dense.view(np.uint32), g[f"{case}_dense"][:, :k].astype(np.float32).view(np.uint32))
+    for (rows, cols), expect in zip(g["offset_shapes"], g["offsets"]):
+        assert O.nvfp4_sd4_offsets(int(rows), int(cols)) == tuple(int(v) for v in expect)
+    # the stand-in generator of the kernel tests gives a well-formed tensor whose values use table entries only
+    plain = O.nvfp4_pack(w)
+    again = O.nvfp4_sd4_from_plain(plain, n, k, np.random.default_rng(1))
+    assert len(again) == len(blob)
+    codes, scales, _ = O.nvfp4_unpack(O.nvfp4_sd4_to_plain(again, n, k), n, k)
+    table = np.frombuffer(again, dtype=np.uint8)[O.nvfp4_sd4_offsets(n, k)[1]:][:16]
+    assert np.all(np.isin(scales, table)) and np.array_equal(codes, O.nvfp4_unpack(plain, n, k)[0])
