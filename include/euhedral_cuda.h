@@ -73,7 +73,9 @@ EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_q3_bf16(const void* device_input, 
 /* reference :136-143 - the scalar Q3 kernel, always. */
 EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_q3_reference_bf16(const void* device_input, const void* device_weights,
         void* device_output, uint32_t rows, uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size);
-/* reference :152-154 - NVFP4 weights (row-split-k128-v1), BF16 rows in and out, same routing as Q3. */
+/* reference :152-154 - NVFP4 weights, BF16 rows in and out, same routing as Q3. The layout is read off the byte size:
+ * row-split-k128-v1 (one E4M3 scale per block) or row-split-k128-sd4-v1 (a 4-bit index per block into the tensor's table
+ * of 16 E4M3 codes); a size that is neither: FORMAT_MISMATCH. */
 EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_nvfp4_bf16(const void* input, const void* weights, void* output,
         uint32_t rows, uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size);
 /* reference :159-167 - the native FP4 route: activations quantized to two NVFP4 terms in `scratch`, block-scaled FP4
