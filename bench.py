@@ -284,6 +284,11 @@ class Bench:
         return synthetic.bf16_rows(rows, k, ACTIVATION_SEED + rows, device="cuda")
 
 
+def synthetic_trellis(n, k, seed, segments):
+    from euhedral_b200 import synthetic
+    return synthetic.trellis_object(n, k, TRELLIS_WIDTH, seed, segments, device="cuda")
+
+
 class LayerSet:
     """One format's layer set on one GPU: `copies` resident copies of every weight tensor, packed activation and output
     buffers on the host (pinned) and the device, and the C-ABI calls of a step in two shapes: one call per tensor (the
@@ -321,7 +326,16 @@ class LayerSet:
         self.bytes_per_step = sum(algorithmic_bytes(fmt, n, k, rows) for rows in rows_list for _, n, k in LAYER)
         self.scratch = None
         if fmt == "trellis":
-            need = max(bench.lib.euhedral_b200_linear_trellis_scratch_bytes(rows, k, n, 1, 0) for rows in rows_list for _, n, k in LAYER)
+            # ... and the layer as the reference's converter stores it: fused objects with one input scale vector per member
+            # (query_key_value: three segments; gate_up: two), tools/euhedral_artifacts/trellis.py:128-146.
+            self.fused = [("query_key_value", 7168, 5120, 3), ("o", 5120, 5120, 1), ("gate_up", 34816, 5120, 2), ("down", 5120, 17408, 1)]
+            self.fused_weights = {}
+            for index, (name, n, k, segments) in enumerate(self.fused):
+                first = synthetic_trellis(n, k, WEIGHT_SEED + 32 + index, segments)
+                self.fused_weights[name] = [first] + [tuple(t.clone() for t in first) for _ in range(copies - 1)]
+            self.fused_out = torch.empty(max(rows_list) * 34816, dtype=torch.int16, device="cuda")
+            shapes = [(n, k, 1) for _, n, k in LAYER] + [(n, k, s) for _, n, k, s in self.fused]
+            need = max(bench.lib.euhedral_b200_linear_trellis_scratch_bytes(rows, k, n, s, 0) for rows in rows_list for n, k, s in shapes)
             self.scratch = [torch.empty(need, dtype=torch.uint8, device="cuda") for _ in LAYER]
             self.scratch_bytes = need
         self._build_calls()
@@ -343,6 +357,12 @@ class LayerSet:
                         entry = lib.euhedral_cuda_linear_q3_bf16 if fmt == "q3" else lib.euhedral_cuda_linear_nvfp4_bf16
                         self.single[copy].append((entry, (x, tensors[0].data_ptr(), y, rows, k, n, tensors[0].numel())))
                 if fmt == "trellis":
+                    for position, (name, n, k, segments) in enumerate(self.fused):
+                        payload, suh, svh, ends = self.fused_weights[name][copy]
+                        self.grouped[copy].append((lib.euhedral_b200_linear_trellis_bf16,
+                                                   (self.inputs[(rows, k)].data_ptr(), payload.data_ptr(), suh.data_ptr(), svh.data_ptr(), ends.data_ptr(),
+                                                    self.fused_out.data_ptr(), self.scratch[position].data_ptr(), self.scratch_bytes, rows, k, n,
+                                                    TRELLIS_WIDTH, segments, 0)))
                     continue
                 entry = lib.euhedral_b200_linear_group_q3_bf16 if fmt == "q3" else lib.euhedral_b200_linear_group_nvfp4_bf16
                 for k in sorted({k for _, _, k in LAYER}):
@@ -379,9 +399,7 @@ def measure_layer_set(bench: Bench, fmt, rows_list, copies, steps, warmup, e2e=F
     layer = LayerSet(bench, fmt, rows_list, copies)
     result = {"rows": list(rows_list), "bytes_per_step": layer.bytes_per_step}
     with torch.cuda.stream(bench.stream), bench.submit():
-        for label, grouped in (("grouped", True), ("single", False)):
-            if grouped and fmt == "trellis":
-                continue
+        for label, grouped in (("fused_objects" if fmt == "trellis" else "grouped", True), ("single", False)):
             seconds = bench.timed(steps, warmup, lambda i: layer.step(i, grouped))
             gbs = layer.bytes_per_step * steps / seconds / 1e9
             result[label] = {"gbs": gbs, "frac_of_hbm_peak": gbs / bench.peaks["hbm"], "us_per_step": seconds / steps * 1e6,

@@ -901,12 +901,24 @@ uint64_t euhedral_b200_static_scratch_bytes(void) { return kStaticScratchBytes; 
 // is allocated or freed. With one split the scratch is not touched.
 static std::atomic<unsigned long long> g_trellis_tag{0x9E3779B97F4A7C15ull ^ (unsigned long long)(uintptr_t)&g_trellis_tag};
 
+// The split count of a one-launch trellis linear when the caller leaves it open: the one that needs the fewest tile rows
+// per SM slot in sequence - waves of resident CTAs times the tile rows of a split, plus a few tile rows' worth of rotate,
+// flag exchange and in-order sum for every split - among splits of 20 tile rows or more.
 static uint32_t trellis_default_splits(uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t tile_words, int sms) {
     const uint32_t groups = rows <= 8u ? 1u : 4u;
     const uint32_t shared = (uint32_t)trellis::kStages * trellis::kStageTiles * 16u * tile_words + trellis::act_bytes((int)groups) + 1024u + 128u;
     const uint32_t per_sm = std::max(1u, std::min(groups == 1u ? (uint32_t)trellis::kResident : 2u, (uint32_t)kGemvSmem / shared));
-    const uint32_t blocks = out_features / 128u, tiles = in_features / 16u;
-    return std::max(1u, std::min(per_sm * (uint32_t)sms / blocks, tiles / 20u));
+    const uint32_t resident = per_sm * (uint32_t)sms, blocks = out_features / 128u, tiles = in_features / 16u;
+    uint32_t best = 1u, best_cost = 0xFFFFFFFFu;
+    for (uint32_t splits = 1u; splits <= std::max(1u, tiles / 20u); ++splits) {
+        const uint32_t waves = (blocks * splits + resident - 1u) / resident;
+        const uint32_t cost = waves * ((tiles + splits - 1u) / splits + (splits > 1u ? 6u : 0u));
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = splits;
+        }
+    }
+    return best;
 }
 
 static uint64_t trellis_flag_bytes(uint32_t out_features, uint32_t splits) {
@@ -928,9 +940,8 @@ static int trellis_linear(unsigned char* scratch, uint64_t scratch_bytes, const 
         scratch = state->static_scratch;
         scratch_bytes = kStaticScratchBytes;
     }
-    // splits == 0: as many as give every SM its full set of resident CTAs once (one wave), each with 20 tile rows or more.
-    // (The reference's host aims at 8 blocks per SM, core/.../artifact/format/TrellisFormat.java:369-376; a caller that
-    // wants that count passes it.)
+    // splits == 0: the count that keeps the SMs' resident CTA slots busiest (trellis_default_splits). (The reference's host
+    // aims at 8 blocks per SM, core/.../artifact/format/TrellisFormat.java:369-376; a caller that wants that count passes it.)
     if (splits == 0u) splits = trellis_default_splits(rows, in_features, out_features, tile_words, state->sms);
     const uint64_t flags = trellis_flag_bytes(out_features, splits);
     const uint64_t partials = splits > 1u ? (uint64_t)splits * rows * out_features * 4u : 0u;
