@@ -21,8 +21,8 @@
 //     a fixed permutation that the activations in shared memory follow.
 //   * The K splits meet without a second launch and without a counter that would need clearing: a CTA stores its FP32
 //     partials, publishes a flag holding this call's tag, and reads the flags of its column block; whoever sees all of
-//     them set adds the partials in split order, rotates, scales and writes BF16. Two CTAs that finish together may both
-//     do that; they write the same bits.
+//     them set adds the partials in split order, rotates, scales and writes BF16, then unsets the flags (a launch replayed
+//     from a CUDA graph carries the same tag again). Two CTAs that finish together may both do that; they write the same bits.
 // Table entries 0, 1, 4 stay callable one by one (their outputs and the scratch layout are the contract); entry 1 is the
 // same kernel reading the activations from the scratch and leaving the partials to entry 4.
 #pragma once
@@ -433,6 +433,11 @@ __global__ void __launch_bounds__(kThreads, P == 1 ? kResident : 2) linear_kerne
             for (int row = warp; row < rows; row += kDecodeWarps)
                 add_and_finish128(job.partials + (size_t)row * n + column0, (size_t)rows * n, splits, job.svh + column0,
                         job.out + (size_t)row * n + column0, lane);
+            // The block is done: its flags stop carrying the tag, so that the same launch replayed from a CUDA graph (same
+            // tag) starts from flags that are not set. A CTA that reads them only now sees them unset and leaves the block
+            // to this one.
+            if (warp == 0)
+                for (int i = lane; i < splits; i += 32) job.flags[(size_t)blockIdx.x * splits + i] = ~job.tag;
         }
     }
 }

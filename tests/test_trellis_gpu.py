@@ -242,3 +242,34 @@ def test_table_abi(dev):
     with pytest.raises(GpuMemoryException) as unavailable:
         dev.gpu.launch_table_kernel("TRELLIS_MMA_ROWS", 1, 1, 1, 256, 1, 1, 0, KernelArguments())
     assert unavailable.value.status == -5
+
+
+def test_one_launch_linear_replayed_from_a_graph(dev):
+    """A captured one-launch linear carries the same flag tag on every replay: each replay must still wait for its own
+    partial sums (the CTA that finishes a column block unsets the block's flags)."""
+    torch = dev.torch
+    rng = np.random.default_rng(45)
+    k, n, w, rows = 2048, 512, 48, 5
+    payload, suh, svh = random_object(rng, k, n, w)
+    linear = DeviceLinear(dev, payload, suh, svh, [n], 140)
+    splits = TrellisFormat.splits(k, n, 140)
+    assert splits > 1
+    lib = dev.gpu.lib
+    need = lib.euhedral_b200_linear_trellis_scratch_bytes(rows, k, n, 1, splits)
+    xs = [random_x(rng, rows, k) for _ in range(4)]
+    d_x, d_y, d_s = dev.put(xs[0]), dev.empty(rows * n * 2), dev.empty(need)
+    t = [h.data_ptr() for h in linear.tensors]
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream), dev.gpu.submit(stream.cuda_stream, pdl=True):
+        args = (d_x.data_ptr(), t[0], t[1], t[2], t[3], d_y.data_ptr(), d_s.data_ptr(), need, rows, k, n, w, 1, splits)
+        assert lib.euhedral_b200_linear_trellis_bf16(*args) == 0          # warm: plans and maps are made before the capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            assert lib.euhedral_b200_linear_trellis_bf16(*args) == 0
+        for x in xs:
+            d_x.copy_(torch.from_numpy(x.view(np.uint8).reshape(-1).copy()))
+            torch.cuda.synchronize()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert np.array_equal(dev.get(d_y, np.uint16, (rows, n)), linear.one_call(x, splits))
