@@ -406,7 +406,7 @@ constexpr int kTableCount = (int)(sizeof(kTable) / sizeof(kTable[0]));
 bool trellis_width_valid(int w) { return w >= 16 && w <= 128 && w % 8 == 0; }
 
 // The payload as [k / 16][n / 16 * W / 4] 8-byte elements; a box is one streaming stage of one 128-column block. The
-// calling thread keeps the last few maps (encoding costs about a microsecond).
+// calling thread keeps the maps of the last 512 objects per width (encoding costs about a microsecond).
 template <int W>
 const CUtensorMap* trellis_payload_map(const uint16_t* words, int k, int n) {
     struct Cached {
@@ -414,14 +414,12 @@ const CUtensorMap* trellis_payload_map(const uint16_t* words, int k, int n) {
         int k, n, w;
         CUtensorMap map;
     };
-    constexpr int kCached = 16;
-    thread_local Cached cache[kCached] = {};
-    thread_local int next = 0;
-    for (int i = 0; i < kCached; ++i)
-        if (cache[i].words == words && cache[i].k == k && cache[i].n == n && cache[i].w == W) return &cache[i].map;
+    constexpr uint32_t kCached = 512;   // direct-mapped by the payload address: every trellis object of a model, per width
+    thread_local std::vector<Cached> cache(kCached);
+    Cached& slot = cache[(uint32_t)(((uintptr_t)words >> 8) * 0x9E3779B1u >> 16) % kCached];
+    if (slot.words == words && slot.k == k && slot.n == n && slot.w == W) return &slot.map;
     const eb::EncodeTiled encode = eb::encoder();
     if (encode == nullptr) return nullptr;
-    Cached& slot = cache[next];
     const cuuint64_t dims[2] = {(cuuint64_t)(n / 16) * (W / 4), (cuuint64_t)(k / 16)}, strides[1] = {(cuuint64_t)(n / 16) * W * 2u};
     const cuuint32_t box[2] = {2u * W, (cuuint32_t)trellis::kStageTiles}, ones[2] = {1u, 1u};
     slot.words = nullptr;
@@ -434,7 +432,6 @@ const CUtensorMap* trellis_payload_map(const uint16_t* words, int k, int n) {
     slot.k = k;
     slot.n = n;
     slot.w = W;
-    next = (next + 1) % kCached;
     return &slot.map;
 }
 
