@@ -102,17 +102,21 @@ def test_prepass_bitwise(dev):
         assert np.array_equal(got, expect), layout
 
 
-@pytest.mark.parametrize("w", [16, 40, 48, 56, 64, 128])
+@pytest.mark.parametrize("w", [16, 24, 32, 40, 48, 56, 64, 72, 80, 88, 96, 104, 112, 120, 128])   # every stored width: every lane decoder
 @pytest.mark.parametrize("target", [8, 140])
 def test_tensor_core_route_matches_float64(dev, w, target):
     rng = np.random.default_rng(w + target)
     k, n = 1024, 512
     payload, suh, svh = random_object(rng, k, n, w, segments=2)
     linear = DeviceLinear(dev, payload, suh, svh, [256, 512], target)
+    splits = TrellisFormat.splits(k, n, target)
     for rows in (1, 5, 8, 13, 40):
         x = random_x(rng, rows, k)
         expect = O.trellis_linear_f64(x, payload, suh, svh, [256, 512])
-        assert within_kernel_tolerance(linear.linear(x), expect), (w, target, rows)
+        got = linear.linear(x)
+        assert within_kernel_tolerance(got, expect), (w, target, rows)
+        if rows in (5, 13):
+            assert np.array_equal(linear.one_call(x, splits), got), (w, target, rows)   # one launch: the same bits
 
 
 # The layer's projection shapes (N x K) at the model's stored widths, one and two segments, through the operator's own
