@@ -20,6 +20,7 @@ def test_nvfp4_offsets(golden):
         assert O.nvfp4_offsets(int(n), int(k)) == tuple(int(v) for v in expect)
     # core/src/test/.../artifact/Nvfp4LayoutTest.java:18-30
     assert O.nvfp4_offsets(3, 1024) == (1536, 1792, 1796)
+    assert O.nvfp4_sd4_offsets(3, 1024)[2] == 1812   # Nvfp4LayoutTest.java:60-79
 
 
 @pytest.mark.parametrize("case", ["gauss", "spread", "padded", "edge"])

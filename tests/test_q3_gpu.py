@@ -162,3 +162,27 @@ def test_launch_geometries(dev, n, k):
             for r in (0, 4):
                 assert np.array_equal(run(dev, x[r:r + 1], blob, n, k)[0], got_bits[r])
 
+
+
+def test_every_fp16_scale_pattern(dev):
+    """The FP16 group scale reaches the sum as its exact FP32 value for every finite bit pattern, subnormals and both
+    zeros included (the reference pins its conversion over all 65,536 patterns, native/tests/test_q3_conversion.py:18-41;
+    NaN payloads are the scalar oracle's business only, native/src/q3/contiguous.cuh:16-20). One row per pattern: a single
+    code 1 under that scale against x = 1, so the output is bf16(f32(scale)) - on the decode kernel and on the scalar one
+    (the scale -0 gives +0: every sum starts at +0)."""
+    n, k = 65536, 128
+    patterns = np.arange(n, dtype=np.uint16)
+    finite = ((patterns >> 10) & 31) != 31
+    codes = np.zeros((n, k), dtype=np.int8)
+    codes[:, 0] = 1
+    scales = np.zeros((n, 2), dtype=np.float16)
+    scales[:, 0] = np.where(finite, patterns, 0).astype(np.uint16).view(np.float16)
+    blob = np.frombuffer(O.q3_assemble(codes, scales, n, k), dtype=np.uint8).copy()
+    x = np.zeros((1, k), dtype=np.uint16)
+    x[0, 0] = 0x3F80   # 1.0
+    expect = O.bf16_bits(scales[:, 0].astype(np.float32))
+    expect[0x8000] = 0   # a sum that starts at +0 stays +0 when -0 is added
+    for reference in (False, True):
+        got = run(dev, x, blob, n, k, reference=reference)[0]
+        wrong = np.flatnonzero(finite & (got != expect))
+        assert wrong.size == 0, (reference, wrong.size, [(hex(int(i)), hex(int(got[i])), hex(int(expect[i]))) for i in wrong[:12]])
