@@ -505,3 +505,144 @@ EXPORT void oracle_float_to_bf16(const float* in, uint16_t* out, uint64_t count)
 }
 
 EXPORT int oracle_abi_version(void) { return 1; }
+
+/* ---------------------------------------------------------------- trellis tile encoder --------------------- */
+
+/* The reference's tile encoder (quantization/src/main/resources/cuda/trellis.cu:34-399, from exllamav3's dense and
+ * fractional Viterbi kernels): a 256-weight tile is quantized to a tail-biting ring of 16-bit states; position i brings
+ * d(i) = ka + bit (i mod 16) of `mask` new bits (mask 0: an integer rate, 0xAAAA: the half-step rates). Costs are FP16:
+ * the first step costs (value - w)^2 (one rounding for the difference, one for the square), every further step
+ * fma(difference, difference, cost of the predecessor) with one rounding; of equal costs the lowest predecessor wins.
+ * Two passes (trellis.cu:93-99,393-396): from an open start at position 128 all round, the best end node (ties by the
+ * kernels' bit-reversed rank, trellis.cu:63-81) is traced back to the node entering position 0; the second pass starts at
+ * position 0 pinned to that node and is traced back in full. Test infrastructure: restated to check an encoder against the
+ * reference's golden tiles (tiles-K-idx / -out / -packed). */
+
+static double g_half_value[65536];      /* every FP16 bit pattern as a double */
+static uint16_t g_state_value[65536];   /* codebook value (FP16 bits) of every state */
+static pthread_once_t g_encoder_once = PTHREAD_ONCE_INIT;
+
+static void encoder_tables(void) {
+    for (uint32_t i = 0; i < 65536u; ++i) {
+        g_half_value[i] = (double)half_to_float((uint16_t)i);
+        g_state_value[i] = trellis_value_bits(i);
+    }
+}
+
+static inline uint16_t double_to_half_bits(double v) {
+    _Float16 h = (_Float16)v; /* one rounding, to nearest even */
+    uint16_t bits;
+    memcpy(&bits, &h, 2);
+    return bits;
+}
+
+/* a < b as the kernels compare FP16 costs (__hlt: false when either is NaN) */
+static inline int half_less(uint16_t a, uint16_t b) {
+    const double x = g_half_value[a], y = g_half_value[b];
+    return x < y;
+}
+
+static inline uint32_t reverse5(uint32_t v) {
+    return ((v & 1u) << 4) | ((v & 2u) << 2) | (v & 4u) | ((v & 8u) >> 2) | ((v & 16u) >> 4);
+}
+
+typedef struct {
+    const float* tiles;
+    uint16_t* indices;
+    float* decoded;
+    int ka;
+    uint32_t mask;
+} encode_ctx;
+
+static inline int position_bits(int position, int ka, uint32_t mask) { return ka + (int)((mask >> (position & 15)) & 1u); }
+
+/* One forward pass; history[ri][node] = the predecessor node chosen for `node` at ring position ri. */
+static void encoder_forward(const uint16_t* w_bits, int roll, int pre_state, int ka, uint32_t mask, uint16_t* cost_a, uint16_t* cost_b,
+        uint16_t** final_costs, uint16_t* history) {
+    uint16_t *costs = cost_a, *previous = cost_b;
+    for (int i = 0; i < 256; ++i) {
+        const int ri = (i + roll) & 255;
+        uint16_t* swap = costs;
+        costs = previous;
+        previous = swap;
+        const int kin = position_bits(ri, ka, mask), kout = position_bits(ri + 1, ka, mask);
+        const int shift = 16 - kout, nodes = 65536 >> kout, branches = 1 << kout;
+        const double w = g_half_value[w_bits[ri]];
+        const int write = pre_state >= 0 || ri < 128;
+        for (int node = 0; node < nodes; ++node) {
+            uint16_t best = 0;
+            int best_from = 0;
+            for (int branch = 0; branch < branches; ++branch) {
+                const int state = (branch << shift) | node, from = state >> kin;
+                const double difference = g_half_value[double_to_half_bits(g_half_value[g_state_value[state]] - w)];
+                uint16_t cost;
+                if (i == 0)
+                    cost = pre_state >= 0 && from != pre_state ? 0x7c00u : double_to_half_bits(difference * difference);
+                else
+                    cost = double_to_half_bits(difference * difference + g_half_value[previous[from]]);
+                if (branch == 0 || half_less(cost, best)) {
+                    best = cost;
+                    best_from = from;
+                }
+            }
+            costs[node] = best;
+            if (write) history[(size_t)ri * 65536u + (size_t)node] = (uint16_t)best_from;
+        }
+    }
+    *final_costs = costs;
+}
+
+static void encode_tiles_range(void* p, uint32_t begin, uint32_t end) {
+    const encode_ctx* c = (const encode_ctx*)p;
+    uint16_t* history = (uint16_t*)malloc((size_t)256 * 65536u * sizeof(uint16_t));
+    uint16_t* cost_a = (uint16_t*)malloc(65536u * sizeof(uint16_t));
+    uint16_t* cost_b = (uint16_t*)malloc(65536u * sizeof(uint16_t));
+    for (uint32_t tile = begin; tile < end; ++tile) {
+        uint16_t w_bits[256];
+        for (int i = 0; i < 256; ++i) w_bits[i] = float_to_half(c->tiles[(size_t)tile * 256u + (size_t)i]);
+        uint16_t* costs = NULL;
+        /* pass 1: open start at position 128; the best of the last step's nodes, ties by the kernels' rank */
+        encoder_forward(w_bits, 128, -1, c->ka, c->mask, cost_a, cost_b, &costs, history);
+        const int last_nodes = 65536 >> position_bits(128, c->ka, c->mask);
+        uint32_t best_key = 0x7c00ffffu;
+        for (int e = 0; e < last_nodes; ++e) {
+            const uint32_t v = (uint32_t)e & 1023u;
+            const uint32_t rank = (reverse5(v >> 5) << 10) | (reverse5(v & 31u) << 5) | ((uint32_t)e >> 10);
+            const uint32_t key = ((uint32_t)costs[e] << 16) | rank;
+            if (key < best_key) best_key = key;
+        }
+        int node = 0;
+        if (best_key < 0x7c000000u) {
+            const uint32_t rank = best_key & 65535u;
+            node = (int)(((rank & 31u) << 10) | (reverse5(rank >> 10) << 5) | reverse5((rank >> 5) & 31u));
+        }
+        /* back to the node that enters position 0 (ring positions 127 down to 0 carry history in this pass) */
+        for (int i = 255; i >= 0; --i) {
+            const int ri = (i + 128) & 255;
+            node = history[(size_t)ri * 65536u + (size_t)node];
+            if (ri == 0) break;
+        }
+        const int pinned = node;
+        /* pass 2: from position 0, pinned; traced back in full */
+        encoder_forward(w_bits, 0, pinned, c->ka, c->mask, cost_a, cost_b, &costs, history);
+        node = pinned;
+        for (int ri = 255; ri >= 0; --ri) {
+            const int from = history[(size_t)ri * 65536u + (size_t)node];
+            const int state = ((from << position_bits(ri, c->ka, c->mask)) | node) & 0xFFFF;
+            node = from;
+            c->indices[(size_t)tile * 256u + (size_t)ri] = (uint16_t)state;
+            c->decoded[(size_t)tile * 256u + (size_t)ri] = half_to_float(g_state_value[state]);
+        }
+    }
+    free(history);
+    free(cost_a);
+    free(cost_b);
+}
+
+/* tiles float32 [count][256] -> indices u16 [count][256] (the 16-bit state of every position), decoded float32. */
+EXPORT void oracle_trellis_encode_tiles(const float* tiles, uint32_t count, int ka, uint32_t mask, uint16_t* indices, float* decoded,
+        int threads) {
+    pthread_once(&g_encoder_once, encoder_tables);
+    encode_ctx c = {tiles, indices, decoded, ka, mask};
+    parallel_rows(encode_tiles_range, &c, count, threads);
+}

@@ -120,3 +120,16 @@ def trellis_linear(x_bits, payload, suh, svh, ends, threads: int | None = None) 
     lib().oracle_trellis_linear(_p(x_bits), _p(payload), _p(suh), _p(svh), _p(ends), C.c_int(len(ends)), _p(y),
                                 C.c_int(rows), C.c_int(k), C.c_int(n), C.c_int(w), C.c_int(threads or default_threads()))
     return y
+
+
+def trellis_encode_tiles(tiles: np.ndarray, ka: int, mask: int = 0, threads: int | None = None):
+    """float32 [count, 256] tiles (kernel element order) -> (states uint16 [count, 256], decoded float32 [count, 256]):
+    the reference's tail-biting Viterbi tile encoder restated (quantization/src/main/resources/cuda/trellis.cu:34-399).
+    ka bits per position plus one where bit (position mod 16) of mask is set (0xAAAA: the half-step rates)."""
+    tiles = np.ascontiguousarray(tiles, dtype=np.float32)
+    count = tiles.shape[0]
+    states = np.empty((count, 256), dtype=np.uint16)
+    decoded = np.empty((count, 256), dtype=np.float32)
+    lib().oracle_trellis_encode_tiles(_p(tiles), C.c_uint32(count), C.c_int(ka), C.c_uint32(mask), _p(states), _p(decoded),
+                                      C.c_int(threads or default_threads()))
+    return states, decoded

@@ -592,3 +592,23 @@ def activations_dense(codes, scales, g) -> np.ndarray:
     value = E2M1_MAGNITUDES[codes & 7].astype(np.float64) * np.where(codes & 8, -1.0, 1.0)
     value = value * np.repeat(e4m3_value(scales).astype(np.float64), 16, axis=2)
     return value.sum(axis=0) * np.asarray(g, dtype=np.float64)[:, None]
+
+
+def trellis_pack_states(states: np.ndarray, ka: int, mask: int = 0) -> np.ndarray:
+    """uint16 [count, 256] states -> int16 [count, w] payload words: the low d(i) bits of state i, most significant bit
+    first, into 32-bit little-endian words (pack.cu / frac.cu as restated in quantization/src/main/resources/cuda/
+    trellis.cu:401-462); w = 16 ka + popcount(mask)."""
+    states = np.asarray(states, dtype=np.uint16)
+    count = states.shape[0]
+    bits_per = np.array([ka + ((mask >> (i & 15)) & 1) for i in range(256)])
+    total = int(bits_per.sum())
+    stream = np.zeros((count, total), dtype=np.uint8)
+    at = 0
+    for i in range(256):
+        d = int(bits_per[i])
+        for b in range(d - 1, -1, -1):
+            stream[:, at] = (states[:, i] >> b) & 1
+            at += 1
+    words = np.packbits(stream.reshape(count, total // 32, 32), axis=2, bitorder="big").reshape(count, total // 32, 4)
+    big = (words[..., 0].astype(np.uint32) << 24) | (words[..., 1].astype(np.uint32) << 16) | (words[..., 2].astype(np.uint32) << 8) | words[..., 3]
+    return big.astype("<u4").view("<i2").reshape(count, total // 16)

@@ -173,6 +173,8 @@ def trellis_cases():
         assert np.array_equal(tref.decode_tiles(packed, w).view(np.uint16), golden.view(np.uint16))
         out[f"tiles_{w}_packed"] = packed[:12]
         out[f"tiles_{w}_out"] = golden[:12]
+        out[f"tiles_{w}_idx"] = np.load(source / f"tiles-{rate}-idx.npy")[:12]    # the encoder's 16-bit states
+    out["tiles_in"] = np.load(source / "tiles-in.npy")[:12]                         # what the encoder was given
     # Random words at every stored width, decoded by the reference's NumPy decoder.
     for w in range(16, 129, 8):
         words = rng.integers(-32768, 32768, size=(3, w), dtype=np.int16)

@@ -150,3 +150,18 @@ def test_nvfp4_sd4_layout_and_values(golden, case):
     codes, scales, _ = O.nvfp4_unpack(O.nvfp4_sd4_to_plain(again, n, k), n, k)
     table = np.frombuffer(again, dtype=np.uint8)[O.nvfp4_sd4_offsets(n, k)[1]:][:16]
     assert np.all(np.isin(scales, table)) and np.array_equal(codes, O.nvfp4_unpack(plain, n, k)[0])
+
+
+@pytest.mark.parametrize("w,ka,mask", [(32, 2, 0), (40, 2, 0xAAAA), (48, 3, 0), (56, 3, 0xAAAA), (64, 4, 0), (80, 5, 0), (96, 6, 0)])
+def test_trellis_tile_encoder_reproduces_the_golden_tiles(golden, w, ka, mask):
+    """The restated tail-biting Viterbi (FP16 costs, lowest predecessor on ties, two passes) gives the reference encoder's
+    own states, decoded values and packed words on its golden tiles, bit for bit, at all seven rates."""
+    from oracle import oracle_c as OC
+    g = golden("trellis")
+    states, decoded = OC.trellis_encode_tiles(g["tiles_in"], ka, mask)
+    assert np.array_equal(states, g[f"tiles_{w}_idx"])
+    assert np.array_equal(decoded.astype(np.float16).view(np.uint16), g[f"tiles_{w}_out"].view(np.uint16))
+    packed = O.trellis_pack_states(states, ka, mask)
+    assert packed.shape[1] == w and np.array_equal(packed, g[f"tiles_{w}_packed"])
+    # and the decoder reads the packed words back to the same values
+    assert np.array_equal(O.trellis_decode_tiles(packed, w).view(np.uint16), g[f"tiles_{w}_out"].view(np.uint16))
