@@ -16,6 +16,7 @@
 #include "nvfp4_native.cuh"
 #include "q3_gemv.cuh"
 #include "trellis.cuh"
+#include "trellis_encode.cuh"
 
 namespace {
 
@@ -82,6 +83,10 @@ void initialize_device(int device, DeviceState* state) {
     if (e == cudaSuccess) e = allow_gemv<nvfp4::FormatSd4>();
     if (e == cudaSuccess) e = allow_gemv<q3::Format>();
     if (e == cudaSuccess) e = allow_big_smem(exact::trellis_linear);
+#define EB_ALLOW_ENCODER(KA, HALF) if (e == cudaSuccess) e = allow_big_smem(trellis_encode::viterbi_kernel<KA, HALF>);
+    EB_ALLOW_ENCODER(2, false) EB_ALLOW_ENCODER(2, true) EB_ALLOW_ENCODER(3, false) EB_ALLOW_ENCODER(3, true)
+    EB_ALLOW_ENCODER(4, false) EB_ALLOW_ENCODER(5, false) EB_ALLOW_ENCODER(6, false)
+#undef EB_ALLOW_ENCODER
 #define EB_ALLOW(W) if (e == cudaSuccess) e = allow_trellis_width<W>();
     EB_TRELLIS_WIDTHS(EB_ALLOW)
 #undef EB_ALLOW
@@ -984,6 +989,48 @@ int euhedral_b200_linear_trellis_bf16(const void* input, const void* words, cons
     alignas(16) static unsigned char unused[16];   // one split: the scratch is never dereferenced
     return trellis_linear(scratch != nullptr ? static_cast<unsigned char*>(scratch) : unused, scratch_bytes, input, words, suh, svh,
             segment_ends, output, rows, in_features, out_features, tile_words, segments, splits);
+}
+
+// The converter's tile encoder: 256-weight tiles (FP32, kernel element order) -> the 16-bit state of every position, for
+// the rates the format stores tiles at (tile_words = 16 x bits per weight: 32, 40, 48, 56, 64, 80, 96). The scratch holds
+// one history slab per resident CTA; `ctas` = how many tiles are encoded side by side.
+static uint32_t encoder_ctas(uint32_t count, int sms) { return std::max(1u, std::min(count, 2u * (uint32_t)sms)); }   // two CTAs fit an SM
+
+uint64_t euhedral_b200_trellis_encode_scratch_bytes(uint32_t count, uint32_t tile_words) {
+    if (tile_words < 32u || tile_words > 96u || tile_words % 8u != 0) return 0;
+    int sms = 148;
+    DeviceState* state = nullptr;
+    if (bind(&state) == EUHEDRAL_CUDA_SUCCESS) sms = state->sms;
+    return (uint64_t)encoder_ctas(count, sms) * trellis_encode::history_bytes((int)(tile_words / 16u));
+}
+
+int euhedral_b200_trellis_encode_tiles(const void* tiles, uint32_t count, uint32_t tile_words, void* states, void* scratch,
+        uint64_t scratch_bytes) {
+    if (tiles == nullptr || states == nullptr || scratch == nullptr || count == 0 || ((uintptr_t)tiles & 3u) != 0 || ((uintptr_t)states & 1u) != 0)
+        return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    const uint32_t ka = tile_words / 16u;
+    const bool half_step = tile_words % 16u == 8u;
+    if (tile_words % 8u != 0 || ka < 2u || ka > 6u || (half_step && ka > 3u)) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    DeviceState* state = nullptr;
+    const int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    const uint32_t ctas = encoder_ctas(count, state->sms);
+    if ((uint64_t)ctas * trellis_encode::history_bytes((int)ka) > scratch_bytes) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
+    const size_t shared = 4u * (65536u >> ka) + 512u;
+    auto run = [&](auto kernel) {
+        return finish(launch(kOrdered, kernel, dim3(ctas), dim3(trellis_encode::kThreads), shared, 1u, static_cast<const float*>(tiles), count,
+                static_cast<uint16_t*>(states), static_cast<uint8_t*>(scratch)));
+    };
+    switch (tile_words) {
+        case 32: return run(trellis_encode::viterbi_kernel<2, false>);
+        case 40: return run(trellis_encode::viterbi_kernel<2, true>);
+        case 48: return run(trellis_encode::viterbi_kernel<3, false>);
+        case 56: return run(trellis_encode::viterbi_kernel<3, true>);
+        case 64: return run(trellis_encode::viterbi_kernel<4, false>);
+        case 80: return run(trellis_encode::viterbi_kernel<5, false>);
+        case 96: return run(trellis_encode::viterbi_kernel<6, false>);
+    }
+    return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
 }
 
 int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t* k_slices,

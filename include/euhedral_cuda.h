@@ -178,6 +178,16 @@ EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_trellis_bf16(const void* input, co
         const void* svh, const void* segment_ends, void* output, void* scratch, uint64_t scratch_bytes, uint32_t rows,
         uint32_t in_features, uint32_t out_features, uint32_t tile_words, uint32_t segments, uint32_t splits);
 
+/* No counterpart in the reference's C ABI (its trellis encoder lives in the quantization module's own CUDA image,
+ * quantization/src/main/resources/cuda/trellis.cu:34-399). The converter's tile encoder: `count` tiles of 256 FP32 weights
+ * in kernel element order -> the 16-bit trellis state of every position (uint16 [count][256]), by the format's tail-biting
+ * Viterbi search; bit for bit the reference encoder's states on its golden tiles. tile_words = 16 x bits per weight, one
+ * of 32, 40, 48, 56, 64, 80, 96 (else -5). scratch: at least euhedral_b200_trellis_encode_scratch_bytes(count, tile_words)
+ * bytes of device memory (-2 if smaller). */
+EUHEDRAL_CUDA_EXPORT uint64_t euhedral_b200_trellis_encode_scratch_bytes(uint32_t count, uint32_t tile_words);
+EUHEDRAL_CUDA_EXPORT int euhedral_b200_trellis_encode_tiles(const void* tiles, uint32_t count, uint32_t tile_words, void* states,
+        void* scratch, uint64_t scratch_bytes);
+
 #ifdef __cplusplus
 }
 #endif
