@@ -1004,9 +1004,10 @@ uint64_t euhedral_b200_trellis_encode_scratch_bytes(uint32_t count, uint32_t til
     return (uint64_t)encoder_ctas(count, sms) * trellis_encode::history_bytes((int)(tile_words / 16u));
 }
 
-int euhedral_b200_trellis_encode_tiles(const void* tiles, uint32_t count, uint32_t tile_words, void* states, void* scratch,
-        uint64_t scratch_bytes) {
-    if (tiles == nullptr || states == nullptr || scratch == nullptr || count == 0 || ((uintptr_t)tiles & 3u) != 0 || ((uintptr_t)states & 1u) != 0)
+int euhedral_b200_trellis_encode_tiles(const void* tiles, uint32_t count, uint32_t tile_words, void* states, void* decoded, void* words,
+        void* scratch, uint64_t scratch_bytes) {
+    if (tiles == nullptr || states == nullptr || scratch == nullptr || count == 0 || ((uintptr_t)tiles & 3u) != 0 || ((uintptr_t)states & 1u) != 0
+            || ((uintptr_t)decoded & 3u) != 0 || ((uintptr_t)words & 3u) != 0)
         return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     const uint32_t ka = tile_words / 16u;
     const bool half_step = tile_words % 16u == 8u;
@@ -1018,19 +1019,25 @@ int euhedral_b200_trellis_encode_tiles(const void* tiles, uint32_t count, uint32
     if ((uint64_t)ctas * trellis_encode::history_bytes((int)ka) > scratch_bytes) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
     const size_t shared = 4u * (65536u >> ka) + 512u;
     auto run = [&](auto kernel) {
-        return finish(launch(kOrdered, kernel, dim3(ctas), dim3(trellis_encode::kThreads), shared, 1u, static_cast<const float*>(tiles), count,
-                static_cast<uint16_t*>(states), static_cast<uint8_t*>(scratch)));
+        return launch(kOrdered, kernel, dim3(ctas), dim3(trellis_encode::kThreads), shared, 1u, static_cast<const float*>(tiles), count,
+                static_cast<uint16_t*>(states), static_cast<float*>(decoded), static_cast<uint8_t*>(scratch));
     };
+    cudaError_t e = cudaErrorInvalidValue;
     switch (tile_words) {
-        case 32: return run(trellis_encode::viterbi_kernel<2, false>);
-        case 40: return run(trellis_encode::viterbi_kernel<2, true>);
-        case 48: return run(trellis_encode::viterbi_kernel<3, false>);
-        case 56: return run(trellis_encode::viterbi_kernel<3, true>);
-        case 64: return run(trellis_encode::viterbi_kernel<4, false>);
-        case 80: return run(trellis_encode::viterbi_kernel<5, false>);
-        case 96: return run(trellis_encode::viterbi_kernel<6, false>);
+        case 32: e = run(trellis_encode::viterbi_kernel<2, false>); break;
+        case 40: e = run(trellis_encode::viterbi_kernel<2, true>); break;
+        case 48: e = run(trellis_encode::viterbi_kernel<3, false>); break;
+        case 56: e = run(trellis_encode::viterbi_kernel<3, true>); break;
+        case 64: e = run(trellis_encode::viterbi_kernel<4, false>); break;
+        case 80: e = run(trellis_encode::viterbi_kernel<5, false>); break;
+        case 96: e = run(trellis_encode::viterbi_kernel<6, false>); break;
     }
-    return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    if (e == cudaSuccess && words != nullptr) {
+        const uint64_t total = (uint64_t)count * (tile_words / 2u);
+        e = launch(kOrdered, trellis_encode::pack_kernel, dim3((unsigned)((total + 255u) / 256u)), dim3(256), 0, 1u,
+                static_cast<const uint16_t*>(states), count, (int)ka, half_step ? 1 : 0, static_cast<uint32_t*>(words));
+    }
+    return finish(e);
 }
 
 int euhedral_b200_decode_plan(int format, uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t* k_slices,

@@ -67,11 +67,12 @@ __device__ __forceinline__ void step(const __half* __restrict__ before, __half* 
     }
 }
 
-// tiles f32 [count][256] -> states u16 [count][256]. history: history_bytes(KA) bytes per CTA.
+// tiles f32 [count][256] -> states u16 [count][256] (and, when asked for, their codebook values as f32). history:
+// history_bytes(KA) bytes per CTA.
 //   grid: any (CTAs take tiles blockIdx.x, + gridDim.x, ...), block kThreads, dynamic shared 4 * (65536 >> KA) + 512 bytes.
 template <int KA, bool kHalfStep>
 __global__ void __launch_bounds__(kThreads, 1) viterbi_kernel(const float* __restrict__ tiles, uint32_t count, uint16_t* __restrict__ states,
-        uint8_t* __restrict__ history) {
+        float* __restrict__ decoded, uint8_t* __restrict__ history) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int kMost = 65536 >> KA;   // nodes of a position that brings KA bits
     constexpr int KB = kHalfStep ? KA + 1 : KA;
@@ -143,12 +144,37 @@ __global__ void __launch_bounds__(kThreads, 1) viterbi_kernel(const float* __res
                     const int kin = position_bits(ri, KA, kHalfStep), kout = position_bits(ri + 1, KA, kHalfStep);
                     const int s = slab[(uint64_t)ri * kMost + (uint32_t)node];
                     const int from = (s << (16 - kout - kin)) | (node >> kin);
-                    states[(uint64_t)tile * 256u + (uint32_t)ri] = (uint16_t)((((uint32_t)from << kin) | (uint32_t)node) & 0xFFFFu);
+                    const uint32_t state = (((uint32_t)from << kin) | (uint32_t)node) & 0xFFFFu;
+                    states[(uint64_t)tile * 256u + (uint32_t)ri] = (uint16_t)state;
+                    if (decoded != nullptr) decoded[(uint64_t)tile * 256u + (uint32_t)ri] = __half2float(__ushort_as_half(trellis::value_bits(state)));
                     node = from;
                 }
             }
         }
     }
+}
+
+// states u16 [count][256] -> payload words [count][w] (16-bit words; w = 16 ka + 8 at a half-step rate): the low d(i) bits of
+// state i, most significant bit first, in 32-bit little-endian words - the ring trellis.cuh reads. A thread per 32-bit word.
+__global__ void __launch_bounds__(256) pack_kernel(const uint16_t* __restrict__ states, uint32_t count, int ka, int half_step,
+        uint32_t* __restrict__ words) {
+    const uint32_t per_tile = (uint32_t)(8 * ka + (half_step ? 4 : 0));   // 32-bit words of a tile
+    const uint64_t index = (uint64_t)blockIdx.x * 256u + threadIdx.x;
+    if (index >= (uint64_t)count * per_tile) return;
+    const uint32_t tile = (uint32_t)(index / per_tile), word = (uint32_t)(index % per_tile);
+    const int first_bit = (int)word * 32;
+    // position i starts at bit i ka + i / 2 (half-step: one more bit before every odd position's successor)
+    uint32_t value = 0;
+    for (int i = 0; i < 256; ++i) {
+        const int start = i * ka + (half_step ? i / 2 : 0), bits = position_bits(i, ka, half_step != 0);
+        if (start + bits <= first_bit) continue;
+        if (start >= first_bit + 32) break;
+        const uint32_t field = (uint32_t)states[(uint64_t)tile * 256u + (uint32_t)i] & ((1u << bits) - 1u);
+        // the field occupies stream bits [start, start + bits); stream bit b of this word is word bit 31 - (b - first_bit)
+        const int shift = first_bit + 32 - (start + bits);
+        value |= shift >= 0 ? field << shift : field >> -shift;
+    }
+    words[index] = value;
 }
 
 }  // namespace trellis_encode

@@ -182,11 +182,12 @@ EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_trellis_bf16(const void* input, co
  * quantization/src/main/resources/cuda/trellis.cu:34-399). The converter's tile encoder: `count` tiles of 256 FP32 weights
  * in kernel element order -> the 16-bit trellis state of every position (uint16 [count][256]), by the format's tail-biting
  * Viterbi search; bit for bit the reference encoder's states on its golden tiles. tile_words = 16 x bits per weight, one
- * of 32, 40, 48, 56, 64, 80, 96 (else -5). scratch: at least euhedral_b200_trellis_encode_scratch_bytes(count, tile_words)
- * bytes of device memory (-2 if smaller). */
+ * of 32, 40, 48, 56, 64, 80, 96 (else -5). decoded (may be null): the states' codebook values, float [count][256]. words
+ * (may be null): the packed payload, int16 [count][tile_words], as the linears read it. scratch: at least
+ * euhedral_b200_trellis_encode_scratch_bytes(count, tile_words) bytes of device memory (-2 if smaller). */
 EUHEDRAL_CUDA_EXPORT uint64_t euhedral_b200_trellis_encode_scratch_bytes(uint32_t count, uint32_t tile_words);
 EUHEDRAL_CUDA_EXPORT int euhedral_b200_trellis_encode_tiles(const void* tiles, uint32_t count, uint32_t tile_words, void* states,
-        void* scratch, uint64_t scratch_bytes);
+        void* decoded, void* words, void* scratch, uint64_t scratch_bytes);
 
 #ifdef __cplusplus
 }

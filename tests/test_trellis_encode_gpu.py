@@ -27,8 +27,10 @@ def encode(dev, tiles, w):
     count = tiles.shape[0]
     need = lib.euhedral_b200_trellis_encode_scratch_bytes(count, w)
     d_t, d_s, d_h = dev.put(np.ascontiguousarray(tiles, dtype=np.float32)), dev.empty(count * 512), dev.empty(need)
+    d_v, d_w = dev.empty(count * 1024), dev.empty(count * w * 2)
     with dev.submit():
-        assert lib.euhedral_b200_trellis_encode_tiles(d_t.data_ptr(), count, w, d_s.data_ptr(), d_h.data_ptr(), need) == 0
+        assert lib.euhedral_b200_trellis_encode_tiles(d_t.data_ptr(), count, w, d_s.data_ptr(), d_v.data_ptr(), d_w.data_ptr(), d_h.data_ptr(), need) == 0
+    encode.decoded, encode.words = dev.get(d_v, np.float32, (count, 256)), dev.get(d_w, np.int16, (count, w))
     return dev.get(d_s, np.uint16, (count, 256))
 
 
@@ -39,6 +41,8 @@ def test_golden_tiles(dev, golden, w, ka, mask):
     assert np.array_equal(states, g[f"tiles_{w}_idx"])
     packed = O.trellis_pack_states(states, ka, mask)
     assert np.array_equal(packed, g[f"tiles_{w}_packed"])
+    assert np.array_equal(encode.words, packed)       # the library's own packing and values
+    assert np.array_equal(encode.decoded.astype(np.float16).view(np.uint16), g[f"tiles_{w}_out"].view(np.uint16))
     assert np.array_equal(O.trellis_decode_tiles(packed, w).view(np.uint16), g[f"tiles_{w}_out"].view(np.uint16))
 
 
@@ -62,7 +66,7 @@ def test_status_codes(dev):
     tiles = dev.put(np.zeros((2, 256), dtype=np.float32))
     out, scratch = dev.empty(1024), dev.empty(1 << 20)
     with dev.submit():
-        assert lib.euhedral_b200_trellis_encode_tiles(tiles.data_ptr(), 2, 72, out.data_ptr(), scratch.data_ptr(), 1 << 20) == library.ROUTE_UNAVAILABLE
-        assert lib.euhedral_b200_trellis_encode_tiles(tiles.data_ptr(), 2, 48, out.data_ptr(), scratch.data_ptr(), 1024) == library.SIZE_OVERFLOW
-        assert lib.euhedral_b200_trellis_encode_tiles(0, 2, 48, out.data_ptr(), scratch.data_ptr(), 1 << 20) == library.INVALID_ARGUMENT
+        assert lib.euhedral_b200_trellis_encode_tiles(tiles.data_ptr(), 2, 72, out.data_ptr(), 0, 0, scratch.data_ptr(), 1 << 20) == library.ROUTE_UNAVAILABLE
+        assert lib.euhedral_b200_trellis_encode_tiles(tiles.data_ptr(), 2, 48, out.data_ptr(), 0, 0, scratch.data_ptr(), 1024) == library.SIZE_OVERFLOW
+        assert lib.euhedral_b200_trellis_encode_tiles(0, 2, 48, out.data_ptr(), 0, 0, scratch.data_ptr(), 1 << 20) == library.INVALID_ARGUMENT
     assert lib.euhedral_b200_trellis_encode_scratch_bytes(2, 48) == 2 * 256 * 8192
