@@ -231,6 +231,8 @@ class Bench:
         self.sms = self.gpu.multiprocessor_count()
         self.stream = torch.cuda.Stream()
         self.peaks = read_peaks()
+        self._converter, self._trellis = None, {}
+        self.convert_seconds, self.convert_tiles, self.convert_error = 0.0, 0, 0.0
 
     def check(self, status):
         if status != 0:
@@ -270,8 +272,7 @@ class Bench:
         torch = self.torch
         local = n if local is None else local
         if fmt == "trellis":
-            # Random trellis words with the reference test-suite's scale distributions (its encoder is not part of this build).
-            return synthetic.trellis_object(local, k, TRELLIS_WIDTH, WEIGHT_SEED + index, 1, device="cuda")
+            return self.trellis_fused([(index, local, k)])
         build, cut = (synthetic.q3_tensor, sharding.q3_rows) if fmt == "q3" else (synthetic.nvfp4_tensor, sharding.nvfp4_rows)
         whole = build(synthetic.gaussian(n, k, WEIGHT_SEED + index, SIGMA, device="cuda"))
         if local == n:
@@ -279,14 +280,31 @@ class Bench:
         # a shard is cut from the whole tensor (NVFP4's tensor scale is the whole tensor's)
         return (torch.from_numpy(cut(whole.cpu().numpy(), n, k, first, local)).cuda(),)
 
+    def trellis_member(self, index, n, k):
+        """The seeded N(0, 0.02^2) weight `index` converted to a trellis object by this build's converter (uncalibrated
+        path, 3 bits per weight); converted once per process."""
+        from euhedral_b200 import synthetic, trellis_convert
+        key = (index, n, k)
+        if key not in self._trellis:
+            if self._converter is None:
+                self._converter = trellis_convert.TrellisConverter("cuda")
+            begin = time.perf_counter()
+            dense = synthetic.gaussian(n, k, WEIGHT_SEED + index, SIGMA, device="cuda")
+            self._trellis[key] = self._converter.quantize(dense, TRELLIS_WIDTH / 16, seed=WEIGHT_SEED + index)
+            self.torch.cuda.synchronize()
+            self.convert_seconds += time.perf_counter() - begin
+            self.convert_tiles += (n // 16) * (k // 16)
+            self.convert_error = max(self.convert_error, self._trellis[key].proxy)
+        return self._trellis[key]
+
+    def trellis_fused(self, members):
+        """(payload, suh [s, k], svh, ends) of the members (index, n, k) side by side along n."""
+        from euhedral_b200 import trellis_convert
+        return trellis_convert.TrellisConverter.fuse([self.trellis_member(*member) for member in members])
+
     def rows(self, rows, k):
         from euhedral_b200 import synthetic
         return synthetic.bf16_rows(rows, k, ACTIVATION_SEED + rows, device="cuda")
-
-
-def synthetic_trellis(n, k, seed, segments):
-    from euhedral_b200 import synthetic
-    return synthetic.trellis_object(n, k, TRELLIS_WIDTH, seed, segments, device="cuda")
 
 
 class LayerSet:
@@ -329,9 +347,10 @@ class LayerSet:
             # ... and the layer as the reference's converter stores it: fused objects with one input scale vector per member
             # (query_key_value: three segments; gate_up: two), tools/euhedral_artifacts/trellis.py:128-146.
             self.fused = [("query_key_value", 7168, 5120, 3), ("o", 5120, 5120, 1), ("gate_up", 34816, 5120, 2), ("down", 5120, 17408, 1)]
+            members = {"query_key_value": (0, 1, 2), "o": (3,), "gate_up": (4, 5), "down": (6,)}
             self.fused_weights = {}
-            for index, (name, n, k, segments) in enumerate(self.fused):
-                first = synthetic_trellis(n, k, WEIGHT_SEED + 32 + index, segments)
+            for name, _, _, _ in self.fused:
+                first = bench.trellis_fused([(i, LAYER[i][1], LAYER[i][2]) for i in members[name]])
                 self.fused_weights[name] = [first] + [tuple(t.clone() for t in first) for _ in range(copies - 1)]
             self.fused_out = torch.empty(max(rows_list) * 34816, dtype=torch.int16, device="cuda")
             shapes = [(n, k, 1) for _, n, k in LAYER] + [(n, k, s) for _, n, k, s in self.fused]
@@ -409,6 +428,11 @@ def measure_layer_set(bench: Bench, fmt, rows_list, copies, steps, warmup, e2e=F
             result["e2e_gbs"] = layer.bytes_per_step * steps / seconds / 1e9
             result["h2d"], result["d2h"] = layer.h2d, layer.d2h
     assert bench.gpu.take_device_error() == 0, "a kernel's bounded wait gave up"
+    if fmt == "trellis":
+        result["weights"] = {"source": "N(0, 0.02^2) seeded, converted by this build's trellis converter (uncalibrated path, 3 bits per weight)",
+                             "tiles": bench.convert_tiles, "convert_seconds": bench.convert_seconds,
+                             "tiles_per_s": bench.convert_tiles / max(bench.convert_seconds, 1e-9),
+                             "worst_rounding_mse_rotated": bench.convert_error}
     del layer
     torch.cuda.empty_cache()
     return result
@@ -427,13 +451,18 @@ def measure_per_shape(bench: Bench, steps_floor=40):
         for index, (name, n, k) in enumerate(shapes):
             if name not in distinct:
                 continue
-            first = bench.weight(fmt, index, n, k)
+            members = {"query_key_value": (0, 1, 2), "gate_up": (4, 5)}.get(name)
+            if fmt == "trellis" and members:      # the converter's fused objects: the members side by side
+                first = bench.trellis_fused([(i, LAYER[i][1], LAYER[i][2]) for i in members])
+            else:
+                first = bench.weight(fmt, index, n, k)
             size = sum(t.numel() * t.element_size() for t in first)
             copies = int(min(128, max(3, math.ceil(2.5 * L2_BYTES / size) + 1)))
             tensors = [first] + [tuple(t.clone() for t in first) for _ in range(copies - 1)]
             scratch = None
             if fmt == "trellis":
-                need = lib.euhedral_b200_linear_trellis_scratch_bytes(5, k, n, 1, 0)
+                segments = first[3].numel()
+                need = lib.euhedral_b200_linear_trellis_scratch_bytes(5, k, n, segments, 0)
                 scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
             for rows in (1, 2, 3, 4, 5):
                 x = bench.rows(rows, k)
@@ -443,7 +472,7 @@ def measure_per_shape(bench: Bench, steps_floor=40):
                     t = tensors[i % copies]
                     if fmt == "trellis":
                         bench.check(lib.euhedral_b200_linear_trellis_bf16(x.data_ptr(), t[0].data_ptr(), t[1].data_ptr(), t[2].data_ptr(), t[3].data_ptr(),
-                                                                           y.data_ptr(), scratch.data_ptr(), need, rows, k, n, TRELLIS_WIDTH, 1, 0))
+                                                                           y.data_ptr(), scratch.data_ptr(), need, rows, k, n, TRELLIS_WIDTH, segments, 0))
                     elif fmt == "q3":
                         bench.check(lib.euhedral_cuda_linear_q3_bf16(x.data_ptr(), t[0].data_ptr(), y.data_ptr(), rows, k, n, t[0].numel()))
                     else:
