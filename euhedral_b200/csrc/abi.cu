@@ -993,15 +993,21 @@ int euhedral_b200_linear_trellis_bf16(const void* input, const void* words, cons
 
 // The converter's tile encoder: 256-weight tiles (FP32, kernel element order) -> the 16-bit state of every position, for
 // the rates the format stores tiles at (tile_words = 16 x bits per weight: 32, 40, 48, 56, 64, 80, 96). The scratch holds
-// one history slab per resident CTA; `ctas` = how many tiles are encoded side by side.
-static uint32_t encoder_ctas(uint32_t count, int sms) { return std::max(1u, std::min(count, 2u * (uint32_t)sms)); }   // two CTAs fit an SM
+// one history slab per group of a resident CTA (one CTA per SM, one or two groups that encode side by side).
+static uint32_t encoder_ctas(uint32_t count, uint32_t ka, int sms) {
+    const uint32_t groups = (uint32_t)trellis_encode::groups_of((int)ka);
+    return std::max(1u, std::min((count + groups - 1u) / groups, (uint32_t)sms));
+}
+static uint64_t encoder_scratch(uint32_t count, uint32_t ka, int sms) {
+    return (uint64_t)encoder_ctas(count, ka, sms) * (uint64_t)trellis_encode::groups_of((int)ka) * trellis_encode::history_bytes((int)ka);
+}
 
 uint64_t euhedral_b200_trellis_encode_scratch_bytes(uint32_t count, uint32_t tile_words) {
     if (tile_words < 32u || tile_words > 96u || tile_words % 8u != 0) return 0;
     int sms = 148;
     DeviceState* state = nullptr;
     if (bind(&state) == EUHEDRAL_CUDA_SUCCESS) sms = state->sms;
-    return (uint64_t)encoder_ctas(count, sms) * trellis_encode::history_bytes((int)(tile_words / 16u));
+    return encoder_scratch(count, tile_words / 16u, sms);
 }
 
 int euhedral_b200_trellis_encode_tiles(const void* tiles, uint32_t count, uint32_t tile_words, void* states, void* decoded, void* words,
@@ -1015,9 +1021,9 @@ int euhedral_b200_trellis_encode_tiles(const void* tiles, uint32_t count, uint32
     DeviceState* state = nullptr;
     const int status = bind(&state);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
-    const uint32_t ctas = encoder_ctas(count, state->sms);
-    if ((uint64_t)ctas * trellis_encode::history_bytes((int)ka) > scratch_bytes) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
-    const size_t shared = 4u * (65536u >> ka) + 512u;
+    const uint32_t ctas = encoder_ctas(count, ka, state->sms);
+    if (encoder_scratch(count, ka, state->sms) > scratch_bytes) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
+    const size_t shared = trellis_encode::shared_bytes((int)ka);
     auto run = [&](auto kernel) {
         return launch(kOrdered, kernel, dim3(ctas), dim3(trellis_encode::kThreads), shared, 1u, static_cast<const float*>(tiles), count,
                 static_cast<uint16_t*>(states), static_cast<float*>(decoded), static_cast<uint8_t*>(scratch));

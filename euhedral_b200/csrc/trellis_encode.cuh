@@ -9,11 +9,15 @@
 // an open start at position 128 all round, the best end node (ties by a bit-reversed rank of the node) traced back to
 // the node that enters position 0; then from position 0 pinned to that node, traced back in full.
 //
-// How it runs here: one CTA per tile at a time (persistent over the tile list), 512 threads. The two cost rows live in
-// shared memory as FP16; a thread takes pairs of neighbouring nodes (they share their predecessors) and evaluates both
-// with packed FP16 arithmetic, recomputing the codebook value of a state from its hash instead of keeping tables. The
-// history - one byte per position and node: which of the 2^d states won - goes to a scratch slab of the CTA in global
-// memory (up to 4 MB per pass) and is read back by one thread for the trace. No waits on other CTAs.
+// How it runs here: one CTA per SM, 1024 threads, persistent over the tile list. The CTA first writes the codebook value of
+// every one of the 65,536 states to shared memory (128 KB of FP16) - a state's neighbours sit side by side there. The
+// threads then work as two groups of 512 that encode tiles independently of each other (a named barrier per group; at
+// 2 and 2.5 bits the cost rows are too large for two groups and one group of 1024 runs): a group keeps its two cost rows
+// in shared memory as FP16; a thread takes runs of 2, 4 or 8 neighbouring nodes, which share their predecessors, reads
+// their values with one load per predecessor and updates their costs with packed FP16 arithmetic and bit selects. The
+// history - one byte per position and node: which of the 2^d states won - goes to a slab of the group in global memory
+// (up to 4 MB per pass) and one thread of the group walks it back; while it does, the other group has the SM's issue
+// slots. No waits on other CTAs.
 #pragma once
 
 #include "common.cuh"
@@ -21,73 +25,127 @@
 
 namespace trellis_encode {
 
-constexpr int kThreads = 512;
+constexpr int kThreads = 1024;
 constexpr uint32_t kInfinity = 0x7C00u;
+constexpr uint32_t kTableBytes = 65536u * 2u;
 
 __host__ __device__ constexpr int position_bits(int position, int ka, bool half_step) { return ka + ((half_step && (position & 1)) ? 1 : 0); }
 
-// Bytes of history one CTA needs: 256 positions x the most nodes of a position.
+// Bytes of history one group needs: 256 positions x the most nodes of a position.
 __host__ __device__ constexpr uint64_t history_bytes(int ka) { return 256ull * (65536ull >> ka); }
+
+// Groups of a CTA that encode side by side: two where their cost rows fit beside the value table.
+__host__ __device__ constexpr int groups_of(int ka) { return ka >= 3 ? 2 : 1; }
+
+// Dynamic shared memory of a CTA: the value table, then per group two cost rows and the tile's 256 weights.
+__host__ __device__ constexpr uint32_t shared_bytes(int ka) { return kTableBytes + (uint32_t)groups_of(ka) * (4u * (65536u >> ka) + 512u); }
 
 __device__ __forceinline__ uint32_t reverse5(uint32_t v) { return __brev(v) >> 27; }
 
-// One step of a pass at ring position `ri`: costs of the nodes after the position from the costs before it.
-template <int KIN, int KOUT>
-__device__ __forceinline__ void step(const __half* __restrict__ before, __half* __restrict__ after, uint8_t* __restrict__ history_row, __half w,
-        bool first, int pinned, bool write) {
+template <int GROUP_THREADS>
+__device__ __forceinline__ void group_sync(int group) {
+    if (GROUP_THREADS == kThreads) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(GROUP_THREADS) : "memory");
+}
+
+// Nodes a thread takes at a time: they must share their predecessors (2^KIN neighbours do) and there should be at least
+// as many runs as threads.
+template <int KIN, int KOUT, int GROUP_THREADS>
+struct Run {
+    static constexpr int kNodes = 65536 >> KOUT;
+    static constexpr int kShared = 1 << KIN;
+    static constexpr int kWanted = kNodes / GROUP_THREADS >= 8 ? 8 : kNodes / GROUP_THREADS >= 4 ? 4 : 2;
+    static constexpr int value = kWanted < kShared ? kWanted : (kShared < 8 ? kShared : 8);
+};
+
+// One step of a pass: costs of the nodes after a position from the costs before it. `table`: FP16 value of every state.
+template <int KIN, int KOUT, int GROUP_THREADS, bool kFirst>
+__device__ __forceinline__ void step(const __half* __restrict__ table, const __half* __restrict__ before, __half* __restrict__ after,
+        uint8_t* __restrict__ history_row, __half w, int pinned, bool write, int tid) {
     constexpr int kShift = 16 - KOUT, kNodes = 65536 >> KOUT, kStates = 1 << KOUT;
-    const __half2 w2 = __half2half2(w), infinity = __half2half2(__ushort_as_half((unsigned short)kInfinity));
-    for (int pair = threadIdx.x; pair < kNodes / 2; pair += kThreads) {
-        const int node = 2 * pair, from_low = node >> KIN;   // both nodes of the pair have the same predecessors
-        __half2 best = infinity;
-        uint32_t winner0 = 0, winner1 = 0;
+    constexpr int G = Run<KIN, KOUT, GROUP_THREADS>::value, H = G / 2;
+    const __half2 w2 = __half2half2(w);
+    const uint32_t infinity = kInfinity | kInfinity << 16;
+    for (int run = tid; run < kNodes / G; run += GROUP_THREADS) {
+        const int node = run * G, from_low = node >> KIN;   // the G nodes of the run have the same predecessors
+        uint32_t best[H], winner[H];
 #pragma unroll
         for (int s = 0; s < kStates; ++s) {
             const uint32_t state = ((uint32_t)s << kShift) | (uint32_t)node;
             const int from = (s << (kShift - KIN)) | from_low;
-            const uint32_t values = trellis::value_pair(state, state + 1u);
-            const __half2 e = __hsub2(*reinterpret_cast<const __half2*>(&values), w2);
-            __half2 cost;
-            if (first) {
-                cost = pinned >= 0 && from != pinned ? infinity : __hmul2(e, e);
+            uint32_t values[H];
+            if constexpr (G == 8) {
+                const uint4 v = *reinterpret_cast<const uint4*>(table + state);
+                values[0] = v.x, values[1] = v.y, values[2] = v.z, values[3] = v.w;
+            } else if constexpr (G == 4) {
+                const uint2 v = *reinterpret_cast<const uint2*>(table + state);
+                values[0] = v.x, values[1] = v.y;
             } else {
-                cost = __hfma2(e, e, __half2half2(before[from]));
+                values[0] = *reinterpret_cast<const uint32_t*>(table + state);
             }
-            if (s == 0 || __hlt(__low2half(cost), __low2half(best))) {
-                best = __halves2half2(__low2half(cost), __high2half(best));
-                winner0 = (uint32_t)s;
-            }
-            if (s == 0 || __hlt(__high2half(cost), __high2half(best))) {
-                best = __halves2half2(__low2half(best), __high2half(cost));
-                winner1 = (uint32_t)s;
+            __half2 previous;
+            if (!kFirst) previous = __half2half2(before[from]);
+#pragma unroll
+            for (int j = 0; j < H; ++j) {
+                const __half2 e = __hsub2(*reinterpret_cast<const __half2*>(&values[j]), w2);
+                uint32_t cost;
+                if (kFirst) {
+                    const __half2 square = __hmul2(e, e);
+                    cost = pinned >= 0 && from != pinned ? infinity : *reinterpret_cast<const uint32_t*>(&square);
+                } else {
+                    const __half2 sum = __hfma2(e, e, previous);
+                    cost = *reinterpret_cast<const uint32_t*>(&sum);
+                }
+                if (s == 0) {
+                    best[j] = cost;
+                    winner[j] = 0;
+                } else {
+                    // strictly less, half by half: the lowest state keeps a tie
+                    const uint32_t less = __hlt2_mask(*reinterpret_cast<const __half2*>(&cost), *reinterpret_cast<const __half2*>(&best[j]));
+                    best[j] = (cost & less) | (best[j] & ~less);
+                    winner[j] = (((uint32_t)s * 0x00010001u) & less) | (winner[j] & ~less);
+                }
             }
         }
-        reinterpret_cast<__half2*>(after)[pair] = best;
-        if (write) reinterpret_cast<uint16_t*>(history_row)[pair] = (uint16_t)(winner0 | winner1 << 8);
+        if constexpr (G == 8) {
+            *reinterpret_cast<uint4*>(after + node) = make_uint4(best[0], best[1], best[2], best[3]);
+            if (write) *reinterpret_cast<uint2*>(history_row + node) = make_uint2(__byte_perm(winner[0], winner[1], 0x6420), __byte_perm(winner[2], winner[3], 0x6420));
+        } else if constexpr (G == 4) {
+            *reinterpret_cast<uint2*>(after + node) = make_uint2(best[0], best[1]);
+            if (write) *reinterpret_cast<uint32_t*>(history_row + node) = __byte_perm(winner[0], winner[1], 0x6420);
+        } else {
+            *reinterpret_cast<uint32_t*>(after + node) = best[0];
+            if (write) *reinterpret_cast<uint16_t*>(history_row + node) = (uint16_t)__byte_perm(winner[0], 0, 0x4420);
+        }
     }
 }
 
 // tiles f32 [count][256] -> states u16 [count][256] (and, when asked for, their codebook values as f32). history:
-// history_bytes(KA) bytes per CTA.
-//   grid: any (CTAs take tiles blockIdx.x, + gridDim.x, ...), block kThreads, dynamic shared 4 * (65536 >> KA) + 512 bytes.
+// history_bytes(KA) bytes per CTA and group.
+//   grid: any (group g of CTA b takes tiles b G + g, + gridDim.x G, ...), block kThreads, dynamic shared shared_bytes(KA).
 template <int KA, bool kHalfStep>
 __global__ void __launch_bounds__(kThreads, 1) viterbi_kernel(const float* __restrict__ tiles, uint32_t count, uint16_t* __restrict__ states,
         float* __restrict__ decoded, uint8_t* __restrict__ history) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int kMost = 65536 >> KA;   // nodes of a position that brings KA bits
     constexpr int KB = kHalfStep ? KA + 1 : KA;
-    __half* row_a = reinterpret_cast<__half*>(smem);
+    constexpr int kGroups = groups_of(KA), T = kThreads / kGroups;
+    __shared__ uint32_t warp_best[kGroups][T / 32];
+    __shared__ int node_shared[kGroups];
+    const int group = kGroups == 1 ? 0 : threadIdx.x / T, tid = threadIdx.x - group * T;
+    __half* table = reinterpret_cast<__half*>(smem);
+    __half* row_a = reinterpret_cast<__half*>(smem + kTableBytes + (uint32_t)group * (4u * kMost + 512u));
     __half* row_b = row_a + kMost;
     __half* weights = row_b + kMost;
-    __shared__ uint32_t warp_best[kThreads / 32];
-    __shared__ int node_shared;
-    uint8_t* slab = history + (uint64_t)blockIdx.x * history_bytes(KA);
-    const int tid = threadIdx.x;
+    uint8_t* slab = history + ((uint64_t)blockIdx.x * kGroups + (uint32_t)group) * history_bytes(KA);
 
-    for (uint32_t tile = blockIdx.x; tile < count; tile += gridDim.x) {
-        __syncthreads();   // the tile before is done with the shared rows
+    for (uint32_t state = threadIdx.x; state < 65536u; state += kThreads) table[state] = __ushort_as_half(trellis::value_bits(state));
+    __syncthreads();
+
+    for (uint32_t tile = blockIdx.x * kGroups + group; tile < count; tile += gridDim.x * kGroups) {
+        group_sync<T>(group);   // the tile before is done with the group's rows
         if (tid < 256) weights[tid] = __float2half_rn(tiles[(uint64_t)tile * 256u + (uint32_t)tid]);
-        __syncthreads();
+        group_sync<T>(group);
         __half *before = row_a, *after = row_b;
         int pinned = -1;
         for (int pass = 0; pass < 2; ++pass) {
@@ -99,29 +157,34 @@ __global__ void __launch_bounds__(kThreads, 1) viterbi_kernel(const float* __res
                 after = swap;
                 const bool write = pass == 1 || ri < 128;
                 uint8_t* row = slab + (uint64_t)ri * kMost;
+                const __half w = weights[ri];
                 // a position brings KA bits, or KA + 1 at odd positions of a half-step rate; the next one likewise
-                if (!kHalfStep || (ri & 1) == 0) {
-                    if (!kHalfStep) step<KA, KA>(before, after, row, weights[ri], i == 0, pinned, write);
-                    else step<KA, KB>(before, after, row, weights[ri], i == 0, pinned, write);
+                if (i == 0) {
+                    if (!kHalfStep) step<KA, KA, T, true>(table, before, after, row, w, pinned, write, tid);
+                    else step<KA, KB, T, true>(table, before, after, row, w, pinned, write, tid);   // both passes start at an even position
+                } else if (!kHalfStep) {
+                    step<KA, KA, T, false>(table, before, after, row, w, pinned, write, tid);
+                } else if ((ri & 1) == 0) {
+                    step<KA, KB, T, false>(table, before, after, row, w, pinned, write, tid);
                 } else {
-                    step<KB, KA>(before, after, row, weights[ri], i == 0, pinned, write);
+                    step<KB, KA, T, false>(table, before, after, row, w, pinned, write, tid);
                 }
-                __syncthreads();
+                group_sync<T>(group);
             }
             if (pass == 0) {
                 // the best node after position 127 (the open pass's last), ties by the rank of the node
                 constexpr int kLast = 65536 >> KA;   // position 128 is even: KA bits
                 uint32_t best = (kInfinity << 16) | 0xFFFFu;
-                for (int e = tid; e < kLast; e += kThreads) {
+                for (int e = tid; e < kLast; e += T) {
                     const uint32_t v = (uint32_t)e & 1023u;
                     const uint32_t rank = (reverse5(v >> 5) << 10) | (reverse5(v & 31u) << 5) | ((uint32_t)e >> 10);
                     best = min(best, ((uint32_t)__half_as_ushort(after[e]) << 16) | rank);
                 }
                 best = __reduce_min_sync(0xFFFFFFFFu, best);
-                if ((tid & 31) == 0) warp_best[tid >> 5] = best;
-                __syncthreads();
+                if ((tid & 31) == 0) warp_best[group][tid >> 5] = best;
+                group_sync<T>(group);
                 if (tid == 0) {
-                    for (int i = 1; i < kThreads / 32; ++i) best = min(best, warp_best[i]);
+                    for (int i = 1; i < T / 32; ++i) best = min(best, warp_best[group][i]);
                     int node = 0;
                     if (best < (kInfinity << 16)) {
                         const uint32_t rank = best & 65535u;
@@ -133,12 +196,11 @@ __global__ void __launch_bounds__(kThreads, 1) viterbi_kernel(const float* __res
                         const int s = slab[(uint64_t)ri * kMost + (uint32_t)node];
                         node = (s << (16 - kout - kin)) | (node >> kin);
                     }
-                    node_shared = node;
+                    node_shared[group] = node;
                 }
-                __syncthreads();
-                pinned = node_shared;
+                group_sync<T>(group);
+                pinned = node_shared[group];
             } else if (tid == 0) {
-                __threadfence_block();
                 int node = pinned;
                 for (int ri = 255; ri >= 0; --ri) {
                     const int kin = position_bits(ri, KA, kHalfStep), kout = position_bits(ri + 1, KA, kHalfStep);
@@ -146,7 +208,7 @@ __global__ void __launch_bounds__(kThreads, 1) viterbi_kernel(const float* __res
                     const int from = (s << (16 - kout - kin)) | (node >> kin);
                     const uint32_t state = (((uint32_t)from << kin) | (uint32_t)node) & 0xFFFFu;
                     states[(uint64_t)tile * 256u + (uint32_t)ri] = (uint16_t)state;
-                    if (decoded != nullptr) decoded[(uint64_t)tile * 256u + (uint32_t)ri] = __half2float(__ushort_as_half(trellis::value_bits(state)));
+                    if (decoded != nullptr) decoded[(uint64_t)tile * 256u + (uint32_t)ri] = __half2float(table[state]);
                     node = from;
                 }
             }

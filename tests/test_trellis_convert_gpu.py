@@ -108,3 +108,27 @@ def test_fused_object_is_its_members_side_by_side(dev, converter):
         alone = DeviceLinear(dev, p.cpu().numpy(), s.cpu().numpy(), v.cpu().numpy(), e.cpu().numpy(), 148).one_call(x, 2)
         assert np.array_equal(fused[:, first:first + alone.shape[1]], alone)
         first += alone.shape[1]
+
+
+def test_degenerate_weights_convert(converter):
+    # all zeros: every RMS takes the 0.1 stand-in, the stored output scales are 0, the object decodes to zeros
+    obj = converter.quantize(torch.zeros(128, 128, device="cuda"), 3.0, seed=2)
+    assert torch.count_nonzero(obj.svh) == 0 and torch.isfinite(obj.suh.float()).all()
+    assert np.all(rebuilt(obj) == 0.0)
+    # one live output channel among dead ones, and BF16 input
+    w = torch.zeros(256, 128, device="cuda")
+    w[17] = torch.randn(128, generator=torch.Generator(device="cuda").manual_seed(1), device="cuda") * 0.05
+    obj = converter.quantize(w.bfloat16(), 4.0, seed=2)
+    back = rebuilt(obj)
+    dense = w.bfloat16().float().cpu().numpy().astype(np.float64)
+    assert np.sum((back - dense) ** 2) / np.sum(dense ** 2) < 0.05
+    assert np.all(np.isfinite(back))
+
+
+def test_without_output_scales(converter):
+    w = gaussian(256, 256, 44)
+    obj = converter.quantize(torch.from_numpy(w).cuda(), 3.0, seed=5, apply_out_scales=False)
+    assert torch.equal(obj.svh.float().abs(), torch.ones(256, device="cuda"))
+    # channels of different energy share one scale now: the error is larger than with output scales, but bounded
+    error = np.sum((rebuilt(obj) - w) ** 2) / np.sum(w.astype(np.float64) ** 2)
+    assert error < 0.08, error
