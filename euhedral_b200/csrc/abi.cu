@@ -14,6 +14,7 @@
 #include "exact_kernels.cuh"
 #include "nvfp4_gemv.cuh"
 #include "nvfp4_native.cuh"
+#include "bf16_gemm.cuh"
 #include "q3_gemv.cuh"
 #include "trellis.cuh"
 #include "trellis_encode.cuh"
@@ -91,6 +92,7 @@ void initialize_device(int device, DeviceState* state) {
     EB_TRELLIS_WIDTHS(EB_ALLOW)
 #undef EB_ALLOW
     if (e == cudaSuccess) e = nvfp4n::initialize();
+    if (e == cudaSuccess) e = bf16n::initialize();
     state->status = (int)e;
 }
 
@@ -392,7 +394,7 @@ struct TableEntry {
     uint8_t sizes[12];
 };
 // Order is the ABI (native/src/host/linear_kernels.c:7-24). Entries whose kernels this build does not carry stay in
-// the table, unavailable: the whole-K prefill kernels and their epilogue, the FP8 kernels, the embedding lookup.
+// the table, unavailable: the whole-K prefill kernels, the FP8 kernels, the embedding lookup.
 const TableEntry kTable[] = {
         {"euhedral_trellis_prepass", 1, 7, {8, 8, 8, 4, 4, 4, 4}},
         {"euhedral_trellis_mma", 1, 12, {8, 8, 8, 8, 8, 8, 4, 4, 4, 4, 4, 4}},
@@ -400,7 +402,7 @@ const TableEntry kTable[] = {
         {"euhedral_trellis_mma_rows64", 0, 11, {8, 8, 8, 8, 8, 4, 4, 4, 4, 4, 4}},
         {"euhedral_trellis_epilogue", 1, 6, {8, 4, 8, 8, 4, 4}},
         {"euhedral_trellis_decode_bf16", 1, 5, {8, 8, 4, 4, 4}},
-        {"euhedral_trellis_epilogue_bf16", 0, 7, {8, 8, 4, 8, 8, 4, 4}},
+        {"euhedral_trellis_epilogue_bf16", 1, 7, {8, 8, 4, 8, 8, 4, 4}},
         {"euhedral_trellis_reference", 1, 11, {8, 8, 8, 8, 8, 4, 8, 4, 4, 4, 4}},
         {"euhedral_trellis_mma_rows_fp8", 0, 11, {8, 8, 8, 8, 8, 4, 4, 4, 4, 4, 4}},
         {"euhedral_trellis_mma_rows64_fp8", 0, 11, {8, 8, 8, 8, 8, 4, 4, 4, 4, 4, 4}},
@@ -480,6 +482,12 @@ cudaError_t launch_trellis_rotate(const void* x, const void* suh, void* act, int
     const long long tasks = (long long)s * rows * (k / 128);
     return launch(kOverlappable, trellis::rotate_kernel, dim3((unsigned)((tasks + 7) / 8)), dim3(256), 0, 1u,
             static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(suh), static_cast<uint16_t*>(act), rows, k, s, layout);
+}
+
+cudaError_t launch_trellis_finish_bf16(const void* rotated, const void* ends, int s, const void* svh, void* out, int rows, int n) {
+    const long long tasks = (long long)rows * (n / 128);
+    return launch(kOverlappable, trellis::finish_bf16_kernel, dim3((unsigned)((tasks + 7) / 8)), dim3(256), 0, 1u,
+            static_cast<const uint16_t*>(rotated), static_cast<const int*>(ends), s, static_cast<const uint16_t*>(svh), static_cast<uint16_t*>(out), rows, n);
 }
 
 cudaError_t launch_trellis_finish(const void* partials, int splits, const void* svh, void* out, int rows, int n) {
@@ -869,6 +877,13 @@ int euhedral_cuda_linear_launch(int32_t kernel, uint32_t grid_x, uint32_t grid_y
             return finish(launch(kOrdered, trellis::decode_bf16_kernel, dim3((unsigned)((tiles + 7) / 8)), dim3(256), 0, 1u,
                     reinterpret_cast<const uint16_t*>(a[0]), reinterpret_cast<uint16_t*>(a[1]), k, n, w));
         }
+        case 6: {   // epilogue_bf16(rotated, ends, s, svh, out, rows, n)
+            const int s = (int)a[2], rows = (int)a[5], n = (int)a[6];
+            if (s <= 0 || rows <= 0 || rows > 65535 || n <= 0 || n % 128 != 0 || ((a[0] | a[3] | a[4]) & 7u) != 0 || (a[1] & 3u) != 0)
+                return EUHEDRAL_CUDA_INVALID_ARGUMENT;   // 8-byte vectors of the products, svh and the output
+            return finish(launch_trellis_finish_bf16(reinterpret_cast<const void*>(a[0]), reinterpret_cast<const void*>(a[1]), s,
+                    reinterpret_cast<const void*>(a[3]), reinterpret_cast<void*>(a[4]), rows, n));
+        }
         case 7: {   // reference(x, words, suh, svh, ends, s, out, rows, k, n, w)
             const int s = (int)a[5], rows = (int)a[7], k = (int)a[8], n = (int)a[9], w = (int)a[10];
             if (s <= 0 || rows <= 0 || k <= 0 || k % 128 != 0 || n <= 0 || n % 128 != 0 || !trellis_width_valid(w)) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
@@ -989,6 +1004,72 @@ int euhedral_b200_linear_trellis_bf16(const void* input, const void* words, cons
     alignas(16) static unsigned char unused[16];   // one split: the scratch is never dereferenced
     return trellis_linear(scratch != nullptr ? static_cast<unsigned char*>(scratch) : unused, scratch_bytes, input, words, suh, svh,
             segment_ends, output, rows, in_features, out_features, tile_words, segments, splits);
+}
+
+// ---- trellis prefill: rotate, decode to BF16, tcgen05 BF16 GEMM per segment, rotate back --------------------------------------
+// The launches of the reference host's prefill plan (core/.../artifact/format/TrellisFormat.java:560-625) as one call: its
+// prepass in the column-order BF16 layout, its decode of the payload to a BF16 matrix, a BF16 linear per segment on the
+// segment's rotated activations, and its BF16 epilogue, over the same scratch layout: activations [s][rows][k], the decoded
+// weight [n][k], the products (segment g at rows * start_g, row stride width_g), each region rounded up to 256 bytes.
+static uint64_t align_scratch(uint64_t bytes) { return (bytes + 255u) & ~(uint64_t)255u; }
+
+uint64_t euhedral_b200_prefill_trellis_scratch_bytes(uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t segments) {
+    return align_scratch((uint64_t)segments * rows * in_features * 2u) + align_scratch((uint64_t)out_features * in_features * 2u)
+            + align_scratch((uint64_t)rows * out_features * 2u);
+}
+
+// out[r][j] = bf16(sum_k input[r][k] * weights[j][k]): the BF16 linear of the prefill plan on its own (the reference's
+// RowExactBf16.linear, core/.../artifact/format/RowExactBf16.java:52-84, takes the same operands).
+int euhedral_b200_linear_bf16(const void* input, const void* weights, void* output, uint32_t rows, uint32_t in_features, uint32_t out_features) {
+    if (input == nullptr || weights == nullptr || output == nullptr || rows == 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    if (in_features == 0 || in_features % 64u != 0 || out_features == 0 || out_features % 128u != 0) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    if ((((uintptr_t)input | (uintptr_t)weights | (uintptr_t)output) & 15u) != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    DeviceState* state = nullptr;
+    const int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    return finish(bf16n::linear(input, weights, output, rows, in_features, out_features, state->sms, t_stream, t_pdl != 0 && t_stream != nullptr,
+            state->error_word));
+}
+
+int euhedral_b200_prefill_trellis_bf16(const void* input, const void* words, const void* suh, const void* svh, const void* segment_ends,
+        const int32_t* host_segment_ends, void* output, void* scratch, uint64_t scratch_bytes, uint32_t rows, uint32_t in_features,
+        uint32_t out_features, uint32_t tile_words, uint32_t segments) {
+    const uint32_t k = in_features, n = out_features;
+    if (input == nullptr || words == nullptr || suh == nullptr || svh == nullptr || segment_ends == nullptr || host_segment_ends == nullptr
+            || output == nullptr || scratch == nullptr || rows == 0 || rows > 0x7FFFFFFFu / 256u || segments == 0 || segments > 64u)
+        return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    if (k == 0 || k % 128u != 0 || n == 0 || n % 128u != 0 || !trellis_width_valid((int)tile_words)) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    if ((((uintptr_t)input | (uintptr_t)suh | (uintptr_t)svh | (uintptr_t)output) & 7u) != 0 || ((uintptr_t)words & 15u) != 0
+            || ((uintptr_t)scratch & 255u) != 0 || ((uintptr_t)segment_ends & 3u) != 0)
+        return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    int32_t start = 0;
+    for (uint32_t g = 0; g < segments; ++g) {   // ascending multiples of 128, the last one n (TrellisLayout.validateSegments)
+        const int32_t end = host_segment_ends[g];
+        if (end <= start || end % 128 != 0 || (uint32_t)end > n) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+        start = end;
+    }
+    if ((uint32_t)start != n) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    if (euhedral_b200_prefill_trellis_scratch_bytes(rows, k, n, segments) > scratch_bytes) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
+    DeviceState* state = nullptr;
+    const int status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    uint8_t* activations = static_cast<uint8_t*>(scratch);
+    uint8_t* decoded = activations + align_scratch((uint64_t)segments * rows * k * 2u);
+    uint8_t* rotated = decoded + align_scratch((uint64_t)n * k * 2u);
+    cudaError_t e = launch_trellis_rotate(input, suh, activations, (int)rows, (int)k, (int)segments, 1);
+    const uint64_t tiles = (uint64_t)(k / 16u) * (n / 16u);
+    if (e == cudaSuccess)
+        e = launch(kOrdered, trellis::decode_bf16_kernel, dim3((unsigned)((tiles + 7u) / 8u)), dim3(256), 0, 1u, static_cast<const uint16_t*>(words),
+                reinterpret_cast<uint16_t*>(decoded), (int)k, (int)n, (int)tile_words);
+    start = 0;
+    for (uint32_t g = 0; g < segments && e == cudaSuccess; ++g) {
+        const uint32_t width = (uint32_t)(host_segment_ends[g] - start);
+        e = bf16n::linear(activations + (uint64_t)g * rows * k * 2u, decoded + (uint64_t)start * k * 2u, rotated + (uint64_t)rows * (uint32_t)start * 2u,
+                rows, k, width, state->sms, t_stream, false, state->error_word);
+        start = host_segment_ends[g];
+    }
+    if (e == cudaSuccess) e = launch_trellis_finish_bf16(rotated, segment_ends, (int)segments, svh, output, (int)rows, (int)n);
+    return finish(e);
 }
 
 // The converter's tile encoder: 256-weight tiles (FP32, kernel element order) -> the 16-bit state of every position, for

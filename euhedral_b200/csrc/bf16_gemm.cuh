@@ -1,0 +1,176 @@
+// BF16 x BF16 -> BF16 linear on tcgen05 (kind::f16, FP32 accumulators in tensor memory) for the trellis prefill route:
+// out[r][j] = bf16(sum_k a[r][k] * b[j][k]) for a [rows][k] and b [n][k], both BF16 and K-major. It stands where the
+// reference's trellis prefill calls its row-exact BF16 linear on the decoded weights
+// (core/.../artifact/format/TrellisFormat.java:560-604, RowExactBf16.java:52-84): every output is one FP32 sum over K in
+// K order whatever the row count, so a row's bits do not depend on the rows beside it.
+//
+// The engine is the NVFP4 prefill kernel's (nvfp4_native.cuh) without scales: a persistent CTA per SM walks 128 x 256
+// output tiles; warp 0 requests the stages by TMA (64 K of the 128 activation rows and of the 256 weight rows: 48 KB,
+// 128-byte swizzle, four stages), one thread of warp 1 issues four K = 16 MMAs per stage and commits the stage back, eight
+// epilogue warps drain the 128 x 256 accumulator into registers, hand it back and round and store. Every wait is bounded.
+#pragma once
+
+#include "nvfp4_native.cuh"
+
+namespace bf16n {
+
+using nvfp4n::kThreads;
+using nvfp4n::kTileM;
+using nvfp4n::kTileN;
+using nvfp4n::kTmemColumns;
+
+constexpr uint32_t kStepK = 64;                                   // BF16 values of K per stage: 128 bytes a row
+constexpr uint32_t kATile = kTileM * 128u, kBTile = kTileN * 128u;
+constexpr uint32_t kStageBytes = kATile + kBTile;
+constexpr uint32_t kStages = 4;
+constexpr uint32_t kSharedBytes = kStages * kStageBytes + 128u + 1024u;   // + barriers + slack to align to 1024
+constexpr uint32_t kWaitFailed = 16u;                             // error bit: a bounded wait of this kernel gave up
+
+// kind::f16 instruction descriptor: FP32 accumulator, BF16 x BF16, both operands K-major, M 128, N 256.
+constexpr uint32_t kInstruction = (1u << 4) | (1u << 7) | (1u << 10) | ((kTileN >> 3) << 17) | ((kTileM >> 4) << 24);
+
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(kInstruction), "r"(accumulate)
+            : "memory");
+}
+
+//   grid: min(tiles, SMs), block nvfp4n::kThreads, dynamic shared kSharedBytes. map_a: [rows][k] BF16, box 64 x 128;
+//   map_b: [n][k] BF16, box 64 x 128 (a B tile is two boxes). n a multiple of 128.
+__global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+        uint16_t* __restrict__ out, uint32_t rows, uint32_t n, uint32_t k, uint32_t* __restrict__ error) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+    uint64_t* empty = full + kStages;
+    uint64_t* acc_full = empty + kStages;
+    uint64_t* acc_empty = acc_full + 1;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const nvfp4n::TileWalk walk(rows, n, kTileN);
+    const uint32_t k_steps = k / kStepK;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            eb::mbar_init(&full[s], 1);
+            eb::mbar_init(&empty[s], 1);
+        }
+        eb::mbar_init(acc_full, 1);
+        eb::mbar_init(acc_empty, 8);
+        eb::mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(eb::smem_u32(tmem_holder)), "r"(kTmemColumns) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    nvfp4n::tcgen05_fence_before();
+    __syncthreads();
+    nvfp4n::tcgen05_fence_after();
+    const uint32_t tmem = *tmem_holder;
+    eb::pdl_launch_dependents();
+    eb::pdl_wait();   // both operands come from the launches before this one
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t step = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < walk.total && ok; tile += gridDim.x) {
+                uint32_t tm, tn;
+                walk.at(tile, &tm, &tn);
+                for (uint32_t ks = 0; ks < k_steps; ++ks, ++step) {
+                    const uint32_t s = step % kStages, round = step / kStages;
+                    if (round > 0 && !eb::mbar_wait(&empty[s], (round - 1u) & 1u)) {
+                        atomicOr(error, kWaitFailed);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* stage = smem + s * kStageBytes;
+                    eb::mbar_arrive_expect_tx(&full[s], kStageBytes);
+                    // rows past the end of a matrix read as zeros (and the transaction still counts the whole box)
+                    eb::tma_load_2d(stage, &map_a, (int)(ks * kStepK), (int)(tm * kTileM), &full[s]);
+                    eb::tma_load_2d(stage + kATile, &map_b, (int)(ks * kStepK), (int)(tn * kTileN), &full[s]);
+                    eb::tma_load_2d(stage + kATile + kBTile / 2u, &map_b, (int)(ks * kStepK), (int)(tn * kTileN + 128u), &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t step = 0, local = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < walk.total && ok; tile += gridDim.x, ++local) {
+                if (local > 0 && !eb::mbar_wait(acc_empty, (local - 1u) & 1u)) {
+                    atomicOr(error, kWaitFailed);
+                    break;
+                }
+                nvfp4n::tcgen05_fence_after();
+                for (uint32_t ks = 0; ks < k_steps; ++ks, ++step) {
+                    const uint32_t s = step % kStages, round = step / kStages;
+                    if (!eb::mbar_wait(&full[s], round & 1u)) {
+                        atomicOr(error, kWaitFailed);
+                        ok = false;
+                        break;
+                    }
+                    nvfp4n::tcgen05_fence_after();
+                    const uint8_t* stage = smem + s * kStageBytes;
+                    const uint64_t a = nvfp4n::tile_descriptor(stage), b = nvfp4n::tile_descriptor(stage + kATile);
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j) mma_bf16(tmem, a + 2u * j, b + 2u * j, (uint32_t)((ks | j) != 0u));   // 32 bytes of K further
+                    nvfp4n::mma_commit(&empty[s]);
+                }
+                if (ok) nvfp4n::mma_commit(acc_full);
+            }
+        }
+    } else {
+        // warp w reads the 32 accumulator rows of lane quarter w % 4; warps 2..5 take columns 0..127, warps 6..9 128..255
+        const uint32_t quarter = warp & 3u, half = (warp - 2u) >> 2;
+        uint32_t local = 0;
+        for (uint32_t tile = blockIdx.x; tile < walk.total; tile += gridDim.x, ++local) {
+            uint32_t tm, tn;
+            walk.at(tile, &tm, &tn);
+            if (!eb::mbar_wait(acc_full, local & 1u)) {
+                if (lane == 0) atomicOr(error, kWaitFailed);
+                break;
+            }
+            nvfp4n::tcgen05_fence_after();
+            uint32_t r[4][32];
+            const uint32_t from = tmem + ((quarter * 32u) << 16) + half * 128u;
+#pragma unroll
+            for (uint32_t cb = 0; cb < 4u; ++cb) nvfp4n::tmem_load_32(r[cb], from + cb * 32u);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            nvfp4n::tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) eb::mbar_arrive(acc_empty);
+            nvfp4n::store_block(r, out, tm * kTileM + quarter * 32u + lane, rows, n, tn * kTileN + half * 128u, 1.0f, false);
+        }
+    }
+    nvfp4n::tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
+    }
+}
+
+inline cudaError_t initialize() { return cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSharedBytes); }
+
+// a [rows][k], b [n][k] -> out [rows][n], all BF16 in device memory, 16-byte aligned; k % 64 == 0, n % 128 == 0.
+inline cudaError_t linear(const void* a, const void* b, void* out, uint32_t rows, uint32_t k, uint32_t n, int sms, cudaStream_t stream, bool pdl,
+        uint32_t* error) {
+    const eb::EncodeTiled encode = eb::encoder();
+    if (encode == nullptr) return cudaErrorNotSupported;
+    CUtensorMap map_a, map_b;
+    const cuuint32_t ones[2] = {1u, 1u}, box[2] = {kStepK, 128u};
+    const cuuint64_t a_dims[2] = {k, rows}, b_dims[2] = {k, n}, strides[1] = {(cuuint64_t)k * 2u};
+    CUresult r = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a), a_dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS)
+        r = encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(b), b_dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    const uint32_t tiles = ((rows + kTileM - 1u) / kTileM) * ((n + kTileN - 1u) / kTileN);
+    return nvfp4n::launch_on(stream, pdl, gemm_kernel, dim3(tiles < (uint32_t)sms ? tiles : (uint32_t)sms), dim3(kThreads), kSharedBytes, map_a, map_b,
+            static_cast<uint16_t*>(out), rows, n, k, error);
+}
+
+}  // namespace bf16n

@@ -141,6 +141,26 @@ __global__ void __launch_bounds__(256) finish_kernel(const float* __restrict__ p
     add_and_finish128(partials + at, (size_t)rows * n, splits, svh + (size_t)(task % blocks) * 128, out + at, lane);
 }
 
+// rotated bf16: the product of segment g starts at element rows * start_g with row stride width_g (start_g, width_g from the
+// exclusive segment ends) -> out bf16 [rows][n] = bf16(svh * H128(rotated)). A warp per (row, 128 columns).
+//   grid ceil(rows * (n / 128) / 8), block 256.
+__global__ void __launch_bounds__(256) finish_bf16_kernel(const uint16_t* __restrict__ rotated, const int* __restrict__ ends, int s,
+        const uint16_t* __restrict__ svh, uint16_t* __restrict__ out, int rows, int n) {
+    const int lane = threadIdx.x & 31, blocks = n >> 7;
+    const long long task = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    eb::pdl_launch_dependents();
+    eb::pdl_wait();
+    if (task >= (long long)rows * blocks) return;
+    const int row = (int)(task / blocks), block_start = (int)(task % blocks) * 128;
+    int g = 0;
+    while (g + 1 < s && block_start >= ends[g]) ++g;
+    const int start = g == 0 ? 0 : ends[g - 1], width = ends[g] - start;
+    const uint2 bits = *reinterpret_cast<const uint2*>(rotated + (size_t)rows * start + (size_t)row * width + (block_start - start) + 4 * lane);
+    float v[4] = {eb::bf16_bits_to_float(bits.x & 0xFFFFu), eb::bf16_bits_to_float(bits.x >> 16), eb::bf16_bits_to_float(bits.y & 0xFFFFu),
+            eb::bf16_bits_to_float(bits.y >> 16)};
+    finish128(v, svh + block_start, out + (size_t)row * n + block_start, lane);
+}
+
 // Payload -> BF16 rotated weight [n][k] (row-major weights of a BF16 linear). A warp per tile, a lane per eight positions.
 //   grid ceil((k / 16) * (n / 16) / 8), block 256.
 __global__ void __launch_bounds__(256) decode_bf16_kernel(const uint16_t* __restrict__ words, uint16_t* __restrict__ out,

@@ -178,6 +178,27 @@ EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_trellis_bf16(const void* input, co
         const void* svh, const void* segment_ends, void* output, void* scratch, uint64_t scratch_bytes, uint32_t rows,
         uint32_t in_features, uint32_t out_features, uint32_t tile_words, uint32_t segments, uint32_t splits);
 
+/* The launches of the reference host's trellis prefill plan (core/.../artifact/format/TrellisFormat.java:560-625: prepass
+ * in the column-order BF16 layout, euhedral_trellis_decode_bf16, its row-exact BF16 linear per segment
+ * (RowExactBf16.java:52-84), euhedral_trellis_epilogue_bf16) as ONE call, the BF16 linear on tcgen05. Arguments as
+ * euhedral_b200_linear_trellis_bf16, plus host_segment_ends: the same `segments` exclusive ends in HOST memory (the
+ * reference's prefill takes them too: they size the per-segment launches). scratch: 256-byte aligned device memory of at
+ * least euhedral_b200_prefill_trellis_scratch_bytes(rows, in_features, out_features, segments) bytes (the plan's three
+ * regions: rotated activations, the decoded BF16 weight, the products). Any row count. -5 for shapes the trellis format
+ * does not have (in/out features not multiples of 128, tile_words), -1 for misaligned pointers or segment ends that are
+ * not ascending multiples of 128 ending at out_features, -2 for too little scratch. */
+EUHEDRAL_CUDA_EXPORT uint64_t euhedral_b200_prefill_trellis_scratch_bytes(uint32_t rows, uint32_t in_features, uint32_t out_features,
+        uint32_t segments);
+EUHEDRAL_CUDA_EXPORT int euhedral_b200_prefill_trellis_bf16(const void* input, const void* words, const void* suh, const void* svh,
+        const void* segment_ends, const int32_t* host_segment_ends, void* output, void* scratch, uint64_t scratch_bytes, uint32_t rows,
+        uint32_t in_features, uint32_t out_features, uint32_t tile_words, uint32_t segments);
+/* The BF16 linear of that plan on its own: output[r][j] = bf16(sum over k of input[r][k] * weights[j][k]) for BF16 weights
+ * [out_features][in_features] (the operands of the reference's RowExactBf16.linear). Every output is one FP32 sum over K in K
+ * order on the tensor cores, whatever the row count. in_features % 64 == 0, out_features % 128 == 0 (else -5); pointers
+ * 16-byte aligned (else -1). */
+EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_bf16(const void* input, const void* weights, void* output, uint32_t rows,
+        uint32_t in_features, uint32_t out_features);
+
 /* No counterpart in the reference's C ABI (its trellis encoder lives in the quantization module's own CUDA image,
  * quantization/src/main/resources/cuda/trellis.cu:34-399). The converter's tile encoder: `count` tiles of 256 FP32 weights
  * in kernel element order -> the 16-bit trellis state of every position (uint16 [count][256]), by the format's tail-biting

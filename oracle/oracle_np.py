@@ -512,6 +512,25 @@ def trellis_linear_kernel_model(x_bits, payload, suh, svh, ends) -> np.ndarray:
     return hadamard128(z) * np.asarray(svh, dtype=np.float16).astype(np.float32)
 
 
+def trellis_prefill_model(x_bits, payload, suh, svh, ends) -> np.ndarray:
+    """Model of the reference's trellis prefill plan (core/.../artifact/format/TrellisFormat.java:560-625): BF16 column-order
+    prepass, the payload decoded to BF16 (native/src/trellis/decode.cuh), a BF16 linear per segment rounded to BF16 (the
+    sum over K in float64 stands in for the tensor core's FP32 accumulation), then bf16(f32(svh) * H128_f32(.))
+    (native/src/trellis/epilogue.cuh:46-61). float32 [rows, n] of the BF16 results."""
+    x = bf16_to_f32(x_bits)
+    kt, nt, w = payload.shape
+    k, n = kt * 16, nt * 16
+    scales = np.asarray(suh, dtype=np.float16).reshape(len(ends), k).astype(np.float32)
+    act = round_bf16(hadamard128((x[None, :, :] * scales[:, None, :]).astype(np.float32))).astype(np.float64)   # [s, rows, k]
+    q = round_bf16(trellis_rotated_weight(payload).astype(np.float32)).astype(np.float64)                        # [k, n]
+    seg = np.repeat(trellis_segment_of_block(ends, n), 128)
+    z = np.zeros((x.shape[0], n), dtype=np.float32)
+    for g in range(len(ends)):
+        cols = seg == g
+        z[:, cols] = round_bf16((act[g] @ q[:, cols]).astype(np.float32))
+    return round_bf16(hadamard128(z) * np.asarray(svh, dtype=np.float16).astype(np.float32))
+
+
 def trellis_fragment_order(values) -> np.ndarray:
     """The reference prepass's FP16 layout: in each group of 16, elements 2q, 2q+1, 2q+8, 2q+9 contiguous at 4q
     (native/src/trellis/prepass.cuh:70-79; native/tests/trellis_reference.py:115-122)."""

@@ -1,0 +1,124 @@
+"""Trellis prefill (rotate, decode to BF16, tcgen05 BF16 linear per segment, rotate back) as one call, and the BF16 epilogue
+table entry, against the oracle's model of the reference's prefill plan."""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from euhedral_b200.gpu import KernelArguments
+from oracle import oracle_np as O
+from tests.gpu_util import Device, random_x
+from tests.test_trellis_gpu import random_object
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    device = Device()
+    yield device
+    assert device.gpu.take_device_error() == 0
+    device.release()
+
+
+def prefill(dev, x_bits, payload, suh, svh, ends):
+    lib = dev.gpu.lib
+    rows, (kt, nt, w) = x_bits.shape[0], payload.shape
+    k, n, s = kt * 16, nt * 16, len(ends)
+    need = lib.euhedral_b200_prefill_trellis_scratch_bytes(rows, k, n, s)
+    host_ends = (C.c_int32 * s)(*ends)
+    d = [dev.put(x_bits), dev.put(payload.astype("<i2")), dev.put(suh.astype("<f2")), dev.put(svh.astype("<f2")),
+         dev.put(np.array(ends, dtype="<i4"))]
+    d_y, d_s = dev.empty(rows * n * 2), dev.empty(need, fill=0x5A)
+    with dev.submit():
+        status = lib.euhedral_b200_prefill_trellis_bf16(*[t.data_ptr() for t in d], C.cast(host_ends, C.c_void_p), d_y.data_ptr(), d_s.data_ptr(),
+                                                        need, rows, k, n, w, s)
+    assert status == 0, status
+    return dev.get(d_y, np.uint16, (rows, n))
+
+
+def close(got_bits, expect):
+    """Both sides are rounded to BF16: where the kernel's FP32 sums and the model's float64 sums fall on different sides of a
+    rounding boundary they differ by one BF16 step (2^-7 of the value at most); beyond that, the reference's own bound."""
+    got = O.bf16_to_f32(got_bits).astype(np.float64)
+    rms = float(np.sqrt(np.mean(expect.astype(np.float64) ** 2)))
+    return np.all(np.abs(got - expect) <= 2.0 ** -7 * np.abs(expect) + 0.004 * rms)
+
+
+@pytest.mark.parametrize("rows,k,n,w,ends", [
+    (128, 256, 256, 48, [256]),              # one tile
+    (300, 384, 640, 48, [640]),              # a ragged last row tile, a half-wide last column tile, six K steps
+    (77, 256, 896, 40, [256, 384, 896]),     # three segments of 256, 128 and 512 columns, half-step rate
+    (1100, 1024, 512, 64, [256, 512]),       # more tiles than one wave of a few SMs' worth, two segments
+])
+def test_against_the_plan_model(dev, rows, k, n, w, ends):
+    rng = np.random.default_rng(rows + n)
+    payload, suh, svh = random_object(rng, k, n, w, segments=len(ends))
+    x = random_x(rng, rows, k)
+    got = prefill(dev, x, payload, suh, svh, ends)
+    expect = O.trellis_prefill_model(x, payload, suh, svh, ends)
+    assert close(got, expect)
+    # and, more loosely, the unrounded float64 linear (the BF16 roundings of the plan are what separates them)
+    exact = O.trellis_linear_f64(x, payload, suh, svh, ends)
+    rms = float(np.sqrt(np.mean(exact ** 2)))
+    assert np.all(np.abs(O.bf16_to_f32(got).astype(np.float64) - exact) <= 0.02 * np.abs(exact) + 0.02 * rms)
+
+
+def test_rows_do_not_depend_on_their_neighbours(dev):
+    rng = np.random.default_rng(5)
+    k, n, w = 256, 384, 48
+    payload, suh, svh = random_object(rng, k, n, w)
+    x = random_x(rng, 200, k)
+    whole = prefill(dev, x, payload, suh, svh, [n])
+    assert np.array_equal(prefill(dev, x[130:131], payload, suh, svh, [n]), whole[130:131])
+    assert np.array_equal(prefill(dev, x[:9], payload, suh, svh, [n]), whole[:9])
+    assert np.array_equal(prefill(dev, x, payload, suh, svh, [n]), whole)      # and twice the same bits
+
+
+def test_epilogue_bf16_table_entry(dev):
+    rng = np.random.default_rng(6)
+    rows, n, ends = 5, 640, [128, 384, 640]
+    svh = rng.uniform(0.01, 1.0, size=n).astype(np.float16)
+    blocks = [O.bf16_bits(rng.standard_normal((rows, b - a)).astype(np.float32)) for a, b in zip([0] + ends[:-1], ends)]
+    rotated = np.concatenate([b.reshape(-1) for b in blocks])                  # segment g at rows * start_g, row stride width_g
+    d_r, d_e, d_v, d_y = dev.put(rotated), dev.put(np.array(ends, dtype="<i4")), dev.put(svh.view(np.uint16)), dev.empty(rows * n * 2)
+    assert dev.gpu.table_kernel_available("TRELLIS_EPILOGUE_BF16")
+    with dev.submit() as gpu:
+        gpu.launch_table_kernel("TRELLIS_EPILOGUE_BF16", n // 128, rows, 1, 128, 1, 1, 0,
+                                KernelArguments().pointer(d_r.data_ptr()).pointer(d_e.data_ptr()).int32(len(ends)).pointer(d_v.data_ptr())
+                                .pointer(d_y.data_ptr()).int32(rows).int32(n))
+    z = np.concatenate([O.bf16_to_f32(b) for b in blocks], axis=1)
+    expect = O.bf16_bits(O.hadamard128(z) * svh.astype(np.float32))
+    assert np.array_equal(dev.get(d_y, np.uint16, (rows, n)), expect)
+
+
+def test_status_codes(dev):
+    lib = dev.gpu.lib
+    x, t = dev.empty(4096), dev.empty(1 << 20)
+    ends = (C.c_int32 * 1)(256)
+    ok = (x.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), C.cast(ends, C.c_void_p), t.data_ptr(), t.data_ptr())
+    assert lib.euhedral_b200_prefill_trellis_bf16(*ok, 1 << 20, 4, 256, 200, 48, 1) == -5        # out features not a multiple of 128
+    assert lib.euhedral_b200_prefill_trellis_bf16(*ok, 1024, 4, 256, 256, 48, 1) == -2           # scratch too small
+    bad = (C.c_int32 * 1)(128)
+    assert lib.euhedral_b200_prefill_trellis_bf16(*ok[:5], C.cast(bad, C.c_void_p), *ok[6:], 1 << 20, 4, 256, 256, 48, 1) == -1   # ends stop short
+    assert lib.euhedral_b200_prefill_trellis_scratch_bytes(4, 256, 256, 1) == 2048 + 131072 + 2048
+
+
+def test_bf16_linear_alone(dev):
+    """The plan's BF16 linear by itself: FP32 sums of exact products, rounded once."""
+    lib = dev.gpu.lib
+    rng = np.random.default_rng(12)
+    for rows, k, n in ((1, 64, 128), (130, 192, 384), (257, 512, 1152)):
+        a, b = O.bf16_bits(rng.standard_normal((rows, k)).astype(np.float32)), O.bf16_bits(rng.standard_normal((n, k)).astype(np.float32))
+        d_a, d_b, d_y = dev.put(a), dev.put(b), dev.empty(rows * n * 2)
+        with dev.submit():
+            assert lib.euhedral_b200_linear_bf16(d_a.data_ptr(), d_b.data_ptr(), d_y.data_ptr(), rows, k, n) == 0
+        exact = O.bf16_to_f32(a).astype(np.float64) @ O.bf16_to_f32(b).astype(np.float64).T
+        got = dev.get(d_y, np.uint16, (rows, n))
+        same = got == O.bf16_bits(exact.astype(np.float32))
+        assert same.mean() > 0.995                                   # FP32 accumulation against float64: a rounding boundary now and then
+        assert np.all(np.abs(O.bf16_to_f32(got).astype(np.float64) - exact) <= 2.0 ** -8 * np.abs(exact) + 1e-4 * np.abs(exact).max())
+    d = dev.empty(1 << 16)
+    assert lib.euhedral_b200_linear_bf16(d.data_ptr(), d.data_ptr(), d.data_ptr(), 4, 96, 128) == -5
+    assert lib.euhedral_b200_linear_bf16(d.data_ptr() + 2, d.data_ptr(), d.data_ptr(), 4, 64, 128) == -1
