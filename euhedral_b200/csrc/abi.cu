@@ -484,6 +484,19 @@ cudaError_t launch_trellis_rotate(const void* x, const void* suh, void* act, int
             static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(suh), static_cast<uint16_t*>(act), rows, k, s, layout);
 }
 
+cudaError_t launch_trellis_decode_bf16(const void* words, void* out, int k, int n, int w) {
+    const uint64_t tiles = (uint64_t)(k / 16) * (uint64_t)(n / 16);
+    switch (w) {
+#define EB_CASE(W) \
+        case W: \
+            return launch(kOrdered, trellis::decode_bf16_kernel<W>, dim3((unsigned)((tiles + 7) / 8)), dim3(256), 0, 1u, \
+                    static_cast<const uint16_t*>(words), static_cast<uint16_t*>(out), k, n);
+        EB_TRELLIS_WIDTHS(EB_CASE)
+#undef EB_CASE
+        default: return cudaErrorInvalidValue;
+    }
+}
+
 cudaError_t launch_trellis_finish_bf16(const void* rotated, const void* ends, int s, const void* svh, void* out, int rows, int n) {
     const long long tasks = (long long)rows * (n / 128);
     return launch(kOverlappable, trellis::finish_bf16_kernel, dim3((unsigned)((tasks + 7) / 8)), dim3(256), 0, 1u,
@@ -871,11 +884,11 @@ int euhedral_cuda_linear_launch(int32_t kernel, uint32_t grid_x, uint32_t grid_y
         }
         case 5: {   // decode_bf16(words, out, k, n, w)
             const int k = (int)a[2], n = (int)a[3], w = (int)a[4];
-            if (k <= 0 || k % 16 != 0 || n <= 0 || n % 16 != 0 || !trellis_width_valid(w)) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+            if (k <= 0 || k % 16 != 0 || n <= 0 || n % 16 != 0 || !trellis_width_valid(w) || ((a[0] | a[1]) & 3u) != 0)
+                return EUHEDRAL_CUDA_INVALID_ARGUMENT;   // 4-byte loads of the ring words, 4-byte stores of value pairs
             const uint64_t tiles = (uint64_t)(k / 16) * (uint64_t)(n / 16);
             if (tiles > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
-            return finish(launch(kOrdered, trellis::decode_bf16_kernel, dim3((unsigned)((tiles + 7) / 8)), dim3(256), 0, 1u,
-                    reinterpret_cast<const uint16_t*>(a[0]), reinterpret_cast<uint16_t*>(a[1]), k, n, w));
+            return finish(launch_trellis_decode_bf16(reinterpret_cast<const void*>(a[0]), reinterpret_cast<void*>(a[1]), k, n, w));
         }
         case 6: {   // epilogue_bf16(rotated, ends, s, svh, out, rows, n)
             const int s = (int)a[2], rows = (int)a[5], n = (int)a[6];
@@ -1006,16 +1019,16 @@ int euhedral_b200_linear_trellis_bf16(const void* input, const void* words, cons
             segment_ends, output, rows, in_features, out_features, tile_words, segments, splits);
 }
 
-// ---- trellis prefill: rotate, decode to BF16, tcgen05 BF16 GEMM per segment, rotate back --------------------------------------
-// The launches of the reference host's prefill plan (core/.../artifact/format/TrellisFormat.java:560-625) as one call: its
-// prepass in the column-order BF16 layout, its decode of the payload to a BF16 matrix, a BF16 linear per segment on the
-// segment's rotated activations, and its BF16 epilogue, over the same scratch layout: activations [s][rows][k], the decoded
-// weight [n][k], the products (segment g at rows * start_g, row stride width_g), each region rounded up to 256 bytes.
+// ---- trellis prefill: rotate, decode to BF16, tcgen05 BF16 GEMM per segment with the rotate-back in its epilogue ----------------
+// The reference host's prefill plan (core/.../artifact/format/TrellisFormat.java:560-625) as one call: its prepass in the
+// column-order BF16 layout, its decode of the payload to a BF16 matrix, and a BF16 linear per segment on the segment's
+// rotated activations whose epilogue does what the plan's BF16 epilogue launch does (round the sums to BF16, rotate each
+// 128-column block, scale by svh), so the products never travel through memory. Scratch: activations [s][rows][k] and the
+// decoded weight [n][k], each rounded up to 256 bytes.
 static uint64_t align_scratch(uint64_t bytes) { return (bytes + 255u) & ~(uint64_t)255u; }
 
 uint64_t euhedral_b200_prefill_trellis_scratch_bytes(uint32_t rows, uint32_t in_features, uint32_t out_features, uint32_t segments) {
-    return align_scratch((uint64_t)segments * rows * in_features * 2u) + align_scratch((uint64_t)out_features * in_features * 2u)
-            + align_scratch((uint64_t)rows * out_features * 2u);
+    return align_scratch((uint64_t)segments * rows * in_features * 2u) + align_scratch((uint64_t)out_features * in_features * 2u);
 }
 
 // out[r][j] = bf16(sum_k input[r][k] * weights[j][k]): the BF16 linear of the prefill plan on its own (the reference's
@@ -1027,20 +1040,21 @@ int euhedral_b200_linear_bf16(const void* input, const void* weights, void* outp
     DeviceState* state = nullptr;
     const int status = bind(&state);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
-    return finish(bf16n::linear(input, weights, output, rows, in_features, out_features, state->sms, t_stream, t_pdl != 0 && t_stream != nullptr,
-            state->error_word));
+    return finish(bf16n::linear(input, weights, output, nullptr, out_features, rows, in_features, out_features, state->sms, t_stream,
+            t_pdl != 0 && t_stream != nullptr, state->error_word));
 }
 
 int euhedral_b200_prefill_trellis_bf16(const void* input, const void* words, const void* suh, const void* svh, const void* segment_ends,
         const int32_t* host_segment_ends, void* output, void* scratch, uint64_t scratch_bytes, uint32_t rows, uint32_t in_features,
         uint32_t out_features, uint32_t tile_words, uint32_t segments) {
     const uint32_t k = in_features, n = out_features;
-    if (input == nullptr || words == nullptr || suh == nullptr || svh == nullptr || segment_ends == nullptr || host_segment_ends == nullptr
-            || output == nullptr || scratch == nullptr || rows == 0 || rows > 0x7FFFFFFFu / 256u || segments == 0 || segments > 64u)
+    (void)segment_ends;   // the device copy of the ends: the fused epilogue needs the host copy only
+    if (input == nullptr || words == nullptr || suh == nullptr || svh == nullptr || host_segment_ends == nullptr || output == nullptr
+            || scratch == nullptr || rows == 0 || rows > 0x7FFFFFFFu / 256u || segments == 0 || segments > 64u)
         return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     if (k == 0 || k % 128u != 0 || n == 0 || n % 128u != 0 || !trellis_width_valid((int)tile_words)) return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
-    if ((((uintptr_t)input | (uintptr_t)suh | (uintptr_t)svh | (uintptr_t)output) & 7u) != 0 || ((uintptr_t)words & 15u) != 0
-            || ((uintptr_t)scratch & 255u) != 0 || ((uintptr_t)segment_ends & 3u) != 0)
+    if ((((uintptr_t)input | (uintptr_t)suh) & 7u) != 0 || (((uintptr_t)words | (uintptr_t)svh | (uintptr_t)output) & 15u) != 0
+            || ((uintptr_t)scratch & 255u) != 0)
         return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     int32_t start = 0;
     for (uint32_t g = 0; g < segments; ++g) {   // ascending multiples of 128, the last one n (TrellisLayout.validateSegments)
@@ -1050,25 +1064,21 @@ int euhedral_b200_prefill_trellis_bf16(const void* input, const void* words, con
     }
     if ((uint32_t)start != n) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     if (euhedral_b200_prefill_trellis_scratch_bytes(rows, k, n, segments) > scratch_bytes) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
+    if ((uint64_t)(k / 16u) * (n / 16u) > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
     DeviceState* state = nullptr;
     const int status = bind(&state);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     uint8_t* activations = static_cast<uint8_t*>(scratch);
     uint8_t* decoded = activations + align_scratch((uint64_t)segments * rows * k * 2u);
-    uint8_t* rotated = decoded + align_scratch((uint64_t)n * k * 2u);
     cudaError_t e = launch_trellis_rotate(input, suh, activations, (int)rows, (int)k, (int)segments, 1);
-    const uint64_t tiles = (uint64_t)(k / 16u) * (n / 16u);
-    if (e == cudaSuccess)
-        e = launch(kOrdered, trellis::decode_bf16_kernel, dim3((unsigned)((tiles + 7u) / 8u)), dim3(256), 0, 1u, static_cast<const uint16_t*>(words),
-                reinterpret_cast<uint16_t*>(decoded), (int)k, (int)n, (int)tile_words);
+    if (e == cudaSuccess) e = launch_trellis_decode_bf16(words, decoded, (int)k, (int)n, (int)tile_words);
     start = 0;
     for (uint32_t g = 0; g < segments && e == cudaSuccess; ++g) {
         const uint32_t width = (uint32_t)(host_segment_ends[g] - start);
-        e = bf16n::linear(activations + (uint64_t)g * rows * k * 2u, decoded + (uint64_t)start * k * 2u, rotated + (uint64_t)rows * (uint32_t)start * 2u,
-                rows, k, width, state->sms, t_stream, false, state->error_word);
+        e = bf16n::linear(activations + (uint64_t)g * rows * k * 2u, decoded + (uint64_t)start * k * 2u, static_cast<uint16_t*>(output) + start,
+                static_cast<const uint16_t*>(svh) + start, n, rows, k, width, state->sms, t_stream, false, state->error_word);
         start = host_segment_ends[g];
     }
-    if (e == cudaSuccess) e = launch_trellis_finish_bf16(rotated, segment_ends, (int)segments, svh, output, (int)rows, (int)n);
     return finish(e);
 }
 

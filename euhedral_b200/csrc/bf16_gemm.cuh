@@ -11,6 +11,7 @@
 #pragma once
 
 #include "nvfp4_native.cuh"
+#include "trellis_codebook.cuh"
 
 namespace bf16n {
 
@@ -37,10 +38,49 @@ __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint6
             : "memory");
 }
 
+// A thread's 128 consecutive sums of one row (one 128-column block of the trellis output) -> the block's final values:
+// the sums rounded to BF16 as the plan's BF16 linear stores them, the block's Hadamard transform in FP32 by the format's
+// butterflies (stage h pairs i with i + h; every a + b and a - b as trellis::hadamard128_warp forms them, so the bits are
+// those of the plan's epilogue kernel), times 1/sqrt(128), times svh, BF16. No other thread is needed.
+__device__ __forceinline__ void store_rotated(uint32_t (&r)[4][32], uint16_t* __restrict__ out, const uint16_t* __restrict__ svh) {
+    float* v = reinterpret_cast<float*>(&r[0][0]);
+#pragma unroll
+    for (int i = 0; i < 128; ++i) v[i] = eb::bf16_bits_to_float(eb::float_to_bf16_bits(v[i]));
+#pragma unroll
+    for (int h = 1; h < 128; h <<= 1) {
+#pragma unroll
+        for (int p = 0; p < 64; ++p) {
+            const int i = (p / h) * 2 * h + (p % h);
+            const float a = v[i], b = v[i + h];
+            v[i] = __fadd_rn(a, b);
+            v[i + h] = __fsub_rn(a, b);
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+        const uint4 scales = *reinterpret_cast<const uint4*>(svh + 8 * c);
+        const uint32_t sw[4] = {scales.x, scales.y, scales.z, scales.w};
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t bits[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float scale = __half2float(__ushort_as_half((unsigned short)(sw[i] >> (16 * e))));
+                bits[e] = eb::float_to_bf16_bits(__fmul_rn(scale, __fmul_rn(v[8 * c + 2 * i + e], trellis::kInvSqrt128)));
+            }
+            packed[i] = bits[0] | bits[1] << 16;
+        }
+        *reinterpret_cast<uint4*>(out + 8 * c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+}
+
 //   grid: min(tiles, SMs), block nvfp4n::kThreads, dynamic shared kSharedBytes. map_a: [rows][k] BF16, box 64 x 128;
-//   map_b: [n][k] BF16, box 64 x 128 (a B tile is two boxes). n a multiple of 128.
+//   map_b: [n][k] BF16, box 64 x 128 (a B tile is two boxes). n a multiple of 128. out: row stride `stride` elements.
+//   svh null: out[r][j] = bf16(sum); else out[r][j] = the trellis output of the 128-column block j belongs to (svh [n]).
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-        uint16_t* __restrict__ out, uint32_t rows, uint32_t n, uint32_t k, uint32_t* __restrict__ error) {
+        uint16_t* __restrict__ out, const uint16_t* __restrict__ svh, uint32_t stride, uint32_t rows, uint32_t n, uint32_t k,
+        uint32_t* __restrict__ error) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -142,7 +182,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             nvfp4n::tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) eb::mbar_arrive(acc_empty);
-            nvfp4n::store_block(r, out, tm * kTileM + quarter * 32u + lane, rows, n, tn * kTileN + half * 128u, 1.0f, false);
+            const uint32_t row = tm * kTileM + quarter * 32u + lane, col = tn * kTileN + half * 128u;
+            if (svh == nullptr) {
+                nvfp4n::store_block(r, out, row, rows, n, col, 1.0f, false);   // row stride n
+            } else if (row < rows && col < n) {
+                store_rotated(r, out + (uint64_t)row * stride + col, svh + col);
+            }
         }
     }
     nvfp4n::tcgen05_fence_before();
@@ -154,9 +199,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
 inline cudaError_t initialize() { return cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSharedBytes); }
 
-// a [rows][k], b [n][k] -> out [rows][n], all BF16 in device memory, 16-byte aligned; k % 64 == 0, n % 128 == 0.
-inline cudaError_t linear(const void* a, const void* b, void* out, uint32_t rows, uint32_t k, uint32_t n, int sms, cudaStream_t stream, bool pdl,
-        uint32_t* error) {
+// a [rows][k], b [n][k] -> out [rows][n] at row stride `stride`, all BF16 in device memory, 16-byte aligned; k % 64 == 0,
+// n % 128 == 0. svh (FP16 [n], may be null): finish the trellis output in the epilogue instead of storing the sums.
+inline cudaError_t linear(const void* a, const void* b, void* out, const void* svh, uint32_t stride, uint32_t rows, uint32_t k, uint32_t n, int sms,
+        cudaStream_t stream, bool pdl, uint32_t* error) {
     const eb::EncodeTiled encode = eb::encoder();
     if (encode == nullptr) return cudaErrorNotSupported;
     CUtensorMap map_a, map_b;
@@ -170,7 +216,7 @@ inline cudaError_t linear(const void* a, const void* b, void* out, uint32_t rows
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     const uint32_t tiles = ((rows + kTileM - 1u) / kTileM) * ((n + kTileN - 1u) / kTileN);
     return nvfp4n::launch_on(stream, pdl, gemm_kernel, dim3(tiles < (uint32_t)sms ? tiles : (uint32_t)sms), dim3(kThreads), kSharedBytes, map_a, map_b,
-            static_cast<uint16_t*>(out), rows, n, k, error);
+            static_cast<uint16_t*>(out), static_cast<const uint16_t*>(svh), stride, rows, n, k, error);
 }
 
 }  // namespace bf16n

@@ -161,22 +161,6 @@ __global__ void __launch_bounds__(256) finish_bf16_kernel(const uint16_t* __rest
     finish128(v, svh + block_start, out + (size_t)row * n + block_start, lane);
 }
 
-// Payload -> BF16 rotated weight [n][k] (row-major weights of a BF16 linear). A warp per tile, a lane per eight positions.
-//   grid ceil((k / 16) * (n / 16) / 8), block 256.
-__global__ void __launch_bounds__(256) decode_bf16_kernel(const uint16_t* __restrict__ words, uint16_t* __restrict__ out,
-        int k, int n, int w) {
-    const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
-    const long long tile = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (tile >= (long long)(k >> 4) * (n >> 4)) return;
-    const int ti = (int)(tile / (n >> 4)), tj = (int)(tile % (n >> 4));
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float value = __half2float(__ushort_as_half(value_bits(window_of_tile(words + (size_t)tile * w, w, 8 * lane + j))));
-        const int kk = 2 * q + 8 * ((j >> 1) & 1) + (j & 1), nn = g + 8 * (j >> 2);
-        out[(size_t)(tj * 16 + nn) * k + ti * 16 + kk] = eb::float_to_bf16_bits(value);
-    }
-}
-
 // ---- the linear ------------------------------------------------------------------------------------------------------
 
 // The 16 k of a tile enter the FP16 MMA in this order of its k index c: k = 2 (c % 4) + (c % 8) / 4 + 8 (c / 8). It is
@@ -250,6 +234,42 @@ struct Lane {
         }
     }
 };
+
+// Payload -> BF16 rotated weight [n][k] (row-major weights of a BF16 linear). A warp per tile; a lane reads its ring words
+// from global memory, takes its eight states as the linear does and stores its four pairs of neighbouring k.
+//   grid ceil((k / 16) * (n / 16) / 8), block 256.
+template <int W>
+__global__ void __launch_bounds__(256) decode_bf16_kernel(const uint16_t* __restrict__ words, uint16_t* __restrict__ out, int k, int n) {
+    using L = Lane<W>;
+    const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+    const long long tile = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (tile >= (long long)(k >> 4) * (n >> 4)) return;
+    const int ti = (int)(tile / (n >> 4)), tj = (int)(tile % (n >> 4));
+    L me;
+    me.init(lane);
+    const uint8_t* ring = reinterpret_cast<const uint8_t*>(words + (size_t)tile * W);
+    uint32_t u[L::kWords + 1];
+#pragma unroll
+    for (int i = 0; i < L::kWords; ++i) u[i] = __ldg(reinterpret_cast<const uint32_t*>(ring + me.at[i]));
+    u[L::kWords] = 0u;
+#pragma unroll
+    for (int i = 0; i < L::kWords; ++i) u[i] = __funnelshift_l(u[i + 1], u[i], me.shift);
+    const uint32_t state[8] = {L::template state<0>(u), L::template state<1>(u), L::template state<2>(u), L::template state<3>(u),
+            L::template state<4>(u), L::template state<5>(u), L::template state<6>(u), L::template state<7>(u)};
+    uint32_t pair[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t low = eb::float_to_bf16_bits(__half2float(__ushort_as_half(value_bits(state[2 * j]))));
+        const uint32_t high = eb::float_to_bf16_bits(__half2float(__ushort_as_half(value_bits(state[2 * j + 1]))));
+        pair[j] = low | high << 16;
+    }
+    // positions 0..3 are tile row g at k = 2q, 2q+1, 2q+8, 2q+9; positions 4..7 the same k of row g + 8
+    uint16_t* row = out + (size_t)(tj * 16 + g) * k + ti * 16 + 2 * q;
+    *reinterpret_cast<uint32_t*>(row) = pair[0];
+    *reinterpret_cast<uint32_t*>(row + 8) = pair[1];
+    *reinterpret_cast<uint32_t*>(row + (size_t)8 * k) = pair[2];
+    *reinterpret_cast<uint32_t*>(row + (size_t)8 * k + 8) = pair[3];
+}
 
 // What a launch of the linear works on. `activations` (the scratch's fragment-order FP16 [s][rows][k], written by a
 // rotate launch) or, when it is null, x and suh. `flags` null: the partials of a split K are left for a finish launch.

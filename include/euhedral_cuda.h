@@ -178,15 +178,17 @@ EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_trellis_bf16(const void* input, co
         const void* svh, const void* segment_ends, void* output, void* scratch, uint64_t scratch_bytes, uint32_t rows,
         uint32_t in_features, uint32_t out_features, uint32_t tile_words, uint32_t segments, uint32_t splits);
 
-/* The launches of the reference host's trellis prefill plan (core/.../artifact/format/TrellisFormat.java:560-625: prepass
- * in the column-order BF16 layout, euhedral_trellis_decode_bf16, its row-exact BF16 linear per segment
- * (RowExactBf16.java:52-84), euhedral_trellis_epilogue_bf16) as ONE call, the BF16 linear on tcgen05. Arguments as
+/* The reference host's trellis prefill plan (core/.../artifact/format/TrellisFormat.java:560-625: prepass in the
+ * column-order BF16 layout, euhedral_trellis_decode_bf16, its row-exact BF16 linear per segment (RowExactBf16.java:52-84),
+ * euhedral_trellis_epilogue_bf16) as ONE call: the BF16 linear runs on tcgen05 and its epilogue does the plan's last
+ * launch (sums rounded to BF16, each 128-column block rotated, times svh), so the products are never stored. Arguments as
  * euhedral_b200_linear_trellis_bf16, plus host_segment_ends: the same `segments` exclusive ends in HOST memory (the
- * reference's prefill takes them too: they size the per-segment launches). scratch: 256-byte aligned device memory of at
- * least euhedral_b200_prefill_trellis_scratch_bytes(rows, in_features, out_features, segments) bytes (the plan's three
- * regions: rotated activations, the decoded BF16 weight, the products). Any row count. -5 for shapes the trellis format
- * does not have (in/out features not multiples of 128, tile_words), -1 for misaligned pointers or segment ends that are
- * not ascending multiples of 128 ending at out_features, -2 for too little scratch. */
+ * reference's prefill takes them too: they size the per-segment launches; segment_ends, the device copy, is not read).
+ * scratch: 256-byte aligned device memory of at least euhedral_b200_prefill_trellis_scratch_bytes(rows, in_features,
+ * out_features, segments) bytes (rotated activations [segments][rows][in], the decoded BF16 weight [out][in]). Any row
+ * count; every row's bits are independent of the rows beside it. -5 for shapes the trellis format does not have
+ * (in/out features not multiples of 128, tile_words), -1 for misaligned pointers (words, svh, output 16 bytes; input, suh
+ * 8) or segment ends that are not ascending multiples of 128 ending at out_features, -2 for too little scratch. */
 EUHEDRAL_CUDA_EXPORT uint64_t euhedral_b200_prefill_trellis_scratch_bytes(uint32_t rows, uint32_t in_features, uint32_t out_features,
         uint32_t segments);
 EUHEDRAL_CUDA_EXPORT int euhedral_b200_prefill_trellis_bf16(const void* input, const void* words, const void* suh, const void* svh,

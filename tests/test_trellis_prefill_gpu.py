@@ -102,7 +102,7 @@ def test_status_codes(dev):
     assert lib.euhedral_b200_prefill_trellis_bf16(*ok, 1024, 4, 256, 256, 48, 1) == -2           # scratch too small
     bad = (C.c_int32 * 1)(128)
     assert lib.euhedral_b200_prefill_trellis_bf16(*ok[:5], C.cast(bad, C.c_void_p), *ok[6:], 1 << 20, 4, 256, 256, 48, 1) == -1   # ends stop short
-    assert lib.euhedral_b200_prefill_trellis_scratch_bytes(4, 256, 256, 1) == 2048 + 131072 + 2048
+    assert lib.euhedral_b200_prefill_trellis_scratch_bytes(4, 256, 256, 1) == 2048 + 131072
 
 
 def test_bf16_linear_alone(dev):
