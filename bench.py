@@ -553,6 +553,56 @@ def measure_prefill(bench: Bench, rows, steps, warmup):
     return result
 
 
+def measure_trellis_prefill(bench: Bench, rows, steps, warmup):
+    """Trellis prefill of the layer's four fused objects at `rows` tokens through the one-call entry (rotate, decode to BF16,
+    tcgen05 BF16 linear per segment with the rotate-back in its epilogue): TFLOP/s of 2 M N K against the measured BF16
+    peak; and the BF16 linear alone on the decoded weight of the largest object."""
+    torch, gpu, lib = bench.torch, bench.gpu, bench.lib
+    objects = [("query_key_value", (0, 1, 2), 7168, 5120), ("o", (3,), 5120, 5120), ("gate_up", (4, 5), 34816, 5120), ("down", (6,), 5120, 17408)]
+    xs, calls, flops = {}, [], 0
+    need = max(lib.euhedral_b200_prefill_trellis_scratch_bytes(rows, k, n, len(members)) for _, members, n, k in objects)
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+    y = torch.empty((rows, 34816), dtype=torch.int16, device="cuda")
+    keep = []
+    for name, members, n, k in objects:
+        payload, suh, svh, ends = bench.trellis_fused([(i, LAYER[i][1], LAYER[i][2]) for i in members])
+        if k not in xs:
+            xs[k] = torch.randn((rows, k), device="cuda", dtype=torch.bfloat16, generator=torch.Generator(device="cuda").manual_seed(ACTIVATION_SEED)).view(torch.int16)
+        host_ends = (C.c_int32 * len(members))(*ends.tolist())
+        keep.append((payload, suh, svh, ends, host_ends))
+        calls.append((xs[k].data_ptr(), payload.data_ptr(), suh.data_ptr(), svh.data_ptr(), ends.data_ptr(), C.cast(host_ends, C.c_void_p), y.data_ptr(),
+                      scratch.data_ptr(), need, rows, k, n, TRELLIS_WIDTH, len(members)))
+        flops += 2 * rows * n * k
+
+    def body(_):
+        for args in calls:
+            bench.check(lib.euhedral_b200_prefill_trellis_bf16(*args))
+
+    # the BF16 linear alone, on the weight the gate_up call just decoded into the scratch (4096 x 34816 x 5120)
+    decoded = scratch.data_ptr() + ((2 * rows * 5120 * 2 + 255) // 256) * 256
+
+    def linear_alone(_):
+        bench.check(lib.euhedral_b200_linear_bf16(xs[5120].data_ptr(), decoded, y.data_ptr(), rows, 5120, 34816))
+
+    with torch.cuda.stream(bench.stream), bench.submit():
+        seconds = bench.timed(steps, warmup, body)
+        bench.check(lib.euhedral_b200_prefill_trellis_bf16(*calls[2]))
+        linear_seconds = bench.timed(steps, 1, linear_alone)
+    assert gpu.take_device_error() == 0
+    tflops, alone = flops * steps / seconds / 1e12, 2 * rows * 34816 * 5120 * steps / linear_seconds / 1e12
+    peak = bench.peaks["bf16"]
+    result = {"rows": rows, "calls": "query_key_value 7168x5120 (3 segments), o, gate_up 34816x5120 (2 segments), down; 3 bits per weight",
+              "ms_per_layer": seconds / steps * 1e3, "tflops": tflops,
+              "bf16_linear_alone": {"shape": f"{rows} x 34816 x 5120", "ms": linear_seconds / steps * 1e3, "tflops": alone,
+                                    "frac_of_measured_bf16": alone / peak if peak else None},
+              "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak if peak else None,
+                           "peak_kind": f"of {bench.peaks['kind']} (cuBLAS BF16 burst)",
+                           "note": "2 M N K over the whole call: the rotate and the decode of the payload to BF16 run before the GEMM and count as time, not as FLOP"}}
+    del keep, calls, scratch, y, xs
+    torch.cuda.empty_cache()
+    return result
+
+
 class Sweep:
     """The 64-layer NVFP4 sweep, N-sharded: every rank holds rows [g N / G, (g + 1) N / G) of every matrix of every layer."""
 
@@ -825,6 +875,11 @@ def run_ours(args):
                     extra["config1_nvfp4_gate_m1"] = dict(zip(("us", "gbs", "frac_of_hbm_peak"), extra["per_shape"]["rows"][key]))
                 except Exception as error:
                     extra["per_shape"] = {"error": repr(error)}
+            if "trellis" in wanted and "prefill" in wanted:
+                try:
+                    extra["trellis_prefill"] = measure_trellis_prefill(bench, 4096, 4, 2)
+                except Exception as error:
+                    extra["trellis_prefill"] = {"error": repr(error)}
             if "prefill" in wanted:
                 extra["nvfp4_prefill"] = {}
                 for rows in (4096, 32768, 131072):
