@@ -78,7 +78,7 @@ __device__ __forceinline__ void store_rotated(uint32_t (&r)[4][32], uint16_t* __
 //   grid: min(tiles, SMs), block nvfp4n::kThreads, dynamic shared kSharedBytes. map_a: [rows][k] BF16, box 64 x 128;
 //   map_b: [n][k] BF16, box 64 x 128 (a B tile is two boxes). n a multiple of 128. out: row stride `stride` elements.
 //   svh null: out[r][j] = bf16(sum); else out[r][j] = the trellis output of the 128-column block j belongs to (svh [n]).
-__global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+__global__ void __launch_bounds__(kThreads, 1) bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         uint16_t* __restrict__ out, const uint16_t* __restrict__ svh, uint32_t stride, uint32_t rows, uint32_t n, uint32_t k,
         uint32_t* __restrict__ error) {
     extern __shared__ uint8_t smem_raw[];
@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     }
 }
 
-inline cudaError_t initialize() { return cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSharedBytes); }
+inline cudaError_t initialize() { return cudaFuncSetAttribute(bf16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSharedBytes); }
 
 // a [rows][k], b [n][k] -> out [rows][n] at row stride `stride`, all BF16 in device memory, 16-byte aligned; k % 64 == 0,
 // n % 128 == 0. svh (FP16 [n], may be null): finish the trellis output in the epilogue instead of storing the sums.
@@ -215,7 +215,7 @@ inline cudaError_t linear(const void* a, const void* b, void* out, const void* s
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     const uint32_t tiles = ((rows + kTileM - 1u) / kTileM) * ((n + kTileN - 1u) / kTileN);
-    return nvfp4n::launch_on(stream, pdl, gemm_kernel, dim3(tiles < (uint32_t)sms ? tiles : (uint32_t)sms), dim3(kThreads), kSharedBytes, map_a, map_b,
+    return nvfp4n::launch_on(stream, pdl, bf16_gemm_kernel, dim3(tiles < (uint32_t)sms ? tiles : (uint32_t)sms), dim3(kThreads), kSharedBytes, map_a, map_b,
             static_cast<uint16_t*>(out), static_cast<const uint16_t*>(svh), stride, rows, n, k, error);
 }
 
