@@ -603,6 +603,38 @@ def measure_trellis_prefill(bench: Bench, rows, steps, warmup):
     return result
 
 
+def measure_q3_prefill(bench: Bench, rows, steps, warmup):
+    """Q3 prefill of the layer at `rows` tokens through the reference's Q3 MX entry points (two exact BF16 terms per weight
+    written to the scratch, one tcgen05 BF16 GEMM over both): TFLOP/s of 2 M N K; the GEMM issues twice that."""
+    torch, gpu, lib = bench.torch, bench.gpu, bench.lib
+    tensors, flops, xs = [], 0, {}
+    for index, (name, n, k) in enumerate(LAYER):
+        blob = bench.weight("q3", index, n, k)[0]
+        if k not in xs:
+            xs[k] = torch.randn((rows, k), device="cuda", dtype=torch.bfloat16, generator=torch.Generator(device="cuda").manual_seed(ACTIVATION_SEED)).view(torch.int16)
+        tensors.append((blob, xs[k], n, k))
+        flops += 2 * rows * n * k
+    need = max(lib.euhedral_cuda_q3_mx_scratch_bytes(rows, k, n) for _, n, k in LAYER)
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+    y = torch.empty((rows, max(n for _, n, _ in LAYER)), dtype=torch.int16, device="cuda")
+
+    def body(_):
+        for blob, x, n, k in tensors:
+            bench.check(lib.euhedral_cuda_linear_q3_mx_bf16(x.data_ptr(), blob.data_ptr(), y.data_ptr(), scratch.data_ptr(), rows, k, n, blob.numel(), need))
+
+    with torch.cuda.stream(bench.stream), bench.submit():
+        seconds = bench.timed(steps, warmup, body)
+    assert gpu.take_device_error() == 0
+    tflops, peak = flops * steps / seconds / 1e12, bench.peaks["bf16"]
+    result = {"rows": rows, "ms_per_layer": seconds / steps * 1e3, "tflops": tflops, "issued_tflops": 2 * tflops,
+              "roofline": {"bound": "tensor", "achieved": 2 * tflops, "algorithmic": tflops, "peak": peak, "unit": "TFLOP/s",
+                           "frac": 2 * tflops / peak if peak else None, "peak_kind": f"of {bench.peaks['kind']} (cuBLAS BF16 burst)",
+                           "note": "achieved = issued FLOP (two BF16 terms per weight); algorithmic = 2 M N K; the expansion of the codes runs before the GEMM and counts as time"}}
+    del tensors, xs, y, scratch
+    torch.cuda.empty_cache()
+    return result
+
+
 class Sweep:
     """The 64-layer NVFP4 sweep, N-sharded: every rank holds rows [g N / G, (g + 1) N / G) of every matrix of every layer."""
 
@@ -875,6 +907,11 @@ def run_ours(args):
                     extra["config1_nvfp4_gate_m1"] = dict(zip(("us", "gbs", "frac_of_hbm_peak"), extra["per_shape"]["rows"][key]))
                 except Exception as error:
                     extra["per_shape"] = {"error": repr(error)}
+            if "prefill" in wanted:
+                try:
+                    extra["q3_prefill"] = measure_q3_prefill(bench, 4096, 4, 2)
+                except Exception as error:
+                    extra["q3_prefill"] = {"error": repr(error)}
             if "trellis" in wanted and "prefill" in wanted:
                 try:
                     extra["trellis_prefill"] = measure_trellis_prefill(bench, 4096, 4, 2)

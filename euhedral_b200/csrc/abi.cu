@@ -723,6 +723,61 @@ int euhedral_cuda_linear_q3_reference_bf16(const void* input, const void* weight
     return q3_reference(state, input, weights, output, rows, in_features, out_features);
 }
 
+// ---- Q3 prefill --------------------------------------------------------------------------------------------------------------
+// The reference's entry points for Q3 linears of 9 rows and more (native/include/euhedral_cuda.h:173-197; its kernels run
+// block-scaled FP8 MMAs of sm_12x on two-term E4M3 activations). Here the operands are exact the other way round: every
+// weight code * f32(scale) is written to the scratch as two BF16 terms whose sum is the weight exactly
+// (bf16n::q3_terms_kernel), and one tcgen05 BF16 GEMM over K' = 2 K multiplies both planes with the unchanged BF16
+// activations, FP32 sums in tensor memory: sums of exact products, rounded once to BF16, as the reference's route gives.
+int euhedral_cuda_q3_mx_available(void) {
+    DeviceState* state = nullptr;
+    return bind(&state) == EUHEDRAL_CUDA_SUCCESS ? 1 : 0;
+}
+
+uint64_t euhedral_cuda_q3_mx_scratch_bytes(uint32_t rows, uint32_t width, uint32_t weight_rows) {
+    (void)rows;   // the activations are read where they are
+    return ((uint64_t)weight_rows * width * 4u + 255u) & ~(uint64_t)255u;
+}
+
+// No K split on this route: the summation order is the K order whatever the tensor's rows.
+void euhedral_cuda_q3_mx_select_split_rows(uint32_t weight_rows) { (void)weight_rows; }
+
+static int q3_prefill(const void* input, const void* weights, void* output, void* scratch, uint32_t rows, uint32_t in_features,
+        uint32_t weight_rows, uint64_t weights_byte_size, uint64_t scratch_byte_size, bool paired) {
+    int status = q3_validate(input, weights, output, rows, in_features, weight_rows, weights_byte_size);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    if (scratch == nullptr) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    // the reference declines the route under exact numerics and row-exact execution (the bits are not the decode kernels')
+    if (in_features % 128u != 0 || weight_rows % (paired ? 256u : 128u) != 0 || g_exact.load() || t_row_exact
+            || (((uintptr_t)input | (uintptr_t)weights | (uintptr_t)output) & 15u) != 0 || ((uintptr_t)scratch & 255u) != 0)
+        return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
+    if (euhedral_cuda_q3_mx_scratch_bytes(rows, in_features, weight_rows) > scratch_byte_size) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
+    DeviceState* state = nullptr;
+    status = bind(&state);
+    if (status != EUHEDRAL_CUDA_SUCCESS) return status;
+    const q3::Geometry geo(weight_rows, in_features);
+    const uint64_t groups = (uint64_t)weight_rows * (in_features / 64u);
+    cudaError_t e = launch(kOrdered, bf16n::q3_terms_kernel, dim3((unsigned)((groups + 255u) / 256u)), dim3(256), 0, 1u,
+            static_cast<const uint8_t*>(weights), geo.scale_offset, static_cast<uint16_t*>(scratch), weight_rows, in_features);
+    if (e == cudaSuccess)
+        e = bf16n::linear(input, scratch, output, nullptr, 0, rows, 2u * in_features, weight_rows, state->sms, t_stream, false, state->error_word,
+                in_features, paired);
+    return finish(e);
+}
+
+int euhedral_cuda_linear_q3_mx_bf16(const void* input, const void* weights, void* output, void* scratch, uint32_t rows, uint32_t in_features,
+        uint32_t out_features, uint64_t weights_byte_size, uint64_t scratch_byte_size) {
+    return q3_prefill(input, weights, output, scratch, rows, in_features, out_features, weights_byte_size, scratch_byte_size, false);
+}
+
+// The paired gate/up region: `outputs` weight rows (gate first), outputs / 2 SwiGLU values per row; gate and up rounded to
+// BF16 before the SwiGLU (the reference's paired kernel, docs/kernels/PREFILL_MX.md). An output tile is 128 columns wide.
+int euhedral_cuda_q3_mx_gate_up_swiglu_bf16(const void* input, const void* weights, void* output, void* scratch, uint32_t rows, uint32_t width,
+        uint32_t outputs, uint64_t weight_bytes, uint64_t scratch_byte_size) {
+    if (outputs % 2u != 0) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
+    return q3_prefill(input, weights, output, scratch, rows, width, outputs, weight_bytes, scratch_byte_size, true);
+}
+
 // ---- NVFP4 ------------------------------------------------------------------------------------------------------------
 
 int euhedral_cuda_linear_nvfp4_bf16(const void* input, const void* weights, void* output, uint32_t rows, uint32_t in_features,

@@ -78,9 +78,10 @@ __device__ __forceinline__ void store_rotated(uint32_t (&r)[4][32], uint16_t* __
 //   grid: min(tiles, SMs), block nvfp4n::kThreads, dynamic shared kSharedBytes. map_a: [rows][k] BF16, box 64 x 128;
 //   map_b: [n][k] BF16, box 64 x 128 (a B tile is two boxes). n a multiple of 128. out: row stride `stride` elements.
 //   svh null: out[r][j] = bf16(sum); else out[r][j] = the trellis output of the 128-column block j belongs to (svh [n]).
+//   a_period: K of map_a (k is a multiple of it). pair_tiles: see below (svh must be null then).
 __global__ void __launch_bounds__(kThreads, 1) bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
         uint16_t* __restrict__ out, const uint16_t* __restrict__ svh, uint32_t stride, uint32_t rows, uint32_t n, uint32_t k,
-        uint32_t* __restrict__ error) {
+        uint32_t a_period, uint32_t pair_tiles, uint32_t* __restrict__ error) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -89,7 +90,10 @@ __global__ void __launch_bounds__(kThreads, 1) bf16_gemm_kernel(const __grid_con
     uint64_t* acc_empty = acc_full + 1;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 1);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const nvfp4n::TileWalk walk(rows, n, kTileN);
+    // pair_tiles != 0: the gate/up region. `n` is the output width (half of the weight rows); an output tile of 128 columns
+    // takes the 128 gate rows at its own place and the 128 up rows pair_tiles * 128 further down as the halves of its B tile.
+    const bool paired = pair_tiles != 0u;
+    const nvfp4n::TileWalk walk(rows, n, paired ? 128u : kTileN);
     const uint32_t k_steps = k / kStepK;
 
     if (threadIdx.x == 0) {
@@ -129,9 +133,11 @@ __global__ void __launch_bounds__(kThreads, 1) bf16_gemm_kernel(const __grid_con
                     uint8_t* stage = smem + s * kStageBytes;
                     eb::mbar_arrive_expect_tx(&full[s], kStageBytes);
                     // rows past the end of a matrix read as zeros (and the transaction still counts the whole box)
-                    eb::tma_load_2d(stage, &map_a, (int)(ks * kStepK), (int)(tm * kTileM), &full[s]);
-                    eb::tma_load_2d(stage + kATile, &map_b, (int)(ks * kStepK), (int)(tn * kTileN), &full[s]);
-                    eb::tma_load_2d(stage + kATile + kBTile / 2u, &map_b, (int)(ks * kStepK), (int)(tn * kTileN + 128u), &full[s]);
+                    // the activations' K index wraps at a_period (the weight's K holds several terms of the same activations)
+                    eb::tma_load_2d(stage, &map_a, (int)((ks * kStepK) % a_period), (int)(tm * kTileM), &full[s]);
+                    const uint32_t low = paired ? tn : 2u * tn, high = paired ? pair_tiles + tn : 2u * tn + 1u;
+                    eb::tma_load_2d(stage + kATile, &map_b, (int)(ks * kStepK), (int)(low * 128u), &full[s]);
+                    eb::tma_load_2d(stage + kATile + kBTile / 2u, &map_b, (int)(ks * kStepK), (int)(high * 128u), &full[s]);
                 }
             }
         }
@@ -175,16 +181,20 @@ __global__ void __launch_bounds__(kThreads, 1) bf16_gemm_kernel(const __grid_con
             }
             nvfp4n::tcgen05_fence_after();
             uint32_t r[4][32];
-            const uint32_t from = tmem + ((quarter * 32u) << 16) + half * 128u;
-#pragma unroll
-            for (uint32_t cb = 0; cb < 4u; ++cb) nvfp4n::tmem_load_32(r[cb], from + cb * 32u);
+            // plain: 128 consecutive columns; paired: 64 gate columns (r[0], r[1]) and the 64 up columns that match them (r[2], r[3])
+            const uint32_t from = tmem + ((quarter * 32u) << 16) + (paired ? half * 64u : half * 128u);
+            const uint32_t other = paired ? from + 128u : from + 64u;
+            nvfp4n::tmem_load_32(r[0], from);
+            nvfp4n::tmem_load_32(r[1], from + 32u);
+            nvfp4n::tmem_load_32(r[2], other);
+            nvfp4n::tmem_load_32(r[3], other + 32u);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             nvfp4n::tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) eb::mbar_arrive(acc_empty);
-            const uint32_t row = tm * kTileM + quarter * 32u + lane, col = tn * kTileN + half * 128u;
+            const uint32_t row = tm * kTileM + quarter * 32u + lane, col = paired ? tn * 128u + half * 64u : tn * kTileN + half * 128u;
             if (svh == nullptr) {
-                nvfp4n::store_block(r, out, row, rows, n, col, 1.0f, false);   // row stride n
+                nvfp4n::store_block(r, out, row, rows, n, col, 1.0f, paired);   // row stride n
             } else if (row < rows && col < n) {
                 store_rotated(r, out + (uint64_t)row * stride + col, svh + col);
             }
@@ -197,26 +207,68 @@ __global__ void __launch_bounds__(kThreads, 1) bf16_gemm_kernel(const __grid_con
     }
 }
 
+// Q3G64_F16S tensor -> two BF16 planes side by side along K, [n][2 k]: columns [0, k) hold hi = bf16(code * scale), columns
+// [k, 2 k) lo = code * scale - hi. code * f32(scale) has at most 14 significant bits, hi keeps 8 and the rest fits BF16:
+// hi + lo is the weight exactly, and both products with a BF16 activation are exact in FP32. A thread per group of 64.
+//   grid ceil(n * (k / 64) / 256), block 256. k a multiple of 128.
+__global__ void __launch_bounds__(256) q3_terms_kernel(const uint8_t* __restrict__ w, uint64_t scale_offset, uint16_t* __restrict__ out,
+        uint32_t n, uint32_t k) {
+    const uint32_t groups = k / 64u;
+    const uint64_t index = (uint64_t)blockIdx.x * 256u + threadIdx.x;
+    if (index >= (uint64_t)n * groups) return;
+    const uint32_t row = (uint32_t)(index / groups), group = (uint32_t)(index % groups);
+    const uint2* packed = reinterpret_cast<const uint2*>(w + index * 24u);
+    const uint2 p0 = packed[0], p1 = packed[1], p2 = packed[2];
+    const uint32_t words[7] = {p0.x, p0.y, p1.x, p1.y, p2.x, p2.y, 0u};
+    const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(w + scale_offset + index * 2u)));
+    uint16_t* hi = out + (uint64_t)row * 2u * k + (uint64_t)group * 64u;
+    uint16_t* lo = hi + k;
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+        uint32_t high[4], low[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t hb[2], lb[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int bit = 3 * (8 * v + 2 * i + e);
+                const uint32_t field = __funnelshift_r(words[bit >> 5], words[(bit >> 5) + 1], bit & 31) & 7u;
+                const float value = __fmul_rn((float)((int)field - (field >= 4u ? 8 : 0)), scale);
+                hb[e] = eb::float_to_bf16_bits(value);
+                lb[e] = eb::float_to_bf16_bits(__fsub_rn(value, eb::bf16_bits_to_float(hb[e])));
+            }
+            high[i] = hb[0] | hb[1] << 16;
+            low[i] = lb[0] | lb[1] << 16;
+        }
+        *reinterpret_cast<uint4*>(hi + 8 * v) = make_uint4(high[0], high[1], high[2], high[3]);
+        *reinterpret_cast<uint4*>(lo + 8 * v) = make_uint4(low[0], low[1], low[2], low[3]);
+    }
+}
+
 inline cudaError_t initialize() { return cudaFuncSetAttribute(bf16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSharedBytes); }
 
 // a [rows][k], b [n][k] -> out [rows][n] at row stride `stride`, all BF16 in device memory, 16-byte aligned; k % 64 == 0,
 // n % 128 == 0. svh (FP16 [n], may be null): finish the trellis output in the epilogue instead of storing the sums.
+// a_k: K of a (k = terms x a_k: b's K holds `terms` planes that all multiply the same activations). paired: b is a gate/up
+// object of n rows (gate first) and out is [rows][n / 2] SwiGLU values.
 inline cudaError_t linear(const void* a, const void* b, void* out, const void* svh, uint32_t stride, uint32_t rows, uint32_t k, uint32_t n, int sms,
-        cudaStream_t stream, bool pdl, uint32_t* error) {
+        cudaStream_t stream, bool pdl, uint32_t* error, uint32_t a_k = 0, bool paired = false) {
+    if (a_k == 0) a_k = k;
     const eb::EncodeTiled encode = eb::encoder();
     if (encode == nullptr) return cudaErrorNotSupported;
     CUtensorMap map_a, map_b;
     const cuuint32_t ones[2] = {1u, 1u}, box[2] = {kStepK, 128u};
-    const cuuint64_t a_dims[2] = {k, rows}, b_dims[2] = {k, n}, strides[1] = {(cuuint64_t)k * 2u};
-    CUresult r = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a), a_dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    const cuuint64_t a_dims[2] = {a_k, rows}, b_dims[2] = {k, n}, strides[1] = {(cuuint64_t)k * 2u}, a_strides[1] = {(cuuint64_t)a_k * 2u};
+    CUresult r = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a), a_dims, a_strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r == CUDA_SUCCESS)
         r = encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(b), b_dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-    const uint32_t tiles = ((rows + kTileM - 1u) / kTileM) * ((n + kTileN - 1u) / kTileN);
+    const uint32_t pair_tiles = paired ? n / 256u : 0u, width = paired ? n / 2u : n;
+    const uint32_t tiles = ((rows + kTileM - 1u) / kTileM) * (paired ? pair_tiles : (n + kTileN - 1u) / kTileN);
     return nvfp4n::launch_on(stream, pdl, bf16_gemm_kernel, dim3(tiles < (uint32_t)sms ? tiles : (uint32_t)sms), dim3(kThreads), kSharedBytes, map_a, map_b,
-            static_cast<uint16_t*>(out), static_cast<const uint16_t*>(svh), stride, rows, n, k, error);
+            static_cast<uint16_t*>(out), static_cast<const uint16_t*>(svh), stride, rows, width, k, a_k, pair_tiles, error);
 }
 
 }  // namespace bf16n

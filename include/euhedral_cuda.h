@@ -178,6 +178,26 @@ EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_trellis_bf16(const void* input, co
         const void* svh, const void* segment_ends, void* output, void* scratch, uint64_t scratch_bytes, uint32_t rows,
         uint32_t in_features, uint32_t out_features, uint32_t tile_words, uint32_t segments, uint32_t splits);
 
+/* Q3 linears of 9 rows and more (reference: native/include/euhedral_cuda.h:173-197, the MXFP8 route of sm_12x). Same
+ * names, arguments and statuses; what runs is this build's own: the weights code * f32(scale) are written to `scratch`
+ * as two BF16 terms whose sum is the weight exactly, and one tcgen05 BF16 GEMM multiplies both planes with the unchanged
+ * BF16 activations (FP32 sums of exact products, rounded once). scratch: 256-byte aligned,
+ * euhedral_cuda_q3_mx_scratch_bytes(rows, width, weight_rows) bytes = 4 bytes per weight (larger than the reference's,
+ * which holds activation planes). -5 (nothing ran) when in_features or the weight rows are not multiples of 128 (256 for
+ * the paired region), under exact numerics or row-exact execution, or for operands not aligned to 16 bytes (scratch:
+ * 256); -3 when weights_byte_size is not the Q3G64_F16S size of the shape; -2 for too little scratch.
+ * euhedral_cuda_q3_mx_select_split_rows is accepted and has no effect: K is never split, so a chunk of a tensor's output
+ * rows gives the whole tensor's bits anyway. */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_q3_mx_available(void);
+EUHEDRAL_CUDA_EXPORT uint64_t euhedral_cuda_q3_mx_scratch_bytes(uint32_t rows, uint32_t width, uint32_t weight_rows);
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_q3_mx_bf16(const void* input, const void* weights, void* output, void* scratch,
+        uint32_t rows, uint32_t in_features, uint32_t out_features, uint64_t weights_byte_size, uint64_t scratch_byte_size);
+EUHEDRAL_CUDA_EXPORT void euhedral_cuda_q3_mx_select_split_rows(uint32_t weight_rows);
+/* The paired gate/up region: `outputs` weight rows (gate first), outputs / 2 SwiGLU values per row, gate and up rounded
+ * to BF16 before the SwiGLU. outputs / 2 a multiple of 128, else -5; odd outputs: -1. */
+EUHEDRAL_CUDA_EXPORT int euhedral_cuda_q3_mx_gate_up_swiglu_bf16(const void* input, const void* weights, void* output, void* scratch,
+        uint32_t rows, uint32_t width, uint32_t outputs, uint64_t weight_bytes, uint64_t scratch_byte_size);
+
 /* The reference host's trellis prefill plan (core/.../artifact/format/TrellisFormat.java:560-625: prepass in the
  * column-order BF16 layout, euhedral_trellis_decode_bf16, its row-exact BF16 linear per segment (RowExactBf16.java:52-84),
  * euhedral_trellis_epilogue_bf16) as ONE call: the BF16 linear runs on tcgen05 and its epilogue does the plan's last
