@@ -7,7 +7,8 @@
 // The engine is the NVFP4 prefill kernel's (nvfp4_native.cuh) without scales: a persistent CTA per SM walks 128 x 256
 // output tiles; warp 0 requests the stages by TMA (64 K of the 128 activation rows and of the 256 weight rows: 48 KB,
 // 128-byte swizzle, four stages), one thread of warp 1 issues four K = 16 MMAs per stage and commits the stage back, eight
-// epilogue warps drain the 128 x 256 accumulator into registers, hand it back and round and store. Every wait is bounded.
+// epilogue warps drain a 128 x 256 accumulator into registers, hand it back and round and store, while the MMAs of the next
+// tile fill the other accumulator (two of 256 columns: all of tensor memory). Every wait is bounded.
 #pragma once
 
 #include "nvfp4_native.cuh"
@@ -86,9 +87,9 @@ __global__ void __launch_bounds__(kThreads, 1) bf16_gemm_kernel(const __grid_con
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
     uint64_t* empty = full + kStages;
-    uint64_t* acc_full = empty + kStages;
-    uint64_t* acc_empty = acc_full + 1;
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    uint64_t* acc_full = empty + kStages;    // two accumulators of 256 columns: the MMAs of a tile run while the tile before is drained
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     // pair_tiles != 0: the gate/up region. `n` is the output width (half of the weight rows); an output tile of 128 columns
     // takes the 128 gate rows at its own place and the 128 up rows pair_tiles * 128 further down as the halves of its B tile.
@@ -101,8 +102,10 @@ __global__ void __launch_bounds__(kThreads, 1) bf16_gemm_kernel(const __grid_con
             eb::mbar_init(&full[s], 1);
             eb::mbar_init(&empty[s], 1);
         }
-        eb::mbar_init(acc_full, 1);
-        eb::mbar_init(acc_empty, 8);
+        for (uint32_t b = 0; b < 2u; ++b) {
+            eb::mbar_init(&acc_full[b], 1);
+            eb::mbar_init(&acc_empty[b], 8);
+        }
         eb::mbar_fence_init();
     }
     if (warp == 1) {
@@ -146,11 +149,13 @@ __global__ void __launch_bounds__(kThreads, 1) bf16_gemm_kernel(const __grid_con
             uint32_t step = 0, local = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < walk.total && ok; tile += gridDim.x, ++local) {
-                if (local > 0 && !eb::mbar_wait(acc_empty, (local - 1u) & 1u)) {
+                const uint32_t buffer = local & 1u, use = local >> 1;
+                if (use > 0 && !eb::mbar_wait(&acc_empty[buffer], (use - 1u) & 1u)) {
                     atomicOr(error, kWaitFailed);
                     break;
                 }
                 nvfp4n::tcgen05_fence_after();
+                const uint32_t accumulator = tmem + buffer * kTileN;
                 for (uint32_t ks = 0; ks < k_steps; ++ks, ++step) {
                     const uint32_t s = step % kStages, round = step / kStages;
                     if (!eb::mbar_wait(&full[s], round & 1u)) {
@@ -162,10 +167,10 @@ __global__ void __launch_bounds__(kThreads, 1) bf16_gemm_kernel(const __grid_con
                     const uint8_t* stage = smem + s * kStageBytes;
                     const uint64_t a = nvfp4n::tile_descriptor(stage), b = nvfp4n::tile_descriptor(stage + kATile);
 #pragma unroll
-                    for (uint32_t j = 0; j < 4u; ++j) mma_bf16(tmem, a + 2u * j, b + 2u * j, (uint32_t)((ks | j) != 0u));   // 32 bytes of K further
+                    for (uint32_t j = 0; j < 4u; ++j) mma_bf16(accumulator, a + 2u * j, b + 2u * j, (uint32_t)((ks | j) != 0u));   // 32 bytes of K further
                     nvfp4n::mma_commit(&empty[s]);
                 }
-                if (ok) nvfp4n::mma_commit(acc_full);
+                if (ok) nvfp4n::mma_commit(&acc_full[buffer]);
             }
         }
     } else {
@@ -175,14 +180,15 @@ __global__ void __launch_bounds__(kThreads, 1) bf16_gemm_kernel(const __grid_con
         for (uint32_t tile = blockIdx.x; tile < walk.total; tile += gridDim.x, ++local) {
             uint32_t tm, tn;
             walk.at(tile, &tm, &tn);
-            if (!eb::mbar_wait(acc_full, local & 1u)) {
+            const uint32_t buffer = local & 1u;
+            if (!eb::mbar_wait(&acc_full[buffer], (local >> 1) & 1u)) {
                 if (lane == 0) atomicOr(error, kWaitFailed);
                 break;
             }
             nvfp4n::tcgen05_fence_after();
             uint32_t r[4][32];
             // plain: 128 consecutive columns; paired: 64 gate columns (r[0], r[1]) and the 64 up columns that match them (r[2], r[3])
-            const uint32_t from = tmem + ((quarter * 32u) << 16) + (paired ? half * 64u : half * 128u);
+            const uint32_t from = tmem + ((quarter * 32u) << 16) + buffer * kTileN + (paired ? half * 64u : half * 128u);
             const uint32_t other = paired ? from + 128u : from + 64u;
             nvfp4n::tmem_load_32(r[0], from);
             nvfp4n::tmem_load_32(r[1], from + 32u);
@@ -191,7 +197,7 @@ __global__ void __launch_bounds__(kThreads, 1) bf16_gemm_kernel(const __grid_con
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             nvfp4n::tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) eb::mbar_arrive(acc_empty);
+            if (lane == 0) eb::mbar_arrive(&acc_empty[buffer]);
             const uint32_t row = tm * kTileM + quarter * 32u + lane, col = paired ? tn * 128u + half * 64u : tn * kTileN + half * 128u;
             if (svh == nullptr) {
                 nvfp4n::store_block(r, out, row, rows, n, col, 1.0f, paired);   // row stride n

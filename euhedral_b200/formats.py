@@ -130,7 +130,11 @@ class TrellisFormat:
             return activations
         return activations + splits * split_rows * n * 4
 
-    def scratch_bytes(self, gpu, rows: int, in_features: int, out_features: int, segments: int = 1) -> int:
+    def scratch_bytes(self, gpu, rows: int, in_features: int, out_features: int, segments: int = 1, row_exact: bool = True) -> int:
+        """What a linear of `rows` rows needs: the tensor-core route's activations and partial sums, or - beyond its row
+        limit and not row-exact - the prefill plan's rotated activations and decoded weight."""
+        if not row_exact and rows > self.settings.mma_max_rows:
+            return gpu.lib.euhedral_b200_prefill_trellis_scratch_bytes(rows, in_features, out_features, segments)
         return self.mma_bytes(rows, in_features, out_features, segments)
 
     def row_exact(self, rows: int) -> bool:
@@ -154,7 +158,7 @@ class TrellisFormat:
         elif launch.row_exact or rows <= self.settings.mma_max_rows:
             run.tensor_core(self.settings)
         else:
-            raise NotImplementedError("the trellis BF16 prefill route is not part of this build")
+            run.prefill(launch.segment_ends)
 
 
 @dataclass
@@ -182,6 +186,16 @@ class _TrellisLaunch:
             KernelArguments().pointer(self.launch.input).pointer(self.words).pointer(self.suh).pointer(self.svh)
             .pointer(self.ends).int32(self.segments).pointer(self.launch.output).int32(self.rows).int32(self.k)
             .int32(self.n).int32(self.w))
+
+    def prefill(self, bounds) -> None:
+        """TrellisFormat.Launch.prefill (java:569-625): the plan's launches - prepass in the BF16 column layout, the payload
+        decoded to BF16, a row-exact BF16 linear per segment, the BF16 epilogue - run as one call of the library."""
+        if bounds is None or len(bounds) != self.segments:
+            raise ValueError("a trellis prefill launch needs the host segment ends of its object")
+        layouts.trellis_validate_segments(list(bounds), self.n)
+        self._require_scratch(self.gpu.lib.euhedral_b200_prefill_trellis_scratch_bytes(self.rows, self.k, self.n, self.segments))
+        self.gpu.prefill_trellis_bf16(self.launch.input, self.words, self.suh, self.svh, self.ends, list(bounds), self.launch.output,
+                                      self.launch.scratch, self.launch.scratch_bytes, self.rows, self.k, self.n, self.w)
 
     def prepass(self, activations: int, layout: int) -> None:
         self.gpu.launch_table_kernel(

@@ -120,10 +120,38 @@ class CudaGpuMemory:
     # ---- linears --------------------------------------------------------------------------------------------------------
     def linear_q3_bf16(self, input: int, weights: int, output: int, rows: int, in_features: int, out_features: int,
                        weight_bytes: int) -> None:
-        """CudaGpuMemory.linearQ3Bf16: more than 8 rows belong to the block-scaled FP8 prefill route, which this build
-        does not carry; they run as groups of 8 on the decode kernel."""
+        """CudaGpuMemory.linearQ3Bf16 (java:1695-1728): more than 8 rows try the prefill route (`invokeQ3Mx`); when it
+        declines - row-exact execution, exact numerics, a shape that is not a multiple of 128 - the decode entry runs
+        the rows as groups of 8."""
+        if rows > Q3_DECODE_MAX_ROWS and self.linear_q3_mx_bf16(input, weights, output, rows, in_features, out_features, weight_bytes):
+            return
         self._check("Q3 linear", self.lib.euhedral_cuda_linear_q3_bf16(input, weights, output, rows, in_features,
                                                                        out_features, weight_bytes))
+
+    def linear_q3_mx_bf16(self, input, weights, output, rows, in_features, out_features, weight_bytes) -> bool:
+        """CudaGpuMemory.invokeQ3Mx: the Q3 prefill entry over the shared scratch. False when the route declined."""
+        if self._row_exact or self._exact or self.lib.euhedral_cuda_q3_mx_available() != 1:
+            return False
+        scratch = self.native_scratch(self.lib.euhedral_cuda_q3_mx_scratch_bytes(rows, in_features, out_features))
+        status = self.lib.euhedral_cuda_linear_q3_mx_bf16(input, weights, output, scratch, rows, in_features, out_features, weight_bytes,
+                                                          self._native_scratch_bytes)
+        if status == library.ROUTE_UNAVAILABLE:
+            return False
+        self._check("Q3 prefill linear", status)
+        return True
+
+    def q3_mx_gate_up_swiglu_bf16(self, input, weights, output, rows, width, outputs, weight_bytes) -> bool:
+        """The paired gate/up region of the Q3 prefill (CudaGpuMemory.q3MxGateUpSwigluBf16): `weights` holds `outputs` rows,
+        gate rows first; `output` gets [rows][outputs / 2] SwiGLU values. False when the route declined."""
+        if self._row_exact or self._exact:
+            return False
+        scratch = self.native_scratch(self.lib.euhedral_cuda_q3_mx_scratch_bytes(rows, width, outputs))
+        status = self.lib.euhedral_cuda_q3_mx_gate_up_swiglu_bf16(input, weights, output, scratch, rows, width, outputs, weight_bytes,
+                                                                  self._native_scratch_bytes)
+        if status == library.ROUTE_UNAVAILABLE:
+            return False
+        self._check("Q3 prefill gate/up SwiGLU", status)
+        return True
 
     def linear_q3_reference_bf16(self, input, weights, output, rows, in_features, out_features, weight_bytes) -> None:
         self._check("Q3 reference linear", self.lib.euhedral_cuda_linear_q3_reference_bf16(
@@ -217,6 +245,15 @@ class CudaGpuMemory:
         device's one-wave default."""
         self._check("trellis linear", self.lib.euhedral_b200_linear_trellis_bf16(
             input, words, suh, svh, ends, output, scratch, scratch_bytes, rows, in_features, out_features, tile_words, segments, splits))
+
+    def prefill_trellis_bf16(self, input: int, words: int, suh: int, svh: int, ends: int, host_ends, output: int, scratch: int,
+                             scratch_bytes: int, rows: int, in_features: int, out_features: int, tile_words: int) -> None:
+        """The reference host's trellis prefill plan (TrellisFormat.prefill) as one call; `host_ends` the segment ends as a
+        Python sequence (the plan's `bounds`)."""
+        bounds = (C.c_int32 * len(host_ends))(*host_ends)
+        self._check("trellis prefill", self.lib.euhedral_b200_prefill_trellis_bf16(
+            input, words, suh, svh, ends, C.cast(bounds, C.c_void_p), output, scratch, scratch_bytes, rows, in_features, out_features, tile_words,
+            len(host_ends)))
 
     # ---- the linear kernel table -------------------------------------------------------------------------------------------
     def table_kernel_available(self, kernel: str | int) -> bool:

@@ -107,3 +107,25 @@ def test_statuses(dev):
         assert prefill(dev, x, blob, 128, 128) == -5
     finally:
         lib.euhedral_cuda_select_exact_numerics(previous)
+
+
+def test_operator_routes_more_than_eight_rows_to_the_prefill(dev):
+    """GroupedLinearFormat.linear / CudaGpuMemory.linear_q3_bf16: 9 rows and more take the prefill route, row-exact launches
+    and shapes it declines the decode kernels."""
+    from euhedral_b200.formats import GroupedLinearFormat, LinearLaunch, TensorHandle
+    rng = np.random.default_rng(41)
+    rows, k, n = 24, 256, 256                            # row-exact launches hold up to 32 rows
+    blob, _ = random_tensor(rng, n, k)
+    x = random_x(rng, rows, k)
+    d_x, d_w, d_y = dev.put(x), dev.put(blob), dev.empty(rows * n * 2)
+    launch = LinearLaunch(d_x.data_ptr(), d_y.data_ptr(), [TensorHandle("w", (n, k), d_w.data_ptr(), blob.size)], rows, k, n)
+    with dev.submit() as gpu:
+        GroupedLinearFormat().linear(gpu, launch)
+    routed = dev.get(d_y, np.uint16, (rows, n))
+    assert np.array_equal(routed, prefill(dev, x, blob, n, k))
+    with dev.submit(row_exact=True) as gpu:
+        GroupedLinearFormat().linear(gpu, launch)
+    exact_rows = dev.get(d_y, np.uint16, (rows, n))
+    with dev.submit() as gpu:                       # one row through the decode kernel: what a row-exact launch must equal
+        gpu.linear_q3_bf16(d_x.data_ptr() + 7 * k * 2, d_w.data_ptr(), d_y.data_ptr(), 1, k, n, blob.size)
+    assert np.array_equal(dev.get(d_y, np.uint16, (rows, n))[0], exact_rows[7])

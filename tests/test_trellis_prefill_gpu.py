@@ -122,3 +122,25 @@ def test_bf16_linear_alone(dev):
     d = dev.empty(1 << 16)
     assert lib.euhedral_b200_linear_bf16(d.data_ptr(), d.data_ptr(), d.data_ptr(), 4, 96, 128) == -5
     assert lib.euhedral_b200_linear_bf16(d.data_ptr() + 2, d.data_ptr(), d.data_ptr(), 4, 64, 128) == -1
+
+
+def test_operator_routes_many_rows_to_the_prefill(dev):
+    """TrellisFormat.linear: beyond the tensor-core route's row limit and not row-exact, the operator runs the prefill plan."""
+    from euhedral_b200.formats import LinearLaunch, TensorHandle, TrellisFormat, TrellisSettings
+    rng = np.random.default_rng(31)
+    rows, k, n, w, ends = 600, 256, 384, 48, [128, 384]
+    payload, suh, svh = random_object(rng, k, n, w, segments=2)
+    x = random_x(rng, rows, k)
+    fmt = TrellisFormat(TrellisSettings(target_ctas=148))
+    tensors = [dev.put(payload.astype("<i2")), dev.put(suh.astype("<f2")), dev.put(svh.astype("<f2")), dev.put(np.array(ends, dtype="<i4"))]
+    shapes = [payload.shape, (2, k), (n,), (2,)]
+    handles = [TensorHandle(f"t{i}", tuple(shape), t.data_ptr(), t.numel()) for i, (t, shape) in enumerate(zip(tensors, shapes))]
+    need = fmt.scratch_bytes(dev.gpu, rows, k, n, 2, row_exact=False)
+    assert need == dev.gpu.lib.euhedral_b200_prefill_trellis_scratch_bytes(rows, k, n, 2)
+    d_x, d_y, d_s = dev.put(x), dev.empty(rows * n * 2), dev.empty(need)
+    with dev.submit() as gpu:
+        fmt.linear(gpu, LinearLaunch(d_x.data_ptr(), d_y.data_ptr(), handles, rows, k, n, scratch=d_s.data_ptr(), scratch_bytes=need, segment_ends=ends))
+    assert np.array_equal(dev.get(d_y, np.uint16, (rows, n)), prefill(dev, x, payload, suh, svh, ends))
+    with pytest.raises(ValueError):
+        with dev.submit() as gpu:
+            fmt.linear(gpu, LinearLaunch(d_x.data_ptr(), d_y.data_ptr(), handles, rows, k, n, scratch=d_s.data_ptr(), scratch_bytes=need))
