@@ -480,6 +480,7 @@ cudaError_t launch_trellis_mma(const uint64_t* a, uint32_t* error) {
 
 cudaError_t launch_trellis_rotate(const void* x, const void* suh, void* act, int rows, int k, int s, int layout) {
     const long long tasks = (long long)s * rows * (k / 128);
+    if (tasks > 2147483647ll) return cudaErrorInvalidValue;   // the kernel counts tasks in 32 bits
     return launch(kOverlappable, trellis::rotate_kernel, dim3((unsigned)((tasks + 7) / 8)), dim3(256), 0, 1u,
             static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(suh), static_cast<uint16_t*>(act), rows, k, s, layout);
 }
@@ -489,7 +490,7 @@ cudaError_t launch_trellis_decode_bf16(const void* words, void* out, int k, int 
     switch (w) {
 #define EB_CASE(W) \
         case W: \
-            return launch(kOrdered, trellis::decode_bf16_kernel<W>, dim3((unsigned)((tiles + 7) / 8)), dim3(256), 0, 1u, \
+            return launch(kOrdered, trellis::decode_bf16_kernel<W>, dim3((unsigned)((tiles + 8 * trellis::kBatch - 1) / (8 * trellis::kBatch))), dim3(256), 0, 1u, \
                     static_cast<const uint16_t*>(words), static_cast<uint16_t*>(out), k, n);
         EB_TRELLIS_WIDTHS(EB_CASE)
 #undef EB_CASE

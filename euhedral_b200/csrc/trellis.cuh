@@ -49,6 +49,7 @@ __host__ __device__ inline int chunk_tiles(int groups, int live) {
     const int fit = (int)((act_bytes(groups) / (uint32_t)live - 32u) / 32u) & ~7;
     return fit < kChunkLimit ? fit : kChunkLimit;
 }
+constexpr int kBatch = 4;                             // tiles a warp of the BF16 decode takes side by side
 constexpr uint32_t kWaitFailed = 4u;                  // error bit: a stage did not arrive (or was never freed)
 
 // ---- pieces shared by the one-kernel linear and the table entries -------------------------------------------------------
@@ -107,12 +108,12 @@ __device__ __forceinline__ void add_and_finish128(const float* __restrict__ part
 //   grid ceil(s * rows * (k / 128) / 8), block 256.
 __global__ void __launch_bounds__(256) rotate_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ suh,
         uint16_t* __restrict__ out, int rows, int k, int s, int layout) {
-    const int lane = threadIdx.x & 31, blocks = k >> 7;
-    const long long task = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const uint32_t blocks = (uint32_t)k >> 7, task = blockIdx.x * 8u + (threadIdx.x >> 5);   // the launch holds fewer than 2^31 tasks
     eb::pdl_launch_dependents();
     eb::pdl_wait();
-    if (task >= (long long)s * rows * blocks) return;
-    const int block = (int)(task % blocks), row = (int)((task / blocks) % rows), seg = (int)(task / ((long long)blocks * rows));
+    if (task >= (uint32_t)s * (uint32_t)rows * blocks) return;
+    const uint32_t block = task % blocks, above = task / blocks, row = above % (uint32_t)rows, seg = above / (uint32_t)rows;
     float v[4];
     rotate128(x + (size_t)row * k + (size_t)block * 128, suh + (size_t)seg * k + (size_t)block * 128, lane, v);
     uint16_t* to = out + ((size_t)seg * rows + row) * k + (size_t)block * 128;
@@ -235,40 +236,50 @@ struct Lane {
     }
 };
 
-// Payload -> BF16 rotated weight [n][k] (row-major weights of a BF16 linear). A warp per tile; a lane reads its ring words
-// from global memory, takes its eight states as the linear does and stores its four pairs of neighbouring k.
-//   grid ceil((k / 16) * (n / 16) / 8), block 256.
+// Payload -> BF16 rotated weight [n][k] (row-major weights of a BF16 linear). A warp takes kBatch tiles side by side: a lane
+// reads its ring words of all of them from global memory first, then takes its eight states of each as the linear does and
+// stores its four pairs of neighbouring k.
+//   grid ceil((k / 16) * (n / 16) / (8 kBatch)), block 256.
 template <int W>
 __global__ void __launch_bounds__(256) decode_bf16_kernel(const uint16_t* __restrict__ words, uint16_t* __restrict__ out, int k, int n) {
     using L = Lane<W>;
     const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
-    const long long tile = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (tile >= (long long)(k >> 4) * (n >> 4)) return;
-    const int ti = (int)(tile / (n >> 4)), tj = (int)(tile % (n >> 4));
+    const uint32_t first = (blockIdx.x * 8u + (threadIdx.x >> 5)) * (uint32_t)kBatch, tiles = (uint32_t)(k >> 4) * (uint32_t)(n >> 4);   // < 2^31
+    if (first >= tiles) return;
     L me;
     me.init(lane);
-    const uint8_t* ring = reinterpret_cast<const uint8_t*>(words + (size_t)tile * W);
-    uint32_t u[L::kWords + 1];
+    uint32_t u[kBatch][L::kWords + 1];
 #pragma unroll
-    for (int i = 0; i < L::kWords; ++i) u[i] = __ldg(reinterpret_cast<const uint32_t*>(ring + me.at[i]));
-    u[L::kWords] = 0u;
+    for (int t = 0; t < kBatch; ++t) {
+        const uint32_t tile = first + t < tiles ? first + t : tiles - 1u;
+        const uint8_t* ring = reinterpret_cast<const uint8_t*>(words + (size_t)tile * W);
 #pragma unroll
-    for (int i = 0; i < L::kWords; ++i) u[i] = __funnelshift_l(u[i + 1], u[i], me.shift);
-    const uint32_t state[8] = {L::template state<0>(u), L::template state<1>(u), L::template state<2>(u), L::template state<3>(u),
-            L::template state<4>(u), L::template state<5>(u), L::template state<6>(u), L::template state<7>(u)};
-    uint32_t pair[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t low = eb::float_to_bf16_bits(__half2float(__ushort_as_half(value_bits(state[2 * j]))));
-        const uint32_t high = eb::float_to_bf16_bits(__half2float(__ushort_as_half(value_bits(state[2 * j + 1]))));
-        pair[j] = low | high << 16;
+        for (int i = 0; i < L::kWords; ++i) u[t][i] = __ldg(reinterpret_cast<const uint32_t*>(ring + me.at[i]));
+        u[t][L::kWords] = 0u;
     }
-    // positions 0..3 are tile row g at k = 2q, 2q+1, 2q+8, 2q+9; positions 4..7 the same k of row g + 8
-    uint16_t* row = out + (size_t)(tj * 16 + g) * k + ti * 16 + 2 * q;
-    *reinterpret_cast<uint32_t*>(row) = pair[0];
-    *reinterpret_cast<uint32_t*>(row + 8) = pair[1];
-    *reinterpret_cast<uint32_t*>(row + (size_t)8 * k) = pair[2];
-    *reinterpret_cast<uint32_t*>(row + (size_t)8 * k + 8) = pair[3];
+#pragma unroll
+    for (int t = 0; t < kBatch; ++t) {
+        const uint32_t tile = first + t;
+        if (tile >= tiles) break;
+        const int ti = (int)(tile / (uint32_t)(n >> 4)), tj = (int)(tile % (uint32_t)(n >> 4));
+#pragma unroll
+        for (int i = 0; i < L::kWords; ++i) u[t][i] = __funnelshift_l(u[t][i + 1], u[t][i], me.shift);
+        const uint32_t state[8] = {L::template state<0>(u[t]), L::template state<1>(u[t]), L::template state<2>(u[t]), L::template state<3>(u[t]),
+                L::template state<4>(u[t]), L::template state<5>(u[t]), L::template state<6>(u[t]), L::template state<7>(u[t])};
+        uint32_t pair[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t low = eb::float_to_bf16_bits(__half2float(__ushort_as_half(value_bits(state[2 * j]))));
+            const uint32_t high = eb::float_to_bf16_bits(__half2float(__ushort_as_half(value_bits(state[2 * j + 1]))));
+            pair[j] = low | high << 16;
+        }
+        // positions 0..3 are tile row g at k = 2q, 2q+1, 2q+8, 2q+9; positions 4..7 the same k of row g + 8
+        uint16_t* row = out + (size_t)(tj * 16 + g) * k + ti * 16 + 2 * q;
+        *reinterpret_cast<uint32_t*>(row) = pair[0];
+        *reinterpret_cast<uint32_t*>(row + 8) = pair[1];
+        *reinterpret_cast<uint32_t*>(row + (size_t)8 * k) = pair[2];
+        *reinterpret_cast<uint32_t*>(row + (size_t)8 * k + 8) = pair[3];
+    }
 }
 
 // What a launch of the linear works on. `activations` (the scratch's fragment-order FP16 [s][rows][k], written by a
