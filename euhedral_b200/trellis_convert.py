@@ -110,12 +110,15 @@ class TrellisConverter:
         need = lib.euhedral_b200_trellis_encode_scratch_bytes(min(count, self.chunk), w)
         if self._scratch is None or self._scratch.numel() < need:
             self._scratch = torch.empty(need, dtype=torch.uint8, device=self.device)
-        # torch's current stream, when it is not the default one (on which the library orders and completes its work itself)
+        # The search runs on torch's current stream so that it is ordered with the tensor work around it. The thread's stream
+        # selection in the library is put back afterwards (a caller may be inside a submission of its own).
         stream = torch.cuda.current_stream(self.device).cuda_stream
-        if stream != 0:
-            status = lib.euhedral_cuda_stream_select(stream)
-            if status != 0:
-                raise RuntimeError(f"stream select failed with status {status}")
+        before = lib.euhedral_cuda_submission_stream() or 0
+        if stream != before:
+            if stream == 0:
+                lib.euhedral_cuda_stream_clear()
+            elif lib.euhedral_cuda_stream_select(stream) != 0:
+                raise RuntimeError("stream select failed")
         try:
             for first in range(0, count, self.chunk):
                 part = min(self.chunk, count - first)
@@ -125,8 +128,11 @@ class TrellisConverter:
                 if status != 0:
                     raise RuntimeError(f"trellis_encode_tiles failed with status {status}")
         finally:
-            if stream != 0:
-                lib.euhedral_cuda_stream_clear()
+            if stream != before:
+                if before == 0:
+                    lib.euhedral_cuda_stream_clear()
+                else:
+                    lib.euhedral_cuda_stream_select(before)
         return values, words
 
     # ---- regularize (TrellisQuantizer.java:242-263) -------------------------------------------------------------------
