@@ -425,20 +425,8 @@ def measure_layer_set(bench: Bench, fmt, rows_list, copies, steps, warmup, e2e=F
                              "calls_per_step": len((layer.grouped if grouped else layer.single)[0]), "launches_per_step": layer.launches(grouped)}
         if e2e:
             seconds = bench.timed(steps, warmup, lambda i: layer.step_e2e(i, True))
-            result["e2e_eager_gbs"] = layer.bytes_per_step * steps / seconds / 1e9
-            # The same end-to-end step - upload, the C-ABI calls, readback - recorded once per resident copy of the weights by
-            # plain stream capture and replayed: how the reference's host runs decode steps (docs/kernels/CUDA_GRAPHS.md).
-            torch.cuda.synchronize()
-            graphs = []
-            for copy in range(layer.copies):
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=bench.stream):
-                    layer.step_e2e(copy, True)
-                graphs.append(graph)
-            seconds = bench.timed(steps, warmup, lambda i: graphs[i % layer.copies].replay())
             result["e2e_gbs"] = layer.bytes_per_step * steps / seconds / 1e9
             result["h2d"], result["d2h"] = layer.h2d, layer.d2h
-            del graphs
     assert bench.gpu.take_device_error() == 0, "a kernel's bounded wait gave up"
     if fmt == "trellis":
         result["weights"] = {"source": "N(0, 0.02^2) seeded, converted by this build's trellis converter (uncalibrated path, 3 bits per weight)",
@@ -900,10 +888,8 @@ def run_ours(args):
                                                            "(dram__bytes_read.sum equals the algorithmic bytes of the launch within 0.1 %)",
                          "peak_kind": f"of {bench.peaks['kind']}", "kernel": "gemv::kernel<q3::Format, 5, true> (every launch of the timed region)"},
             "e2e": {"value": head.get("e2e_gbs"), "unit": "GB/s", "h2d_bytes_per_step": head.get("h2d"), "d2h_bytes_per_step": head.get("d2h"),
-                    "eager": head.get("e2e_eager_gbs"),
                     "note": "per step: the activations uploaded from pinned host memory, the four C-ABI calls, every result read back to pinned "
-                            "memory, on one stream; value = that step recorded by stream capture and replayed (as the reference's host runs decode "
-                            "steps), eager = the same calls issued one by one"},
+                            "memory, all on one stream (the same step recorded by stream capture and replayed measured the same)"},
             "gpu_launches": grouped["launches_per_step"] * args.steps,
         })
         extra["q3_one_call_per_tensor"] = head["single"]
