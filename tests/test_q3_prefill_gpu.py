@@ -129,3 +129,24 @@ def test_operator_routes_more_than_eight_rows_to_the_prefill(dev):
     with dev.submit() as gpu:                       # one row through the decode kernel: what a row-exact launch must equal
         gpu.linear_q3_bf16(d_x.data_ptr() + 7 * k * 2, d_w.data_ptr(), d_y.data_ptr(), 1, k, n, blob.size)
     assert np.array_equal(dev.get(d_y, np.uint16, (rows, n))[0], exact_rows[7])
+
+
+@pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408)])
+def test_model_shapes_at_4096_rows(dev, n, k):
+    """Full size (gate and down at 4096 tokens): sampled rows against the FP32-accumulated C oracle, and against the decode
+    kernel on the same rows - two independent sums of the same exact products, a BF16 step apart at most."""
+    from oracle import oracle_c as OC
+    from tests.test_q3_gpu import run
+    rng = np.random.default_rng(0xE2)
+    weights = (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
+    blob = OC.q3_quantize(weights)
+    x = random_x(np.random.default_rng(0xA9), 4096, k)
+    got = prefill(dev, x, blob, n, k)
+    sample = np.array([0, 1, 127, 128, 2049, 3000, 4094, 4095])
+    expect = OC.q3_linear(x[sample], blob, n, k).astype(np.float64)
+    g = O.bf16_to_f32(got[sample]).astype(np.float64)
+    scale = np.abs(expect).max(axis=1, keepdims=True)
+    assert np.all(np.abs(g - expect) <= 2.0 ** -8 * np.abs(expect) + 2e-5 * scale)
+    decode = O.bf16_to_f32(run(dev, x[sample], blob, n, k)).astype(np.float64)
+    assert np.all(np.abs(g - decode) <= 2.0 ** -7 * np.abs(decode) + 2e-5 * scale)
+    assert (got[sample] == run(dev, x[sample], blob, n, k)).mean() > 0.97

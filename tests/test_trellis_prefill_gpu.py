@@ -144,3 +144,36 @@ def test_operator_routes_many_rows_to_the_prefill(dev):
     with pytest.raises(ValueError):
         with dev.submit() as gpu:
             fmt.linear(gpu, LinearLaunch(d_x.data_ptr(), d_y.data_ptr(), handles, rows, k, n, scratch=d_s.data_ptr(), scratch_bytes=need))
+
+
+def test_gate_up_at_4096_rows_against_the_decode_route(dev):
+    """Full size (the fused gate_up object, two segments, 4096 tokens): sampled rows of the prefill against the one-launch
+    trellis linear on the same rows. The two routes round differently on the way (BF16 against FP16 activations and
+    weights, BF16 products against FP32), so they agree to the reference's bound with the BF16 steps added, not to the bit."""
+    import torch
+    from euhedral_b200 import synthetic
+    lib = dev.gpu.lib
+    rows, k, n, w, ends = 4096, 5120, 34816, 48, [17408, 34816]
+    payload, suh, svh, d_ends = synthetic.trellis_object(n, k, w, 77, 2, device="cuda")
+    x = synthetic.bf16_rows(rows, k, 78, device="cuda")
+    need = lib.euhedral_b200_prefill_trellis_scratch_bytes(rows, k, n, 2)
+    scratch, y = torch.empty(need, dtype=torch.uint8, device="cuda"), torch.empty((rows, n), dtype=torch.int16, device="cuda")
+    host_ends = (C.c_int32 * 2)(*ends)
+    with dev.submit():
+        assert lib.euhedral_b200_prefill_trellis_bf16(x.data_ptr(), payload.data_ptr(), suh.data_ptr(), svh.data_ptr(), d_ends.data_ptr(),
+                                                      C.cast(host_ends, C.c_void_p), y.data_ptr(), scratch.data_ptr(), need, rows, k, n, w, 2) == 0
+    sample = torch.tensor([0, 127, 128, 2500, 4095], device="cuda")
+    xs = x[sample].contiguous()
+    need2 = lib.euhedral_b200_linear_trellis_scratch_bytes(5, k, n, 2, 0)
+    scratch2, y2 = torch.empty(max(need2, 256), dtype=torch.uint8, device="cuda"), torch.empty((5, n), dtype=torch.int16, device="cuda")
+    with dev.submit():
+        assert lib.euhedral_b200_linear_trellis_bf16(xs.data_ptr(), payload.data_ptr(), suh.data_ptr(), svh.data_ptr(), d_ends.data_ptr(), y2.data_ptr(),
+                                                     scratch2.data_ptr(), need2, 5, k, n, w, 2, 0) == 0
+    torch.cuda.synchronize()
+    got = O.bf16_to_f32(y[sample].cpu().numpy().view(np.uint16)).astype(np.float64)
+    decode = O.bf16_to_f32(y2.cpu().numpy().view(np.uint16)).astype(np.float64)
+    rms = float(np.sqrt(np.mean(decode ** 2)))
+    # BF16 weights and activations carry 2^-9 relative rounding each: about 0.002 rms of independent error per output, so the
+    # largest of 174,080 differences sits near five of those; the root mean square is the sharper statement
+    assert np.all(np.abs(got - decode) <= 2.0 ** -6 * np.abs(decode) + 0.02 * rms)
+    assert np.sqrt(np.mean((got - decode) ** 2)) < 0.004 * rms
