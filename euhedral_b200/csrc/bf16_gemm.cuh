@@ -213,6 +213,172 @@ __global__ void __launch_bounds__(kThreads, 1) bf16_gemm_kernel(const __grid_con
     }
 }
 
+// ---- the same GEMM on CTA pairs -----------------------------------------------------------------------------------------
+// Two CTAs of a cluster share an output tile of 256 rows x 256 columns: each holds its own 128 activation rows and HALF of
+// the weight tile (128 weight rows); one thread of the even CTA issues tcgen05.mma.cta_group::2 (M 256, N 256, K 16), which
+// reads both CTAs' shared memory and accumulates each CTA's 128 rows in its own tensor memory. A stage is 32 KB per CTA
+// instead of 48 KB for the same FLOP: a third fewer operand bytes from L2 per FLOP and six stages in flight instead of four.
+// No multicast loads: each CTA requests its own tiles, and both CTAs' loads are counted on the even CTA's stage barrier
+// (the pair form of the TMA load may signal a barrier of the peer), so no thread relays arrivals between the CTAs. Used for calls of kPairRows rows and more.
+constexpr uint32_t kPairStages = 6;
+constexpr uint32_t kPairStageBytes = kATile + 128u * 128u;
+constexpr uint32_t kPairShared = kPairStages * kPairStageBytes + 256u + 1024u;
+constexpr uint32_t kPairInstruction = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
+constexpr uint32_t kPairRows = 512;
+
+// A tiled TMA load of a CTA of a pair whose completion is counted on a barrier of either CTA of the pair (`bar`: a
+// shared::cluster address). No multicast: the box lands in the executing CTA's shared memory only.
+__device__ __forceinline__ void pair_tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                         eb::smem_u32(dst)),
+            "l"(map), "r"(c0), "r"(c1), "r"(bar)
+            : "memory");
+}
+
+__device__ __forceinline__ void pair_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(kPairInstruction), "r"(accumulate)
+            : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) bf16_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+        const __grid_constant__ CUtensorMap map_b, uint16_t* __restrict__ out, const uint16_t* __restrict__ svh, uint32_t stride, uint32_t rows,
+        uint32_t n, uint32_t k, uint32_t a_period, uint32_t pair_tiles, uint32_t* __restrict__ error) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);
+    uint64_t* empty = full + kPairStages;
+    uint64_t* acc_full = empty + kPairStages;
+    uint64_t* acc_empty = acc_full + 1;          // even CTA: both CTAs' epilogue warps have drained the accumulator
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t rank = eb::cluster_rank(), pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    // pair_tiles != 0: the gate/up region; the even CTA's half of the weight tile is the gate rows, the odd CTA's the up rows.
+    const bool paired = pair_tiles != 0u;
+    const uint32_t tiles_m = (rows + 255u) / 256u, tiles_n = paired ? pair_tiles : (n + 255u) / 256u, items = tiles_m * tiles_n;
+    const uint32_t k_steps = k / kStepK;
+    // Panels of kPanel tile columns; inside a panel the row index runs fastest across the panel's columns.
+    auto place = [&](uint32_t item, uint32_t* tm, uint32_t* tn) {
+        const uint32_t per_panel = tiles_m * nvfp4n::kPanel, panel = item / per_panel, rest = item - panel * per_panel;
+        const uint32_t width = min(nvfp4n::kPanel, tiles_n - panel * nvfp4n::kPanel);
+        *tm = rest / width;
+        *tn = panel * nvfp4n::kPanel + rest % width;
+    };
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kPairStages; ++s) {
+            eb::mbar_init(&full[s], 1);
+            eb::mbar_init(&empty[s], 1);
+        }
+        eb::mbar_init(acc_full, 1);
+        eb::mbar_init(acc_empty, 16);
+        eb::mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(eb::smem_u32(tmem_holder)), "r"(kTmemColumns) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    nvfp4n::tcgen05_fence_before();
+    __syncthreads();
+    eb::cluster_sync();   // both CTAs' barriers exist before anything arrives on them from the other CTA
+    nvfp4n::tcgen05_fence_after();
+    const uint32_t tmem = *tmem_holder;
+    eb::pdl_launch_dependents();
+    eb::pdl_wait();   // both operands come from the launches before this one
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t step = 0;
+            bool ok = true;
+            for (uint32_t item = pair; item < items && ok; item += pairs) {
+                uint32_t tm, tn;
+                place(item, &tm, &tn);
+                const uint32_t row_tile = 2u * tm + rank;                      // this CTA's 128 rows
+                const uint32_t weight_tile = paired ? (rank == 0u ? tn : pair_tiles + tn) : 2u * tn + rank;   // its 128 weight rows
+                for (uint32_t ks = 0; ks < k_steps; ++ks, ++step) {
+                    const uint32_t s = step % kPairStages, round = step / kPairStages;
+                    if (round > 0 && !eb::mbar_wait(&empty[s], (round - 1u) & 1u)) {
+                        atomicOr(error, kWaitFailed);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* stage = smem + s * kPairStageBytes;
+                    // both CTAs' boxes are counted on the even CTA's barrier, where the thread that issues the MMAs waits
+                    if (rank == 0u) eb::mbar_arrive_expect_tx(&full[s], 2u * kPairStageBytes);
+                    const uint32_t bar = eb::map_to_rank(eb::smem_u32(&full[s]), 0u);
+                    pair_tma_load_2d(stage, &map_a, (int)((ks * kStepK) % a_period), (int)(row_tile * kTileM), bar);
+                    pair_tma_load_2d(stage + kATile, &map_b, (int)(ks * kStepK), (int)(weight_tile * 128u), bar);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0u) {   // the odd CTA issues nothing: its tiles are read by the even CTA's MMAs
+            uint32_t step = 0, local = 0;
+            bool ok = true;
+            for (uint32_t item = pair; item < items && ok; item += pairs, ++local) {
+                if (local > 0 && !eb::mbar_wait(acc_empty, (local - 1u) & 1u)) {
+                    atomicOr(error, kWaitFailed);
+                    break;
+                }
+                nvfp4n::tcgen05_fence_after();
+                for (uint32_t ks = 0; ks < k_steps; ++ks, ++step) {
+                    const uint32_t s = step % kPairStages, round = step / kPairStages;
+                    if (!eb::mbar_wait(&full[s], round & 1u)) {
+                        atomicOr(error, kWaitFailed);
+                        ok = false;
+                        break;
+                    }
+                    nvfp4n::tcgen05_fence_after();
+                    const uint8_t* stage = smem + s * kPairStageBytes;
+                    const uint64_t a = nvfp4n::tile_descriptor(stage), b = nvfp4n::tile_descriptor(stage + kATile);
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j) pair_mma_bf16(tmem, a + 2u * j, b + 2u * j, (uint32_t)((ks | j) != 0u));
+                    nvfp4n::pair_commit(&empty[s]);
+                }
+                if (ok) nvfp4n::pair_commit(acc_full);
+            }
+        }
+    } else {
+        // Epilogue, in both CTAs, each over its own 128 rows: as in bf16_gemm_kernel.
+        const uint32_t quarter = warp & 3u, half = (warp - 2u) >> 2;
+        uint32_t local = 0;
+        for (uint32_t item = pair; item < items; item += pairs, ++local) {
+            uint32_t tm, tn;
+            place(item, &tm, &tn);
+            if (!eb::mbar_wait(acc_full, local & 1u)) {
+                if (lane == 0) atomicOr(error, kWaitFailed);
+                break;
+            }
+            nvfp4n::tcgen05_fence_after();
+            uint32_t r[4][32];
+            const uint32_t from = tmem + ((quarter * 32u) << 16) + (paired ? half * 64u : half * 128u);
+            const uint32_t other = paired ? from + 128u : from + 64u;
+            nvfp4n::tmem_load_32(r[0], from);
+            nvfp4n::tmem_load_32(r[1], from + 32u);
+            nvfp4n::tmem_load_32(r[2], other);
+            nvfp4n::tmem_load_32(r[3], other + 32u);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            nvfp4n::tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) nvfp4n::arrive_at_rank(acc_empty, 0u);
+            const uint32_t row = (2u * tm + rank) * kTileM + quarter * 32u + lane, col = paired ? tn * 128u + half * 64u : tn * kTileN + half * 128u;
+            if (svh == nullptr) {
+                nvfp4n::store_block(r, out, row, rows, n, col, 1.0f, paired);   // row stride n
+            } else if (row < rows && col < n) {
+                store_rotated(r, out + (uint64_t)row * stride + col, svh + col);
+            }
+        }
+    }
+    nvfp4n::tcgen05_fence_before();
+    __syncthreads();
+    eb::cluster_sync();   // neither CTA leaves while the other may still read its shared memory or arrive on its barriers
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
+    }
+}
+
 // Q3G64_F16S tensor -> two BF16 planes side by side along K, [n][2 k]: columns [0, k) hold hi = bf16(code * scale), columns
 // [k, 2 k) lo = code * scale - hi. code * f32(scale) has at most 14 significant bits, hi keeps 8 and the rest fits BF16:
 // hi + lo is the weight exactly, and both products with a BF16 activation are exact in FP32. A thread per group of 64.
@@ -251,7 +417,13 @@ __global__ void __launch_bounds__(256) q3_terms_kernel(const uint8_t* __restrict
     }
 }
 
-inline cudaError_t initialize() { return cudaFuncSetAttribute(bf16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSharedBytes); }
+inline cudaError_t initialize() {
+    const cudaError_t e = cudaFuncSetAttribute(bf16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSharedBytes);
+    return e != cudaSuccess ? e : cudaFuncSetAttribute(bf16_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairShared);
+}
+
+// Whether calls of kPairRows rows and more run on CTA pairs (process-wide; same bits either way).
+inline bool g_pairs = true;
 
 // a [rows][k], b [n][k] -> out [rows][n] at row stride `stride`, all BF16 in device memory, 16-byte aligned; k % 64 == 0,
 // n % 128 == 0. svh (FP16 [n], may be null): finish the trellis output in the epilogue instead of storing the sums.
@@ -272,6 +444,12 @@ inline cudaError_t linear(const void* a, const void* b, void* out, const void* s
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     const uint32_t pair_tiles = paired ? n / 256u : 0u, width = paired ? n / 2u : n;
+    if (rows >= kPairRows && g_pairs) {
+        const uint32_t items = ((rows + 255u) / 256u) * (paired ? pair_tiles : (n + 255u) / 256u);
+        const uint32_t ctas = 2u * std::max(1u, std::min((uint32_t)sms / 2u, items));
+        return nvfp4n::launch_on(stream, pdl, bf16_gemm_pair_kernel, dim3(ctas), dim3(kThreads), kPairShared, map_a, map_b, static_cast<uint16_t*>(out),
+                static_cast<const uint16_t*>(svh), stride, rows, width, k, a_k, pair_tiles, error);
+    }
     const uint32_t tiles = ((rows + kTileM - 1u) / kTileM) * (paired ? pair_tiles : (n + kTileN - 1u) / kTileN);
     return nvfp4n::launch_on(stream, pdl, bf16_gemm_kernel, dim3(tiles < (uint32_t)sms ? tiles : (uint32_t)sms), dim3(kThreads), kSharedBytes, map_a, map_b,
             static_cast<uint16_t*>(out), static_cast<const uint16_t*>(svh), stride, rows, width, k, a_k, pair_tiles, error);

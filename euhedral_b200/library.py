@@ -69,6 +69,7 @@ SIGNATURES = {
     "euhedral_cuda_linear_q3_mx_bf16": (C.c_int, [_ptr, _ptr, _ptr, _ptr, _u32, _u32, _u32, _u64, _u64]),
     "euhedral_cuda_q3_mx_select_split_rows": (None, [_u32]),
     "euhedral_cuda_q3_mx_gate_up_swiglu_bf16": (C.c_int, [_ptr, _ptr, _ptr, _ptr, _u32, _u32, _u32, _u64, _u64]),
+    "euhedral_b200_select_bf16_pairs": (None, [C.c_int]),
     "euhedral_b200_linear_bf16": (C.c_int, [_ptr, _ptr, _ptr, _u32, _u32, _u32]),
     "euhedral_b200_prefill_trellis_scratch_bytes": (_u64, [_u32, _u32, _u32, _u32]),
     "euhedral_b200_prefill_trellis_bf16": (C.c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _u64, _u32, _u32, _u32, _u32, _u32]),

@@ -198,6 +198,9 @@ EUHEDRAL_CUDA_EXPORT void euhedral_cuda_q3_mx_select_split_rows(uint32_t weight_
 EUHEDRAL_CUDA_EXPORT int euhedral_cuda_q3_mx_gate_up_swiglu_bf16(const void* input, const void* weights, void* output, void* scratch,
         uint32_t rows, uint32_t width, uint32_t outputs, uint64_t weight_bytes, uint64_t scratch_byte_size);
 
+/* Process-wide: whether the BF16 linear behind the trellis and Q3 prefill runs calls of 512 rows and more on CTA pairs
+ * (tcgen05 cta_group::2: a 256 x 256 tile over two SMs). Same bits either way. On by default. */
+EUHEDRAL_CUDA_EXPORT void euhedral_b200_select_bf16_pairs(int enabled);
 /* The reference host's trellis prefill plan (core/.../artifact/format/TrellisFormat.java:560-625: prepass in the
  * column-order BF16 layout, euhedral_trellis_decode_bf16, its row-exact BF16 linear per segment (RowExactBf16.java:52-84),
  * euhedral_trellis_epilogue_bf16) as ONE call: the BF16 linear runs on tcgen05 and its epilogue does the plan's last

@@ -150,3 +150,18 @@ def test_model_shapes_at_4096_rows(dev, n, k):
     decode = O.bf16_to_f32(run(dev, x[sample], blob, n, k)).astype(np.float64)
     assert np.all(np.abs(g - decode) <= 2.0 ** -7 * np.abs(decode) + 2e-5 * scale)
     assert (got[sample] == run(dev, x[sample], blob, n, k)).mean() > 0.97
+
+
+def test_cta_pairs_give_the_single_cta_bits(dev):
+    lib = dev.gpu.lib
+    rng = np.random.default_rng(52)
+    rows, k, n = 700, 384, 768
+    blob, _ = random_tensor(rng, n, k)
+    x = random_x(rng, rows, k)
+    pairs, pairs_swiglu = prefill(dev, x, blob, n, k), prefill(dev, x, blob, n, k, paired=True)
+    lib.euhedral_b200_select_bf16_pairs(0)
+    try:
+        assert np.array_equal(prefill(dev, x, blob, n, k), pairs)
+        assert np.array_equal(prefill(dev, x, blob, n, k, paired=True), pairs_swiglu)
+    finally:
+        lib.euhedral_b200_select_bf16_pairs(1)

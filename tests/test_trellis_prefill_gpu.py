@@ -177,3 +177,20 @@ def test_gate_up_at_4096_rows_against_the_decode_route(dev):
     # largest of 174,080 differences sits near five of those; the root mean square is the sharper statement
     assert np.all(np.abs(got - decode) <= 2.0 ** -6 * np.abs(decode) + 0.02 * rms)
     assert np.sqrt(np.mean((got - decode) ** 2)) < 0.004 * rms
+
+
+def test_cta_pairs_give_the_single_cta_bits(dev):
+    """Calls of 512 rows and more run the BF16 linear on CTA pairs; the K order and the accumulation are the same."""
+    lib = dev.gpu.lib
+    rng = np.random.default_rng(51)
+    for rows, k, n, w, ends in ((600, 256, 640, 48, [640]), (1100, 512, 896, 48, [256, 384, 896])):
+        payload, suh, svh = random_object(rng, k, n, w, segments=len(ends))
+        x = random_x(rng, rows, k)
+        pairs = prefill(dev, x, payload, suh, svh, ends)
+        lib.euhedral_b200_select_bf16_pairs(0)
+        try:
+            single = prefill(dev, x, payload, suh, svh, ends)
+        finally:
+            lib.euhedral_b200_select_bf16_pairs(1)
+        assert np.array_equal(pairs, single)
+        assert close(pairs, O.trellis_prefill_model(x, payload, suh, svh, ends))
