@@ -109,3 +109,72 @@ def test_decode_plans_stay_launchable_and_cut_k_by_k_alone():
                 assert plan["shared_bytes"] <= 227 * 1024
                 cut = (plan["k_slices"], plan["pieces"], plan["piece_chunks"])
                 assert cuts.setdefault((fmt, k), cut) == cut
+
+
+def test_prefill_entry_points_validate_without_a_device():
+    lib = library.load()
+    # sizes are pure arithmetic
+    assert lib.euhedral_cuda_q3_mx_scratch_bytes(4096, 5120, 17408) == 17408 * 5120 * 4
+    assert lib.euhedral_b200_prefill_trellis_scratch_bytes(100, 256, 384, 2) == 2 * 100 * 256 * 2 + 384 * 256 * 2
+    assert lib.euhedral_b200_prefill_trellis_scratch_bytes(3, 128, 128, 1) == 768 + 32768      # each region rounded up to 256 bytes
+    # argument checks come before any device work
+    assert lib.euhedral_cuda_linear_q3_mx_bf16(None, 16, 16, 256, 9, 128, 128, 1, 1 << 20) == library.INVALID_ARGUMENT
+    assert lib.euhedral_cuda_linear_q3_mx_bf16(16, 16, 16, 256, 9, 128, 128, 12345, 1 << 20) == library.FORMAT_MISMATCH
+    size = layouts.q3_byte_size(128, 128)
+    assert lib.euhedral_cuda_linear_q3_mx_bf16(16, 16, 16, 256, 9, 128, 128, size, 16) == library.SIZE_OVERFLOW
+    assert lib.euhedral_cuda_linear_q3_mx_bf16(16, 16, 16, 128, 9, 128, 128, size, 1 << 20) == library.ROUTE_UNAVAILABLE   # scratch not 256-aligned
+    assert lib.euhedral_cuda_q3_mx_gate_up_swiglu_bf16(16, 16, 16, 256, 9, 128, 129, size, 1 << 20) == library.INVALID_ARGUMENT
+    ends = (C.c_int32 * 1)(256)
+    host = C.cast(ends, C.c_void_p)
+    assert lib.euhedral_b200_prefill_trellis_bf16(256, 256, 256, 256, 256, host, 256, 256, 1 << 30, 4, 256, 200, 48, 1) == library.ROUTE_UNAVAILABLE
+    assert lib.euhedral_b200_prefill_trellis_bf16(256, 256, 256, 256, 256, host, 256, 256, 1 << 30, 4, 256, 384, 48, 1) == library.INVALID_ARGUMENT
+    assert lib.euhedral_b200_prefill_trellis_bf16(256, 256, 256, 256, 256, host, 256, 256, 16, 4, 256, 256, 48, 1) == library.SIZE_OVERFLOW
+    assert lib.euhedral_b200_linear_bf16(16, 16, 16, 4, 96, 128) == library.ROUTE_UNAVAILABLE
+    assert lib.euhedral_b200_linear_bf16(16, 16, 18, 4, 64, 128) == library.INVALID_ARGUMENT
+    assert lib.euhedral_b200_trellis_encode_tiles(None, 1, 48, 16, None, None, 16, 1 << 20) == library.INVALID_ARGUMENT
+    assert lib.euhedral_b200_trellis_encode_tiles(16, 1, 72, 16, None, None, 16, 1 << 20) == library.ROUTE_UNAVAILABLE
+    lib.euhedral_cuda_q3_mx_select_split_rows(17408)      # accepted, no effect
+    lib.euhedral_cuda_q3_mx_select_split_rows(0)
+
+
+def test_operators_route_by_row_count(monkeypatch):
+    """CudaGpuMemory.linear_q3_bf16 and TrellisFormat.linear pick the prefill entries by row count (the reference's
+    linearQ3Bf16 and TrellisFormat.linear), shown with a library that only records what was called."""
+    from euhedral_b200 import gpu as G
+    from euhedral_b200.formats import LinearLaunch, TensorHandle, TrellisFormat, TrellisSettings
+    calls = []
+
+    class Recorder:
+        def __getattr__(self, name):
+            def call(*args):
+                calls.append((name, args))
+                if name == "euhedral_cuda_q3_mx_available":
+                    return 1
+                if name.endswith("scratch_bytes"):
+                    return 4096
+                if name == "euhedral_cuda_malloc":
+                    args[1]._obj.value = 0x10000
+                    return 0
+                return 0
+            return call
+
+    memory = G.CudaGpuMemory.__new__(G.CudaGpuMemory)
+    memory.lib, memory._native_scratch, memory._native_scratch_bytes = Recorder(), 0x10000, 1 << 20
+    memory.linear_q3_bf16(16, 32, 48, 8, 256, 256, 99)
+    assert [name for name, _ in calls] == ["euhedral_cuda_linear_q3_bf16"]          # 8 rows: the decode entry
+    calls.clear()
+    memory.linear_q3_bf16(16, 32, 48, 9, 256, 256, 99)
+    assert "euhedral_cuda_linear_q3_mx_bf16" in [name for name, _ in calls] and "euhedral_cuda_linear_q3_bf16" not in [name for name, _ in calls]
+    calls.clear()
+    memory._row_exact = True
+    memory.linear_q3_bf16(16, 32, 48, 9, 256, 256, 99)
+    assert [name for name, _ in calls] == ["euhedral_cuda_linear_q3_bf16"]          # row-exact launches stay on the decode kernels
+    memory._row_exact = False
+    calls.clear()
+    fmt = TrellisFormat(TrellisSettings(target_ctas=148))
+    handles = [TensorHandle("p", (16, 16, 48), 0x1000, 16 * 16 * 96), TensorHandle("suh", (1, 256), 0x2000, 512),
+               TensorHandle("svh", (256,), 0x3000, 512), TensorHandle("ends", (1,), 0x4000, 4)]
+    fmt.linear(memory, LinearLaunch(0x5000, 0x6000, handles, 600, 256, 256, scratch=0x7000, scratch_bytes=1 << 20, segment_ends=[256]))
+    assert [name for name, _ in calls][-1] == "euhedral_b200_prefill_trellis_bf16"
+    with pytest.raises(ValueError):
+        fmt.linear(memory, LinearLaunch(0x5000, 0x6000, handles, 600, 256, 256, scratch=0x7000, scratch_bytes=1 << 20))
