@@ -480,7 +480,14 @@ cudaError_t launch_trellis_mma(const uint64_t* a, uint32_t* error) {
 
 cudaError_t launch_trellis_rotate(const void* x, const void* suh, void* act, int rows, int k, int s, int layout) {
     const long long tasks = (long long)s * rows * (k / 128);
-    if (tasks > 2147483647ll) return cudaErrorInvalidValue;   // the kernel counts tasks in 32 bits
+    if (tasks > 2147483647ll) return cudaErrorInvalidValue;   // the kernels count tasks in 32 bits
+    if (layout == 1 && rows >= 64 && s <= 65535 && (((uintptr_t)x | (uintptr_t)suh | (uintptr_t)act) & 15u) == 0) {
+        // many rows in the BF16 column layout (the prefill plan): blocks through shared memory, a thread per block
+        const long long per_segment = (long long)rows * (k / 128);
+        return launch(kOverlappable, trellis::rotate_rows_kernel, dim3((unsigned)((per_segment + 127) / 128), (unsigned)s),
+                dim3(trellis::kRotateRowsThreads), 0, 1u, static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(suh),
+                static_cast<uint16_t*>(act), (uint32_t)rows, (uint32_t)k);
+    }
     return launch(kOverlappable, trellis::rotate_kernel, dim3((unsigned)((tasks + 7) / 8)), dim3(256), 0, 1u,
             static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(suh), static_cast<uint16_t*>(act), rows, k, s, layout);
 }

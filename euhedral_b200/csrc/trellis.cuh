@@ -129,6 +129,72 @@ __global__ void __launch_bounds__(256) rotate_kernel(const uint16_t* __restrict_
     }
 }
 
+// The same rotation in the BF16 column layout for many rows (the prefill plan's prepass): a CTA of 128 threads takes 128
+// consecutive 128-column blocks of one segment - 32 KB of x, which is contiguous - through shared memory: coalesced 16-byte
+// loads in, a thread per block (the 128 values in registers, the seven butterfly stages without a shuffle: every a + b and
+// a - b as hadamard128_warp forms them, so the bits are the same), coalesced 16-byte stores out.
+//   grid (ceil(rows * (k / 128) / 128), s), block 128, static shared 128 x 272 bytes.
+constexpr int kRotateRowsThreads = 128;
+__global__ void __launch_bounds__(kRotateRowsThreads) rotate_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ suh,
+        uint16_t* __restrict__ out, uint32_t rows, uint32_t k) {
+    constexpr uint32_t kPitch = 272;   // bytes of a block's row in shared memory: 256 + 16, so that 8 threads' 16-byte loads tile the banks
+    __shared__ __align__(16) uint8_t stage[kRotateRowsThreads * kPitch];
+    const uint32_t t = threadIdx.x, blocks = k >> 7, seg = blockIdx.y;
+    const uint32_t total = rows * blocks, first = blockIdx.x * (uint32_t)kRotateRowsThreads;   // < 2^31 blocks per segment
+    const uint32_t count = min((uint32_t)kRotateRowsThreads, total - first);
+    eb::pdl_launch_dependents();
+    eb::pdl_wait();
+    const uint4* from = reinterpret_cast<const uint4*>(x + (size_t)first * 128);
+#pragma unroll
+    for (uint32_t i = 0; i < 16u; ++i) {
+        const uint32_t chunk = i * kRotateRowsThreads + t;   // 16-byte chunk of the CTA's span: block chunk / 16, piece chunk % 16
+        if (chunk < count * 16u) *reinterpret_cast<uint4*>(stage + (chunk >> 4) * kPitch + (chunk & 15u) * 16u) = from[chunk];
+    }
+    __syncthreads();
+    if (t < count) {
+        const uint32_t block = (first + t) % blocks;
+        const uint4* scales = reinterpret_cast<const uint4*>(suh + (size_t)seg * k + (size_t)block * 128);
+        uint8_t* mine = stage + t * kPitch;
+        float v[128];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            const uint4 xb = *reinterpret_cast<const uint4*>(mine + 16 * c), sb = scales[c];
+            const uint32_t xw[4] = {xb.x, xb.y, xb.z, xb.w}, sw[4] = {sb.x, sb.y, sb.z, sb.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t xs = (xw[j >> 1] >> (16 * (j & 1))) & 0xFFFFu, ss = (sw[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+                v[8 * c + j] = __fmul_rn(eb::bf16_bits_to_float(xs), __half2float(__ushort_as_half((unsigned short)ss)));
+            }
+        }
+#pragma unroll
+        for (int h = 1; h < 128; h <<= 1) {
+#pragma unroll
+            for (int p = 0; p < 64; ++p) {
+                const int i = (p / h) * 2 * h + (p % h);
+                const float a = v[i], b = v[i + h];
+                v[i] = __fadd_rn(a, b);
+                v[i + h] = __fsub_rn(a, b);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                packed[i] = (uint32_t)eb::float_to_bf16_bits(__fmul_rn(v[8 * c + 2 * i], kInvSqrt128))
+                        | (uint32_t)eb::float_to_bf16_bits(__fmul_rn(v[8 * c + 2 * i + 1], kInvSqrt128)) << 16;
+            *reinterpret_cast<uint4*>(mine + 16 * c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+    }
+    __syncthreads();
+    uint4* to = reinterpret_cast<uint4*>(out + ((size_t)seg * rows * k) + (size_t)first * 128);
+#pragma unroll
+    for (uint32_t i = 0; i < 16u; ++i) {
+        const uint32_t chunk = i * kRotateRowsThreads + t;
+        if (chunk < count * 16u) to[chunk] = *reinterpret_cast<const uint4*>(stage + (chunk >> 4) * kPitch + (chunk & 15u) * 16u);
+    }
+}
+
 // partials f32 [splits][rows][n] -> out bf16 [rows][n]. A warp per (row, 128 columns).
 //   grid ceil(rows * (n / 128) / 8), block 256.
 __global__ void __launch_bounds__(256) finish_kernel(const float* __restrict__ partials, int splits, const uint16_t* __restrict__ svh,

@@ -82,9 +82,9 @@ def test_decode_bf16_bitwise(dev, w):
     assert np.array_equal(got, O.bf16_bits(O.trellis_rotated_weight(payload).astype(np.float32).T))
 
 
-def test_prepass_bitwise(dev):
+@pytest.mark.parametrize("rows,k,s", [(3, 1024, 2), (203, 384, 3)])     # few rows: a warp per block; many: a thread per block
+def test_prepass_bitwise(dev, rows, k, s):
     rng = np.random.default_rng(3)
-    rows, k, s = 3, 1024, 2
     x = random_x(rng, rows, k)
     suh = (rng.choice([-1.0, 1.0], size=(s, k)) * rng.uniform(0.5, 2.0, size=(s, k))).astype(np.float16)
     d_x, d_suh, d_out = dev.put(x), dev.put(suh), dev.empty(s * rows * k * 2)
