@@ -194,3 +194,20 @@ def test_cta_pairs_give_the_single_cta_bits(dev):
             lib.euhedral_b200_select_bf16_pairs(1)
         assert np.array_equal(pairs, single)
         assert close(pairs, O.trellis_prefill_model(x, payload, suh, svh, ends))
+
+
+def test_column_shards_equal_the_whole(dev):
+    """N-sharding for several GPUs: a shard of the object's output columns (the reference's rows() operator cuts on segment
+    boundaries) run as a self-contained object gives the whole object's columns bit for bit - every 128-column block is one
+    FP32 sum over K per row, whatever stands beside it."""
+    from euhedral_b200 import sharding
+    rng = np.random.default_rng(61)
+    rows, k, n, w, ends = 530, 384, 1024, 48, [256, 512, 768, 1024]
+    payload, suh, svh = random_object(rng, k, n, w, segments=4)
+    x = random_x(rng, rows, k)
+    whole = prefill(dev, x, payload, suh, svh, ends)
+    parts = []
+    for first, count in ((0, 256), (256, 512), (768, 256)):      # one segment, two segments, the last segment
+        p, s, v, e = sharding.trellis_rows(payload, suh, svh, ends, first, count)
+        parts.append(prefill(dev, x, p, s, v, [int(end) for end in e]))
+    assert np.array_equal(np.concatenate(parts, axis=1), whole)
