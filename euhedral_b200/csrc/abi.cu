@@ -737,6 +737,8 @@ int euhedral_cuda_linear_q3_reference_bf16(const void* input, const void* weight
 // weight code * f32(scale) is written to the scratch as two BF16 terms whose sum is the weight exactly
 // (bf16n::q3_terms_kernel), and one tcgen05 BF16 GEMM over K' = 2 K multiplies both planes with the unchanged BF16
 // activations, FP32 sums in tensor memory: sums of exact products, rounded once to BF16, as the reference's route gives.
+constexpr uint32_t kQ3PrefillMinRows = 33;
+
 int euhedral_cuda_q3_mx_available(void) {
     DeviceState* state = nullptr;
     return bind(&state) == EUHEDRAL_CUDA_SUCCESS ? 1 : 0;
@@ -755,8 +757,10 @@ static int q3_prefill(const void* input, const void* weights, void* output, void
     int status = q3_validate(input, weights, output, rows, in_features, weight_rows, weights_byte_size);
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     if (scratch == nullptr) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
-    // the reference declines the route under exact numerics and row-exact execution (the bits are not the decode kernels')
-    if (in_features % 128u != 0 || weight_rows % (paired ? 256u : 128u) != 0 || g_exact.load() || t_row_exact
+    // the reference declines the route under exact numerics and row-exact execution (the bits are not the decode kernels');
+    // here it also declines up to 32 rows, which the decode kernels take as groups of 8 several times faster than the
+    // expansion of the whole tensor costs (gate at 32 rows: 90 us against 330)
+    if (rows <= kQ3PrefillMinRows - 1u || in_features % 128u != 0 || weight_rows % (paired ? 256u : 128u) != 0 || g_exact.load() || t_row_exact
             || (((uintptr_t)input | (uintptr_t)weights | (uintptr_t)output) & 15u) != 0 || ((uintptr_t)scratch & 255u) != 0)
         return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
     if (euhedral_cuda_q3_mx_scratch_bytes(rows, in_features, weight_rows) > scratch_byte_size) return EUHEDRAL_CUDA_SIZE_OVERFLOW;

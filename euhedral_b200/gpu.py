@@ -121,8 +121,8 @@ class CudaGpuMemory:
     def linear_q3_bf16(self, input: int, weights: int, output: int, rows: int, in_features: int, out_features: int,
                        weight_bytes: int) -> None:
         """CudaGpuMemory.linearQ3Bf16 (java:1695-1728): more than 8 rows try the prefill route (`invokeQ3Mx`); when it
-        declines - row-exact execution, exact numerics, a shape that is not a multiple of 128 - the decode entry runs
-        the rows as groups of 8."""
+        declines - up to 32 rows, row-exact execution, exact numerics, a shape that is not a multiple of 128 - the decode
+        entry runs the rows as groups of 8."""
         if rows > Q3_DECODE_MAX_ROWS and self.linear_q3_mx_bf16(input, weights, output, rows, in_features, out_features, weight_bytes):
             return
         self._check("Q3 linear", self.lib.euhedral_cuda_linear_q3_bf16(input, weights, output, rows, in_features,

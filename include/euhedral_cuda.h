@@ -183,7 +183,8 @@ EUHEDRAL_CUDA_EXPORT int euhedral_b200_linear_trellis_bf16(const void* input, co
  * as two BF16 terms whose sum is the weight exactly, and one tcgen05 BF16 GEMM multiplies both planes with the unchanged
  * BF16 activations (FP32 sums of exact products, rounded once). scratch: 256-byte aligned,
  * euhedral_cuda_q3_mx_scratch_bytes(rows, width, weight_rows) bytes = 4 bytes per weight (larger than the reference's,
- * which holds activation planes). -5 (nothing ran) when in_features or the weight rows are not multiples of 128 (256 for
+ * which holds activation planes). -5 (nothing ran) for 32 rows and fewer (the decode entry point runs them as groups of 8,
+ * several times faster than expanding the tensor), when in_features or the weight rows are not multiples of 128 (256 for
  * the paired region), under exact numerics or row-exact execution, or for operands not aligned to 16 bytes (scratch:
  * 256); -3 when weights_byte_size is not the Q3G64_F16S size of the shape; -2 for too little scratch.
  * euhedral_cuda_q3_mx_select_split_rows is accepted and has no effect: K is never split, so a chunk of a tensor's output

@@ -118,12 +118,13 @@ def test_prefill_entry_points_validate_without_a_device():
     assert lib.euhedral_b200_prefill_trellis_scratch_bytes(100, 256, 384, 2) == 2 * 100 * 256 * 2 + 384 * 256 * 2
     assert lib.euhedral_b200_prefill_trellis_scratch_bytes(3, 128, 128, 1) == 768 + 32768      # each region rounded up to 256 bytes
     # argument checks come before any device work
-    assert lib.euhedral_cuda_linear_q3_mx_bf16(None, 16, 16, 256, 9, 128, 128, 1, 1 << 20) == library.INVALID_ARGUMENT
-    assert lib.euhedral_cuda_linear_q3_mx_bf16(16, 16, 16, 256, 9, 128, 128, 12345, 1 << 20) == library.FORMAT_MISMATCH
+    assert lib.euhedral_cuda_linear_q3_mx_bf16(None, 16, 16, 256, 40, 128, 128, 1, 1 << 20) == library.INVALID_ARGUMENT
+    assert lib.euhedral_cuda_linear_q3_mx_bf16(16, 16, 16, 256, 40, 128, 128, 12345, 1 << 20) == library.FORMAT_MISMATCH
     size = layouts.q3_byte_size(128, 128)
-    assert lib.euhedral_cuda_linear_q3_mx_bf16(16, 16, 16, 256, 9, 128, 128, size, 16) == library.SIZE_OVERFLOW
-    assert lib.euhedral_cuda_linear_q3_mx_bf16(16, 16, 16, 128, 9, 128, 128, size, 1 << 20) == library.ROUTE_UNAVAILABLE   # scratch not 256-aligned
-    assert lib.euhedral_cuda_q3_mx_gate_up_swiglu_bf16(16, 16, 16, 256, 9, 128, 129, size, 1 << 20) == library.INVALID_ARGUMENT
+    assert lib.euhedral_cuda_linear_q3_mx_bf16(16, 16, 16, 256, 40, 128, 128, size, 16) == library.SIZE_OVERFLOW
+    assert lib.euhedral_cuda_linear_q3_mx_bf16(16, 16, 16, 256, 32, 128, 128, size, 1 << 20) == library.ROUTE_UNAVAILABLE   # few rows: the decode kernels
+    assert lib.euhedral_cuda_linear_q3_mx_bf16(16, 16, 16, 128, 40, 128, 128, size, 1 << 20) == library.ROUTE_UNAVAILABLE   # scratch not 256-aligned
+    assert lib.euhedral_cuda_q3_mx_gate_up_swiglu_bf16(16, 16, 16, 256, 40, 128, 129, size, 1 << 20) == library.INVALID_ARGUMENT
     ends = (C.c_int32 * 1)(256)
     host = C.cast(ends, C.c_void_p)
     assert lib.euhedral_b200_prefill_trellis_bf16(256, 256, 256, 256, 256, host, 256, 256, 1 << 30, 4, 256, 200, 48, 1) == library.ROUTE_UNAVAILABLE

@@ -34,7 +34,7 @@ def prefill(dev, x_bits, blob, n, k, paired=False, **select):
     return dev.get(d_y, np.uint16, (rows, width))
 
 
-@pytest.mark.parametrize("rows,k,n", [(9, 128, 128), (200, 512, 384), (130, 1024, 1152), (1030, 256, 640)])
+@pytest.mark.parametrize("rows,k,n", [(33, 128, 128), (200, 512, 384), (130, 1024, 1152), (1030, 256, 640)])
 def test_against_float64(dev, rows, k, n):
     rng = np.random.default_rng(rows + k)
     blob, dense = random_tensor(rng, n, k)
@@ -56,7 +56,7 @@ def test_rows_do_not_depend_on_their_neighbours(dev):
     blob, _ = random_tensor(rng, n, k)
     x = random_x(rng, 140, k)
     whole = prefill(dev, x, blob, n, k)
-    assert np.array_equal(prefill(dev, x[129:139], blob, n, k), whole[129:139])
+    assert np.array_equal(prefill(dev, x[100:139], blob, n, k), whole[100:139])
     # a chunk of the output rows of the tensor gives the whole tensor's bits (select_split_rows has nothing to fix)
     dev.gpu.lib.euhedral_cuda_q3_mx_select_split_rows(n)
     half_blob, _ = slice_rows(blob, n, k, 128, 128)
@@ -93,15 +93,17 @@ def test_statuses(dev):
     lib = dev.gpu.lib
     rng = np.random.default_rng(1)
     blob, _ = random_tensor(rng, 128, 128)
-    x = random_x(rng, 9, 128)
+    x = random_x(rng, 40, 128)
     assert prefill(dev, x, blob, 128, 128, row_exact=True) == -5          # row-exact execution declines the route
+    assert prefill(dev, x[:32], blob, 128, 128) == -5                     # 32 rows and fewer belong to the decode kernels
+    assert not isinstance(prefill(dev, x[:33], blob, 128, 128), int)
     d = dev.empty(1 << 20)
     p = d.data_ptr()
-    assert lib.euhedral_cuda_linear_q3_mx_bf16(p, p, p, p, 9, 128, 128, blob.size - 1, 1 << 20) == -3      # not the tensor's size
-    assert lib.euhedral_cuda_linear_q3_mx_bf16(p, p, p, p, 9, 128, 128, blob.size, 1024) == -2             # scratch too small
+    assert lib.euhedral_cuda_linear_q3_mx_bf16(p, p, p, p, 40, 128, 128, blob.size - 1, 1 << 20) == -3      # not the tensor's size
+    assert lib.euhedral_cuda_linear_q3_mx_bf16(p, p, p, p, 40, 128, 128, blob.size, 1024) == -2             # scratch too small
     assert lib.euhedral_cuda_q3_mx_scratch_bytes(9, 128, 128) == 128 * 128 * 4
     small, _ = random_tensor(rng, 64, 128)
-    assert lib.euhedral_cuda_linear_q3_mx_bf16(p, p, p, p, 9, 128, 64, small.size, 1 << 20) == -5          # weight rows not a multiple of 128
+    assert lib.euhedral_cuda_linear_q3_mx_bf16(p, p, p, p, 40, 128, 64, small.size, 1 << 20) == -5          # weight rows not a multiple of 128
     previous = lib.euhedral_cuda_select_exact_numerics(1)
     try:
         assert prefill(dev, x, blob, 128, 128) == -5
@@ -109,26 +111,27 @@ def test_statuses(dev):
         lib.euhedral_cuda_select_exact_numerics(previous)
 
 
-def test_operator_routes_more_than_eight_rows_to_the_prefill(dev):
-    """GroupedLinearFormat.linear / CudaGpuMemory.linear_q3_bf16: 9 rows and more take the prefill route, row-exact launches
-    and shapes it declines the decode kernels."""
+def test_operator_routes_by_row_count(dev):
+    """GroupedLinearFormat.linear / CudaGpuMemory.linear_q3_bf16: more than 8 rows try the prefill route; it takes 33 rows and
+    more, and leaves fewer rows, row-exact launches and shapes it declines to the decode kernels."""
     from euhedral_b200.formats import GroupedLinearFormat, LinearLaunch, TensorHandle
     rng = np.random.default_rng(41)
-    rows, k, n = 24, 256, 256                            # row-exact launches hold up to 32 rows
+    rows, k, n = 40, 256, 256
     blob, _ = random_tensor(rng, n, k)
     x = random_x(rng, rows, k)
     d_x, d_w, d_y = dev.put(x), dev.put(blob), dev.empty(rows * n * 2)
-    launch = LinearLaunch(d_x.data_ptr(), d_y.data_ptr(), [TensorHandle("w", (n, k), d_w.data_ptr(), blob.size)], rows, k, n)
+    handle = TensorHandle("w", (n, k), d_w.data_ptr(), blob.size)
     with dev.submit() as gpu:
-        GroupedLinearFormat().linear(gpu, launch)
-    routed = dev.get(d_y, np.uint16, (rows, n))
-    assert np.array_equal(routed, prefill(dev, x, blob, n, k))
-    with dev.submit(row_exact=True) as gpu:
-        GroupedLinearFormat().linear(gpu, launch)
-    exact_rows = dev.get(d_y, np.uint16, (rows, n))
-    with dev.submit() as gpu:                       # one row through the decode kernel: what a row-exact launch must equal
-        gpu.linear_q3_bf16(d_x.data_ptr() + 7 * k * 2, d_w.data_ptr(), d_y.data_ptr(), 1, k, n, blob.size)
-    assert np.array_equal(dev.get(d_y, np.uint16, (rows, n))[0], exact_rows[7])
+        GroupedLinearFormat().linear(gpu, LinearLaunch(d_x.data_ptr(), d_y.data_ptr(), [handle], rows, k, n))
+    assert np.array_equal(dev.get(d_y, np.uint16, (rows, n)), prefill(dev, x, blob, n, k))
+    # 24 rows: the prefill entry declines, the decode kernels run them as groups of 8, each row bitwise its one-row call
+    for select in ({}, {"row_exact": True}):
+        with dev.submit(**select) as gpu:
+            GroupedLinearFormat().linear(gpu, LinearLaunch(d_x.data_ptr(), d_y.data_ptr(), [handle], 24, k, n))
+        many = dev.get(d_y, np.uint16, (rows, n))[:24].copy()
+        with dev.submit() as gpu:
+            gpu.linear_q3_bf16(d_x.data_ptr() + 7 * k * 2, d_w.data_ptr(), d_y.data_ptr(), 1, k, n, blob.size)
+        assert np.array_equal(dev.get(d_y, np.uint16, (rows, n))[0], many[7])
 
 
 @pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408)])
