@@ -133,7 +133,7 @@ class TrellisFormat:
     def scratch_bytes(self, gpu, rows: int, in_features: int, out_features: int, segments: int = 1, row_exact: bool = True) -> int:
         """What a linear of `rows` rows needs: the tensor-core route's activations and partial sums, or - beyond its row
         limit and not row-exact - the prefill plan's rotated activations and decoded weight."""
-        if not row_exact and rows > self.settings.mma_max_rows:
+        if not row_exact and rows >= self.settings.whole_k_rows:
             return gpu.lib.euhedral_b200_prefill_trellis_scratch_bytes(rows, in_features, out_features, segments)
         return self.mma_bytes(rows, in_features, out_features, segments)
 
@@ -155,10 +155,14 @@ class TrellisFormat:
                              ends.device_address, rows, k, n, w, segments)
         if gpu.exact_numerics():
             run.reference()
-        elif launch.row_exact or rows <= self.settings.mma_max_rows:
+        elif launch.row_exact or rows < self.settings.whole_k_rows:
             run.tensor_core(self.settings)
         else:
-            run.prefill(launch.segment_ends)
+            # The reference keeps up to mma_max_rows rows on its whole-K tensor-core kernels; this build does not carry
+            # those, and its prefill plan takes any row count: launches of whole_k_rows rows and more that need not be
+            # row-exact run the plan. An object of one segment needs no host copy of its ends.
+            bounds = launch.segment_ends if launch.segment_ends is not None or segments != 1 else [n]
+            run.prefill(bounds)
 
 
 @dataclass

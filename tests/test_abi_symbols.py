@@ -177,5 +177,10 @@ def test_operators_route_by_row_count(monkeypatch):
                TensorHandle("svh", (256,), 0x3000, 512), TensorHandle("ends", (1,), 0x4000, 4)]
     fmt.linear(memory, LinearLaunch(0x5000, 0x6000, handles, 600, 256, 256, scratch=0x7000, scratch_bytes=1 << 20, segment_ends=[256]))
     assert [name for name, _ in calls][-1] == "euhedral_b200_prefill_trellis_bf16"
-    with pytest.raises(ValueError):
-        fmt.linear(memory, LinearLaunch(0x5000, 0x6000, handles, 600, 256, 256, scratch=0x7000, scratch_bytes=1 << 20))
+    calls.clear()
+    fmt.linear(memory, LinearLaunch(0x5000, 0x6000, handles, 64, 256, 256, scratch=0x7000, scratch_bytes=1 << 20))   # one segment: ends = [n]
+    assert [name for name, _ in calls][-1] == "euhedral_b200_prefill_trellis_bf16"
+    calls.clear()
+    fmt.linear(memory, LinearLaunch(0x5000, 0x6000, handles, 63, 256, 256, scratch=0x7000, scratch_bytes=1 << 20))
+    assert "euhedral_b200_prefill_trellis_bf16" not in [name for name, _ in calls]
+    assert [name for name, _ in calls].count("euhedral_cuda_linear_launch") >= 2                                      # prepass + mma

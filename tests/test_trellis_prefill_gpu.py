@@ -141,9 +141,20 @@ def test_operator_routes_many_rows_to_the_prefill(dev):
     with dev.submit() as gpu:
         fmt.linear(gpu, LinearLaunch(d_x.data_ptr(), d_y.data_ptr(), handles, rows, k, n, scratch=d_s.data_ptr(), scratch_bytes=need, segment_ends=ends))
     assert np.array_equal(dev.get(d_y, np.uint16, (rows, n)), prefill(dev, x, payload, suh, svh, ends))
-    with pytest.raises(ValueError):
+    with pytest.raises(ValueError):      # two segments: the plan needs their ends on the host
         with dev.submit() as gpu:
             fmt.linear(gpu, LinearLaunch(d_x.data_ptr(), d_y.data_ptr(), handles, rows, k, n, scratch=d_s.data_ptr(), scratch_bytes=need))
+    # 64 rows and more that need not be row-exact run the plan too (the whole-K kernels of the reference are not carried);
+    # fewer rows, and row-exact launches, stay on the tensor-core decode route
+    whole = prefill(dev, x, payload, suh, svh, ends)
+    for count, expect_plan in ((64, True), (63, False)):
+        need = fmt.scratch_bytes(dev.gpu, count, k, n, 2, row_exact=False)
+        d_s = dev.empty(need)
+        with dev.submit() as gpu:
+            fmt.linear(gpu, LinearLaunch(d_x.data_ptr(), d_y.data_ptr(), handles, count, k, n, scratch=d_s.data_ptr(), scratch_bytes=need, segment_ends=ends))
+        got = dev.get(d_y, np.uint16, (rows, n))[:count]
+        assert np.array_equal(got, whole[:count]) == expect_plan
+        assert close(got, O.trellis_prefill_model(x[:count], payload, suh, svh, ends)) or not expect_plan
 
 
 def test_gate_up_at_4096_rows_against_the_decode_route(dev):
