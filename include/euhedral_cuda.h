@@ -107,7 +107,8 @@ EUHEDRAL_CUDA_EXPORT int euhedral_cuda_linear_launch(int32_t kernel, uint32_t gr
 /* ---- additions without a counterpart in the reference -------------------------------------------------------------- */
 
 /* Reads and clears the current device's kernel error word: nonzero when a bounded wait inside a kernel gave up
- * (bit 0 NVFP4 GEMV, bit 1 Q3 GEMV, bit 2 trellis GEMM, bit 3 NVFP4 prefill GEMM). Synchronizes the device. */
+ * (bit 0 NVFP4 GEMV, bit 1 Q3 GEMV, bit 2 trellis GEMM, bit 3 NVFP4 prefill GEMM, bit 4 the BF16 GEMM of the Q3 and trellis
+ * prefill). Synchronizes the device. */
 EUHEDRAL_CUDA_EXPORT int euhedral_b200_take_device_error(uint32_t* word);
 /* How a decode GEMV of this shape runs. k_slices (cluster size), pieces (warps that share a 16-row tile's slice) and
  * piece_chunks (128-value chunks of the widest piece) depend on the format and in_features only and fix the summation
