@@ -769,7 +769,7 @@ static int q3_prefill(const void* input, const void* weights, void* output, void
     if (status != EUHEDRAL_CUDA_SUCCESS) return status;
     const q3::Geometry geo(weight_rows, in_features);
     const uint64_t groups = (uint64_t)weight_rows * (in_features / 64u);
-    cudaError_t e = launch(kOrdered, bf16n::q3_terms_kernel, dim3((unsigned)((groups + 255u) / 256u)), dim3(256), 0, 1u,
+    cudaError_t e = launch(kOrdered, bf16n::q3_terms_kernel, dim3((unsigned)((groups * 8u + 255u) / 256u)), dim3(256), 0, 1u,
             static_cast<const uint8_t*>(weights), geo.scale_offset, static_cast<uint16_t*>(scratch), weight_rows, in_features);
     if (e == cudaSuccess)
         e = bf16n::linear(input, scratch, output, nullptr, 0, rows, 2u * in_features, weight_rows, state->sms, t_stream, false, state->error_word,

@@ -381,40 +381,36 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) bf16_ge
 
 // Q3G64_F16S tensor -> two BF16 planes side by side along K, [n][2 k]: columns [0, k) hold hi = bf16(code * scale), columns
 // [k, 2 k) lo = code * scale - hi. code * f32(scale) has at most 14 significant bits, hi keeps 8 and the rest fits BF16:
-// hi + lo is the weight exactly, and both products with a BF16 activation are exact in FP32. A thread per group of 64.
-//   grid ceil(n * (k / 64) / 256), block 256. k a multiple of 128.
+// hi + lo is the weight exactly, and both products with a BF16 activation are exact in FP32. Eight threads per group of 64:
+// a thread takes 8 codes (24 bits) and writes 16 bytes of each plane, so a warp's stores are whole 128-byte lines.
+//   grid ceil(n * (k / 64) * 8 / 256), block 256. k a multiple of 128.
 __global__ void __launch_bounds__(256) q3_terms_kernel(const uint8_t* __restrict__ w, uint64_t scale_offset, uint16_t* __restrict__ out,
         uint32_t n, uint32_t k) {
     const uint32_t groups = k / 64u;
-    const uint64_t index = (uint64_t)blockIdx.x * 256u + threadIdx.x;
-    if (index >= (uint64_t)n * groups) return;
-    const uint32_t row = (uint32_t)(index / groups), group = (uint32_t)(index % groups);
-    const uint2* packed = reinterpret_cast<const uint2*>(w + index * 24u);
-    const uint2 p0 = packed[0], p1 = packed[1], p2 = packed[2];
-    const uint32_t words[7] = {p0.x, p0.y, p1.x, p1.y, p2.x, p2.y, 0u};
-    const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(w + scale_offset + index * 2u)));
-    uint16_t* hi = out + (uint64_t)row * 2u * k + (uint64_t)group * 64u;
-    uint16_t* lo = hi + k;
+    const uint64_t index = (uint64_t)blockIdx.x * 256u + threadIdx.x, group_index = index >> 3;
+    if (group_index >= (uint64_t)n * groups) return;
+    const uint32_t sub = (uint32_t)index & 7u, row = (uint32_t)(group_index / groups), group = (uint32_t)(group_index % groups);
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(w + group_index * 24u);
+    const uint32_t byte = 3u * sub, word = byte >> 2;              // the thread's 24 bits start at this byte of the group's 24
+    const uint32_t bits = __funnelshift_r(__ldg(words + word), __ldg(words + min(word + 1u, 5u)), 8u * (byte & 3u));
+    const float scale = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const uint16_t*>(w + scale_offset) + group_index)));
+    uint32_t high[4], low[4];
 #pragma unroll
-    for (int v = 0; v < 8; ++v) {
-        uint32_t high[4], low[4];
+    for (int i = 0; i < 4; ++i) {
+        uint32_t hb[2], lb[2];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t hb[2], lb[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int bit = 3 * (8 * v + 2 * i + e);
-                const uint32_t field = __funnelshift_r(words[bit >> 5], words[(bit >> 5) + 1], bit & 31) & 7u;
-                const float value = __fmul_rn((float)((int)field - (field >= 4u ? 8 : 0)), scale);
-                hb[e] = eb::float_to_bf16_bits(value);
-                lb[e] = eb::float_to_bf16_bits(__fsub_rn(value, eb::bf16_bits_to_float(hb[e])));
-            }
-            high[i] = hb[0] | hb[1] << 16;
-            low[i] = lb[0] | lb[1] << 16;
+        for (int e = 0; e < 2; ++e) {
+            const uint32_t field = (bits >> (3 * (2 * i + e))) & 7u;
+            const float value = __fmul_rn((float)((int)field - (field >= 4u ? 8 : 0)), scale);
+            hb[e] = eb::float_to_bf16_bits(value);
+            lb[e] = eb::float_to_bf16_bits(__fsub_rn(value, eb::bf16_bits_to_float(hb[e])));
         }
-        *reinterpret_cast<uint4*>(hi + 8 * v) = make_uint4(high[0], high[1], high[2], high[3]);
-        *reinterpret_cast<uint4*>(lo + 8 * v) = make_uint4(low[0], low[1], low[2], low[3]);
+        high[i] = hb[0] | hb[1] << 16;
+        low[i] = lb[0] | lb[1] << 16;
     }
+    uint16_t* hi = out + (uint64_t)row * 2u * k + (uint64_t)group * 64u + 8u * sub;
+    *reinterpret_cast<uint4*>(hi) = make_uint4(high[0], high[1], high[2], high[3]);
+    *reinterpret_cast<uint4*>(hi + k) = make_uint4(low[0], low[1], low[2], low[3]);
 }
 
 inline cudaError_t initialize() {
