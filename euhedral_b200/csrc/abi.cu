@@ -951,8 +951,8 @@ int euhedral_cuda_linear_launch(int32_t kernel, uint32_t grid_x, uint32_t grid_y
         }
         case 5: {   // decode_bf16(words, out, k, n, w)
             const int k = (int)a[2], n = (int)a[3], w = (int)a[4];
-            if (k <= 0 || k % 16 != 0 || n <= 0 || n % 16 != 0 || !trellis_width_valid(w) || ((a[0] | a[1]) & 3u) != 0)
-                return EUHEDRAL_CUDA_INVALID_ARGUMENT;   // 4-byte loads of the ring words, 4-byte stores of value pairs
+            if (k <= 0 || k % 16 != 0 || n <= 0 || n % 16 != 0 || !trellis_width_valid(w) || (a[0] & 3u) != 0 || (a[1] & 15u) != 0)
+                return EUHEDRAL_CUDA_INVALID_ARGUMENT;   // 4-byte loads of the ring words, 16-byte stores of eight values
             const uint64_t tiles = (uint64_t)(k / 16) * (uint64_t)(n / 16);
             if (tiles > 2147483647ull) return EUHEDRAL_CUDA_SIZE_OVERFLOW;
             return finish(launch_trellis_decode_bf16(reinterpret_cast<const void*>(a[0]), reinterpret_cast<void*>(a[1]), k, n, w));

@@ -304,12 +304,15 @@ struct Lane {
 
 // Payload -> BF16 rotated weight [n][k] (row-major weights of a BF16 linear). A warp takes kBatch tiles side by side: a lane
 // reads its ring words of all of them from global memory first, then takes its eight states of each as the linear does and
-// stores its four pairs of neighbouring k.
+// stores 16 contiguous bytes of one weight row (the quad's pairs regrouped through shared memory).
 //   grid ceil((k / 16) * (n / 16) / (8 kBatch)), block 256.
 template <int W>
 __global__ void __launch_bounds__(256) decode_bf16_kernel(const uint16_t* __restrict__ words, uint16_t* __restrict__ out, int k, int n) {
     using L = Lane<W>;
     const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+    constexpr int kExchangePitch = 40;   // words of an exchange row: 32 lanes + 8, so that a quarter warp's 16-byte loads tile the banks
+    __shared__ __align__(16) uint32_t exchange_rows[8][4 * kExchangePitch];
+    uint32_t* exchange = exchange_rows[threadIdx.x >> 5];
     const uint32_t first = (blockIdx.x * 8u + (threadIdx.x >> 5)) * (uint32_t)kBatch, tiles = (uint32_t)(k >> 4) * (uint32_t)(n >> 4);   // < 2^31
     if (first >= tiles) return;
     L me;
@@ -339,12 +342,15 @@ __global__ void __launch_bounds__(256) decode_bf16_kernel(const uint16_t* __rest
             const uint32_t high = eb::float_to_bf16_bits(__half2float(__ushort_as_half(value_bits(state[2 * j + 1]))));
             pair[j] = low | high << 16;
         }
-        // positions 0..3 are tile row g at k = 2q, 2q+1, 2q+8, 2q+9; positions 4..7 the same k of row g + 8
-        uint16_t* row = out + (size_t)(tj * 16 + g) * k + ti * 16 + 2 * q;
-        *reinterpret_cast<uint32_t*>(row) = pair[0];
-        *reinterpret_cast<uint32_t*>(row + 8) = pair[1];
-        *reinterpret_cast<uint32_t*>(row + (size_t)8 * k) = pair[2];
-        *reinterpret_cast<uint32_t*>(row + (size_t)8 * k + 8) = pair[3];
+        // positions 0..3 are tile row g at k = 2q, 2q+1, 2q+8, 2q+9; positions 4..7 the same k of row g + 8. The four lanes of a
+        // quad trade their pairs through shared memory so that each stores 16 contiguous bytes: lane q gets pair q of all
+        // four, i.e. k 0..7 (q = 0) or 8..15 (q = 1) of row g, or the same of row g + 8 (q = 2, 3).
+        __syncwarp();   // the tile before has been read out of the exchange rows
+#pragma unroll
+        for (int j = 0; j < 4; ++j) exchange[j * kExchangePitch + lane] = pair[j];
+        __syncwarp();
+        const uint4 mine = *reinterpret_cast<const uint4*>(exchange + q * kExchangePitch + 4 * g);
+        *reinterpret_cast<uint4*>(out + (size_t)(tj * 16 + g + 8 * (q >> 1)) * k + ti * 16 + 8 * (q & 1)) = mine;
     }
 }
 
