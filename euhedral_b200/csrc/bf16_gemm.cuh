@@ -250,9 +250,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) bf16_ge
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);
     uint64_t* empty = full + kPairStages;
-    uint64_t* acc_full = empty + kPairStages;
-    uint64_t* acc_empty = acc_full + 1;          // even CTA: both CTAs' epilogue warps have drained the accumulator
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    uint64_t* acc_full = empty + kPairStages;    // two accumulators of 256 columns: a tile's MMAs run while the tile before is drained
+    uint64_t* acc_empty = acc_full + 2;          // even CTA: both CTAs' epilogue warps have drained the accumulator
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t rank = eb::cluster_rank(), pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     // pair_tiles != 0: the gate/up region; the even CTA's half of the weight tile is the gate rows, the odd CTA's the up rows.
@@ -272,8 +272,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) bf16_ge
             eb::mbar_init(&full[s], 1);
             eb::mbar_init(&empty[s], 1);
         }
-        eb::mbar_init(acc_full, 1);
-        eb::mbar_init(acc_empty, 16);
+        for (uint32_t b = 0; b < 2u; ++b) {
+            eb::mbar_init(&acc_full[b], 1);
+            eb::mbar_init(&acc_empty[b], 16);
+        }
         eb::mbar_fence_init();
     }
     if (warp == 1) {
@@ -318,11 +320,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) bf16_ge
             uint32_t step = 0, local = 0;
             bool ok = true;
             for (uint32_t item = pair; item < items && ok; item += pairs, ++local) {
-                if (local > 0 && !eb::mbar_wait(acc_empty, (local - 1u) & 1u)) {
+                const uint32_t buffer = local & 1u, use = local >> 1;
+                if (use > 0 && !eb::mbar_wait(&acc_empty[buffer], (use - 1u) & 1u)) {
                     atomicOr(error, kWaitFailed);
                     break;
                 }
                 nvfp4n::tcgen05_fence_after();
+                const uint32_t accumulator = tmem + buffer * kTileN;
                 for (uint32_t ks = 0; ks < k_steps; ++ks, ++step) {
                     const uint32_t s = step % kPairStages, round = step / kPairStages;
                     if (!eb::mbar_wait(&full[s], round & 1u)) {
@@ -334,10 +338,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) bf16_ge
                     const uint8_t* stage = smem + s * kPairStageBytes;
                     const uint64_t a = nvfp4n::tile_descriptor(stage), b = nvfp4n::tile_descriptor(stage + kATile);
 #pragma unroll
-                    for (uint32_t j = 0; j < 4u; ++j) pair_mma_bf16(tmem, a + 2u * j, b + 2u * j, (uint32_t)((ks | j) != 0u));
+                    for (uint32_t j = 0; j < 4u; ++j) pair_mma_bf16(accumulator, a + 2u * j, b + 2u * j, (uint32_t)((ks | j) != 0u));
                     nvfp4n::pair_commit(&empty[s]);
                 }
-                if (ok) nvfp4n::pair_commit(acc_full);
+                if (ok) nvfp4n::pair_commit(&acc_full[buffer]);
             }
         }
     } else {
@@ -347,13 +351,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) bf16_ge
         for (uint32_t item = pair; item < items; item += pairs, ++local) {
             uint32_t tm, tn;
             place(item, &tm, &tn);
-            if (!eb::mbar_wait(acc_full, local & 1u)) {
+            const uint32_t buffer = local & 1u;
+            if (!eb::mbar_wait(&acc_full[buffer], (local >> 1) & 1u)) {
                 if (lane == 0) atomicOr(error, kWaitFailed);
                 break;
             }
             nvfp4n::tcgen05_fence_after();
             uint32_t r[4][32];
-            const uint32_t from = tmem + ((quarter * 32u) << 16) + (paired ? half * 64u : half * 128u);
+            const uint32_t from = tmem + ((quarter * 32u) << 16) + buffer * kTileN + (paired ? half * 64u : half * 128u);
             const uint32_t other = paired ? from + 128u : from + 64u;
             nvfp4n::tmem_load_32(r[0], from);
             nvfp4n::tmem_load_32(r[1], from + 32u);
@@ -362,7 +367,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) bf16_ge
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             nvfp4n::tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) nvfp4n::arrive_at_rank(acc_empty, 0u);
+            if (lane == 0) nvfp4n::arrive_at_rank(&acc_empty[buffer], 0u);
             const uint32_t row = (2u * tm + rank) * kTileM + quarter * 32u + lane, col = paired ? tn * 128u + half * 64u : tn * kTileN + half * 128u;
             if (svh == nullptr) {
                 nvfp4n::store_block(r, out, row, rows, n, col, 1.0f, paired);   // row stride n
