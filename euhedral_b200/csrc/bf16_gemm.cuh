@@ -402,16 +402,20 @@ __global__ void __launch_bounds__(256) q3_terms_kernel(const uint8_t* __restrict
     uint32_t high[4], low[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        uint32_t hb[2], lb[2];
+        float value[2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
+            // the 3-bit two's complement code as a float without an integer conversion: code + 4 = field ^ 4 sits in the
+            // mantissa of 2^23, and 2^23 + 4 is subtracted (exact)
             const uint32_t field = (bits >> (3 * (2 * i + e))) & 7u;
-            const float value = __fmul_rn((float)((int)field - (field >= 4u ? 8 : 0)), scale);
-            hb[e] = eb::float_to_bf16_bits(value);
-            lb[e] = eb::float_to_bf16_bits(__fsub_rn(value, eb::bf16_bits_to_float(hb[e])));
+            value[e] = __fmul_rn(__fsub_rn(__uint_as_float(0x4B000000u | (field ^ 4u)), 8388612.0f), scale);
         }
-        high[i] = hb[0] | hb[1] << 16;
-        low[i] = lb[0] | lb[1] << 16;
+        // round to nearest even in one conversion per pair; the values are finite
+        const __nv_bfloat162 top = __floats2bfloat162_rn(value[0], value[1]);
+        const float2 back = __bfloat1622float2(top);
+        const __nv_bfloat162 rest = __floats2bfloat162_rn(__fsub_rn(value[0], back.x), __fsub_rn(value[1], back.y));
+        high[i] = *reinterpret_cast<const uint32_t*>(&top);
+        low[i] = *reinterpret_cast<const uint32_t*>(&rest);
     }
     uint16_t* hi = out + (uint64_t)row * 2u * k + (uint64_t)group * 64u + 8u * sub;
     *reinterpret_cast<uint4*>(hi) = make_uint4(high[0], high[1], high[2], high[3]);
