@@ -67,6 +67,13 @@ __device__ __forceinline__ void rotate128(const uint16_t* __restrict__ x, const 
     hadamard128_warp(v, lane);
 }
 
+// Two floats rounded to nearest even into one BF16 pair by the hardware conversion (low half from `low`); for finite values
+// the bits of eb::float_to_bf16_bits.
+__device__ __forceinline__ uint32_t bf16_pair(float low, float high) {
+    const __nv_bfloat162 both = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<const uint32_t*>(&both);
+}
+
 __device__ __forceinline__ uint32_t half_pair(float low, float high) {
     return (uint32_t)__half_as_ushort(__float2half_rn(low)) | (uint32_t)__half_as_ushort(__float2half_rn(high)) << 16;
 }
@@ -180,9 +187,7 @@ __global__ void __launch_bounds__(kRotateRowsThreads) rotate_rows_kernel(const u
         for (int c = 0; c < 16; ++c) {
             uint32_t packed[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                packed[i] = (uint32_t)eb::float_to_bf16_bits(__fmul_rn(v[8 * c + 2 * i], kInvSqrt128))
-                        | (uint32_t)eb::float_to_bf16_bits(__fmul_rn(v[8 * c + 2 * i + 1], kInvSqrt128)) << 16;
+            for (int i = 0; i < 4; ++i) packed[i] = bf16_pair(__fmul_rn(v[8 * c + 2 * i], kInvSqrt128), __fmul_rn(v[8 * c + 2 * i + 1], kInvSqrt128));
             *reinterpret_cast<uint4*>(mine + 16 * c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         }
     }
@@ -338,9 +343,9 @@ __global__ void __launch_bounds__(256) decode_bf16_kernel(const uint16_t* __rest
         uint32_t pair[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const uint32_t low = eb::float_to_bf16_bits(__half2float(__ushort_as_half(value_bits(state[2 * j]))));
-            const uint32_t high = eb::float_to_bf16_bits(__half2float(__ushort_as_half(value_bits(state[2 * j + 1]))));
-            pair[j] = low | high << 16;
+            const uint32_t values = value_pair(state[2 * j], state[2 * j + 1]);   // two FP16 codebook values
+            const float2 wide = __half22float2(*reinterpret_cast<const __half2*>(&values));
+            pair[j] = bf16_pair(wide.x, wide.y);
         }
         // positions 0..3 are tile row g at k = 2q, 2q+1, 2q+8, 2q+9; positions 4..7 the same k of row g + 8. The four lanes of a
         // quad trade their pairs through shared memory so that each stores 16 contiguous bytes: lane q gets pair q of all
