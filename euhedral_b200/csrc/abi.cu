@@ -759,7 +759,7 @@ static int q3_prefill(const void* input, const void* weights, void* output, void
     if (scratch == nullptr) return EUHEDRAL_CUDA_INVALID_ARGUMENT;
     // the reference declines the route under exact numerics and row-exact execution (the bits are not the decode kernels');
     // here it also declines up to 32 rows, which the decode kernels take as groups of 8 several times faster than the
-    // expansion of the whole tensor costs (gate at 32 rows: 90 us against 190)
+    // expansion of the whole tensor costs (gate at 32 rows: 90 us against 160)
     if (rows <= kQ3PrefillMinRows - 1u || in_features % 128u != 0 || weight_rows % (paired ? 256u : 128u) != 0 || g_exact.load() || t_row_exact
             || (((uintptr_t)input | (uintptr_t)weights | (uintptr_t)output) & 15u) != 0 || ((uintptr_t)scratch & 255u) != 0)
         return EUHEDRAL_CUDA_ROUTE_UNAVAILABLE;
