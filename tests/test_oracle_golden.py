@@ -165,3 +165,20 @@ def test_trellis_tile_encoder_reproduces_the_golden_tiles(golden, w, ka, mask):
     assert packed.shape[1] == w and np.array_equal(packed, g[f"tiles_{w}_packed"])
     # and the decoder reads the packed words back to the same values
     assert np.array_equal(O.trellis_decode_tiles(packed, w).view(np.uint16), g[f"tiles_{w}_out"].view(np.uint16))
+
+
+def test_q3_weights_are_two_bf16_terms_exactly():
+    """The Q3 prefill's claim, for EVERY finite FP16 scale and every code: code * f32(scale) = hi + lo with hi = bf16(code *
+    scale) and lo = bf16(code * scale - hi), both roundings to nearest even, and nothing is lost (the residual after hi has at
+    most six significant bits)."""
+    scales = np.arange(65536, dtype=np.uint16).view(np.float16)
+    scales = scales[np.isfinite(scales)].astype(np.float32)
+    for code in range(-4, 4):
+        value = np.float32(code) * scales                       # exact: 3 bits times 11 bits
+        assert np.array_equal(value.astype(np.float64), np.float64(code) * scales.astype(np.float64))
+        hi = O.bf16_to_f32(O.bf16_bits(value))
+        rest = value - hi                                        # exact in float32 (Sterbenz-like: same binade or below)
+        assert np.array_equal(rest.astype(np.float64), value.astype(np.float64) - hi.astype(np.float64))
+        lo = O.bf16_to_f32(O.bf16_bits(rest))
+        assert np.array_equal(lo, rest)                          # the residual is a BF16 value: no second rounding error
+        assert np.array_equal(hi.astype(np.float64) + lo.astype(np.float64), value.astype(np.float64))
