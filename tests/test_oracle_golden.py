@@ -182,3 +182,20 @@ def test_q3_weights_are_two_bf16_terms_exactly():
         lo = O.bf16_to_f32(O.bf16_bits(rest))
         assert np.array_equal(lo, rest)                          # the residual is a BF16 value: no second rounding error
         assert np.array_equal(hi.astype(np.float64) + lo.astype(np.float64), value.astype(np.float64))
+
+
+def test_trellis_prefill_model_is_the_linear_up_to_its_bf16_roundings():
+    """The model of the reference's prefill plan (BF16 activations, BF16 decoded weight, BF16 products, BF16 output) against the
+    unrounded float64 linear of the same object: they differ by those roundings only."""
+    rng = np.random.default_rng(17)
+    k, n, w, ends = 256, 384, 48, [128, 384]
+    payload = rng.integers(-32768, 32768, size=(k // 16, n // 16, w), dtype=np.int16)
+    suh = (rng.choice([-1.0, 1.0], size=(2, k)) * rng.uniform(0.5, 2.0, size=(2, k))).astype(np.float16)
+    svh = rng.uniform(0.01, 1.0, size=n).astype(np.float16)
+    x = O.bf16_bits(rng.standard_normal((7, k)).astype(np.float32))
+    model = O.trellis_prefill_model(x, payload, suh, svh, ends).astype(np.float64)
+    exact = O.trellis_linear_f64(x, payload, suh, svh, ends)
+    rms = float(np.sqrt(np.mean(exact ** 2)))
+    assert np.all(np.abs(model - exact) <= 0.02 * np.abs(exact) + 0.02 * rms)
+    assert np.sqrt(np.mean((model - exact) ** 2)) < 0.006 * rms
+    assert np.array_equal(O.bf16_to_f32(O.bf16_bits(model.astype(np.float32))), model.astype(np.float32))   # BF16 values
