@@ -1113,7 +1113,7 @@ int euhedral_b200_linear_bf16(const void* input, const void* weights, void* outp
 
 // Process-wide: whether BF16 linears of 512 rows and more (the trellis and Q3 prefill) run on CTA pairs. Same bits either
 // way; on by default.
-void euhedral_b200_select_bf16_pairs(int enabled) { bf16n::g_pairs = enabled != 0; }
+void euhedral_b200_select_bf16_pairs(int enabled) { bf16n::g_pairs.store(enabled != 0); }
 
 int euhedral_b200_prefill_trellis_bf16(const void* input, const void* words, const void* suh, const void* svh, const void* segment_ends,
         const int32_t* host_segment_ends, void* output, void* scratch, uint64_t scratch_bytes, uint32_t rows, uint32_t in_features,

@@ -11,6 +11,8 @@
 // tile fill the other accumulator (two of 256 columns: all of tensor memory). Every wait is bounded.
 #pragma once
 
+#include <atomic>
+
 #include "nvfp4_native.cuh"
 #include "trellis_codebook.cuh"
 
@@ -428,7 +430,7 @@ inline cudaError_t initialize() {
 }
 
 // Whether calls of kPairRows rows and more run on CTA pairs (process-wide; same bits either way).
-inline bool g_pairs = true;
+inline std::atomic<bool> g_pairs{true};
 
 // a [rows][k], b [n][k] -> out [rows][n] at row stride `stride`, all BF16 in device memory, 16-byte aligned; k % 64 == 0,
 // n % 128 == 0. svh (FP16 [n], may be null): finish the trellis output in the epilogue instead of storing the sums.
@@ -449,7 +451,7 @@ inline cudaError_t linear(const void* a, const void* b, void* out, const void* s
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     const uint32_t pair_tiles = paired ? n / 256u : 0u, width = paired ? n / 2u : n;
-    if (rows >= kPairRows && g_pairs) {
+    if (rows >= kPairRows && g_pairs.load()) {
         const uint32_t items = ((rows + 255u) / 256u) * (paired ? pair_tiles : (n + 255u) / 256u);
         const uint32_t ctas = 2u * std::max(1u, std::min((uint32_t)sms / 2u, items));
         return nvfp4n::launch_on(stream, pdl, bf16_gemm_pair_kernel, dim3(ctas), dim3(kThreads), kPairShared, map_a, map_b, static_cast<uint16_t*>(out),
